@@ -1,0 +1,407 @@
+#!/usr/bin/env python
+"""Benchmark of the fused norm+activation path (forward + backward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload cfg2|cfg5:<ln|rms>:<fp32|bf16>:<D>]
+
+One step = LayerNorm->GELU (or RMSNorm->SiLU) forward, backward (dX + per-CTA
+dgamma/dbeta partials), the partial reduce, and for N > 1 the NCCL allreduce of
+the [2, D] gradients.  Default workload: x[32,1024,1024] fp32, LayerNorm -> exact
+GELU, eps 1e-5, per GPU (weak scaling).  `cfg5:*` is the whole-box sweep: 2^20
+rows split evenly over the ranks (strong scaling).
+
+Prints ONE JSON line on rank 0.  `value` is algorithmic HBM GB/s of the whole job
+(inputs resident in HBM), `e2e` the same metric through the host-buffer C-ABI call
+(pinned host buffers, copies inside the timed region), `roofline` the dominant
+kernel against the measured HBM peak, `cpu_baseline` the reference's CPU path on
+a bounded sample on this box's host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+METRIC = "fused_norm_act_fwd_bwd_hbm_gbs"
+UNIT = "GB/s"
+FALLBACK_HBM_GBS = 6650.0          # earlier measurement on this pool, used only without MEASURED_PEAKS.json
+
+
+# ----------------------------------------------------------------- workloads
+class Workload:
+    def __init__(self, spec: str, world: int):
+        self.spec = spec
+        if spec == "cfg2":
+            self.kind, self.dtype, self.D = "ln", torch.float32, 1024
+            self.rows_per_rank, self.scaling = 32 * 1024, "weak"
+            self.name = "LayerNorm->GELU(erf) fwd+bwd fp32 x[32,1024,1024] per GPU (BASELINE configs[1])"
+        elif spec.startswith("cfg5:"):
+            _, kind, dt, D = spec.split(":")
+            self.kind, self.D = kind, int(D)
+            self.dtype = {"fp32": torch.float32, "bf16": torch.bfloat16}[dt]
+            total = 1 << 20
+            if total % world:
+                raise SystemExit("cfg5 needs a world size that divides 2^20")
+            self.rows_per_rank, self.scaling = total // world, "strong"
+            self.name = f"{'LayerNorm->GELU' if kind == 'ln' else 'RMSNorm->SiLU'} fwd+bwd {dt} 2^20 rows x D={D} (BASELINE configs[4])"
+        else:
+            raise SystemExit(f"unknown workload {spec}")
+        self.act = 1 if self.kind == "ln" else 2          # GELU behind LayerNorm, SiLU behind RMSNorm
+        self.eps = 1e-5 if self.kind == "ln" else 1e-6
+        self.elt = 4 if self.dtype == torch.float32 else 2
+
+    # algorithmic bytes, per rank
+    def fwd_bytes(self, rows=None):
+        n = self.rows_per_rank if rows is None else rows
+        stats = 8 * n if self.kind == "ln" else 4 * n
+        params = (2 if self.kind == "ln" else 1) * self.D * self.elt
+        return 2 * n * self.D * self.elt + stats + params
+
+    def bwd_bytes(self, rows=None):
+        n = self.rows_per_rank if rows is None else rows
+        stats = 8 * n if self.kind == "ln" else 4 * n
+        params = (2 if self.kind == "ln" else 1) * self.D * (self.elt + 4)     # read gamma/beta, write fp32 grads
+        return 3 * n * self.D * self.elt + stats + params
+
+    def step_bytes(self, rows=None):
+        return self.fwd_bytes(rows) + self.bwd_bytes(rows)
+
+
+def synth_inputs(w: Workload, rows: int, device, seed: int):
+    """Synthetic N(0,1) activations, gamma = 1 + N(0,0.02), beta = N(0,0.02)."""
+    gen = torch.Generator(device=device).manual_seed(seed)
+    x = torch.randn(rows, w.D, device=device, generator=gen).to(w.dtype)
+    dy = torch.randn(rows, w.D, device=device, generator=gen).to(w.dtype)
+    gamma = (1 + 0.02 * torch.randn(w.D, device=device, generator=gen)).to(w.dtype)
+    beta = (0.02 * torch.randn(w.D, device=device, generator=gen)).to(w.dtype) if w.kind == "ln" else None
+    return x, dy, gamma, beta
+
+
+# -------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Polls NVML for SM clock and throttle reasons while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def sample(self):
+        if self.nv is None:
+            return
+        try:
+            self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+            r = self.nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+            names = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+                     0x4: "sw_power_cap", 0x80: "hw_power_brake"}
+            for bit, nm in names.items():
+                if r & bit:
+                    self.reasons.add(nm)
+        except Exception:
+            pass
+
+    def __enter__(self):
+        def loop():
+            while not self._stop.is_set():
+                self.sample()
+                time.sleep(0.002)
+        self._thread = threading.Thread(target=loop, daemon=True)
+        self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------- reference arm
+def reference_cpu_run(w: Workload, steps: int, warmup: int, budget_s: float = 20.0):
+    """The reference's own modules (oracle/_ref: Nott headers + libtorch CPU, all host threads),
+    forward + autograd backward, on a bounded row sample of the workload (at most 32 Mi elements,
+    which is the whole of the default workload); timed inside the harness so only the module calls
+    are on the clock.  Falls back to the single-core C port when the reference library was not
+    built.  Returns (GB/s, seconds per step, sample rows, passes, description)."""
+    from oracle import reference as R
+    from oracle import cpu_oracle as O
+
+    use_ref = R.available()
+    bf16 = w.dtype == torch.bfloat16
+    if use_ref:
+        sample_rows = max(1, min(w.rows_per_rank, (32 << 20) // w.D))
+        compute = 2 if bf16 else 0       # the reference runs in the tensor's own dtype
+        per = R.time_norm_act(w.kind, sample_rows, w.D, w.eps, w.act, compute, iters=1, warmup=max(1, min(warmup, 2)))
+        n = max(1, min(steps, int(budget_s / max(per, 1e-6))))
+        sec = R.time_norm_act(w.kind, sample_rows, w.D, w.eps, w.act, compute, iters=n, warmup=0)
+        cores = R.num_threads()
+    else:
+        sample_rows = min(w.rows_per_rank, 512)
+        rng = np.random.default_rng(0)
+        x = rng.standard_normal((sample_rows, w.D)).astype(np.float32)
+        dy = rng.standard_normal((sample_rows, w.D)).astype(np.float32)
+        gamma = (1 + 0.02 * rng.standard_normal(w.D)).astype(np.float32)
+        beta = (0.02 * rng.standard_normal(w.D)).astype(np.float32)
+
+        def one():
+            if w.kind == "ln":
+                O.layernorm_act(x, gamma, beta, dy, w.eps, w.act)
+            else:
+                O.rmsnorm_act(x, gamma, dy, w.eps, w.act)
+
+        one()
+        t0 = time.perf_counter()
+        one()
+        per = time.perf_counter() - t0
+        n = max(1, min(steps, int(budget_s / max(per, 1e-6))))
+        t0 = time.perf_counter()
+        for _ in range(n):
+            one()
+        sec = (time.perf_counter() - t0) / n
+        cores = 1
+    gbs = w.step_bytes(sample_rows) / sec / 1e9
+    desc = {
+        "value": gbs, "unit": UNIT, "cores": cores,
+        "kind": "reference" if use_ref else "port",
+        "sample": f"{sample_rows} of {w.rows_per_rank} rows x D={w.D}, {n} timed fwd+bwd passes, "
+                  + ("Nott modules on libtorch CPU, native " + ("bf16" if bf16 else "fp32") if use_ref
+                     else "scalar C restatement in fp64"),
+        "rows_per_s": sample_rows / sec, "ms_per_pass": sec * 1e3, "host_cpus": os.cpu_count(),
+    }
+    return gbs, sec, sample_rows, n, desc
+
+
+def run_reference_arm(args, w: Workload, rank: int, world: int):
+    if rank != 0:
+        return
+    gbs, sec, sample_rows, n, desc = reference_cpu_run(w, args.steps, args.warmup, budget_s=60.0)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": world, "steps": n,
+        "warmup": min(args.warmup, 3), "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": w.scaling,
+        "vs_baseline": None, "dtype": "f32" if w.dtype == torch.float32 else "bf16", "data": "synthetic",
+        "config": {"workload": w.name, "rows_per_step": sample_rows, "D": w.D,
+                   "note": "reference CPU implementation on the host cores; each step is a bounded row sample"},
+        "cpu_baseline": desc,
+        "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "rows_per_s": sample_rows / sec, "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------ our arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=50)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg2")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    w = Workload(args.workload, world)
+
+    if args.impl == "reference":
+        run_reference_arm(args, w, rank, world)
+        return
+
+    import torch.distributed as dist
+    from thot_b200 import abi
+    from thot_b200.sharding import allreduce_param_grads
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    abi.lib()
+
+    rows, D = w.rows_per_rank, w.D
+    x, dy, gamma, beta = synth_inputs(w, rows, dev, seed=1234 + rank)
+    code = abi.dtype_code(w.dtype)
+    y, dx = torch.empty_like(x), torch.empty_like(x)
+    mean = torch.empty(rows, dtype=torch.float32, device=dev)
+    rstd = torch.empty(rows, dtype=torch.float32, device=dev)
+    ncols = (2 if w.kind == "ln" else 1) * D
+    partials = torch.empty(abi.workspace_bytes(abi.WS_NORM_BWD, rows, D, code) // 4, dtype=torch.float32, device=dev)
+    grads = torch.empty(ncols, dtype=torch.float32, device=dev)
+    L = abi.lib()
+    import ctypes
+    nparts = ctypes.c_int64(0)
+    P = lambda t: None if t is None else ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    px, pdy, pg, pb, py, pdx, pm, pr, pp, pgr = map(P, (x, dy, gamma, beta, y, dx, mean, rstd, partials, grads))
+    stream = torch.cuda.current_stream()
+    st = ctypes.c_void_p(stream.cuda_stream)
+
+    def fwd():
+        if w.kind == "ln":
+            abi.check(L.nb2_layernorm_fwd(px, pg, pb, py, pm, pr, rows, D, w.eps, code, w.act, st))
+        else:
+            abi.check(L.nb2_rmsnorm_fwd(px, pg, py, pr, rows, D, w.eps, code, w.act, st))
+
+    def bwd():
+        if w.kind == "ln":
+            abi.check(L.nb2_layernorm_bwd(px, pdy, pg, pb, pm, pr, pdx, pp, ctypes.byref(nparts), rows, D, code, w.act, st))
+        else:
+            abi.check(L.nb2_rmsnorm_bwd(px, pdy, pg, pr, pdx, pp, ctypes.byref(nparts), rows, D, code, w.act, st))
+
+    def reduce_grads():
+        abi.check(L.nb2_colreduce_partials(pp, nparts.value, ncols, pgr, st))
+
+    def step():
+        fwd()
+        bwd()
+        reduce_grads()
+        if world > 1:
+            allreduce_param_grads(grads)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+
+    # ---- timed region: exactly K steps, device time, max over ranks
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    clocks = ClockSampler(local)
+    with clocks:
+        e0.record(stream)
+        for _ in range(args.steps):
+            step()
+        e1.record(stream)
+        clocks.sample()                      # the queue is still draining here
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    barrier()
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    sec_per_step = ms / 1e3 / args.steps
+    value = w.step_bytes() * world / sec_per_step / 1e9
+
+    # ---- per-kernel durations inside the same step sequence (CUDA events around each launch)
+    n_prof = min(args.steps, 200)
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(n_prof)]
+    for i in range(n_prof):
+        ev[i][0].record(stream); fwd()
+        ev[i][1].record(stream); bwd()
+        ev[i][2].record(stream); reduce_grads()
+        ev[i][3].record(stream)
+        if world > 1:
+            allreduce_param_grads(grads)
+    torch.cuda.synchronize()
+    t_fwd = float(np.mean([ev[i][0].elapsed_time(ev[i][1]) for i in range(n_prof)])) / 1e3
+    t_bwd = float(np.mean([ev[i][1].elapsed_time(ev[i][2]) for i in range(n_prof)])) / 1e3
+    t_red = float(np.mean([ev[i][2].elapsed_time(ev[i][3]) for i in range(n_prof)])) / 1e3
+
+    peaks_file = ROOT / "MEASURED_PEAKS.json"
+    if peaks_file.exists():
+        peak, peak_src = float(json.loads(peaks_file.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    else:
+        peak, peak_src = FALLBACK_HBM_GBS, "fallback"
+    traffic = None
+    tf = ROOT / "profiles" / "traffic.json"
+    if tf.exists():
+        traffic = json.loads(tf.read_text()).get(f"{w.kind}_bwd:{args.workload}")
+    bwd_gbs = w.bwd_bytes() / t_bwd / 1e9
+    fwd_gbs = w.fwd_bytes() / t_fwd / 1e9
+    roofline = {"bound": "hbm", "kernel": "norm_bwd_kernel (dX + dgamma/dbeta partials)", "achieved": bwd_gbs,
+                "peak": peak, "unit": "GB/s", "frac": bwd_gbs / peak, "traffic": traffic, "peak_source": peak_src,
+                "frac_of_nominal_8000": bwd_gbs / 8000.0}
+    kernels = {
+        "norm_fwd_kernel": {"ms": t_fwd * 1e3, "achieved_gbs": fwd_gbs, "frac": fwd_gbs / peak, "frac_of_nominal_8000": fwd_gbs / 8000.0},
+        "norm_bwd_kernel": {"ms": t_bwd * 1e3, "achieved_gbs": bwd_gbs, "frac": bwd_gbs / peak, "frac_of_nominal_8000": bwd_gbs / 8000.0},
+        "colreduce_kernel": {"ms": t_red * 1e3},
+    }
+
+    # ---- end to end through the host-buffer C-ABI call (pinned host memory, copies timed)
+    e2e = None
+    if not args.no_e2e:
+        e2e_rows = min(rows, 1 << 16)       # bounded so pinned host buffers stay modest on wide rows
+        hs = abi.HostStep(e2e_rows, D, w.dtype) if w.kind == "ln" else None
+        if hs is not None:
+            hx = x[:e2e_rows].cpu().pin_memory(); hdy = dy[:e2e_rows].cpu().pin_memory()
+            hg, hb = gamma.cpu(), beta.cpu()
+            hy = torch.empty_like(hx).pin_memory(); hdx = torch.empty_like(hx).pin_memory()
+            hgr = torch.empty(2, D, dtype=torch.float32).pin_memory()
+            n_e2e = max(3, min(args.steps, 30))
+            for _ in range(3):
+                hs.step(hx, hdy, hg, hb, hy, hdx, hgr, w.eps, w.act)
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(n_e2e):
+                hs.step(hx, hdy, hg, hb, hy, hdx, hgr, w.eps, w.act)
+            torch.cuda.synchronize()
+            dt = (time.perf_counter() - t0) / n_e2e
+            if world > 1:
+                t = torch.tensor([dt], device=dev, dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                dt = float(t.item())
+            hs.close()
+            act_bytes = e2e_rows * D * w.elt
+            e2e = {"value": w.step_bytes(e2e_rows) * world / dt / 1e9, "unit": UNIT,
+                   "h2d_bytes_per_step": 2 * act_bytes + 2 * D * w.elt, "d2h_bytes_per_step": 2 * act_bytes + 2 * D * 4,
+                   "ms_per_step": dt * 1e3, "rows_per_step": e2e_rows, "steps": n_e2e,
+                   "call": "nb2_layernorm_act_step_host (x, dY in; y, dX, dgamma|dbeta out)"}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        try:
+            cpu = reference_cpu_run(w, 1000, 2, budget_s=15.0)[4]
+        except Exception as exc:      # a missing oracle must not hide the GPU numbers
+            cpu = {"error": str(exc)}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": sec_per_step * 1e3, "higher_is_better": True,
+            "scaling": w.scaling, "vs_baseline": None,
+            "dtype": "f32" if w.dtype == torch.float32 else "bf16", "data": "synthetic",
+            "config": {"workload": w.name, "rows_per_gpu": rows, "D": D, "global_rows": rows * world,
+                       "l2": "inputs larger than L2 (each step streams %.0f MB per GPU)" % (w.step_bytes() / 1e6),
+                       "collective": "NCCL allreduce of [%d] fp32 per step" % ncols if world > 1 else "none"},
+            "rows_per_s": rows * world / sec_per_step,
+            "frac_of_nominal_8000_per_gpu": value / world / 8000.0,
+            "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu, "e2e": e2e,
+            "clocks": clocks.summary(), "gpu_launches": 3 * args.steps,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

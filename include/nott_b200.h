@@ -1,0 +1,248 @@
+/*
+ * nott_b200.h — C ABI of libnott_b200.so: hand-written sm_100a kernels for the
+ * memory-bound row-op path of the Nott (MoonFlowww/Thot) C++ library.
+ *
+ * Conventions
+ *   - Every function returns an int status: 0 = ok, < 0 = invalid argument
+ *     (NB2_ERR_*), > 0 = the cudaError_t the launch produced.  Nothing throws.
+ *     nb2_last_error_string() describes the last non-zero status of the
+ *     calling thread.
+ *   - All pointers are DEVICE pointers unless the name ends in `_host`.
+ *     Outputs are caller-allocated; no function here allocates or frees device
+ *     memory, synchronises the device, or touches any stream but `stream`.
+ *     `stream` is a cudaStream_t passed as void* so the header needs no CUDA
+ *     include.
+ *   - Tensors are row-major `[rows, D]` views of Nott's contiguous `(B,S,D)`
+ *     tensors (the reference makes them contiguous in normalise_to_sequence,
+ *     src/block/details/transformers/classic.hpp:217-273).
+ *   - `dtype` selects the element type of activations AND of the affine
+ *     parameters (NB2_F32 or NB2_BF16).  Statistics, partial sums and every
+ *     intermediate are fp32 (fp64 in the partial reduce).
+ *   - There is no CPU fallback: without a CUDA device every compute entry
+ *     point returns the CUDA error.
+ *
+ * Each declaration cites the reference interface it replaces, by the file's
+ * path inside the MoonFlowww/Thot project.
+ */
+#ifndef NOTT_B200_H
+#define NOTT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* every symbol declared here is exported; everything else in the library is hidden */
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+#define NB2_ABI_VERSION 1
+
+/* element types */
+enum { NB2_F32 = 0, NB2_BF16 = 1 };
+
+/* activation fused behind a norm, or applied stand-alone.  The numbering is
+ * this library's own; the host layer maps Nott::Activation::Type
+ * (src/activation/activation.hpp:6-21) onto it. */
+enum { NB2_ACT_NONE = 0, NB2_ACT_GELU = 1, NB2_ACT_SILU = 2 };
+
+/* index types for the embedding gather */
+enum { NB2_I32 = 0, NB2_I64 = 1 };
+
+/* status codes (< 0) */
+enum {
+    NB2_OK = 0,
+    NB2_ERR_NULL = -1,        /* a required pointer is NULL              */
+    NB2_ERR_SHAPE = -2,       /* rows/D/stride out of the supported range */
+    NB2_ERR_DTYPE = -3,       /* unknown dtype / act / index type         */
+    NB2_ERR_ALIGN = -4,       /* pointer or stride alignment              */
+    NB2_ERR_WORKSPACE = -5,   /* workspace too small                      */
+    NB2_ERR_DEVICE = -6       /* device-side status word reported a fault */
+};
+
+/* which operation a workspace query is for */
+enum {
+    NB2_WS_NORM_BWD = 0,      /* per-CTA dgamma/dbeta (or dweight) partials */
+    NB2_WS_EMBEDDING_BWD = 1, /* sort keys + radix-sort temporary           */
+    NB2_WS_ROPE_TABLE = 2     /* cos/sin table [S, hd/2, 2] fp32            */
+};
+
+int nb2_abi_version(void);
+const char* nb2_last_error_string(void);
+
+/* Number of SMs the library sized its persistent grids for on the current
+ * device (148 on B200); <= 0 when no device is usable. */
+int nb2_sm_count(void);
+
+/*
+ * Workspace sizes, in bytes, for the calls that need scratch memory.
+ *   NB2_WS_NORM_BWD      : a = rows, b = D            -> partials buffer
+ *   NB2_WS_EMBEDDING_BWD : a = tokens, b = vocab rows -> sort scratch
+ *   NB2_WS_ROPE_TABLE    : a = seq_len, b = head_dim  -> cos/sin table
+ * Returns 0 for unknown `op`.
+ */
+size_t nb2_workspace_bytes(int op, int64_t a, int64_t b, int dtype);
+
+/* ------------------------------------------------------------------ *
+ * LayerNorm (+ fused GELU / SiLU)
+ * Replaces torch::nn::LayerNorm::forward as Nott's blocks call it
+ * (src/block/details/transformers/classic.hpp:436,445,520; bert.hpp:189;
+ * vision.hpp:193) followed, when `act` != NONE, by
+ * Nott::Activation::Details::apply (src/activation/apply.hpp:24-57) with
+ * GeLU (details/gelu.hpp:11-15, exact erf) or SiLU (details/silu.hpp:12-16).
+ *   y = act( (x - mean) * rstd * gamma + beta ),  rstd = 1/sqrt(var_biased + eps)
+ * gamma/beta may be NULL (elementwise_affine=false, classic.hpp:54-57).
+ * mean/rstd ([rows] fp32) are written for the backward; either may be NULL
+ * for inference.
+ * ------------------------------------------------------------------ */
+int nb2_layernorm_fwd(const void* x, const void* gamma, const void* beta,
+                      void* y, float* mean, float* rstd,
+                      int64_t rows, int64_t D, double eps,
+                      int dtype, int act, void* stream);
+
+/*
+ * Backward of the above (what libtorch autograd runs for
+ * native_layer_norm_backward + gelu_backward/silu_backward when Nott calls
+ * loss.backward(), src/core.hpp:3811-3820).  Writes dx and one
+ * [2, D] fp32 partial (dgamma row, dbeta row) per CTA into `partials`
+ * (size nb2_workspace_bytes(NB2_WS_NORM_BWD, rows, D, dtype)); `n_partials`
+ * receives how many were written.  Finish with nb2_colreduce_partials.
+ * partials may be NULL when gamma is NULL (no affine gradients wanted).
+ */
+int nb2_layernorm_bwd(const void* x, const void* dy, const void* gamma, const void* beta,
+                      const float* mean, const float* rstd,
+                      void* dx, float* partials, int64_t* n_partials_host,
+                      int64_t rows, int64_t D,
+                      int dtype, int act, void* stream);
+
+/* ------------------------------------------------------------------ *
+ * RMSNorm (+ fused GELU / SiLU)
+ * Replaces Nott's RMSNormImpl::forward
+ * (src/block/details/transformers/mamba.hpp:124-142; options eps=1e-6,
+ * learnable, :25-28):  y = act( x * rsqrt(mean(x^2) + eps) * weight ).
+ * weight may be NULL (learnable=false).  rstd ([rows] fp32) may be NULL.
+ * ------------------------------------------------------------------ */
+int nb2_rmsnorm_fwd(const void* x, const void* weight,
+                    void* y, float* rstd,
+                    int64_t rows, int64_t D, double eps,
+                    int dtype, int act, void* stream);
+
+/* Backward: dx and per-CTA [1, D] fp32 dweight partials (same workspace
+ * query and second pass as LayerNorm, with 1 row per partial). */
+int nb2_rmsnorm_bwd(const void* x, const void* dy, const void* weight,
+                    const float* rstd,
+                    void* dx, float* partials, int64_t* n_partials_host,
+                    int64_t rows, int64_t D,
+                    int dtype, int act, void* stream);
+
+/*
+ * Second pass: out[c] = sum_p partials[p, c] for c < ncols, summed in fp64 in
+ * a fixed order (deterministic), written as fp32.  For LayerNorm ncols = 2*D
+ * (out = [dgamma | dbeta]); for RMSNorm ncols = D.
+ */
+int nb2_colreduce_partials(const float* partials, int64_t n_partials, int64_t ncols,
+                           float* out, void* stream);
+
+/* ------------------------------------------------------------------ *
+ * Stand-alone activations: Nott::Activation::Details::GeLU / SiLU
+ * (src/activation/details/gelu.hpp:11-15, silu.hpp:12-16; Swish,
+ * swish.hpp:12-17, is the same function).  n = number of elements.
+ * bwd: dx = dy * act'(x)   (SiLU' is the reference's own dSiLU,
+ * src/activation/details/dsilu.hpp:14-15).
+ * ------------------------------------------------------------------ */
+int nb2_act_fwd(const void* x, void* y, int64_t n, int dtype, int act, void* stream);
+int nb2_act_bwd(const void* x, const void* dy, void* dx, int64_t n, int dtype, int act, void* stream);
+
+/* ------------------------------------------------------------------ *
+ * SiLU gate: out[r, c] = silu(a[r, c]) * b[r, c],  r < rows, c < H.
+ * Replaces Nott::Activation::Details::SwiGLU
+ * (src/activation/details/swiglu.hpp:13-25: a | b are the two halves of one
+ * [rows, 2H] tensor -> lda = ldb = 2H, b = a + H) and Mamba's gated feed
+ * forward `up * silu(gate)` (mamba.hpp:441-449: separate contiguous tensors
+ * -> lda = ldb = H, a = gate, b = up).  ld* are row strides in ELEMENTS.
+ * out is [rows, H] with row stride ldo.
+ * bwd: da = dy * b * silu'(a),  db = dy * silu(a); da/db use strides ldda/lddb.
+ * ------------------------------------------------------------------ */
+int nb2_silu_gate_fwd(const void* a, int64_t lda, const void* b, int64_t ldb,
+                      void* out, int64_t ldo,
+                      int64_t rows, int64_t H, int dtype, void* stream);
+int nb2_silu_gate_bwd(const void* a, int64_t lda, const void* b, int64_t ldb,
+                      const void* dy, int64_t lddy,
+                      void* da, int64_t ldda, void* db, int64_t lddb,
+                      int64_t rows, int64_t H, int dtype, void* stream);
+
+/* ------------------------------------------------------------------ *
+ * Token-embedding gather: out[t, :] = table[ids[t], :], a bit copy.
+ * Replaces torch::nn::Embedding::forward as called by BertEmbeddingImpl
+ * (src/block/details/transformers/bert.hpp:162-163,176-187),
+ * TokenEmbeddingImpl (ebt.hpp:124-126) and the learned positional encoding
+ * (classic.hpp:366-370).  ids are int32 or int64 (`index_type`).
+ * An id outside [0, vocab) never faults: that output row is zero-filled and,
+ * if `status` (device int64[2]) is non-NULL, status[0] is set to 1 and
+ * status[1] to the offending token position.
+ * ------------------------------------------------------------------ */
+int nb2_embedding_fwd(const void* table, const void* ids, void* out,
+                      int64_t tokens, int64_t vocab, int64_t D,
+                      int dtype, int index_type, int64_t* status, void* stream);
+
+/*
+ * Backward: dtable[v, :] = sum over {t : ids[t] == v} of dout[t, :], summed in
+ * fp32 in ascending t (deterministic), rows without tokens set to zero.
+ * Every row of dtable is written.  `workspace` has
+ * nb2_workspace_bytes(NB2_WS_EMBEDDING_BWD, tokens, vocab, dtype) bytes.
+ */
+int nb2_embedding_bwd(const void* dout, const void* ids, void* dtable,
+                      int64_t tokens, int64_t vocab, int64_t D,
+                      int dtype, int index_type,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------ *
+ * Rotary embedding, rotate-half pairing (i, i + hd/2).  The reference has no
+ * implementation (only docs/sub/block/README.md:132-136 mentions it); the
+ * place it belongs is between the (B,H,S,hd) view and the attention kernel
+ * in MultiHeadAttentionImpl::forward (src/attention/details/head.hpp:70-74).
+ *   angle(s, i) = float(pos[s]) * float(theta^(-2i/hd)),   i < hd/2
+ *   out[i]        = x[i]*cos - x[i+hd/2]*sin
+ *   out[i+hd/2]   = x[i+hd/2]*cos + x[i]*sin
+ * Layout: x, out are [B, S, H, hd] contiguous.  positions (int32 [S]) may be
+ * NULL for 0..S-1.  The cos/sin table ([S, hd/2] float2, fp32) is built once
+ * by nb2_rope_table and reused for q, k and the backward.
+ * bwd is the rotation by -angle (`inverse` != 0).
+ * ------------------------------------------------------------------ */
+int nb2_rope_table(float* cos_sin, const int32_t* positions,
+                   int64_t S, int64_t hd, double theta, void* stream);
+int nb2_rope_apply(const void* x, const float* cos_sin, void* out,
+                   int64_t B, int64_t S, int64_t H, int64_t hd,
+                   int dtype, int inverse, void* stream);
+
+/* ------------------------------------------------------------------ *
+ * Host-buffer training step of the fused LayerNorm->activation path: the call
+ * a host-resident caller makes (the reference stages batches from pinned host
+ * memory itself, src/core.hpp:4197-4227).  x_host, dy_host, y_host, dx_host
+ * are HOST pointers (pinned for full speed); the call copies row chunks in on
+ * one stream, runs fwd + bwd, copies y and dx out on another, and returns
+ * after dgamma_dbeta_host ([2, D] fp32) is complete.  `ctx` is created once
+ * per (device, max rows per call, D, dtype) and owns the device staging
+ * buffers; creating and destroying it are the only calls in this library that
+ * allocate device memory.
+ * ------------------------------------------------------------------ */
+typedef struct nb2_host_ctx nb2_host_ctx;
+int nb2_host_ctx_create(nb2_host_ctx** ctx, int64_t max_rows, int64_t D, int dtype, int64_t chunk_rows);
+int nb2_host_ctx_destroy(nb2_host_ctx* ctx);
+int nb2_layernorm_act_step_host(nb2_host_ctx* ctx,
+                                const void* x_host, const void* dy_host,
+                                const void* gamma_host, const void* beta_host,
+                                void* y_host, void* dx_host, float* dgamma_dbeta_host,
+                                int64_t rows, int64_t D, double eps, int dtype, int act);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NOTT_B200_H */

@@ -1,0 +1,113 @@
+"""TEST INFRASTRUCTURE, NOT PRODUCT CODE: numpy front end of oracle_rowops.c.
+
+Inputs are fp32 numpy arrays (bf16 cases pass bf16-representable fp32 values);
+outputs are float64 arrays, which the tests round to the precision under test.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_double, c_int, c_int64, c_void_p
+
+import numpy as np
+
+from . import build_ref
+
+ACT_NONE, ACT_GELU, ACT_SILU = 0, 1, 2
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        path = build_ref.C_LIB if build_ref.C_LIB.exists() else build_ref.build_c_oracle()
+        _lib = ctypes.CDLL(str(path))
+        _lib.orc_embedding.restype = c_int64
+    return _lib
+
+
+def _f32(a):
+    return None if a is None else np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _p(a):
+    return None if a is None else c_void_p(a.ctypes.data)
+
+
+def layernorm_act(x, gamma, beta, dy, eps, act=ACT_NONE):
+    x, gamma, beta, dy = _f32(x), _f32(gamma), _f32(beta), _f32(dy)
+    rows, D = x.shape
+    y = np.empty((rows, D)); mean = np.empty(rows); rstd = np.empty(rows)
+    dx = np.empty((rows, D)) if dy is not None else None
+    dg = np.empty(D) if dy is not None else None
+    db = np.empty(D) if dy is not None else None
+    lib().orc_layernorm_act(_p(x), _p(gamma), _p(beta), _p(dy), c_int64(rows), c_int64(D), c_double(eps), c_int(act),
+                            _p(y), _p(mean), _p(rstd), _p(dx), _p(dg), _p(db))
+    return dict(y=y, mean=mean, rstd=rstd, dx=dx, dgamma=dg, dbeta=db)
+
+
+def rmsnorm_act(x, weight, dy, eps, act=ACT_NONE):
+    x, weight, dy = _f32(x), _f32(weight), _f32(dy)
+    rows, D = x.shape
+    y = np.empty((rows, D)); rstd = np.empty(rows)
+    dx = np.empty((rows, D)) if dy is not None else None
+    dw = np.empty(D) if dy is not None else None
+    lib().orc_rmsnorm_act(_p(x), _p(weight), _p(dy), c_int64(rows), c_int64(D), c_double(eps), c_int(act),
+                          _p(y), _p(rstd), _p(dx), _p(dw))
+    return dict(y=y, rstd=rstd, dx=dx, dweight=dw)
+
+
+def act(x, dy, act_code):
+    x, dy = _f32(x), _f32(dy)
+    y = np.empty(x.shape); dx = np.empty(x.shape) if dy is not None else None
+    lib().orc_act(_p(x), _p(dy), c_int64(x.size), c_int(act_code), _p(y), _p(dx))
+    return dict(y=y, dx=dx)
+
+
+def silu_gate(a, b, dy):
+    """a, b: 2-D fp32 arrays, possibly row-strided views with unit column stride."""
+    assert a.dtype == np.float32 and b.dtype == np.float32
+    assert a.strides[1] == 4 and b.strides[1] == 4
+    rows, H = a.shape
+    dy = _f32(dy)
+    out = np.empty((rows, H))
+    da = np.empty((rows, H)) if dy is not None else None
+    db = np.empty((rows, H)) if dy is not None else None
+    lib().orc_silu_gate(_p(a), c_int64(a.strides[0] // 4), _p(b), c_int64(b.strides[0] // 4), _p(dy), c_int64(H),
+                        c_int64(rows), c_int64(H), _p(out), _p(da), _p(db))
+    return dict(out=out, da=da, db=db)
+
+
+def embedding(table, ids):
+    """table: any 2-D array (rows copied byte for byte); -> (out, first bad position or -1)."""
+    table = np.ascontiguousarray(table)
+    ids = np.ascontiguousarray(ids, dtype=np.int64).reshape(-1)
+    vocab, D = table.shape
+    out = np.empty((ids.size, D), dtype=table.dtype)
+    bad = lib().orc_embedding(_p(table), _p(ids), c_int64(ids.size), c_int64(vocab),
+                              c_int64(D * table.dtype.itemsize), _p(out))
+    return out, int(bad)
+
+
+def embedding_bwd(dout, ids, vocab):
+    dout = _f32(dout)
+    ids = np.ascontiguousarray(ids, dtype=np.int64).reshape(-1)
+    D = dout.shape[-1]
+    dtable = np.empty((vocab, D))
+    lib().orc_embedding_bwd(_p(dout), _p(ids), c_int64(ids.size), c_int64(vocab), c_int64(D), _p(dtable))
+    return dtable
+
+
+def rope_table(S, hd, theta=10000.0, positions=None):
+    cs = np.empty((S, hd // 2, 2), dtype=np.float32)
+    pos = None if positions is None else np.ascontiguousarray(positions, dtype=np.int32)
+    lib().orc_rope_table(_p(pos), c_int64(S), c_int64(hd), c_double(theta), _p(cs))
+    return cs
+
+
+def rope_apply(x, cos_sin, inverse=False):
+    x = _f32(x)
+    B, S, H, hd = x.shape
+    out = np.empty(x.shape)
+    lib().orc_rope_apply(_p(x), _p(np.ascontiguousarray(cos_sin, dtype=np.float32)), c_int64(B), c_int64(S),
+                         c_int64(H), c_int64(hd), c_int(int(inverse)), _p(out))
+    return out

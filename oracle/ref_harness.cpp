@@ -1,0 +1,256 @@
+// TEST INFRASTRUCTURE, NOT PRODUCT CODE.
+//
+// The reference's own CPU implementation of the row-op path, compiled from the
+// reference's headers where they lie (never copied) against the installed
+// libtorch, behind a small C interface so Python can drive it with raw buffers.
+// Built by oracle/build_ref.py into oracle/_ref/libnott_ref.so.
+//
+// Reference code exercised here (paths inside the MoonFlowww/Thot project):
+//   - Nott::Activation::Details::apply        src/activation/apply.hpp:24-57
+//     (GeLU details/gelu.hpp:11-15, SiLU silu.hpp:12-16, SwiGLU swiglu.hpp:13-25)
+//   - Mamba RMSNorm module                    src/block/details/transformers/mamba.hpp:110-150
+//   - Mamba gated feed forward `up * silu(gate)`  mamba.hpp:443-446 (that one
+//     expression, restated: it is private to EncoderLayerImpl)
+//   - torch::nn::LayerNorm built the way the blocks build it
+//     src/block/details/transformers/classic.hpp:399-404 (options :54-57)
+//   - EBT TokenEmbedding (nn::Embedding gather)   src/block/details/transformers/ebt.hpp:81-160
+//
+// Buffers are always fp32 (or int64 ids) on the host; `compute` picks the dtype
+// the modules run in: 0 = fp32, 1 = fp64 (arbiter for long sums), 2 = native
+// bf16 (informational: the reference rounds after every ATen op there).
+#include <torch/torch.h>
+
+#include <chrono>
+#include <cstdint>
+#include <cstring>
+#include <string>
+
+#include "src/activation/apply.hpp"
+#include "src/block/details/transformers/mamba.hpp"
+#include "src/block/details/transformers/ebt.hpp"
+
+namespace {
+
+thread_local std::string g_error;
+
+torch::ScalarType compute_type(int compute) {
+    switch (compute) {
+        case 1: return torch::kFloat64;
+        case 2: return torch::kBFloat16;
+        default: return torch::kFloat32;
+    }
+}
+
+torch::Tensor wrap(const float* p, std::vector<int64_t> shape, int compute) {
+    auto t = torch::from_blob(const_cast<float*>(p), shape, torch::kFloat32);
+    return compute == 0 ? t : t.to(compute_type(compute));
+}
+
+void store(const torch::Tensor& t, float* out) {
+    if (out == nullptr || !t.defined()) return;
+    auto f = t.detach().to(torch::kFloat32).contiguous();
+    std::memcpy(out, f.data_ptr<float>(), sizeof(float) * static_cast<size_t>(f.numel()));
+}
+void store_f64(const torch::Tensor& t, double* out) {
+    if (out == nullptr || !t.defined()) return;
+    auto f = t.detach().to(torch::kFloat64).contiguous();
+    std::memcpy(out, f.data_ptr<double>(), sizeof(double) * static_cast<size_t>(f.numel()));
+}
+
+Nott::Activation::Type act_type(int act) {
+    // 0 none, 1 GeLU, 2 SiLU -- the numbering of the CUDA library's ABI
+    switch (act) {
+        case 1: return Nott::Activation::Type::GeLU;
+        case 2: return Nott::Activation::Type::SiLU;
+        default: return Nott::Activation::Type::Identity;
+    }
+}
+
+template <class F>
+int guarded(F&& f) {
+    try {
+        f();
+        return 0;
+    } catch (const std::exception& e) {
+        g_error = e.what();
+        return 1;
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* ref_last_error() { return g_error.c_str(); }
+int ref_get_num_threads() { return at::get_num_threads(); }
+void ref_set_num_threads(int n) { at::set_num_threads(n); }
+
+// LayerNorm -> activation, forward (+ backward when dy != NULL).
+// gamma/beta NULL -> elementwise_affine(false).  dgamma64/dbeta64 receive the
+// gradients at the module's compute precision widened to double.
+int ref_layernorm_act(const float* x, const float* gamma, const float* beta, const float* dy,
+                      int64_t rows, int64_t D, double eps, int act, int compute,
+                      float* y, float* dx, float* dgamma, float* dbeta,
+                      double* dgamma64, double* dbeta64) {
+    return guarded([&] {
+        const bool affine = gamma != nullptr;
+        auto options = torch::nn::LayerNormOptions(std::vector<int64_t>{D}).eps(eps).elementwise_affine(affine);
+        torch::nn::LayerNorm norm(options);
+        norm->to(compute_type(compute));
+        if (affine) {
+            torch::NoGradGuard ng;
+            norm->weight.copy_(wrap(gamma, {D}, compute));
+            norm->bias.copy_(wrap(beta, {D}, compute));
+        }
+        auto xin = wrap(x, {rows, D}, compute).clone().requires_grad_(dy != nullptr);
+        auto out = Nott::Activation::Details::apply(act_type(act), norm->forward(xin));
+        store(out, y);
+        if (dy != nullptr) {
+            out.backward(wrap(dy, {rows, D}, compute));
+            store(xin.grad(), dx);
+            if (affine) {
+                store(norm->weight.grad(), dgamma);
+                store(norm->bias.grad(), dbeta);
+                store_f64(norm->weight.grad(), dgamma64);
+                store_f64(norm->bias.grad(), dbeta64);
+            }
+        }
+    });
+}
+
+// Nott's RMSNorm module -> activation.  weight NULL -> learnable=false.
+int ref_rmsnorm_act(const float* x, const float* weight, const float* dy,
+                    int64_t rows, int64_t D, double eps, int act, int compute,
+                    float* y, float* dx, float* dweight, double* dweight64) {
+    return guarded([&] {
+        namespace M = Nott::Block::Details::Transformer::Mamba;
+        M::RMSNormOptions opt{};
+        opt.eps = eps;
+        opt.learnable = weight != nullptr;
+        M::Detail::RMSNorm norm(D, opt);
+        norm->to(compute_type(compute));
+        if (weight != nullptr) {
+            torch::NoGradGuard ng;
+            norm->named_parameters()["weight"].copy_(wrap(weight, {D}, compute));
+        }
+        auto xin = wrap(x, {rows, D}, compute).clone().requires_grad_(dy != nullptr);
+        auto out = Nott::Activation::Details::apply(act_type(act), norm->forward(xin));
+        store(out, y);
+        if (dy != nullptr) {
+            out.backward(wrap(dy, {rows, D}, compute));
+            store(xin.grad(), dx);
+            if (weight != nullptr) {
+                store(norm->named_parameters()["weight"].grad(), dweight);
+                store_f64(norm->named_parameters()["weight"].grad(), dweight64);
+            }
+        }
+    });
+}
+
+// apply(GeLU|SiLU) on a flat tensor.
+int ref_act(const float* x, const float* dy, int64_t n, int act, int compute, float* y, float* dx) {
+    return guarded([&] {
+        auto xin = wrap(x, {n}, compute).clone().requires_grad_(dy != nullptr);
+        auto out = Nott::Activation::Details::apply(act_type(act), xin);
+        store(out, y);
+        if (dy != nullptr) {
+            out.backward(wrap(dy, {n}, compute));
+            store(xin.grad(), dx);
+        }
+    });
+}
+
+// apply(SwiGLU) on one [rows, 2H] tensor; dinput is [rows, 2H].
+int ref_swiglu(const float* input, const float* dy, int64_t rows, int64_t H, int compute,
+               float* out, float* dinput) {
+    return guarded([&] {
+        auto xin = wrap(input, {rows, 2 * H}, compute).clone().requires_grad_(dy != nullptr);
+        auto o = Nott::Activation::Details::apply(Nott::Activation::Type::SwiGLU, xin);
+        store(o, out);
+        if (dy != nullptr) {
+            o.backward(wrap(dy, {rows, H}, compute));
+            store(xin.grad(), dinput);
+        }
+    });
+}
+
+// Mamba's gated feed forward on separate tensors: up * silu(gate).
+int ref_mamba_gate(const float* gate, const float* up, const float* dy, int64_t rows, int64_t H, int compute,
+                   float* out, float* dgate, float* dup) {
+    return guarded([&] {
+        auto g = wrap(gate, {rows, H}, compute).clone().requires_grad_(dy != nullptr);
+        auto u = wrap(up, {rows, H}, compute).clone().requires_grad_(dy != nullptr);
+        auto o = u * torch::silu(g);
+        store(o, out);
+        if (dy != nullptr) {
+            o.backward(wrap(dy, {rows, H}, compute));
+            store(g.grad(), dgate);
+            store(u.grad(), dup);
+        }
+    });
+}
+
+// EBT TokenEmbedding (discrete modality) gather; ids int64 as the reference requires.
+// dout != NULL also returns the dense table gradient.
+int ref_token_embedding(const float* table, const int64_t* ids, const float* dout,
+                        int64_t tokens, int64_t vocab, int64_t D, int compute,
+                        float* out, float* dtable) {
+    return guarded([&] {
+        namespace E = Nott::Block::Details::Transformer::EBT;
+        E::ModalityOptions opt{};
+        opt.type = E::ModalityType::Discrete;
+        opt.vocab_size = vocab;
+        opt.embed_dim = D;
+        E::Detail::TokenEmbedding emb(opt);
+        emb->to(compute_type(compute));
+        auto weight = emb->named_parameters()["embedding.weight"];
+        {
+            torch::NoGradGuard ng;
+            weight.copy_(wrap(table, {vocab, D}, compute));
+        }
+        auto idt = torch::from_blob(const_cast<int64_t*>(ids), {tokens}, torch::kInt64);
+        auto o = emb->forward(idt);
+        store(o, out);
+        if (dout != nullptr) {
+            o.backward(wrap(dout, {tokens, D}, compute));
+            store(weight.grad(), dtable);
+        }
+    });
+}
+
+// Times forward + autograd backward of LayerNorm->act (rms == 0) or Nott's
+// RMSNorm->act (rms != 0) on seeded N(0,1) inputs that are built once; only the
+// module calls are inside the clock.  Returns seconds per iteration (mean of
+// `iters` after `warmup`), or a negative value on error.
+double ref_time_norm_act(int rms, int64_t rows, int64_t D, double eps, int act, int compute,
+                         int iters, int warmup) {
+    double result = -1.0;
+    guarded([&] {
+        namespace M = Nott::Block::Details::Transformer::Mamba;
+        torch::manual_seed(0);
+        const auto dt = compute_type(compute);
+        auto x = torch::randn({rows, D}).to(dt).requires_grad_(true);
+        auto dy = torch::randn({rows, D}).to(dt);
+        torch::nn::LayerNorm ln(torch::nn::LayerNormOptions(std::vector<int64_t>{D}).eps(eps));
+        M::RMSNormOptions opt{};
+        opt.eps = eps;
+        M::Detail::RMSNorm rn(D, opt);
+        ln->to(dt);
+        rn->to(dt);
+        auto once = [&] {
+            auto h = rms ? rn->forward(x) : ln->forward(x);
+            auto out = Nott::Activation::Details::apply(act_type(act), h);
+            out.backward(dy);
+            x.mutable_grad().reset();
+            for (auto& p : (rms ? rn->parameters() : ln->parameters())) p.mutable_grad().reset();
+        };
+        for (int i = 0; i < warmup; ++i) once();
+        const auto t0 = std::chrono::steady_clock::now();
+        for (int i = 0; i < iters; ++i) once();
+        const auto t1 = std::chrono::steady_clock::now();
+        result = std::chrono::duration<double>(t1 - t0).count() / (iters > 0 ? iters : 1);
+    });
+    return result;
+}
+
+}  // extern "C"

@@ -1,0 +1,130 @@
+"""TEST INFRASTRUCTURE, NOT PRODUCT CODE: numpy front end of oracle/_ref/libnott_ref.so,
+the reference's own modules (compiled from its headers) running on libtorch CPU.
+
+compute: 0 = fp32, 1 = fp64, 2 = native bf16 (see ref_harness.cpp).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_double, c_int, c_int64, c_void_p
+
+import numpy as np
+
+from . import build_ref
+
+_lib = None
+
+
+def available() -> bool:
+    return build_ref.REF_LIB.exists()
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        import torch  # noqa: F401  (loads libtorch before the harness resolves it)
+
+        if not build_ref.REF_LIB.exists():
+            raise RuntimeError("oracle/_ref/libnott_ref.so is not built (needs the reference checkout)")
+        _lib = ctypes.CDLL(str(build_ref.REF_LIB))
+        _lib.ref_last_error.restype = ctypes.c_char_p
+        _lib.ref_time_norm_act.restype = c_double
+    return _lib
+
+
+def _chk(rc):
+    if rc != 0:
+        raise RuntimeError("reference harness: " + lib().ref_last_error().decode())
+
+
+def _f32(a):
+    return None if a is None else np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _p(a):
+    return None if a is None else c_void_p(a.ctypes.data)
+
+
+def num_threads() -> int:
+    return int(lib().ref_get_num_threads())
+
+
+def set_num_threads(n: int) -> None:
+    lib().ref_set_num_threads(c_int(n))
+
+
+def layernorm_act(x, gamma, beta, dy, eps, act=0, compute=0):
+    x, gamma, beta, dy = _f32(x), _f32(gamma), _f32(beta), _f32(dy)
+    rows, D = x.shape
+    y = np.empty((rows, D), np.float32)
+    bwd = dy is not None
+    dx = np.empty((rows, D), np.float32) if bwd else None
+    aff = bwd and gamma is not None
+    dg = np.empty(D, np.float32) if aff else None
+    db = np.empty(D, np.float32) if aff else None
+    dg64 = np.empty(D, np.float64) if aff else None
+    db64 = np.empty(D, np.float64) if aff else None
+    _chk(lib().ref_layernorm_act(_p(x), _p(gamma), _p(beta), _p(dy), c_int64(rows), c_int64(D), c_double(eps),
+                                 c_int(act), c_int(compute), _p(y), _p(dx), _p(dg), _p(db), _p(dg64), _p(db64)))
+    return dict(y=y, dx=dx, dgamma=dg, dbeta=db, dgamma64=dg64, dbeta64=db64)
+
+
+def rmsnorm_act(x, weight, dy, eps, act=0, compute=0):
+    x, weight, dy = _f32(x), _f32(weight), _f32(dy)
+    rows, D = x.shape
+    y = np.empty((rows, D), np.float32)
+    bwd = dy is not None
+    dx = np.empty((rows, D), np.float32) if bwd else None
+    dw = np.empty(D, np.float32) if bwd and weight is not None else None
+    dw64 = np.empty(D, np.float64) if bwd and weight is not None else None
+    _chk(lib().ref_rmsnorm_act(_p(x), _p(weight), _p(dy), c_int64(rows), c_int64(D), c_double(eps), c_int(act),
+                               c_int(compute), _p(y), _p(dx), _p(dw), _p(dw64)))
+    return dict(y=y, dx=dx, dweight=dw, dweight64=dw64)
+
+
+def act(x, dy, act_code, compute=0):
+    x, dy = _f32(x), _f32(dy)
+    y = np.empty(x.shape, np.float32)
+    dx = np.empty(x.shape, np.float32) if dy is not None else None
+    _chk(lib().ref_act(_p(x), _p(dy), c_int64(x.size), c_int(act_code), c_int(compute), _p(y), _p(dx)))
+    return dict(y=y, dx=dx)
+
+
+def swiglu(inp, dy, compute=0):
+    inp, dy = _f32(inp), _f32(dy)
+    rows, H2 = inp.shape
+    H = H2 // 2
+    out = np.empty((rows, H), np.float32)
+    dinp = np.empty((rows, H2), np.float32) if dy is not None else None
+    _chk(lib().ref_swiglu(_p(inp), _p(dy), c_int64(rows), c_int64(H), c_int(compute), _p(out), _p(dinp)))
+    return dict(out=out, dinput=dinp)
+
+
+def mamba_gate(gate, up, dy, compute=0):
+    gate, up, dy = _f32(gate), _f32(up), _f32(dy)
+    rows, H = gate.shape
+    out = np.empty((rows, H), np.float32)
+    dg = np.empty((rows, H), np.float32) if dy is not None else None
+    du = np.empty((rows, H), np.float32) if dy is not None else None
+    _chk(lib().ref_mamba_gate(_p(gate), _p(up), _p(dy), c_int64(rows), c_int64(H), c_int(compute), _p(out), _p(dg), _p(du)))
+    return dict(out=out, dgate=dg, dup=du)
+
+
+def token_embedding(table, ids, dout=None, compute=0):
+    table, dout = _f32(table), _f32(dout)
+    ids = np.ascontiguousarray(ids, dtype=np.int64).reshape(-1)
+    vocab, D = table.shape
+    out = np.empty((ids.size, D), np.float32)
+    dtable = np.empty((vocab, D), np.float32) if dout is not None else None
+    _chk(lib().ref_token_embedding(_p(table), _p(ids), _p(dout), c_int64(ids.size), c_int64(vocab), c_int64(D),
+                                   c_int(compute), _p(out), _p(dtable)))
+    return dict(out=out, dtable=dtable)
+
+
+def time_norm_act(kind, rows, D, eps, act, compute=0, iters=10, warmup=2) -> float:
+    """Seconds per forward+backward of the reference modules, timed inside the harness."""
+    t = lib().ref_time_norm_act(c_int(1 if kind == "rms" else 0), c_int64(rows), c_int64(D), c_double(eps),
+                                c_int(act), c_int(compute), c_int(iters), c_int(warmup))
+    if t < 0:
+        raise RuntimeError("reference harness: " + lib().ref_last_error().decode())
+    return float(t)

@@ -1,0 +1,199 @@
+"""LayerNorm / RMSNorm (+GELU/SiLU) CUDA kernels, called through the C ABI, against the
+CPU oracle, the committed reference outputs and (when built) the reference itself."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import cpu_oracle as O
+from oracle import reference as R
+from tests import tol
+from tests.gpu_util import bits, check, make, to_dev
+from thot_b200 import abi
+
+pytestmark = pytest.mark.gpu
+
+NORM_CASES = ["ln_d512_none", "ln_d1024_gelu", "ln_d7_silu_eps1e-12", "ln_d2048_gelu_noaffine",
+              "ln_d768_gelu_bf16", "rms_d4096_none_bf16", "rms_d768_silu", "rms_d33_gelu_noweight"]
+
+
+def run_gpu(kind, x, gamma, beta, dy, eps, act):
+    if kind == "ln":
+        y, mean, rstd = abi.layernorm_fwd(x, gamma, beta, eps, act)
+        dx, gb = abi.layernorm_bwd(x, dy, gamma, beta, mean, rstd, act, want_param_grads=gamma is not None)
+        out = dict(y=y, dx=dx, mean=mean, rstd=rstd)
+        if gb is not None:
+            out["dgamma"], out["dbeta"] = gb[0], gb[1]
+        return out
+    y, rstd = abi.rmsnorm_fwd(x, gamma, eps, act)
+    dx, dw = abi.rmsnorm_bwd(x, dy, gamma, rstd, act, want_param_grads=gamma is not None)
+    out = dict(y=y, dx=dx, rstd=rstd)
+    if dw is not None:
+        out["dweight"] = dw
+    return out
+
+
+@pytest.mark.parametrize("name", NORM_CASES)
+def test_golden_reference_outputs(golden_dir, name):
+    z = np.load(golden_dir / f"{name}.npz")
+    g = {k: z[k] for k in z.files}
+    dtype = torch.bfloat16 if bool(g["bf16"]) else torch.float32
+    kind = str(g["kind"])
+    x, dy = to_dev(g["x"], dtype), to_dev(g["dy"], dtype)
+    gamma = to_dev(g["gamma"], dtype) if "gamma" in g else None
+    beta = to_dev(g["beta"], dtype) if "beta" in g else None
+    out = run_gpu(kind, x, gamma, beta, dy, float(g["eps"]), int(g["act"]))
+    check(out["y"], g["y_f32"], "y")
+    check(out["dx"], g["dx_f32"], "dx")
+    for k in ("dgamma", "dbeta", "dweight"):
+        if k in out:
+            if dtype == torch.float32:
+                tol.long_sum_close(out[k].cpu().numpy(), g[f"{k}_f32"], g[f"{k}_f64x"])
+            else:
+                tol.bf16_ulp_close(tol.to_bf16_bits(out[k].cpu().numpy()), g[f"{k}_f64x"])
+
+
+SHAPES = [(1, 1), (3, 7), (33, 512), (5, 513), (300, 768), (64, 1024), (37, 2048), (19, 4096),
+          (3, 8191), (9, 8192), (2, 16384), (4, 20000)]
+
+
+@pytest.mark.parametrize("kind", ["ln", "rms"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("act", [abi.ACT_NONE, abi.ACT_GELU, abi.ACT_SILU])
+def test_against_oracle_over_shapes(kind, dtype, act):
+    eps = 1e-5 if kind == "ln" else 1e-6
+    for i, (rows, D) in enumerate(SHAPES):
+        seed = 100 + i
+        x, xn = make((rows, D), seed, dtype)
+        dy, dyn = make((rows, D), seed + 1000, dtype)
+        gamma, gn = make((D,), seed + 2000, dtype, 0.02, 1.0)
+        beta, bn = make((D,), seed + 3000, dtype, 0.02) if kind == "ln" else (None, None)
+        out = run_gpu(kind, x, gamma, beta, dy, eps, act)
+        ref = O.layernorm_act(xn, gn, bn, dyn, eps, act) if kind == "ln" else O.rmsnorm_act(xn, gn, dyn, eps, act)
+        what = f"{kind} {dtype} act={act} rows={rows} D={D}"
+        check(out["y"], ref["y"], what + " y")
+        check(out["dx"], ref["dx"], what + " dx")
+        tol.fp32_close(out["rstd"].cpu().numpy(), ref["rstd"], rtol=2e-6, atol=0)
+        if kind == "ln":
+            tol.fp32_close(out["mean"].cpu().numpy(), ref["mean"], rtol=1e-5, atol=1e-6)
+        for k in ("dgamma", "dbeta", "dweight"):
+            if k in out:
+                if dtype == torch.float32:
+                    tol.fp32_close(out[k].cpu().numpy(), ref[k])
+                else:
+                    tol.bf16_ulp_close(tol.to_bf16_bits(out[k].cpu().numpy()), ref[k])
+
+
+def test_config1_layernorm_forward_fp32_full_size():
+    """x[64,128,512] ~N(0,1), gamma=1+N(0,0.02), beta~N(0,0.02), eps=1e-5, seed 0."""
+    torch.manual_seed(0)
+    x = torch.randn(64, 128, 512)
+    gamma = 1 + 0.02 * torch.randn(512)
+    beta = 0.02 * torch.randn(512)
+    y, mean, rstd = abi.layernorm_fwd(x.view(-1, 512).cuda(), gamma.cuda(), beta.cuda(), 1e-5)
+    ref = O.layernorm_act(x.view(-1, 512).numpy(), gamma.numpy(), beta.numpy(), None, 1e-5)
+    check(y, ref["y"], "config 1 y")
+    if R.available():   # the reference's own module on CPU, same inputs
+        r = R.layernorm_act(x.view(-1, 512).numpy(), gamma.numpy(), beta.numpy(), None, 1e-5)
+        check(y, r["y"], "config 1 y vs reference")
+
+
+def test_config2_layernorm_gelu_fwd_bwd_fp32_full_size():
+    """x[32,1024,1024], dY same shape, exact-erf GELU, eps=1e-5: y, dX, dgamma, dbeta."""
+    rows, D = 32 * 1024, 1024
+    x, xn = make((rows, D), 0, torch.float32)
+    dy, dyn = make((rows, D), 1, torch.float32)
+    gamma, gn = make((D,), 2, torch.float32, 0.02, 1.0)
+    beta, bn = make((D,), 3, torch.float32, 0.02)
+    out = run_gpu("ln", x, gamma, beta, dy, 1e-5, abi.ACT_GELU)
+    ref = O.layernorm_act(xn, gn, bn, dyn, 1e-5, O.ACT_GELU)
+    check(out["y"], ref["y"], "config 2 y")
+    check(out["dx"], ref["dx"], "config 2 dx")
+    if R.available():
+        r = R.layernorm_act(xn, gn, bn, dyn, 1e-5, 1)
+        check(out["y"], r["y"], "config 2 y vs reference")
+        check(out["dx"], r["dx"], "config 2 dx vs reference")
+        # 32768-term fp32 sums: closer to the fp64 oracle than the fp32 reference, or in tolerance
+        tol.long_sum_close(out["dgamma"].cpu().numpy(), r["dgamma"], ref["dgamma"])
+        tol.long_sum_close(out["dbeta"].cpu().numpy(), r["dbeta"], ref["dbeta"])
+    tol.fp32_close(out["dgamma"].cpu().numpy(), ref["dgamma"])
+    tol.fp32_close(out["dbeta"].cpu().numpy(), ref["dbeta"])
+    # run-to-run determinism
+    again = run_gpu("ln", x, gamma, beta, dy, 1e-5, abi.ACT_GELU)
+    for k in ("y", "dx", "dgamma", "dbeta"):
+        assert torch.equal(out[k], again[k]), k
+
+
+def _sampled_rows_check(kind, dtype, rows, D, act, eps, sample=48):
+    """Full-size run on the GPU; rows are independent, so a scattered sample of them is
+    checked against the oracle, and the parameter gradients through additivity over row blocks."""
+    x, _ = make((rows, D), 7, dtype)
+    dy, _ = make((rows, D), 8, dtype)
+    gamma, gn = make((D,), 9, dtype, 0.02, 1.0)
+    beta, bn = make((D,), 10, dtype, 0.02) if kind == "ln" else (None, None)
+    out = run_gpu(kind, x, gamma, beta, dy, eps, act)
+    idx = torch.linspace(0, rows - 1, sample).long()
+    xs, dys = x[idx.cuda()].float().cpu().numpy(), dy[idx.cuda()].float().cpu().numpy()
+    ref = O.layernorm_act(xs, gn, bn, dys, eps, act) if kind == "ln" else O.rmsnorm_act(xs, gn, dys, eps, act)
+    check(out["y"][idx.cuda()], ref["y"], "sampled y")
+    check(out["dx"][idx.cuda()], ref["dx"], "sampled dx")
+    # checksum of checksums: gradients of the whole = sum of gradients of 8 row blocks
+    keys = ("dgamma", "dbeta") if kind == "ln" else ("dweight",)
+    acc = {k: torch.zeros(D, dtype=torch.float64, device="cuda") for k in keys}
+    step = rows // 8
+    for b in range(8):
+        sl = slice(b * step, rows if b == 7 else (b + 1) * step)
+        part = run_gpu(kind, x[sl], gamma, None if beta is None else beta, dy[sl], eps, act)
+        for k in keys:
+            acc[k] += part[k].double()
+    for k in keys:
+        tol.fp32_close(out[k].cpu().numpy(), acc[k].cpu().numpy(), rtol=2e-5, atol=2e-4)
+    # first block against the oracle pins the blocks themselves
+    nb = min(step, 512)
+    part = run_gpu(kind, x[:nb], gamma, beta, dy[:nb], eps, act)
+    xs, dys = x[:nb].float().cpu().numpy(), dy[:nb].float().cpu().numpy()
+    ref = O.layernorm_act(xs, gn, bn, dys, eps, act) if kind == "ln" else O.rmsnorm_act(xs, gn, dys, eps, act)
+    for k in keys:
+        if dtype == torch.float32:
+            tol.fp32_close(part[k].cpu().numpy(), ref[k])
+        else:
+            tol.bf16_ulp_close(tol.to_bf16_bits(part[k].cpu().numpy()), ref[k])
+
+
+def test_config3_rmsnorm_bf16_full_size():
+    """x[16,4096,4096] bf16, weight=1+N(0,0.02), eps=1e-6, fwd + bwd."""
+    _sampled_rows_check("rms", torch.bfloat16, 16 * 4096, 4096, abi.ACT_NONE, 1e-6)
+
+
+@pytest.mark.parametrize("kind,act", [("ln", abi.ACT_GELU), ("rms", abi.ACT_SILU)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("D", [768, 2048, 8192])
+def test_config5_sweep_shapes_sampled(kind, act, dtype, D):
+    """The whole-box sweep's widths at 2^16 rows per GPU (2^20 rows over 16 shards)."""
+    _sampled_rows_check(kind, dtype, 1 << 16, D, act, 1e-5 if kind == "ln" else 1e-6, sample=24)
+
+
+def test_no_affine_no_stats_and_empty():
+    x, xn = make((17, 1024), 5, torch.float32)
+    y, mean, rstd = abi.layernorm_fwd(x, None, None, 1e-5, abi.ACT_GELU, want_stats=False)
+    assert mean is None and rstd is None
+    check(y, O.layernorm_act(xn, None, None, None, 1e-5, O.ACT_GELU)["y"], "no affine y")
+    y, rstd = abi.rmsnorm_fwd(x, None, 1e-6, abi.ACT_NONE)
+    check(y, O.rmsnorm_act(xn, None, None, 1e-6)["y"], "no weight y")
+    e = torch.empty(0, 1024, device="cuda")
+    y, mean, rstd = abi.layernorm_fwd(e, None, None, 1e-5)
+    assert y.shape == (0, 1024)
+    dx, gb = abi.layernorm_bwd(e, e, None, None, mean, rstd, want_param_grads=True)
+    assert dx.shape == (0, 1024) and float(gb.abs().sum()) == 0.0
+
+
+def test_unaligned_views_take_the_any_width_path():
+    base, bn = make((9 * 1024 + 1,), 6, torch.float32)
+    x = base[1:].view(9, 1024)                       # 4-byte aligned only
+    gamma, gn = make((1024,), 7, torch.float32, 0.02, 1.0)
+    beta, bnn = make((1024,), 8, torch.float32, 0.02)
+    assert x.data_ptr() % 16 != 0
+    y, mean, rstd = abi.layernorm_fwd(x, gamma, beta, 1e-5, abi.ACT_SILU)
+    ref = O.layernorm_act(bn[1:].reshape(9, 1024), gn, bnn, None, 1e-5, O.ACT_SILU)
+    check(y, ref["y"], "unaligned y")

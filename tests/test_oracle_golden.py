@@ -1,0 +1,98 @@
+"""The plain-C oracle (oracle/oracle_rowops.c) against the committed outputs of the
+reference's own modules (tests/golden/*.npz, made by tests/golden/make_golden.py)."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+from oracle import cpu_oracle as O
+from tests import tol
+
+NORM_CASES = ["ln_d512_none", "ln_d1024_gelu", "ln_d7_silu_eps1e-12", "ln_d2048_gelu_noaffine",
+              "ln_d768_gelu_bf16", "rms_d4096_none_bf16", "rms_d768_silu", "rms_d33_gelu_noweight"]
+
+
+def load(golden_dir, name):
+    z = np.load(golden_dir / f"{name}.npz")
+    return {k: z[k] for k in z.files}
+
+
+@pytest.mark.parametrize("name", NORM_CASES)
+def test_norm_oracle_matches_reference(golden_dir, name):
+    g = load(golden_dir, name)
+    eps, act = float(g["eps"]), int(g["act"])
+    if str(g["kind"]) == "ln":
+        o = O.layernorm_act(g["x"], g.get("gamma"), g.get("beta"), g["dy"], eps, act)
+        sums = ("dgamma", "dbeta") if "gamma" in g else ()
+    else:
+        o = O.rmsnorm_act(g["x"], g.get("gamma"), g["dy"], eps, act)
+        sums = ("dweight",) if "gamma" in g else ()
+    for k in ("y", "dx"):
+        tol.fp32_close(o[k], g[f"{k}_f32"])
+        # the fp64 run of the reference modules is the tighter pin
+        np.testing.assert_allclose(o[k], g[f"{k}_f64"], rtol=2e-6, atol=2e-7)
+    for k in sums:
+        tol.long_sum_close(o[k], g[f"{k}_f32"], g[f"{k}_f64x"])
+        np.testing.assert_allclose(o[k], g[f"{k}_f64x"], rtol=1e-9, atol=1e-9)
+
+
+@pytest.mark.parametrize("name,code", [("gelu", O.ACT_GELU), ("silu", O.ACT_SILU)])
+def test_activation_oracle_matches_reference(golden_dir, name, code):
+    g = load(golden_dir, "act_gelu_silu")
+    o = O.act(g["x"], g["dy"], code)
+    tol.fp32_close(o["y"], g[f"{name}_y_f32"])
+    tol.fp32_close(o["dx"], g[f"{name}_dx_f32"])
+    np.testing.assert_allclose(o["y"], g[f"{name}_y_f64"], rtol=2e-6, atol=2e-7)
+    np.testing.assert_allclose(o["dx"], g[f"{name}_dx_f64"], rtol=2e-6, atol=2e-7)
+
+
+def test_silu_gate_oracle_matches_swiglu_and_mamba(golden_dir):
+    g = load(golden_dir, "silu_gate")
+    inp = g["input"]
+    H = inp.shape[1] // 2
+    o = O.silu_gate(inp[:, :H], inp[:, H:], g["dy"])            # row-strided halves, as SwiGLU sees them
+    tol.fp32_close(o["out"], g["swiglu_out_f32"])
+    tol.fp32_close(o["da"], g["swiglu_dinput_f32"][:, :H])
+    tol.fp32_close(o["db"], g["swiglu_dinput_f32"][:, H:])
+    np.testing.assert_allclose(o["out"], g["swiglu_out_f64"], rtol=2e-6, atol=2e-7)
+    o2 = O.silu_gate(np.ascontiguousarray(inp[:, :H]), np.ascontiguousarray(inp[:, H:]), g["dy"])
+    tol.fp32_close(o2["out"], g["mamba_out_f32"])
+    tol.fp32_close(o2["da"], g["mamba_dgate_f32"])
+    tol.fp32_close(o2["db"], g["mamba_dup_f32"])
+
+
+def test_embedding_oracle_is_bit_exact(golden_dir):
+    g = load(golden_dir, "embedding")
+    out, bad = O.embedding(g["table"], g["ids"])
+    assert bad == -1
+    assert out.tobytes() == g["out"].tobytes()
+    dt = O.embedding_bwd(g["dout"], g["ids"], g["table"].shape[0])
+    tol.fp32_close(dt, g["dtable_f32"])
+    np.testing.assert_allclose(dt, g["dtable_f64"], rtol=2e-6, atol=2e-7)
+
+
+def test_embedding_oracle_flags_bad_ids():
+    table = np.arange(12, dtype=np.float32).reshape(4, 3)
+    out, bad = O.embedding(table, np.array([1, 7, -1, 3]))
+    assert bad == 1
+    assert (out[1] == 0).all() and (out[2] == 0).all()
+    assert (out[0] == table[1]).all() and (out[3] == table[3]).all()
+
+
+def test_rope_oracle_properties():
+    # no reference implementation exists: check the definition's own invariants
+    rng = np.random.default_rng(0)
+    S, hd = 9, 16
+    cs = O.rope_table(S, hd, 10000.0)
+    assert cs.shape == (S, hd // 2, 2)
+    assert np.allclose(cs[0, :, 0], 1.0) and np.allclose(cs[0, :, 1], 0.0)          # position 0: identity
+    np.testing.assert_allclose(cs[..., 0] ** 2 + cs[..., 1] ** 2, 1.0, atol=1e-6)
+    np.testing.assert_allclose(cs[3, 0], [np.cos(3.0), np.sin(3.0)], rtol=1e-6)     # i = 0: angle = pos
+    x = rng.standard_normal((2, S, 3, hd)).astype(np.float32)
+    y = O.rope_apply(x, cs)
+    np.testing.assert_allclose((y ** 2).sum(-1), (x.astype(np.float64) ** 2).sum(-1), rtol=1e-6)   # a rotation
+    back = O.rope_apply(y.astype(np.float32), cs, inverse=True)
+    np.testing.assert_allclose(back, x, atol=1e-6)
+    pos = np.array([5, 0, 2], dtype=np.int32)
+    cs2 = O.rope_table(3, hd, 10000.0, positions=pos)
+    assert np.array_equal(cs2[0], O.rope_table(6, hd)[5]) and np.array_equal(cs2[2], cs[2])

@@ -1,0 +1,285 @@
+"""ctypes binding of libnott_b200.so (the C ABI in include/nott_b200.h).
+
+This is the thinnest possible host: it passes raw device pointers of torch
+tensors to the extern "C" entry points on torch's current stream.  torch is
+used only for device memory and streams.  If the library is missing or a call
+fails, it raises; there is no CPU or eager fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_double, c_int, c_int64, c_size_t, c_void_p, POINTER
+from pathlib import Path
+
+import torch
+
+F32, BF16 = 0, 1
+ACT_NONE, ACT_GELU, ACT_SILU = 0, 1, 2
+I32, I64 = 0, 1
+WS_NORM_BWD, WS_EMBEDDING_BWD, WS_ROPE_TABLE = 0, 1, 2
+
+LIB_PATH = Path(__file__).resolve().parent / "libnott_b200.so"
+
+_SIGNATURES = {
+    "nb2_abi_version": (c_int, []),
+    "nb2_last_error_string": (c_char_p, []),
+    "nb2_sm_count": (c_int, []),
+    "nb2_workspace_bytes": (c_size_t, [c_int, c_int64, c_int64, c_int]),
+    "nb2_layernorm_fwd": (c_int, [c_void_p] * 6 + [c_int64, c_int64, c_double, c_int, c_int, c_void_p]),
+    "nb2_layernorm_bwd": (c_int, [c_void_p] * 8 + [POINTER(c_int64), c_int64, c_int64, c_int, c_int, c_void_p]),
+    "nb2_rmsnorm_fwd": (c_int, [c_void_p] * 4 + [c_int64, c_int64, c_double, c_int, c_int, c_void_p]),
+    "nb2_rmsnorm_bwd": (c_int, [c_void_p] * 6 + [POINTER(c_int64), c_int64, c_int64, c_int, c_int, c_void_p]),
+    "nb2_colreduce_partials": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
+    "nb2_act_fwd": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
+    "nb2_act_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
+    "nb2_silu_gate_fwd": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
+    "nb2_silu_gate_bwd": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
+                                  c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
+    "nb2_embedding_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p]),
+    "nb2_embedding_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int,
+                                  c_void_p, c_size_t, c_void_p]),
+    "nb2_rope_table": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_double, c_void_p]),
+    "nb2_rope_apply": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_void_p]),
+    "nb2_host_ctx_create": (c_int, [POINTER(c_void_p), c_int64, c_int64, c_int, c_int64]),
+    "nb2_host_ctx_destroy": (c_int, [c_void_p]),
+    "nb2_layernorm_act_step_host": (c_int, [c_void_p] * 8 + [c_int64, c_int64, c_double, c_int, c_int]),
+}
+
+_lib = None
+
+
+class Nb2Error(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"libnott_b200 status {status}: {message}")
+        self.status = status
+
+
+def lib() -> ctypes.CDLL:
+    """Load libnott_b200.so (once).  Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m thot_b200._build` "
+                "(this package has no CPU fallback)")
+        handle = ctypes.CDLL(str(LIB_PATH))
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = handle
+    return _lib
+
+
+def check(status: int) -> None:
+    if status != 0:
+        raise Nb2Error(status, lib().nb2_last_error_string().decode())
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise TypeError(f"libnott_b200 supports float32 and bfloat16, not {dt}")
+
+
+def _p(t):
+    return None if t is None else c_void_p(t.data_ptr())
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dev(t: torch.Tensor) -> None:
+    if not t.is_cuda:
+        raise ValueError("libnott_b200 works on CUDA tensors only (no CPU fallback)")
+
+
+def workspace_bytes(op: int, a: int, b: int, dtype: int = F32) -> int:
+    return int(lib().nb2_workspace_bytes(op, a, b, dtype))
+
+
+# --------------------------------------------------------------- norm + act
+def layernorm_fwd(x, gamma, beta, eps: float, act: int = ACT_NONE, want_stats: bool = True):
+    """x [rows, D] contiguous -> (y, mean, rstd)."""
+    _dev(x)
+    rows, D = x.shape
+    y = torch.empty_like(x)
+    mean = torch.empty(rows, dtype=torch.float32, device=x.device) if want_stats else None
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device) if want_stats else None
+    check(lib().nb2_layernorm_fwd(_p(x), _p(gamma), _p(beta), _p(y), _p(mean), _p(rstd), rows, D, eps,
+                                  dtype_code(x.dtype), act, _stream()))
+    return y, mean, rstd
+
+
+def layernorm_bwd(x, dy, gamma, beta, mean, rstd, act: int = ACT_NONE, want_param_grads: bool = True):
+    """-> (dx, dgamma_dbeta [2, D] fp32 or None)."""
+    _dev(x)
+    rows, D = x.shape
+    dx = torch.empty_like(x)
+    code = dtype_code(x.dtype)
+    partials, out = None, None
+    n = c_int64(0)
+    if want_param_grads:
+        ws = workspace_bytes(WS_NORM_BWD, rows, D, code)
+        partials = torch.empty(ws // 4, dtype=torch.float32, device=x.device)
+    check(lib().nb2_layernorm_bwd(_p(x), _p(dy), _p(gamma), _p(beta), _p(mean), _p(rstd), _p(dx), _p(partials),
+                                  ctypes.byref(n), rows, D, code, act, _stream()))
+    if want_param_grads:
+        out = torch.empty(2, D, dtype=torch.float32, device=x.device)
+        if rows == 0:
+            out.zero_()
+        else:
+            check(lib().nb2_colreduce_partials(_p(partials), n.value, 2 * D, _p(out), _stream()))
+    return dx, out
+
+
+def rmsnorm_fwd(x, weight, eps: float, act: int = ACT_NONE, want_stats: bool = True):
+    _dev(x)
+    rows, D = x.shape
+    y = torch.empty_like(x)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device) if want_stats else None
+    check(lib().nb2_rmsnorm_fwd(_p(x), _p(weight), _p(y), _p(rstd), rows, D, eps, dtype_code(x.dtype), act, _stream()))
+    return y, rstd
+
+
+def rmsnorm_bwd(x, dy, weight, rstd, act: int = ACT_NONE, want_param_grads: bool = True):
+    """-> (dx, dweight [D] fp32 or None)."""
+    _dev(x)
+    rows, D = x.shape
+    dx = torch.empty_like(x)
+    code = dtype_code(x.dtype)
+    partials, out = None, None
+    n = c_int64(0)
+    if want_param_grads:
+        ws = workspace_bytes(WS_NORM_BWD, rows, D, code)
+        partials = torch.empty(ws // 4, dtype=torch.float32, device=x.device)
+    check(lib().nb2_rmsnorm_bwd(_p(x), _p(dy), _p(weight), _p(rstd), _p(dx), _p(partials), ctypes.byref(n),
+                                rows, D, code, act, _stream()))
+    if want_param_grads:
+        out = torch.empty(D, dtype=torch.float32, device=x.device)
+        if rows == 0:
+            out.zero_()
+        else:
+            check(lib().nb2_colreduce_partials(_p(partials), n.value, D, _p(out), _stream()))
+    return dx, out
+
+
+# -------------------------------------------------------------- activations
+def act_fwd(x, act: int):
+    _dev(x)
+    y = torch.empty_like(x)
+    check(lib().nb2_act_fwd(_p(x), _p(y), x.numel(), dtype_code(x.dtype), act, _stream()))
+    return y
+
+
+def act_bwd(x, dy, act: int):
+    _dev(x)
+    dx = torch.empty_like(x)
+    check(lib().nb2_act_bwd(_p(x), _p(dy), _p(dx), x.numel(), dtype_code(x.dtype), act, _stream()))
+    return dx
+
+
+def _ld(t):
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError("silu gate operands must be 2-D with unit column stride")
+    return t.stride(0)
+
+
+def silu_gate_fwd(a, b):
+    """out = silu(a) * b; a, b may be row-strided views (halves of a [rows, 2H] tensor)."""
+    _dev(a)
+    rows, H = a.shape
+    out = torch.empty(rows, H, dtype=a.dtype, device=a.device)
+    check(lib().nb2_silu_gate_fwd(_p(a), _ld(a), _p(b), _ld(b), _p(out), H, rows, H, dtype_code(a.dtype), _stream()))
+    return out
+
+
+def silu_gate_bwd(a, b, dy, da=None, db=None):
+    _dev(a)
+    rows, H = a.shape
+    if da is None:
+        da = torch.empty(rows, H, dtype=a.dtype, device=a.device)
+    if db is None:
+        db = torch.empty(rows, H, dtype=a.dtype, device=a.device)
+    check(lib().nb2_silu_gate_bwd(_p(a), _ld(a), _p(b), _ld(b), _p(dy), _ld(dy), _p(da), _ld(da), _p(db), _ld(db),
+                                  rows, H, dtype_code(a.dtype), _stream()))
+    return da, db
+
+
+# ---------------------------------------------------------------- embedding
+def _index_code(ids):
+    if ids.dtype == torch.int32:
+        return I32
+    if ids.dtype == torch.int64:
+        return I64
+    raise TypeError(f"token ids must be int32 or int64, not {ids.dtype}")
+
+
+def embedding_fwd(table, ids, status=None):
+    _dev(table)
+    vocab, D = table.shape
+    flat = ids.reshape(-1)
+    out = torch.empty(flat.numel(), D, dtype=table.dtype, device=table.device)
+    check(lib().nb2_embedding_fwd(_p(table), _p(flat), _p(out), flat.numel(), vocab, D, dtype_code(table.dtype),
+                                  _index_code(ids), _p(status), _stream()))
+    return out.view(*ids.shape, D)
+
+
+def embedding_bwd(dout, ids, vocab: int):
+    _dev(dout)
+    D = dout.shape[-1]
+    flat = ids.reshape(-1)
+    d2 = dout.reshape(-1, D)
+    dtable = torch.empty(vocab, D, dtype=dout.dtype, device=dout.device)
+    ws_bytes = workspace_bytes(WS_EMBEDDING_BWD, flat.numel(), vocab, dtype_code(dout.dtype))
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dout.device)
+    check(lib().nb2_embedding_bwd(_p(d2), _p(flat), _p(dtable), flat.numel(), vocab, D, dtype_code(dout.dtype),
+                                  _index_code(ids), _p(ws), ws_bytes, _stream()))
+    return dtable
+
+
+# --------------------------------------------------------------------- rope
+def rope_table(S: int, hd: int, theta: float = 10000.0, positions=None, device="cuda"):
+    cs = torch.empty(S, hd // 2, 2, dtype=torch.float32, device=device)
+    check(lib().nb2_rope_table(_p(cs), _p(positions), S, hd, theta, _stream()))
+    return cs
+
+
+def rope_apply(x, cos_sin, inverse: bool = False):
+    """x [B, S, H, hd] contiguous."""
+    _dev(x)
+    B, S, H, hd = x.shape
+    out = torch.empty_like(x)
+    check(lib().nb2_rope_apply(_p(x), _p(cos_sin), _p(out), B, S, H, hd, dtype_code(x.dtype), int(inverse), _stream()))
+    return out
+
+
+# ------------------------------------------------------ host-buffer pipeline
+class HostStep:
+    """Fused LayerNorm->activation fwd+bwd on HOST buffers (pinned tensors)."""
+
+    def __init__(self, max_rows: int, D: int, dtype: torch.dtype = torch.float32, chunk_rows: int = 0):
+        self._ctx = c_void_p()
+        self.D, self.dtype = D, dtype
+        check(lib().nb2_host_ctx_create(ctypes.byref(self._ctx), max_rows, D, dtype_code(dtype), chunk_rows))
+
+    def step(self, x, dy, gamma, beta, y, dx, dgamma_dbeta, eps: float, act: int):
+        for t in (x, dy, gamma, beta, y, dx, dgamma_dbeta):
+            if t.is_cuda:
+                raise ValueError("HostStep takes host tensors")
+        rows = x.shape[0]
+        check(lib().nb2_layernorm_act_step_host(self._ctx, _p(x), _p(dy), _p(gamma), _p(beta), _p(y), _p(dx),
+                                                _p(dgamma_dbeta), rows, self.D, eps, dtype_code(self.dtype), act))
+
+    def close(self):
+        if self._ctx:
+            lib().nb2_host_ctx_destroy(self._ctx)
+            self._ctx = c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

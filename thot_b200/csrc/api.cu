@@ -1,0 +1,238 @@
+// extern "C" entry points of libnott_b200.so: argument validation, then the
+// launchers.  Declarations and the reference interfaces they replace are in
+// include/nott_b200.h.
+#include <stdarg.h>
+#include <string.h>
+#include "launchers.h"
+
+namespace nb2 {
+
+static thread_local char g_err[512] = "ok";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+int cuda_status(cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return 0;
+    set_error("%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
+    return (int)e;
+}
+
+int sm_count() {
+    static thread_local int cached_dev = -1, cached_sms = 0;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (dev != cached_dev) {
+        int sms = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+        cached_dev = dev;
+        cached_sms = sms;
+    }
+    return cached_sms;
+}
+
+static bool dtype_ok(int d) { return d == NB2_F32 || d == NB2_BF16; }
+static bool act_ok(int a) { return a == NB2_ACT_NONE || a == NB2_ACT_GELU || a == NB2_ACT_SILU; }
+static bool idx_ok(int i) { return i == NB2_I32 || i == NB2_I64; }
+
+static int require_device() {
+    const int sms = sm_count();
+    if (sms > 0) return 0;
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaErrorNoDevice;
+    return cuda_status(e, "no usable CUDA device (this library has no CPU fallback)");
+}
+
+static int norm_fwd(bool rms, const void* x, const void* gamma, const void* beta, void* y, float* mean,
+                    float* rstd, int64_t rows, int64_t D, double eps, int dtype, int act, void* stream) {
+    NB2_REQUIRE(dtype_ok(dtype), NB2_ERR_DTYPE, "norm fwd: unknown dtype %d", dtype);
+    NB2_REQUIRE(act_ok(act), NB2_ERR_DTYPE, "norm fwd: unknown activation %d", act);
+    NB2_REQUIRE(rows >= 0 && D > 0, NB2_ERR_SHAPE, "norm fwd: rows=%lld D=%lld (need rows >= 0, D > 0)", (long long)rows, (long long)D);
+    NB2_REQUIRE(D < ((int64_t)1 << 31), NB2_ERR_SHAPE, "norm fwd: D=%lld exceeds 2^31-1", (long long)D);
+    if (rows == 0) return 0;
+    NB2_REQUIRE(x != nullptr && y != nullptr, NB2_ERR_NULL, "norm fwd: x or y is NULL");
+    int rc = require_device();
+    if (rc != 0) return rc;
+    NormArgs a{};
+    a.x = x; a.gamma = gamma; a.beta = rms ? nullptr : beta; a.y = y;
+    a.mean_out = mean; a.rstd_out = rstd; a.rows = rows; a.D = D; a.eps = (float)eps;
+    a.act = act; a.rms = rms; a.stream = (cudaStream_t)stream;
+    return dtype == NB2_F32 ? launch_norm_fwd<float>(a) : launch_norm_fwd<__nv_bfloat16>(a);
+}
+
+static int norm_bwd(bool rms, const void* x, const void* dy, const void* gamma, const void* beta,
+                    const float* mean, const float* rstd, void* dx, float* partials, int64_t* n_partials,
+                    int64_t rows, int64_t D, int dtype, int act, void* stream) {
+    NB2_REQUIRE(dtype_ok(dtype), NB2_ERR_DTYPE, "norm bwd: unknown dtype %d", dtype);
+    NB2_REQUIRE(act_ok(act), NB2_ERR_DTYPE, "norm bwd: unknown activation %d", act);
+    NB2_REQUIRE(rows >= 0 && D > 0, NB2_ERR_SHAPE, "norm bwd: rows=%lld D=%lld (need rows >= 0, D > 0)", (long long)rows, (long long)D);
+    NB2_REQUIRE(D < ((int64_t)1 << 31), NB2_ERR_SHAPE, "norm bwd: D=%lld exceeds 2^31-1", (long long)D);
+    if (n_partials) *n_partials = 0;
+    if (rows == 0) return 0;
+    NB2_REQUIRE(x && dy && dx && rstd && (rms || mean), NB2_ERR_NULL, "norm bwd: x, dy, dx, rstd%s must be non-NULL", rms ? "" : ", mean");
+    NB2_REQUIRE(partials == nullptr || n_partials != nullptr, NB2_ERR_NULL, "norm bwd: partials given but n_partials_host is NULL");
+    int rc = require_device();
+    if (rc != 0) return rc;
+    NormArgs a{};
+    a.x = x; a.dy = dy; a.gamma = gamma; a.beta = rms ? nullptr : beta; a.mean = mean; a.rstd = rstd;
+    a.dx = dx; a.partials = partials; a.rows = rows; a.D = D; a.act = act; a.rms = rms;
+    a.stream = (cudaStream_t)stream;
+    return dtype == NB2_F32 ? launch_norm_bwd<float>(a, n_partials) : launch_norm_bwd<__nv_bfloat16>(a, n_partials);
+}
+
+}  // namespace nb2
+
+using namespace nb2;
+
+extern "C" {
+
+int nb2_abi_version(void) { return NB2_ABI_VERSION; }
+const char* nb2_last_error_string(void) { return g_err; }
+int nb2_sm_count(void) { return sm_count(); }
+
+size_t nb2_workspace_bytes(int op, int64_t a, int64_t b, int dtype) {
+    switch (op) {
+        case NB2_WS_NORM_BWD: {
+            // a = rows, b = D.  Upper bound over LayerNorm (2 partial rows) and both paths.
+            if (a <= 0 || b <= 0) return 256;
+            int sms = sm_count();
+            if (sms <= 0) sms = 148;
+            const int epv = dtype == NB2_BF16 ? 8 : 4;
+            const int vpt = 16 / epv;
+            int64_t parts = norm_bwd_generic_parts(a);
+            if (b % epv == 0) {
+                const int tpr = pick_tpr(b / epv, vpt);
+                if (tpr != 0) {
+                    const int64_t g = norm_bwd_grid(a, tpr, sms);
+                    if (g > parts) parts = g;
+                }
+            }
+            return (size_t)parts * 2 * (size_t)b * sizeof(float) + 256;
+        }
+        case NB2_WS_EMBEDDING_BWD: return embedding_bwd_workspace(a, b);
+        case NB2_WS_ROPE_TABLE: return a > 0 && b > 1 ? (size_t)a * (size_t)(b / 2) * 2 * sizeof(float) : 0;
+        default: return 0;
+    }
+}
+
+int nb2_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
+                      int64_t rows, int64_t D, double eps, int dtype, int act, void* stream) {
+    return norm_fwd(false, x, gamma, beta, y, mean, rstd, rows, D, eps, dtype, act, stream);
+}
+int nb2_layernorm_bwd(const void* x, const void* dy, const void* gamma, const void* beta, const float* mean,
+                      const float* rstd, void* dx, float* partials, int64_t* n_partials_host,
+                      int64_t rows, int64_t D, int dtype, int act, void* stream) {
+    return norm_bwd(false, x, dy, gamma, beta, mean, rstd, dx, partials, n_partials_host, rows, D, dtype, act, stream);
+}
+int nb2_rmsnorm_fwd(const void* x, const void* weight, void* y, float* rstd, int64_t rows, int64_t D,
+                    double eps, int dtype, int act, void* stream) {
+    return norm_fwd(true, x, weight, nullptr, y, nullptr, rstd, rows, D, eps, dtype, act, stream);
+}
+int nb2_rmsnorm_bwd(const void* x, const void* dy, const void* weight, const float* rstd, void* dx,
+                    float* partials, int64_t* n_partials_host, int64_t rows, int64_t D, int dtype, int act,
+                    void* stream) {
+    return norm_bwd(true, x, dy, weight, nullptr, nullptr, rstd, dx, partials, n_partials_host, rows, D, dtype, act, stream);
+}
+
+int nb2_colreduce_partials(const float* partials, int64_t n_partials, int64_t ncols, float* out, void* stream) {
+    NB2_REQUIRE(n_partials >= 0 && ncols >= 0, NB2_ERR_SHAPE, "colreduce: n_partials=%lld ncols=%lld", (long long)n_partials, (long long)ncols);
+    NB2_REQUIRE(n_partials < ((int64_t)1 << 31), NB2_ERR_SHAPE, "colreduce: too many partials");
+    if (ncols == 0) return 0;
+    NB2_REQUIRE(out != nullptr && (partials != nullptr || n_partials == 0), NB2_ERR_NULL, "colreduce: NULL pointer");
+    int rc = require_device();
+    if (rc != 0) return rc;
+    return launch_colreduce(partials, n_partials, ncols, out, (cudaStream_t)stream);
+}
+
+int nb2_act_fwd(const void* x, void* y, int64_t n, int dtype, int act, void* stream) {
+    NB2_REQUIRE(dtype_ok(dtype) && act_ok(act), NB2_ERR_DTYPE, "act fwd: dtype=%d act=%d", dtype, act);
+    NB2_REQUIRE(n >= 0, NB2_ERR_SHAPE, "act fwd: n=%lld", (long long)n);
+    if (n == 0) return 0;
+    NB2_REQUIRE(x && y, NB2_ERR_NULL, "act fwd: NULL pointer");
+    int rc = require_device();
+    if (rc != 0) return rc;
+    return launch_act(x, nullptr, y, n, dtype, act, false, (cudaStream_t)stream);
+}
+int nb2_act_bwd(const void* x, const void* dy, void* dx, int64_t n, int dtype, int act, void* stream) {
+    NB2_REQUIRE(dtype_ok(dtype) && act_ok(act), NB2_ERR_DTYPE, "act bwd: dtype=%d act=%d", dtype, act);
+    NB2_REQUIRE(n >= 0, NB2_ERR_SHAPE, "act bwd: n=%lld", (long long)n);
+    if (n == 0) return 0;
+    NB2_REQUIRE(x && dy && dx, NB2_ERR_NULL, "act bwd: NULL pointer");
+    int rc = require_device();
+    if (rc != 0) return rc;
+    return launch_act(x, dy, dx, n, dtype, act, true, (cudaStream_t)stream);
+}
+
+int nb2_silu_gate_fwd(const void* a, int64_t lda, const void* b, int64_t ldb, void* out, int64_t ldo,
+                      int64_t rows, int64_t H, int dtype, void* stream) {
+    NB2_REQUIRE(dtype_ok(dtype), NB2_ERR_DTYPE, "silu gate fwd: dtype=%d", dtype);
+    NB2_REQUIRE(rows >= 0 && H >= 0, NB2_ERR_SHAPE, "silu gate fwd: rows=%lld H=%lld", (long long)rows, (long long)H);
+    if (rows == 0 || H == 0) return 0;
+    NB2_REQUIRE(lda >= H && ldb >= H && ldo >= H, NB2_ERR_SHAPE, "silu gate fwd: a row stride is smaller than H=%lld", (long long)H);
+    NB2_REQUIRE(a && b && out, NB2_ERR_NULL, "silu gate fwd: NULL pointer");
+    int rc = require_device();
+    if (rc != 0) return rc;
+    return launch_silu_gate(a, lda, b, ldb, nullptr, 0, out, ldo, nullptr, 0, rows, H, dtype, false, (cudaStream_t)stream);
+}
+int nb2_silu_gate_bwd(const void* a, int64_t lda, const void* b, int64_t ldb, const void* dy, int64_t lddy,
+                      void* da, int64_t ldda, void* db, int64_t lddb, int64_t rows, int64_t H, int dtype,
+                      void* stream) {
+    NB2_REQUIRE(dtype_ok(dtype), NB2_ERR_DTYPE, "silu gate bwd: dtype=%d", dtype);
+    NB2_REQUIRE(rows >= 0 && H >= 0, NB2_ERR_SHAPE, "silu gate bwd: rows=%lld H=%lld", (long long)rows, (long long)H);
+    if (rows == 0 || H == 0) return 0;
+    NB2_REQUIRE(lda >= H && ldb >= H && lddy >= H && ldda >= H && lddb >= H, NB2_ERR_SHAPE,
+                "silu gate bwd: a row stride is smaller than H=%lld", (long long)H);
+    NB2_REQUIRE(a && b && dy && da && db, NB2_ERR_NULL, "silu gate bwd: NULL pointer");
+    int rc = require_device();
+    if (rc != 0) return rc;
+    return launch_silu_gate(a, lda, b, ldb, dy, lddy, da, ldda, db, lddb, rows, H, dtype, true, (cudaStream_t)stream);
+}
+
+int nb2_embedding_fwd(const void* table, const void* ids, void* out, int64_t tokens, int64_t vocab, int64_t D,
+                      int dtype, int index_type, int64_t* status, void* stream) {
+    NB2_REQUIRE(dtype_ok(dtype) && idx_ok(index_type), NB2_ERR_DTYPE, "embedding fwd: dtype=%d index_type=%d", dtype, index_type);
+    NB2_REQUIRE(tokens >= 0 && vocab > 0 && D > 0, NB2_ERR_SHAPE, "embedding fwd: tokens=%lld vocab=%lld D=%lld", (long long)tokens, (long long)vocab, (long long)D);
+    if (tokens == 0) return 0;
+    NB2_REQUIRE(table && ids && out, NB2_ERR_NULL, "embedding fwd: NULL pointer");
+    int rc = require_device();
+    if (rc != 0) return rc;
+    return launch_embedding_fwd(table, ids, out, tokens, vocab, D, dtype, index_type, status, (cudaStream_t)stream);
+}
+int nb2_embedding_bwd(const void* dout, const void* ids, void* dtable, int64_t tokens, int64_t vocab, int64_t D,
+                      int dtype, int index_type, void* workspace, size_t workspace_bytes, void* stream) {
+    NB2_REQUIRE(dtype_ok(dtype) && idx_ok(index_type), NB2_ERR_DTYPE, "embedding bwd: dtype=%d index_type=%d", dtype, index_type);
+    NB2_REQUIRE(tokens >= 0 && vocab > 0 && vocab < ((int64_t)1 << 31) && D > 0, NB2_ERR_SHAPE,
+                "embedding bwd: tokens=%lld vocab=%lld D=%lld", (long long)tokens, (long long)vocab, (long long)D);
+    NB2_REQUIRE(dtable && (tokens == 0 || (dout && ids)), NB2_ERR_NULL, "embedding bwd: NULL pointer");
+    int rc = require_device();
+    if (rc != 0) return rc;
+    return launch_embedding_bwd(dout, ids, dtable, tokens, vocab, D, dtype, index_type, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+int nb2_rope_table(float* cos_sin, const int32_t* positions, int64_t S, int64_t hd, double theta, void* stream) {
+    NB2_REQUIRE(S >= 0 && hd >= 2 && hd % 2 == 0, NB2_ERR_SHAPE, "rope table: S=%lld head_dim=%lld (need an even head_dim >= 2)", (long long)S, (long long)hd);
+    NB2_REQUIRE(theta > 0.0, NB2_ERR_SHAPE, "rope table: theta=%g must be positive", theta);
+    if (S == 0) return 0;
+    NB2_REQUIRE(cos_sin != nullptr, NB2_ERR_NULL, "rope table: NULL output");
+    int rc = require_device();
+    if (rc != 0) return rc;
+    return launch_rope_table(cos_sin, positions, S, hd, theta, (cudaStream_t)stream);
+}
+int nb2_rope_apply(const void* x, const float* cos_sin, void* out, int64_t B, int64_t S, int64_t H, int64_t hd,
+                   int dtype, int inverse, void* stream) {
+    NB2_REQUIRE(dtype_ok(dtype), NB2_ERR_DTYPE, "rope: dtype=%d", dtype);
+    NB2_REQUIRE(B >= 0 && S >= 0 && H >= 0 && hd >= 2 && hd % 2 == 0, NB2_ERR_SHAPE,
+                "rope: B=%lld S=%lld H=%lld head_dim=%lld", (long long)B, (long long)S, (long long)H, (long long)hd);
+    NB2_REQUIRE(S < ((int64_t)1 << 31) && H * hd < ((int64_t)1 << 31), NB2_ERR_SHAPE, "rope: S or H*head_dim exceeds 2^31-1");
+    if (B == 0 || S == 0 || H == 0) return 0;
+    NB2_REQUIRE(x && cos_sin && out, NB2_ERR_NULL, "rope: NULL pointer");
+    int rc = require_device();
+    if (rc != 0) return rc;
+    return launch_rope_apply(x, cos_sin, out, B, S, H, hd, dtype, inverse != 0, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,209 @@
+// Token-embedding gather (forward) and its deterministic scatter-add (backward).
+//
+// Reference semantics: torch::nn::Embedding::forward as Nott calls it
+// (src/block/details/transformers/bert.hpp:162-163,176-187; ebt.hpp:124-126;
+// classic.hpp:366-370): out[t,:] = table[ids[t],:], and through autograd
+// dtable[v,:] = sum_{t: ids[t]==v} dout[t,:].
+#include <cub/device/device_radix_sort.cuh>
+#include "launchers.h"
+
+namespace nb2 {
+
+template <typename I> __device__ __forceinline__ int64_t load_id(const void* ids, int64_t t) {
+    return (int64_t)reinterpret_cast<const I*>(ids)[t];
+}
+
+// ------------------------------------------------------------------- forward
+// A CTA copies EMB_TOK table rows per iteration, so each thread keeps EMB_TOK
+// independent 16-byte loads in flight; a bad id yields a zero row and a status
+// word instead of a fault.
+constexpr int EMB_TOK = 4;
+
+template <typename I, bool VEC, int ELT>
+__global__ void __launch_bounds__(256)
+embedding_fwd_kernel(const uint8_t* __restrict__ table, const void* __restrict__ ids,
+                     uint8_t* __restrict__ out, int64_t tokens, int64_t vocab, int64_t row_bytes,
+                     int64_t* __restrict__ status) {
+    for (int64_t t0 = (int64_t)blockIdx.x * EMB_TOK; t0 < tokens; t0 += (int64_t)gridDim.x * EMB_TOK) {
+        int64_t id[EMB_TOK];
+        bool ok[EMB_TOK];
+#pragma unroll
+        for (int k = 0; k < EMB_TOK; ++k) {
+            id[k] = (t0 + k < tokens) ? load_id<I>(ids, t0 + k) : 0;
+            ok[k] = id[k] >= 0 && id[k] < vocab;
+            if (!ok[k] && t0 + k < tokens && threadIdx.x == 0 && status != nullptr) {
+                status[0] = 1;
+                status[1] = t0 + k;
+            }
+        }
+        if constexpr (VEC) {
+            const int64_t nv = row_bytes >> 4;
+            for (int64_t v = threadIdx.x; v < nv; v += blockDim.x) {
+                uint4 r[EMB_TOK];
+#pragma unroll
+                for (int k = 0; k < EMB_TOK; ++k) {
+                    r[k] = make_uint4(0u, 0u, 0u, 0u);
+                    if (t0 + k < tokens && ok[k])
+                        r[k] = __ldg(reinterpret_cast<const uint4*>(table + id[k] * row_bytes) + v);
+                }
+#pragma unroll
+                for (int k = 0; k < EMB_TOK; ++k)
+                    if (t0 + k < tokens) st_stream(out + (t0 + k) * row_bytes + (v << 4), r[k]);
+            }
+        } else {
+            // element-wise copy for rows that are not 16-byte multiples / aligned
+            const int64_t ne = row_bytes / ELT;
+            for (int k = 0; k < EMB_TOK; ++k) {
+                if (t0 + k >= tokens) break;
+                for (int64_t e = threadIdx.x; e < ne; e += blockDim.x) {
+                    if constexpr (ELT == 4) {
+                        reinterpret_cast<uint32_t*>(out + (t0 + k) * row_bytes)[e] =
+                            ok[k] ? reinterpret_cast<const uint32_t*>(table + id[k] * row_bytes)[e] : 0u;
+                    } else {
+                        reinterpret_cast<uint16_t*>(out + (t0 + k) * row_bytes)[e] =
+                            ok[k] ? reinterpret_cast<const uint16_t*>(table + id[k] * row_bytes)[e] : (uint16_t)0;
+                    }
+                }
+            }
+        }
+    }
+}
+
+template <typename I>
+static int launch_emb_fwd_i(const void* table, const void* ids, void* out, int64_t tokens, int64_t vocab,
+                            int64_t D, int dtype, int64_t* status, cudaStream_t st) {
+    if (tokens == 0 || D == 0) return 0;
+    const int elt = dtype == NB2_F32 ? 4 : 2;
+    const int64_t row_bytes = D * elt;
+    const bool vec_ok = (row_bytes % 16 == 0) && aligned16(table) && aligned16(out);
+    int64_t grid = (tokens + EMB_TOK - 1) / EMB_TOK;
+    const int64_t cap = (int64_t)sm_count() * 16;
+    if (grid > cap) grid = cap;
+    const uint8_t* tb = (const uint8_t*)table;
+    uint8_t* ob = (uint8_t*)out;
+    if (vec_ok)
+        embedding_fwd_kernel<I, true, 4><<<(unsigned)grid, 256, 0, st>>>(tb, ids, ob, tokens, vocab, row_bytes, status);
+    else if (elt == 4)
+        embedding_fwd_kernel<I, false, 4><<<(unsigned)grid, 256, 0, st>>>(tb, ids, ob, tokens, vocab, row_bytes, status);
+    else
+        embedding_fwd_kernel<I, false, 2><<<(unsigned)grid, 256, 0, st>>>(tb, ids, ob, tokens, vocab, row_bytes, status);
+    return cuda_status(cudaGetLastError(), "embedding fwd launch");
+}
+
+int launch_embedding_fwd(const void* table, const void* ids, void* out, int64_t tokens, int64_t vocab,
+                         int64_t D, int dtype, int index_type, int64_t* status, cudaStream_t st) {
+    return index_type == NB2_I32 ? launch_emb_fwd_i<int32_t>(table, ids, out, tokens, vocab, D, dtype, status, st)
+                                 : launch_emb_fwd_i<int64_t>(table, ids, out, tokens, vocab, D, dtype, status, st);
+}
+
+// ------------------------------------------------------------------ backward
+// keys = (id << 32 | t) radix-sorted, so equal ids are contiguous and ordered by
+// t; one CTA per run start sums its run in fp32 in that order.  No atomics: the
+// result is bit-reproducible.  Ids outside [0, vocab) get the key id = vocab and
+// are skipped.
+template <typename I>
+__global__ void __launch_bounds__(256)
+embedding_keys_kernel(const void* __restrict__ ids, uint64_t* __restrict__ keys, int64_t tokens, int64_t vocab) {
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= tokens) return;
+    int64_t id = load_id<I>(ids, t);
+    if (id < 0 || id >= vocab) id = vocab;
+    keys[t] = ((uint64_t)id << 32) | (uint64_t)(uint32_t)t;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+embedding_bwd_kernel(const T* __restrict__ dout, const uint64_t* __restrict__ keys, T* __restrict__ dtable,
+                     int64_t tokens, int64_t vocab, int64_t D, bool vec) {
+    constexpr int EPV = VecTraits<T>::EPV;
+    for (int64_t i = blockIdx.x; i < tokens; i += gridDim.x) {
+        const uint64_t k0 = keys[i];
+        const int64_t id = (int64_t)(k0 >> 32);
+        if (id >= vocab) continue;
+        if (i > 0 && (int64_t)(keys[i - 1] >> 32) == id) continue;   // not a run start
+        T* dst = dtable + id * D;
+        if (vec) {
+            for (int64_t v = threadIdx.x; v < D / EPV; v += blockDim.x) {
+                float acc[EPV];
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) acc[e] = 0.f;
+                for (int64_t j = i; j < tokens; ++j) {
+                    const uint64_t kj = keys[j];
+                    if ((int64_t)(kj >> 32) != id) break;
+                    const int64_t t = (int64_t)(kj & 0xffffffffu);
+                    float f[EPV];
+                    unpack<T>(ld_stream(dout + t * D + v * EPV), f);
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e) acc[e] += f[e];
+                }
+                *reinterpret_cast<uint4*>(dst + v * EPV) = pack<T>(acc);
+            }
+        } else {
+            for (int64_t c = threadIdx.x; c < D; c += blockDim.x) {
+                float acc = 0.f;
+                for (int64_t j = i; j < tokens; ++j) {
+                    const uint64_t kj = keys[j];
+                    if ((int64_t)(kj >> 32) != id) break;
+                    acc += to_f32(dout[(int64_t)(kj & 0xffffffffu) * D + c]);
+                }
+                dst[c] = from_f32<T>(acc);
+            }
+        }
+    }
+}
+
+static int key_bits(int64_t vocab) {
+    int b = 1;
+    while (((int64_t)1 << b) <= vocab && b < 31) ++b;   // ids 0..vocab inclusive (sentinel)
+    return 32 + b;
+}
+
+static size_t cub_temp_bytes(int64_t tokens, int64_t vocab) {
+    size_t bytes = 0;
+    cub::DeviceRadixSort::SortKeys(nullptr, bytes, (const uint64_t*)nullptr, (uint64_t*)nullptr,
+                                   (int)tokens, 0, key_bits(vocab));
+    return bytes;
+}
+
+static size_t round256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+size_t embedding_bwd_workspace(int64_t tokens, int64_t vocab) {
+    if (tokens <= 0) return 256;
+    return 2 * round256((size_t)tokens * 8) + round256(cub_temp_bytes(tokens, vocab)) + 256;
+}
+
+int launch_embedding_bwd(const void* dout, const void* ids, void* dtable, int64_t tokens, int64_t vocab,
+                         int64_t D, int dtype, int index_type, void* ws, size_t ws_bytes, cudaStream_t st) {
+    const int elt = dtype == NB2_F32 ? 4 : 2;
+    int rc = cuda_status(cudaMemsetAsync(dtable, 0, (size_t)vocab * D * elt, st), "embedding bwd memset");
+    if (rc != 0 || tokens == 0 || D == 0) return rc;
+    NB2_REQUIRE(tokens < ((int64_t)1 << 31), NB2_ERR_SHAPE, "embedding bwd: %lld tokens exceed 2^31-1", (long long)tokens);
+    NB2_REQUIRE(ws != nullptr, NB2_ERR_NULL, "embedding bwd: workspace is NULL");
+    NB2_REQUIRE(ws_bytes >= embedding_bwd_workspace(tokens, vocab), NB2_ERR_WORKSPACE,
+                "embedding bwd: workspace %zu < required %zu", ws_bytes, embedding_bwd_workspace(tokens, vocab));
+    uint8_t* base = (uint8_t*)(((uintptr_t)ws + 255) & ~(uintptr_t)255);
+    uint64_t* keys_in = (uint64_t*)base;
+    uint64_t* keys_out = (uint64_t*)(base + round256((size_t)tokens * 8));
+    void* temp = base + 2 * round256((size_t)tokens * 8);
+    size_t temp_bytes = cub_temp_bytes(tokens, vocab);
+
+    const unsigned kgrid = (unsigned)((tokens + 255) / 256);
+    if (index_type == NB2_I32) embedding_keys_kernel<int32_t><<<kgrid, 256, 0, st>>>(ids, keys_in, tokens, vocab);
+    else                       embedding_keys_kernel<int64_t><<<kgrid, 256, 0, st>>>(ids, keys_in, tokens, vocab);
+    rc = cuda_status(cudaGetLastError(), "embedding keys launch");
+    if (rc != 0) return rc;
+    rc = cuda_status(cub::DeviceRadixSort::SortKeys(temp, temp_bytes, keys_in, keys_out, (int)tokens, 0,
+                                                    key_bits(vocab), st), "embedding key sort");
+    if (rc != 0) return rc;
+    const bool vec = (D * elt) % 16 == 0 && aligned16(dout) && aligned16(dtable);
+    int64_t grid = tokens;
+    const int64_t cap = (int64_t)sm_count() * 64;
+    if (grid > cap) grid = cap;
+    if (dtype == NB2_F32)
+        embedding_bwd_kernel<float><<<(unsigned)grid, 128, 0, st>>>((const float*)dout, keys_out, (float*)dtable, tokens, vocab, D, vec);
+    else
+        embedding_bwd_kernel<__nv_bfloat16><<<(unsigned)grid, 128, 0, st>>>((const __nv_bfloat16*)dout, keys_out, (__nv_bfloat16*)dtable, tokens, vocab, D, vec);
+    return cuda_status(cudaGetLastError(), "embedding bwd launch");
+}
+
+}  // namespace nb2

@@ -1,0 +1,22 @@
+// Internal launch functions behind the extern "C" entry points in api.cu.
+#pragma once
+#include "nb2_common.cuh"
+#include "norm_dispatch.cuh"
+
+namespace nb2 {
+
+int launch_act(const void* x, const void* dy, void* out, int64_t n, int dtype, int act, bool bwd, cudaStream_t st);
+int launch_silu_gate(const void* a, int64_t lda, const void* b, int64_t ldb,
+                     const void* dy, int64_t lddy, void* o0, int64_t ldo0, void* o1, int64_t ldo1,
+                     int64_t rows, int64_t H, int dtype, bool bwd, cudaStream_t st);
+int launch_colreduce(const float* partials, int64_t n_partials, int64_t ncols, float* out, cudaStream_t st);
+int launch_embedding_fwd(const void* table, const void* ids, void* out, int64_t tokens, int64_t vocab,
+                         int64_t D, int dtype, int index_type, int64_t* status, cudaStream_t st);
+size_t embedding_bwd_workspace(int64_t tokens, int64_t vocab);
+int launch_embedding_bwd(const void* dout, const void* ids, void* dtable, int64_t tokens, int64_t vocab,
+                         int64_t D, int dtype, int index_type, void* ws, size_t ws_bytes, cudaStream_t st);
+int launch_rope_table(float* cos_sin, const int32_t* positions, int64_t S, int64_t hd, double theta, cudaStream_t st);
+int launch_rope_apply(const void* x, const float* cos_sin, void* out, int64_t B, int64_t S, int64_t H,
+                      int64_t hd, int dtype, bool inverse, cudaStream_t st);
+
+}  // namespace nb2

@@ -1,0 +1,121 @@
+// Shared device/host helpers for the sm_100a row-op kernels.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/nott_b200.h"
+
+namespace nb2 {
+
+// ---------------------------------------------------------------- host side
+void set_error(const char* fmt, ...);
+int  cuda_status(cudaError_t e, const char* what);
+int  sm_count();           // SMs of the current device (cached per device)
+
+#define NB2_REQUIRE(cond, code, ...)            \
+    do {                                        \
+        if (!(cond)) {                          \
+            ::nb2::set_error(__VA_ARGS__);      \
+            return (code);                      \
+        }                                       \
+    } while (0)
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// -------------------------------------------------------------- device side
+// A 16-byte vector of activations: 4 fp32 or 8 bf16.
+template <typename T> struct VecTraits;
+template <> struct VecTraits<float> { static constexpr int EPV = 4; };
+template <> struct VecTraits<__nv_bfloat16> { static constexpr int EPV = 8; };
+
+// Streaming (evict-first) 16-byte global load/store: every activation byte on
+// this path is touched once per kernel, so it should not displace the affine
+// parameters and rope tables that live in L2.
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+    return __ldcs(reinterpret_cast<const uint4*>(p));
+}
+__device__ __forceinline__ void st_stream(void* p, uint4 v) {
+    __stcs(reinterpret_cast<uint4*>(p), v);
+}
+__device__ __forceinline__ uint4 ld_param(const void* p) {
+    return __ldg(reinterpret_cast<const uint4*>(p));
+}
+
+// unpack one 16-byte vector into EPV floats / pack EPV floats into 16 bytes
+template <typename T> __device__ __forceinline__ void unpack(const uint4& v, float* f);
+template <> __device__ __forceinline__ void unpack<float>(const uint4& v, float* f) {
+    f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y);
+    f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+}
+template <> __device__ __forceinline__ void unpack<__nv_bfloat16>(const uint4& v, float* f) {
+    // bf16 -> fp32 is a 16-bit left shift; element 0 is the low half-word.
+    f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u);
+    f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u);
+    f[4] = __uint_as_float(v.z << 16); f[5] = __uint_as_float(v.z & 0xffff0000u);
+    f[6] = __uint_as_float(v.w << 16); f[7] = __uint_as_float(v.w & 0xffff0000u);
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);   // round-to-nearest-even
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+template <typename T> __device__ __forceinline__ uint4 pack(const float* f);
+template <> __device__ __forceinline__ uint4 pack<float>(const float* f) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]),
+                      __float_as_uint(f[2]), __float_as_uint(f[3]));
+}
+template <> __device__ __forceinline__ uint4 pack<__nv_bfloat16>(const float* f) {
+    return make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]),
+                      pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+}
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// ------------------------------------------------------------- activations
+// GELU is the exact-erf form torch::gelu defaults to; SiLU is x*sigmoid(x).
+constexpr float kInvSqrt2   = 0.70710678118654752440f;
+constexpr float kInvSqrt2Pi = 0.39894228040143267794f;
+
+template <int ACT> __device__ __forceinline__ float act_fwd(float z) {
+    if constexpr (ACT == NB2_ACT_GELU) {
+        return 0.5f * z * (1.0f + erff(z * kInvSqrt2));
+    } else if constexpr (ACT == NB2_ACT_SILU) {
+        return __fdividef(z, 1.0f + __expf(-z));
+    } else {
+        return z;
+    }
+}
+// d act(z) / dz
+template <int ACT> __device__ __forceinline__ float act_grad(float z) {
+    if constexpr (ACT == NB2_ACT_GELU) {
+        const float cdf = 0.5f * (1.0f + erff(z * kInvSqrt2));
+        const float pdf = kInvSqrt2Pi * __expf(-0.5f * z * z);
+        return fmaf(z, pdf, cdf);
+    } else if constexpr (ACT == NB2_ACT_SILU) {
+        const float s = __fdividef(1.0f, 1.0f + __expf(-z));
+        return s * fmaf(z, 1.0f - s, 1.0f);      // sigma(z) (1 + z (1 - sigma(z)))
+    } else {
+        return 1.0f;
+    }
+}
+
+// ---------------------------------------------------------------- reductions
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// named barrier over `nthreads` threads (a multiple of 32), id 1..15
+__device__ __forceinline__ void named_barrier(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+}  // namespace nb2
