@@ -78,6 +78,16 @@ const char* nb2_last_error_string(void);
 int nb2_sm_count(void);
 
 /*
+ * Reads (synchronously) the device status word of the current device into
+ * *status_host and, if `clear` != 0, resets it.  The bulk-async norm kernels bound
+ * every wait; one that gives up records (code << 16 | CTA index) there and the
+ * kernel returns early, so a mis-programmed copy shows up as NB2_ERR_DEVICE
+ * from this call instead of a hung GPU.  0 = no kernel gave up.  Has no
+ * counterpart in the reference (its errors are host-side C++ exceptions only).
+ */
+int nb2_device_status(unsigned int* status_host, int clear);
+
+/*
  * Workspace sizes, in bytes, for the calls that need scratch memory.
  *   NB2_WS_NORM_BWD      : a = rows, b = D            -> partials buffer
  *   NB2_WS_EMBEDDING_BWD : a = tokens, b = vocab rows -> sort scratch

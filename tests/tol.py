@@ -1,10 +1,21 @@
 """Tolerances of the parity tests, in one place.
 
 fp32 outputs  : |got - ref| <= 1e-6 + 1e-5 * |ref|
-bf16 outputs  : within 2 bf16 ulp of the fp32-accumulated result rounded to bf16
-long fp32 sums (dgamma, dbeta, dweight): the fp32 tolerance against the fp32
-    reference, OR at least as close to the fp64 result as the fp32 reference is
-    (a different summation order of 1e4..1e6 terms is not an error).
+bf16 outputs  : within 2 bf16 ulp of the fp32-accumulated result rounded to bf16, or
+    inside the fp32 absolute tolerance (1e-6): where fp32 arithmetic itself cancels
+    (GELU's 1 + erf(z/sqrt2) for z < -5 is a multiple of 6e-8) a bf16 output cannot be
+    held to a tighter absolute error than the fp32 path it is computed in.
+fp32 outputs against the LIVE fp32 reference (libtorch CPU) are adjudicated by the fp64
+    result where one exists: an element passes when inside the tolerance of the fp32
+    reference OR at least as close to fp64 as the fp32 reference is.  (libtorch's fp32
+    CPU GELU is itself 1.1e-6 off in the tail around z = -3.5.)
+long fp32 sums over n rows (dgamma, dbeta, dweight): a sum of n terms of unit scale has
+    natural magnitude sqrt(n) even where it cancels to ~0, and fp32 accumulation (ours and
+    the reference's alike) carries an error proportional to that magnitude.  The relative
+    tolerance is therefore applied to max(|ref|, sqrt(n)):
+        |got - ref64| <= 1e-6 + 1e-5 * max(|ref64|, sqrt(n)),
+    or inside the fp32 tolerance of the fp32 reference, or at least as close to fp64 as the
+    fp32 reference is.
 integer / byte outputs: exact.
 """
 from __future__ import annotations
@@ -28,16 +39,31 @@ def fp32_close(got, ref, rtol=FP32_RTOL, atol=FP32_ATOL):
                              f"got {got[i]!r} ref {ref[i]!r} err {err[i]:.3e}")
 
 
-def long_sum_close(got, ref32, ref64, scale_atol=None):
-    """dgamma/dbeta/dweight: pass per element if inside the fp32 tolerance of the fp32
-    reference or not farther from the fp64 reference than the fp32 reference is
-    (plus one fp32 ulp of slack)."""
+def fp32_close_adjudicated(got, ref32, ref64):
+    """got vs the live fp32 reference, with the fp64 result as arbiter (see module docstring)."""
     got = np.asarray(got, np.float64); ref32 = np.asarray(ref32, np.float64); ref64 = np.asarray(ref64, np.float64)
-    ok_tol = np.abs(got - ref32) <= FP32_ATOL + FP32_RTOL * np.abs(ref32)
+    ok = np.abs(got - ref32) <= FP32_ATOL + FP32_RTOL * np.abs(ref32)
     slack = np.spacing(np.abs(ref64).astype(np.float32)).astype(np.float64)
-    ok_f64 = np.abs(got - ref64) <= np.abs(ref32 - ref64) + slack
-    ok_abs = np.abs(got - ref64) <= FP32_ATOL + FP32_RTOL * np.abs(ref64)
-    bad = ~(ok_tol | ok_f64 | ok_abs)
+    ok |= np.abs(got - ref64) <= np.abs(ref32 - ref64) + slack
+    if not ok.all():
+        i = np.unravel_index(np.argmax(~ok), ok.shape)
+        raise AssertionError(f"{(~ok).sum()} of {ok.size} elements neither within tolerance of the fp32 reference nor "
+                             f"closer to fp64; first at {i}: got {got[i]!r} ref32 {ref32[i]!r} ref64 {ref64[i]!r}")
+
+
+def long_sum_close(got, ref64, n_terms, ref32=None):
+    """dgamma/dbeta/dweight over `n_terms` rows; see the module docstring for the rule."""
+    got = np.asarray(got, np.float64); ref64 = np.asarray(ref64, np.float64)
+    scale = np.maximum(np.abs(ref64), float(n_terms) ** 0.5)
+    ok = np.abs(got - ref64) <= FP32_ATOL + FP32_RTOL * scale
+    if ref32 is not None:
+        ref32 = np.asarray(ref32, np.float64)
+        slack = np.spacing(np.abs(ref64).astype(np.float32)).astype(np.float64)
+        ok |= np.abs(got - ref32) <= FP32_ATOL + FP32_RTOL * np.abs(ref32)
+        ok |= np.abs(got - ref64) <= np.abs(ref32 - ref64) + slack
+    else:
+        ref32 = ref64
+    bad = ~ok
     if bad.any():
         i = int(np.argmax(bad))
         raise AssertionError(f"{bad.sum()} of {bad.size} long sums fail; first at {i}: got {got.flat[i]!r} "
@@ -64,6 +90,8 @@ def bf16_ulp_close(got_bits, ref_values, max_ulp=BF16_MAX_ULP):
     """got_bits: uint16 bf16 patterns; ref_values: fp32/fp64 reference before rounding."""
     ref_bits = to_bf16_bits(ref_values)
     d = np.abs(_ordered(got_bits) - _ordered(ref_bits))
+    inside_abs = np.abs(bf16_bits_to_f32(got_bits).astype(np.float64) - np.asarray(ref_values, np.float64)) <= FP32_ATOL
+    d = np.where(inside_abs, 0, d)
     if (d > max_ulp).any():
         i = np.unravel_index(np.argmax(d), d.shape)
         raise AssertionError(f"{(d > max_ulp).sum()} of {d.size} elements differ by more than {max_ulp} bf16 ulp; "

@@ -24,6 +24,7 @@ _SIGNATURES = {
     "nb2_abi_version": (c_int, []),
     "nb2_last_error_string": (c_char_p, []),
     "nb2_sm_count": (c_int, []),
+    "nb2_device_status": (c_int, [POINTER(ctypes.c_uint), c_int]),
     "nb2_workspace_bytes": (c_size_t, [c_int, c_int64, c_int64, c_int]),
     "nb2_layernorm_fwd": (c_int, [c_void_p] * 6 + [c_int64, c_int64, c_double, c_int, c_int, c_void_p]),
     "nb2_layernorm_bwd": (c_int, [c_void_p] * 8 + [POINTER(c_int64), c_int64, c_int64, c_int, c_int, c_void_p]),
@@ -94,6 +95,13 @@ def _stream():
 def _dev(t: torch.Tensor) -> None:
     if not t.is_cuda:
         raise ValueError("libnott_b200 works on CUDA tensors only (no CPU fallback)")
+
+
+def device_status(clear: bool = True) -> int:
+    """Synchronising read of the device status word; raises Nb2Error if a kernel gave up waiting."""
+    word = ctypes.c_uint(0)
+    check(lib().nb2_device_status(ctypes.byref(word), int(clear)))
+    return int(word.value)
 
 
 def workspace_bytes(op: int, a: int, b: int, dtype: int = F32) -> int:

@@ -35,6 +35,25 @@ int sm_count() {
     return cached_sms;
 }
 
+int current_device_slot() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) dev = 0;
+    return dev % kMaxDevices;
+}
+
+// One status word per device: the ring kernels record here (code << 16 | CTA) when a
+// bounded wait gives up.  The symbol's device address is looked up once per device.
+__device__ unsigned int g_device_status[4];
+unsigned int* device_status_ptr() {
+    static thread_local unsigned int* ptrs[kMaxDevices] = {};
+    unsigned int*& p = ptrs[current_device_slot()];
+    if (p == nullptr) {
+        void* addr = nullptr;
+        if (cudaGetSymbolAddress(&addr, g_device_status) == cudaSuccess) p = static_cast<unsigned int*>(addr);
+    }
+    return p;
+}
+
 static bool dtype_ok(int d) { return d == NB2_F32 || d == NB2_BF16; }
 static bool act_ok(int a) { return a == NB2_ACT_NONE || a == NB2_ACT_GELU || a == NB2_ACT_SILU; }
 static bool idx_ok(int i) { return i == NB2_I32 || i == NB2_I64; }
@@ -61,7 +80,8 @@ static int norm_fwd(bool rms, const void* x, const void* gamma, const void* beta
     a.x = x; a.gamma = gamma; a.beta = rms ? nullptr : beta; a.y = y;
     a.mean_out = mean; a.rstd_out = rstd; a.rows = rows; a.D = D; a.eps = (float)eps;
     a.act = act; a.rms = rms; a.stream = (cudaStream_t)stream;
-    return dtype == NB2_F32 ? launch_norm_fwd<float>(a) : launch_norm_fwd<__nv_bfloat16>(a);
+    if (dtype == NB2_F32) return rms ? launch_norm_fwd<float, true>(a) : launch_norm_fwd<float, false>(a);
+    return rms ? launch_norm_fwd<__nv_bfloat16, true>(a) : launch_norm_fwd<__nv_bfloat16, false>(a);
 }
 
 static int norm_bwd(bool rms, const void* x, const void* dy, const void* gamma, const void* beta,
@@ -81,7 +101,8 @@ static int norm_bwd(bool rms, const void* x, const void* dy, const void* gamma, 
     a.x = x; a.dy = dy; a.gamma = gamma; a.beta = rms ? nullptr : beta; a.mean = mean; a.rstd = rstd;
     a.dx = dx; a.partials = partials; a.rows = rows; a.D = D; a.act = act; a.rms = rms;
     a.stream = (cudaStream_t)stream;
-    return dtype == NB2_F32 ? launch_norm_bwd<float>(a, n_partials) : launch_norm_bwd<__nv_bfloat16>(a, n_partials);
+    if (dtype == NB2_F32) return rms ? launch_norm_bwd<float, true>(a, n_partials) : launch_norm_bwd<float, false>(a, n_partials);
+    return rms ? launch_norm_bwd<__nv_bfloat16, true>(a, n_partials) : launch_norm_bwd<__nv_bfloat16, false>(a, n_partials);
 }
 
 }  // namespace nb2
@@ -93,6 +114,22 @@ extern "C" {
 int nb2_abi_version(void) { return NB2_ABI_VERSION; }
 const char* nb2_last_error_string(void) { return g_err; }
 int nb2_sm_count(void) { return sm_count(); }
+
+int nb2_device_status(unsigned int* status_host, int clear) {
+    NB2_REQUIRE(status_host != nullptr, NB2_ERR_NULL, "device status: NULL output");
+    unsigned int* p = device_status_ptr();
+    if (p == nullptr) return cuda_status(cudaGetLastError(), "device status word lookup");
+    int rc = cuda_status(cudaMemcpy(status_host, p, sizeof(unsigned int), cudaMemcpyDeviceToHost), "device status read");
+    if (rc != 0) return rc;
+    if (clear && *status_host != 0) rc = cuda_status(cudaMemset(p, 0, sizeof(unsigned int)), "device status clear");
+    if (rc != 0) return rc;
+    if (*status_host != 0) {
+        set_error("a norm kernel gave up waiting: code %u in CTA %u (1 = a tile never arrived, 2 = a stage was never released)",
+                  *status_host >> 16, *status_host & 0xffffu);
+        return NB2_ERR_DEVICE;
+    }
+    return 0;
+}
 
 size_t nb2_workspace_bytes(int op, int64_t a, int64_t b, int dtype) {
     switch (op) {

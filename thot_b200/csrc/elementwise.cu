@@ -130,7 +130,7 @@ silu_gate_vec_kernel(const T* __restrict__ a, int64_t lda, const T* __restrict__
             if (BWD) unpack<T>(dv[k], fd);
 #pragma unroll
             for (int e = 0; e < EPV; ++e) {
-                const float s = __fdividef(1.0f, 1.0f + __expf(-fa[e]));
+                const float s = fast_rcp(1.0f + fast_ex2(fa[e] * -1.44269504088896340736f));
                 const float silu = fa[e] * s;
                 if (BWD) {
                     r0v[e] = fd[e] * fb[e] * (s * fmaf(fa[e], 1.0f - s, 1.0f));   // da
@@ -156,7 +156,7 @@ silu_gate_scalar_kernel(const T* __restrict__ a, int64_t lda, const T* __restric
          i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t r = i / H, c = i - r * H;
         const float fa = to_f32(a[r * lda + c]), fb = to_f32(b[r * ldb + c]);
-        const float s = __fdividef(1.0f, 1.0f + __expf(-fa));
+        const float s = fast_rcp(1.0f + fast_ex2(fa * -1.44269504088896340736f));
         if (BWD) {
             const float d = to_f32(dy[r * lddy + c]);
             o0[r * ldo0 + c] = from_f32<T>(d * fb * (s * fmaf(fa, 1.0f - s, 1.0f)));

@@ -1,9 +1,51 @@
-// Backward launcher: dX + per-CTA partials in one persistent kernel; the
-// any-D path uses a dX kernel and a column-sum kernel instead.
+// Backward launcher: dX + per-CTA partials in one persistent kernel (bulk-async
+// ring where the shape fits it exactly, else register-row); the any-width path
+// uses a dX kernel and a column-sum kernel instead.
 #pragma once
 #include "norm_dispatch.cuh"
 
 namespace nb2 {
+
+template <typename T, int TPR, int VPT, int ACT, bool RMS>
+static int launch_bwd_tma(const NormArgs& a, int64_t* n_partials) {
+    auto kern = norm_bwd_tma_kernel<T, TPR, VPT, ACT, RMS, true>;
+    const TmaTiling t = tma_tiling(a.D, (int)sizeof(T), TPR, 2);
+    NB2_REQUIRE(t.smem <= kTmaMaxSmem, NB2_ERR_SHAPE, "norm ring kernel: %zu bytes of shared memory exceed the SM", t.smem);
+    static thread_local size_t configured_all[kMaxDevices] = {};
+    size_t& configured = configured_all[current_device_slot()];
+    if (t.smem > configured) {
+        int rc = cuda_status(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)t.smem),
+                             "norm_bwd_tma_kernel shared memory");
+        if (rc != 0) return rc;
+        configured = t.smem;
+    }
+    const int grid = (int)tma_grid(a.rows, t.tile_rows, sm_count());
+    kern<<<grid, kTmaThreads, t.smem, a.stream>>>((const T*)a.x, (const T*)a.dy, (const T*)a.gamma, (const T*)a.beta,
+                                                  a.mean, a.rstd, (T*)a.dx, a.partials, a.rows, (int)a.D,
+                                                  t.tile_rows, t.stages, device_status_ptr());
+    if (n_partials) *n_partials = a.partials ? grid : 0;
+    return cuda_status(cudaGetLastError(), "norm_bwd_tma_kernel launch");
+}
+
+template <typename T, int ACT, bool RMS>
+static int launch_bwd_tma_shape(const NormArgs& a, TmaShape s, int64_t* n_partials) {
+    constexpr int EPV = VecTraits<T>::EPV;
+    constexpr int V16 = 16 / EPV;
+    if (s.vpt == 3) {
+        if constexpr (EPV == 4) return launch_bwd_tma<T, 64, 3, ACT, RMS>(a, n_partials);
+        else return launch_bwd_tma<T, 32, 3, ACT, RMS>(a, n_partials);
+    }
+    switch (s.tpr) {
+        case 32:  return launch_bwd_tma<T, 32, V16, ACT, RMS>(a, n_partials);
+        case 64:  return launch_bwd_tma<T, 64, V16, ACT, RMS>(a, n_partials);
+        case 128: return launch_bwd_tma<T, 128, V16, ACT, RMS>(a, n_partials);
+        case 256: return launch_bwd_tma<T, 256, V16, ACT, RMS>(a, n_partials);
+        case 512: return launch_bwd_tma<T, 512, V16, ACT, RMS>(a, n_partials);
+        default: break;
+    }
+    set_error("norm bwd: no ring kernel for threads-per-row %d", s.tpr);
+    return NB2_ERR_SHAPE;
+}
 
 template <typename T, int TPR, int ACT, bool RMS>
 static int launch_bwd_cfg(const NormArgs& a, int64_t* n_partials) {
@@ -22,6 +64,10 @@ template <typename T, int ACT, bool RMS>
 static int launch_bwd_act(const NormArgs& a, int64_t* n_partials) {
     constexpr int EPV = VecTraits<T>::EPV;
     if (norm_fast_path_ok<T>(a, bwd_vpt<T>())) {
+        const TmaShape s = tma_bwd_shape(a.D, EPV);
+        const bool affine = a.gamma != nullptr && (RMS || a.beta != nullptr);
+        if (s.tpr != 0 && affine && tma_preferred(RMS, a.D, (int)sizeof(T), true) && tma_fits(a.D, (int)sizeof(T), s.tpr, 2))
+            return launch_bwd_tma_shape<T, ACT, RMS>(a, s, n_partials);
         switch (pick_tpr(a.D / EPV, bwd_vpt<T>())) {
             case 32:  return launch_bwd_cfg<T, 32, ACT, RMS>(a, n_partials);
             case 64:  return launch_bwd_cfg<T, 64, ACT, RMS>(a, n_partials);
@@ -54,18 +100,13 @@ static int launch_bwd_act(const NormArgs& a, int64_t* n_partials) {
 }
 
 template <typename T, bool RMS>
-static int launch_bwd_rms(const NormArgs& a, int64_t* n_partials) {
+int launch_norm_bwd(const NormArgs& a, int64_t* n_partials) {
     switch (a.act) {
         case NB2_ACT_NONE: return launch_bwd_act<T, NB2_ACT_NONE, RMS>(a, n_partials);
         case NB2_ACT_GELU: return launch_bwd_act<T, NB2_ACT_GELU, RMS>(a, n_partials);
         case NB2_ACT_SILU: return launch_bwd_act<T, NB2_ACT_SILU, RMS>(a, n_partials);
         default: set_error("unknown activation %d", a.act); return NB2_ERR_DTYPE;
     }
-}
-
-template <typename T>
-int launch_norm_bwd(const NormArgs& a, int64_t* n_partials) {
-    return a.rms ? launch_bwd_rms<T, true>(a, n_partials) : launch_bwd_rms<T, false>(a, n_partials);
 }
 
 }  // namespace nb2

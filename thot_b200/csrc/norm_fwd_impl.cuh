@@ -1,10 +1,46 @@
-// Forward launcher: picks (threads per row, activation, norm kind) and launches
-// the persistent register-row kernel, or the any-D kernel when the row is
-// not 16-byte vectorisable.
+// Forward launcher: bulk-async ring kernel where the shape fits it exactly,
+// else the register-row kernel, else the any-width kernel.
 #pragma once
 #include "norm_dispatch.cuh"
 
 namespace nb2 {
+
+template <typename T, int TPR, int VPT, int ACT, bool RMS>
+static int launch_fwd_tma(const NormArgs& a) {
+    auto kern = norm_fwd_tma_kernel<T, TPR, VPT, ACT, RMS, true>;
+    const TmaTiling t = tma_tiling(a.D, (int)sizeof(T), TPR, 1);
+    NB2_REQUIRE(t.smem <= kTmaMaxSmem, NB2_ERR_SHAPE, "norm ring kernel: %zu bytes of shared memory exceed the SM", t.smem);
+    static thread_local size_t configured_all[kMaxDevices] = {};
+    size_t& configured = configured_all[current_device_slot()];
+    if (t.smem > configured) {
+        int rc = cuda_status(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)t.smem),
+                             "norm_fwd_tma_kernel shared memory");
+        if (rc != 0) return rc;
+        configured = t.smem;
+    }
+    const int grid = (int)tma_grid(a.rows, t.tile_rows, sm_count());
+    kern<<<grid, kTmaThreads, t.smem, a.stream>>>((const T*)a.x, (const T*)a.gamma, (const T*)a.beta, (T*)a.y,
+                                                  a.mean_out, a.rstd_out, a.rows, (int)a.D, a.eps, t.tile_rows,
+                                                  t.stages, device_status_ptr());
+    return cuda_status(cudaGetLastError(), "norm_fwd_tma_kernel launch");
+}
+
+template <typename T, int ACT, bool RMS>
+static int launch_fwd_tma_shape(const NormArgs& a, TmaShape s) {
+    constexpr int EPV = VecTraits<T>::EPV;
+    constexpr int V32 = 32 / EPV, V24 = 24 / EPV;
+    if (s.vpt == V24 && s.tpr == 32) return launch_fwd_tma<T, 32, V24, ACT, RMS>(a);
+    switch (s.tpr) {
+        case 32:  return launch_fwd_tma<T, 32, V32, ACT, RMS>(a);
+        case 64:  return launch_fwd_tma<T, 64, V32, ACT, RMS>(a);
+        case 128: return launch_fwd_tma<T, 128, V32, ACT, RMS>(a);
+        case 256: return launch_fwd_tma<T, 256, V32, ACT, RMS>(a);
+        case 512: return launch_fwd_tma<T, 512, V32, ACT, RMS>(a);
+        default: break;
+    }
+    set_error("norm fwd: no ring kernel for threads-per-row %d", s.tpr);
+    return NB2_ERR_SHAPE;
+}
 
 template <typename T, int TPR, int ACT, bool RMS>
 static int launch_fwd_cfg(const NormArgs& a) {
@@ -25,6 +61,10 @@ template <typename T, int ACT, bool RMS>
 static int launch_fwd_act(const NormArgs& a) {
     constexpr int EPV = VecTraits<T>::EPV;
     if (norm_fast_path_ok<T>(a, fwd_vpt<T>())) {
+        const TmaShape s = tma_fwd_shape(a.D, EPV);
+        const bool affine = a.gamma != nullptr && (RMS || a.beta != nullptr);
+        if (s.tpr != 0 && affine && tma_preferred(RMS, a.D, (int)sizeof(T), false) && tma_fits(a.D, (int)sizeof(T), s.tpr, 1))
+            return launch_fwd_tma_shape<T, ACT, RMS>(a, s);
         switch (pick_tpr(a.D / EPV, fwd_vpt<T>())) {
             case 32:  return launch_fwd_cfg<T, 32, ACT, RMS>(a);
             case 64:  return launch_fwd_cfg<T, 64, ACT, RMS>(a);
@@ -44,18 +84,13 @@ static int launch_fwd_act(const NormArgs& a) {
 }
 
 template <typename T, bool RMS>
-static int launch_fwd_rms(const NormArgs& a) {
+int launch_norm_fwd(const NormArgs& a) {
     switch (a.act) {
         case NB2_ACT_NONE: return launch_fwd_act<T, NB2_ACT_NONE, RMS>(a);
         case NB2_ACT_GELU: return launch_fwd_act<T, NB2_ACT_GELU, RMS>(a);
         case NB2_ACT_SILU: return launch_fwd_act<T, NB2_ACT_SILU, RMS>(a);
         default: set_error("unknown activation %d", a.act); return NB2_ERR_DTYPE;
     }
-}
-
-template <typename T>
-int launch_norm_fwd(const NormArgs& a) {
-    return a.rms ? launch_fwd_rms<T, true>(a) : launch_fwd_rms<T, false>(a);
 }
 
 }  // namespace nb2

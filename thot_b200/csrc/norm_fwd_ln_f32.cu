@@ -1,0 +1,2 @@
+#include "norm_fwd_impl.cuh"
+template int nb2::launch_norm_fwd<float, false>(const nb2::NormArgs&);

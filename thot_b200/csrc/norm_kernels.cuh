@@ -227,7 +227,7 @@ norm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy,
                     }
                     acc_g[j][e] = fmaf(dz, h, acc_g[j][e]);
                     if constexpr (!RMS) acc_b[j][e] += dz;
-                    const float gv = has_g ? dz * g[e] : dz;
+                    const float gv = has_g ? __fmul_rn(dz, g[e]) : dz;   // rounded once: g - mean(g) cancels exactly
                     s1 += gv;
                     s2 = fmaf(gv, h, s2);
                     xh[j][e] = h;
@@ -369,7 +369,7 @@ norm_bwd_generic_dx(const T* __restrict__ x, const T* __restrict__ dy,
                 if (!RMS && beta != nullptr) z += to_f32(beta[c]);
                 dz *= act_grad<ACT>(z);
             }
-            const float gv = dz * g;
+            const float gv = __fmul_rn(dz, g);
             s1 += gv;
             s2 = fmaf(gv, h, s2);
         }
@@ -385,7 +385,7 @@ norm_bwd_generic_dx(const T* __restrict__ x, const T* __restrict__ dy,
                 if (!RMS && beta != nullptr) z += to_f32(beta[c]);
                 dz *= act_grad<ACT>(z);
             }
-            xo[c] = from_f32<T>(rs * (dz * g - m1 - h * m2));
+            xo[c] = from_f32<T>(rs * (__fmul_rn(dz, g) - m1 - h * m2));
         }
     }
 }
