@@ -8,7 +8,7 @@ namespace nb2 {
 
 template <typename T, int TPR, int VPT, int ACT, bool RMS>
 static int launch_bwd_tma(const NormArgs& a, int64_t* n_partials) {
-    auto kern = norm_bwd_tma_kernel<T, TPR, VPT, ACT, RMS, true>;
+    auto kern = norm_bwd_tma_kernel<T, TPR, VPT, ACT, RMS>;
     const TmaTiling t = tma_tiling(a.D, (int)sizeof(T), TPR, 2);
     NB2_REQUIRE(t.smem <= kTmaMaxSmem, NB2_ERR_SHAPE, "norm ring kernel: %zu bytes of shared memory exceed the SM", t.smem);
     static thread_local size_t configured_all[kMaxDevices] = {};
@@ -19,10 +19,10 @@ static int launch_bwd_tma(const NormArgs& a, int64_t* n_partials) {
         if (rc != 0) return rc;
         configured = t.smem;
     }
-    const int grid = (int)tma_grid(a.rows, t.tile_rows, sm_count());
+    const int grid = (int)tma_grid(a.rows, TPR, sm_count());
     kern<<<grid, kTmaThreads, t.smem, a.stream>>>((const T*)a.x, (const T*)a.dy, (const T*)a.gamma, (const T*)a.beta,
                                                   a.mean, a.rstd, (T*)a.dx, a.partials, a.rows, (int)a.D,
-                                                  t.tile_rows, t.stages, device_status_ptr());
+                                                  t.stages, device_status_ptr());
     if (n_partials) *n_partials = a.partials ? grid : 0;
     return cuda_status(cudaGetLastError(), "norm_bwd_tma_kernel launch");
 }

@@ -66,39 +66,43 @@ static inline int64_t norm_bwd_generic_parts(int64_t rows) {
 
 // ---- bulk-async ring kernels: exact-fit shapes only (D == TPR * VPT * EPV), parameters present.
 struct TmaShape { int tpr, vpt; };
+static inline TmaShape tma_bwd_shape_fwddecl(int64_t D, int epv);
 // forward holds 32 elements per thread and row (24 for the 768-wide rows)
 static inline TmaShape tma_fwd_shape(int64_t D, int epv) {
+    if (const char* e = getenv("NB2_FWD_EPT")) { if (atoi(e) == 16) return tma_bwd_shape_fwddecl(D, epv); }
     if (D == 768) return {32, 24 / epv};
     for (int tpr = 32; tpr <= 512; tpr *= 2)
         if (D == (int64_t)tpr * 32) return {tpr, 32 / epv};
     return {0, 0};
 }
 // backward holds 16 (its accumulators take the registers)
+static inline TmaShape tma_bwd_shape(int64_t D, int epv);
+static inline TmaShape tma_bwd_shape_fwddecl(int64_t D, int epv) { return tma_bwd_shape(D, epv); }
 static inline TmaShape tma_bwd_shape(int64_t D, int epv) {
     if (D == 768) return epv == 4 ? TmaShape{64, 3} : TmaShape{32, 3};
     for (int tpr = 32; tpr <= 512; tpr *= 2)
         if (D == (int64_t)tpr * 16) return {tpr, 16 / epv};
     return {0, 0};
 }
-// rows per tile and stages of the ring for `nsrc` streamed tensors
-struct TmaTiling { int tile_rows, stages; size_t smem; };
+// ring depth: every row group gets `stages` row slots; one "layer" (a slot of every
+// group) is 32-64 KiB, and the rings may take what 200 KiB leave after the parameters
+struct TmaTiling { int stages; size_t smem; };
 static inline TmaTiling tma_tiling(int64_t D, int elt, int tpr, int nsrc) {
     const int rpc = kTmaThreads / tpr;
-    const int64_t row_bytes = D * elt;
-    int m = 1;
-    while ((int64_t)rpc * (m * 2) * row_bytes * nsrc <= 65536) m *= 2;      // a stage of up to 64 KiB
-    TmaTiling t;
-    t.tile_rows = rpc * m;
-    const size_t stage = (size_t)t.tile_rows * row_bytes * nsrc;
+    const size_t layer = (size_t)rpc * D * elt * nsrc;
     const size_t fixed = kTmaHeaderBytes + 2 * (size_t)tma_param_bytes((int)D, elt);
+    TmaTiling t;
     t.stages = 2;
-    if (fixed + 3 * stage <= 160 * 1024) t.stages = 3;
-    t.smem = fixed + t.stages * stage;
+    int max_stages = 4;
+    if (const char* e = getenv("NB2_TMA_STAGES")) max_stages = atoi(e);
+    while (t.stages < max_stages && fixed + (size_t)(t.stages + 1) * layer <= 216 * 1024) ++t.stages;
+    t.smem = fixed + t.stages * layer;
     return t;
 }
-static inline int64_t tma_grid(int64_t rows, int tile_rows, int sms) {
-    const int64_t tiles = (rows + tile_rows - 1) / tile_rows;
-    return tiles < sms ? (tiles < 1 ? 1 : tiles) : sms;
+static inline int64_t tma_grid(int64_t rows, int tpr, int sms) {
+    const int rpc = kTmaThreads / tpr;
+    const int64_t need = (rows + rpc - 1) / rpc;
+    return need < sms ? (need < 1 ? 1 : need) : sms;
 }
 
 // Should this (norm, direction, dtype, D) use the ring kernels?  Measured on B200 over

@@ -7,7 +7,7 @@ namespace nb2 {
 
 template <typename T, int TPR, int VPT, int ACT, bool RMS>
 static int launch_fwd_tma(const NormArgs& a) {
-    auto kern = norm_fwd_tma_kernel<T, TPR, VPT, ACT, RMS, true>;
+    auto kern = norm_fwd_tma_kernel<T, TPR, VPT, ACT, RMS>;
     const TmaTiling t = tma_tiling(a.D, (int)sizeof(T), TPR, 1);
     NB2_REQUIRE(t.smem <= kTmaMaxSmem, NB2_ERR_SHAPE, "norm ring kernel: %zu bytes of shared memory exceed the SM", t.smem);
     static thread_local size_t configured_all[kMaxDevices] = {};
@@ -18,18 +18,28 @@ static int launch_fwd_tma(const NormArgs& a) {
         if (rc != 0) return rc;
         configured = t.smem;
     }
-    const int grid = (int)tma_grid(a.rows, t.tile_rows, sm_count());
+    const int grid = (int)tma_grid(a.rows, TPR, sm_count());
     kern<<<grid, kTmaThreads, t.smem, a.stream>>>((const T*)a.x, (const T*)a.gamma, (const T*)a.beta, (T*)a.y,
-                                                  a.mean_out, a.rstd_out, a.rows, (int)a.D, a.eps, t.tile_rows,
-                                                  t.stages, device_status_ptr());
+                                                  a.mean_out, a.rstd_out, a.rows, (int)a.D, a.eps, t.stages,
+                                                  device_status_ptr());
     return cuda_status(cudaGetLastError(), "norm_fwd_tma_kernel launch");
 }
 
 template <typename T, int ACT, bool RMS>
 static int launch_fwd_tma_shape(const NormArgs& a, TmaShape s) {
     constexpr int EPV = VecTraits<T>::EPV;
-    constexpr int V32 = 32 / EPV, V24 = 24 / EPV;
+    constexpr int V32 = 32 / EPV, V24 = 24 / EPV, V16 = 16 / EPV;
     if (s.vpt == V24 && s.tpr == 32) return launch_fwd_tma<T, 32, V24, ACT, RMS>(a);
+    if (s.vpt == V16) {           // experiment: 16 elements per thread
+        switch (s.tpr) {
+            case 32:  return launch_fwd_tma<T, 32, V16, ACT, RMS>(a);
+            case 64:  return launch_fwd_tma<T, 64, V16, ACT, RMS>(a);
+            case 128: return launch_fwd_tma<T, 128, V16, ACT, RMS>(a);
+            case 256: return launch_fwd_tma<T, 256, V16, ACT, RMS>(a);
+            case 512: return launch_fwd_tma<T, 512, V16, ACT, RMS>(a);
+            default: break;
+        }
+    }
     switch (s.tpr) {
         case 32:  return launch_fwd_tma<T, 32, V32, ACT, RMS>(a);
         case 64:  return launch_fwd_tma<T, 64, V32, ACT, RMS>(a);

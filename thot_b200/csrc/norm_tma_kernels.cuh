@@ -1,18 +1,16 @@
 // LayerNorm / RMSNorm (+ fused activation) forward and backward, bulk-async
-// variant for sm_100a: one persistent CTA of 16 warps per SM.  Tiles of whole
-// rows stream from HBM into a shared-memory ring with cp.async.bulk (TMA, this
-// CTA only, no multicast) completing on mbarriers; the warps read the tiles from
-// shared memory, reduce the row statistics with warp shuffles and write the
-// outputs with 16-byte coalesced stores.  The bytes in flight per SM are the
-// ring, independent of register use, so HBM stays busy while rows are reduced.
+// variant for sm_100a: one persistent CTA of 16 warps per SM.  Whole rows stream
+// from HBM into shared-memory rings with cp.async.bulk (TMA, this CTA only, no
+// multicast) completing on mbarriers; the warps move a row from shared memory
+// into registers, reduce its statistics with warp shuffles and write the output
+// with 16-byte coalesced stores.  The bytes in flight per SM are the rings,
+// independent of register use, so HBM stays busy while rows are being reduced.
 //
-// There is no dedicated producer warp: 16 warps is 4 per scheduler, which leaves
-// each thread 128 registers (a 17th warp would cut that to 96 and spill the
-// backward accumulators).  Thread 0 refills a stage as soon as every warp has
-// released it, one tile behind the tile it is about to consume.
-//
-// Work split inside a tile: a group of TPR threads owns a row, each thread VPT
-// 16-byte vectors of it (the same mapping as the register-row kernels).
+// Work split: a group of TPR threads owns a row, each thread VPT 16-byte vectors
+// of it (the mapping of the register-row kernels).  16 warps is 4 per scheduler,
+// which leaves each thread 128 registers; a 17th (producer) warp would cut that
+// to 96 and spill the backward accumulators, so each group's first thread issues
+// the group's copies itself.
 //
 // Every wait is bounded: a barrier that does not complete within the limit
 // makes the CTA record a code in the device status word and leave.
@@ -23,13 +21,11 @@ namespace nb2 {
 
 // `status` kernel argument: a device word, 0 = ok, else (code << 16 | blockIdx) of the
 // first CTA that gave up waiting.
-constexpr unsigned int kStatusFullTimeout = 1;    // tile never arrived
-constexpr unsigned int kStatusEmptyTimeout = 2;   // stage never released
+constexpr unsigned int kStatusFullTimeout = 1;    // a requested row never arrived
 constexpr long long kWaitCycleLimit = 4000000000LL;   // ~2 s at 1.9 GHz
 
 constexpr int kTmaWarps = 16;
 constexpr int kTmaThreads = kTmaWarps * 32;
-constexpr int kTmaHeaderBytes = 1024;             // barriers + reduction scratch, ahead of the ring
 constexpr int kTmaMaxStages = 8;
 constexpr uint32_t kBulkChunk = 32768;            // bytes per cp.async.bulk
 
@@ -106,259 +102,199 @@ __device__ __forceinline__ bool group_all(bool ok, int barrier_id) {
     }
 }
 
-// The ring of one CTA: one source tensor forward (x), two backward (x, dy); a
-// stage holds the same row range of each source.  The feeder lives in shared
-// memory (only thread 0 issues copies; keeping its state out of registers
-// leaves them to the row maths).
-struct TileFeeder {
-    const uint8_t* src0;
-    const uint8_t* src1;          // nullptr when there is one source
-    unsigned int* status;
-    int64_t rows;
-    int64_t ntiles;
-    uint64_t policy;
-    int row_bytes, tile_rows, stages;
-    uint32_t tile_bytes, stage_bytes;
-    int next_issue;               // my next tile (per-CTA sequence number) to copy
-    int abort_flag;
-};
-
-// Shared memory: header (kTmaHeaderBytes: full[8] | empty[8] | red_a[64] | red_b[64] | TileFeeder),
-// then gamma and beta (the reads of a row's parameters are shared-memory reads: a
-// per-row global load sits on the critical path of every row even when it hits L1),
-// then the ring.
+// Every row group owns a private ring of `stages` row slots.  Its leader thread
+// requests rows ahead; a slot is re-requested as soon as the group has moved the
+// row into registers, i.e. before the row's arithmetic, so the copies of the next
+// rows overlap all of it.  Groups never wait for one another.
+//
+// Shared memory: header (full barriers [16 groups][8 stages], reduction scratch,
+// abort flag), then gamma and beta (a per-row global load of the parameters would
+// sit on the critical path of every row even when it hits L1), then the rings.
+constexpr int kTmaMaxGroups = 16;
+constexpr int kTmaHeaderBytes = 2048;
 __host__ __device__ inline int tma_param_bytes(int D, int elt) { return (D * elt + 1023) & ~1023; }
 
 struct TmaSmem {
-    uint64_t* full;
-    uint64_t* empty;
-    float* red_a;
-    float* red_b;
-    TileFeeder* f;
-    uint8_t* ring;
-    const uint4* gamma;           // the affine parameters, copied once per CTA
+    uint64_t* full;               // [kTmaMaxGroups][kTmaMaxStages]
+    float* red_a;                 // [64]
+    float* red_b;                 // [64]
+    volatile int* abort_flag;
+    const uint4* gamma;
     const uint4* beta;
-    // param_bytes: bytes of ONE parameter vector, rounded up to 16 (see tma_param_bytes)
+    uint8_t* ring;
     __device__ __forceinline__ TmaSmem(uint8_t* smem, int param_bytes)
-        : full(reinterpret_cast<uint64_t*>(smem)), empty(reinterpret_cast<uint64_t*>(smem) + kTmaMaxStages),
-          red_a(reinterpret_cast<float*>(smem + 128)), red_b(reinterpret_cast<float*>(smem + 384)),
-          f(reinterpret_cast<TileFeeder*>(smem + 640)), ring(smem + kTmaHeaderBytes + 2 * param_bytes),
+        : full(reinterpret_cast<uint64_t*>(smem)),
+          red_a(reinterpret_cast<float*>(smem + 1024)), red_b(reinterpret_cast<float*>(smem + 1280)),
+          abort_flag(reinterpret_cast<volatile int*>(smem + 1536)),
           gamma(reinterpret_cast<const uint4*>(smem + kTmaHeaderBytes)),
-          beta(reinterpret_cast<const uint4*>(smem + kTmaHeaderBytes + param_bytes)) {}
-    __device__ __forceinline__ volatile int* abort_flag() const { return &f->abort_flag; }
-
-    __device__ __forceinline__ bool tile_exists(int k) const {
-        return (int64_t)blockIdx.x + (int64_t)k * gridDim.x < f->ntiles;
-    }
-    // thread 0: copy my k-th tile (tile index blockIdx.x + k * gridDim.x) into stage k % stages
-    __device__ __forceinline__ void issue(int k) const {
-        const TileFeeder& t = *f;
-        const int64_t tile = (int64_t)blockIdx.x + (int64_t)k * gridDim.x;
-        const int s = k % t.stages;
-        const int64_t r0 = tile * t.tile_rows;
-        const int64_t nr = (t.rows - r0 < t.tile_rows) ? t.rows - r0 : t.tile_rows;
-        const uint32_t bytes = (uint32_t)nr * t.row_bytes;
-        mbar_arrive_expect_tx(&full[s], t.src1 != nullptr ? 2 * bytes : bytes);
-        uint8_t* dst = ring + (size_t)s * t.stage_bytes;
-        const uint8_t* a = t.src0 + r0 * (int64_t)t.row_bytes;
-        for (uint32_t off = 0; off < bytes; off += kBulkChunk) {
-            const uint32_t n = bytes - off < kBulkChunk ? bytes - off : kBulkChunk;
-            bulk_g2s(dst + off, a + off, n, &full[s], t.policy);
-        }
-        if (t.src1 != nullptr) {
-            const uint8_t* b = t.src1 + r0 * (int64_t)t.row_bytes;
-            for (uint32_t off = 0; off < bytes; off += kBulkChunk) {
-                const uint32_t n = bytes - off < kBulkChunk ? bytes - off : kBulkChunk;
-                bulk_g2s(dst + t.tile_bytes + off, b + off, n, &full[s], t.policy);
-            }
-        }
-    }
-    // thread 0, opportunistically: refill every stage that all warps have released
-    __device__ __forceinline__ void poll() const {
-        while (tile_exists(f->next_issue)) {
-            const int kp = f->next_issue - f->stages;             // the tile whose stage is recycled
-            if (!mbar_try_wait(&empty[kp % f->stages], (uint32_t)((kp / f->stages) & 1))) break;
-            issue(f->next_issue);
-            f->next_issue = f->next_issue + 1;
-        }
-    }
-    // thread 0, before the CTA consumes its k-th tile: make sure that tile has been requested
-    __device__ __forceinline__ void ensure(int k) const {
-        while (f->next_issue <= k && tile_exists(f->next_issue)) {
-            const int kp = f->next_issue - f->stages;
-            if (!mbar_wait_bounded(&empty[kp % f->stages], (uint32_t)((kp / f->stages) & 1), abort_flag(),
-                                   kStatusEmptyTimeout, f->status)) {
-                // gave up: let the copies already in flight land before leaving
-                for (int kb = kp + 1; kb < f->next_issue; ++kb)
-                    mbar_wait_drain(&full[kb % f->stages], (uint32_t)((kb / f->stages) & 1));
-                return;
-            }
-            issue(f->next_issue);
-            f->next_issue = f->next_issue + 1;
-        }
-    }
+          beta(reinterpret_cast<const uint4*>(smem + kTmaHeaderBytes + param_bytes)),
+          ring(smem + kTmaHeaderBytes + 2 * param_bytes) {}
 };
 
-__device__ __forceinline__ void tma_setup(const TmaSmem& sm, const void* src0, const void* src1, int64_t rows,
-                                          int row_bytes, int tile_rows, int stages, unsigned int* status,
+// parameters into shared memory, barriers initialised; ends with a CTA barrier
+__device__ __forceinline__ void tma_setup(const TmaSmem& sm, int groups, int stages, int row_bytes,
                                           const void* gamma, const void* beta) {
     for (int i = threadIdx.x; i < row_bytes / 16; i += blockDim.x) {
         if (gamma != nullptr) const_cast<uint4*>(sm.gamma)[i] = ld_param(reinterpret_cast<const uint4*>(gamma) + i);
         if (beta != nullptr) const_cast<uint4*>(sm.beta)[i] = ld_param(reinterpret_cast<const uint4*>(beta) + i);
     }
     if (threadIdx.x == 0) {
-        TileFeeder& t = *sm.f;
-        t.src0 = reinterpret_cast<const uint8_t*>(src0);
-        t.src1 = reinterpret_cast<const uint8_t*>(src1);
-        t.status = status;
-        t.rows = rows;
-        t.ntiles = (rows + tile_rows - 1) / tile_rows;
-        t.policy = policy_evict_first();
-        t.row_bytes = row_bytes;
-        t.tile_rows = tile_rows;
-        t.stages = stages;
-        t.tile_bytes = (uint32_t)tile_rows * row_bytes;
-        t.stage_bytes = (src1 != nullptr ? 2u : 1u) * t.tile_bytes;
-        t.next_issue = 0;
-        t.abort_flag = 0;
-        for (int s = 0; s < stages; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], kTmaWarps); }
+        for (int g = 0; g < groups; ++g)
+            for (int s = 0; s < stages; ++s) mbar_init(&sm.full[g * kTmaMaxStages + s], 1);
+        *sm.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        for (int k = 0; k < stages && sm.tile_exists(k); ++k) sm.issue(k);      // prologue: fill the ring
-        sm.f->next_issue = stages;
+}
+
+// group leader: request one row of each source into a slot
+__device__ __forceinline__ void request_row(uint64_t* bar, uint8_t* slot, const uint8_t* src0, const uint8_t* src1,
+                                            int64_t row, uint32_t row_bytes, uint64_t policy) {
+    mbar_arrive_expect_tx(bar, src1 != nullptr ? 2 * row_bytes : row_bytes);
+    for (uint32_t off = 0; off < row_bytes; off += kBulkChunk) {
+        const uint32_t n = row_bytes - off < kBulkChunk ? row_bytes - off : kBulkChunk;
+        bulk_g2s(slot + off, src0 + row * (int64_t)row_bytes + off, n, bar, policy);
+        if (src1 != nullptr) bulk_g2s(slot + row_bytes + off, src1 + row * (int64_t)row_bytes + off, n, bar, policy);
     }
 }
 
 // ------------------------------------------------------------------ forward
-// FAST: D == TPR * VPT * EPV exactly and the affine parameters are present, so the
-// inner loops carry no predicates.
-template <typename T, int TPR, int VPT, int ACT, bool RMS, bool FAST>
+// D == TPR * VPT * EPV exactly and the affine parameters are present (the host
+// checks both), so the inner loops carry no predicates.
+template <typename T, int TPR, int VPT, int ACT, bool RMS>
 __global__ void __launch_bounds__(kTmaThreads, 1)
 norm_fwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
                     T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
-                    int64_t rows, int D, float eps, int tile_rows, int stages,
-                    unsigned int* __restrict__ status) {
+                    int64_t rows, int D, float eps, int stages, unsigned int* __restrict__ status) {
     constexpr int EPV = VecTraits<T>::EPV;
-    constexpr int RPC = kTmaThreads / TPR;        // row slots
+    constexpr int RPC = kTmaThreads / TPR;        // row groups
     constexpr int WPR = (TPR + 31) / 32;
     static_assert(kTmaThreads % TPR == 0, "row groups must tile the CTA");
-    static_assert(TPR <= 32 || RPC <= 14, "one named barrier per multi-warp row slot");
+    static_assert(TPR <= 32 || RPC <= 14, "one named barrier per multi-warp row group");
 
     extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t row_bytes = (uint32_t)D * sizeof(T);
     const TmaSmem sm(smem, tma_param_bytes(D, (int)sizeof(T)));
-    const int row_bytes = D * (int)sizeof(T);
-    const uint32_t stage_bytes = (uint32_t)tile_rows * row_bytes;
-    const int64_t ntiles = (rows + tile_rows - 1) / tile_rows;
-    tma_setup(sm, x, nullptr, rows, row_bytes, tile_rows, stages, status, gamma, RMS ? nullptr : beta);
+    tma_setup(sm, RPC, stages, (int)row_bytes, gamma, RMS ? nullptr : beta);
 
-    const int nvec = D / EPV;
-    const int slot = threadIdx.x / TPR;
+    const int grp = threadIdx.x / TPR;
     const int tr = threadIdx.x % TPR;
     const float inv_d = 1.0f / (float)D;
-    const bool has_g = FAST || gamma != nullptr;
-    const bool has_b = !RMS && (FAST || beta != nullptr);
-
-    int k = 0;
-    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++k) {
-        const int s = k % stages;
-        if (threadIdx.x == 0) { sm.poll(); sm.ensure(k); }
-        bool ok = mbar_wait_bounded(&sm.full[s], (uint32_t)((k / stages) & 1), sm.abort_flag(), kStatusFullTimeout, status);
-        ok = group_all<TPR>(ok, slot + 1);
-        if (!ok) break;
-        const int64_t r0 = tile * tile_rows;
-        const int nr = (int)((rows - r0 < tile_rows) ? rows - r0 : tile_rows);
-        const uint8_t* stage = sm.ring + (size_t)s * stage_bytes;
-
-        for (int r = slot; r < nr; r += RPC) {
-            const uint4* srow = reinterpret_cast<const uint4*>(stage + (size_t)r * row_bytes);
-            float v[VPT][EPV];
-            float sum = 0.f;
-#pragma unroll
-            for (int j = 0; j < VPT; ++j) {
-                if (FAST || (tr + j * TPR) < nvec) {
-                    unpack<T>(srow[tr + j * TPR], v[j]);
-#pragma unroll
-                    for (int e = 0; e < EPV; ++e) sum += RMS ? v[j][e] * v[j][e] : v[j][e];
-                }
-            }
-            float mu = 0.f, rs;
-            if constexpr (RMS) {
-                rs = rsqrtf(row_sum<TPR>(sum, sm.red_a + slot * WPR, slot + 1) * inv_d + eps);
-            } else {
-                mu = row_sum<TPR>(sum, sm.red_a + slot * WPR, slot + 1) * inv_d;
-                float q = 0.f;
-#pragma unroll
-                for (int j = 0; j < VPT; ++j) {
-                    if (FAST || (tr + j * TPR) < nvec) {
-#pragma unroll
-                        for (int e = 0; e < EPV; ++e) { v[j][e] -= mu; q = fmaf(v[j][e], v[j][e], q); }
-                    }
-                }
-                rs = rsqrtf(row_sum<TPR>(q, sm.red_b + slot * WPR, slot + 1) * inv_d + eps);
-            }
-            const int64_t row = r0 + r;
-            if (tr == 0) {
-                if (!RMS && mean_out != nullptr) mean_out[row] = mu;
-                if (rstd_out != nullptr) rstd_out[row] = rs;
-            }
-            T* yr = y + row * (int64_t)D;
-#pragma unroll
-            for (int j = 0; j < VPT; ++j) {
-                if (FAST || (tr + j * TPR) < nvec) {
-                    float g[EPV], b[EPV], o[EPV];
-                    if (has_g) unpack<T>(sm.gamma[tr + j * TPR], g);
-                    if (has_b) unpack<T>(sm.beta[tr + j * TPR], b);
-#pragma unroll
-                    for (int e = 0; e < EPV; ++e) {
-                        float z = v[j][e] * rs;                 // v already holds x - mean for LayerNorm
-                        if (has_g) z = has_b ? fmaf(z, g[e], b[e]) : z * g[e];
-                        else if (has_b) z += b[e];
-                        o[e] = act_fwd<ACT>(z);
-                    }
-                    st_stream(yr + (size_t)(tr + j * TPR) * EPV, pack<T>(o));
-                }
-            }
-            if constexpr (TPR > 32 && RMS) named_barrier(slot + 1, TPR);   // red_a reuse
+    uint64_t* full = sm.full + grp * kTmaMaxStages;
+    uint8_t* ring = sm.ring + (size_t)grp * stages * row_bytes;
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(x);
+    const int64_t first = (int64_t)blockIdx.x * RPC + grp;
+    const int64_t stride = (int64_t)gridDim.x * RPC;
+    uint64_t policy = 0;
+    if (tr == 0) {
+        policy = policy_evict_first();
+        for (int s = 0; s < stages; ++s) {
+            const int64_t row = first + s * stride;
+            if (row < rows) request_row(&full[s], ring + (size_t)s * row_bytes, src, nullptr, row, row_bytes, policy);
         }
-        __syncwarp();
-        if ((threadIdx.x & 31) == 0) mbar_arrive(&sm.empty[s]);             // this warp is done with the stage
-        if (threadIdx.x == 0) sm.poll();
+    }
+
+    int i = 0;
+    for (int64_t row = first; row < rows; row += stride, ++i) {
+        const int s = i % stages;
+        bool ok = mbar_wait_bounded(&full[s], (uint32_t)((i / stages) & 1), sm.abort_flag, kStatusFullTimeout, status);
+        ok = group_all<TPR>(ok, grp + 1);
+        if (!ok) break;
+        const uint4* srow = reinterpret_cast<const uint4*>(ring + (size_t)s * row_bytes);
+        float v[VPT][EPV];
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            unpack<T>(srow[tr + j * TPR], v[j]);
+#pragma unroll
+            for (int e = 0; e < EPV; ++e) sum += RMS ? v[j][e] * v[j][e] : v[j][e];
+        }
+        // The first reduction doubles as the point where every thread of the group has its
+        // part of the row in registers: the slot is free, request the row `stages` ahead.
+        float mu = 0.f, rs;
+        const float red0 = row_sum<TPR>(sum, sm.red_a + grp * WPR, grp + 1) * inv_d;
+        if (tr == 0) {
+            const int64_t ahead = row + (int64_t)stages * stride;
+            if (ahead < rows) request_row(&full[s], ring + (size_t)s * row_bytes, src, nullptr, ahead, row_bytes, policy);
+        }
+        if constexpr (RMS) {
+            rs = rsqrtf(red0 + eps);
+        } else {
+            mu = red0;
+            float q = 0.f;
+#pragma unroll
+            for (int j = 0; j < VPT; ++j)
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) { v[j][e] -= mu; q = fmaf(v[j][e], v[j][e], q); }
+            rs = rsqrtf(row_sum<TPR>(q, sm.red_b + grp * WPR, grp + 1) * inv_d + eps);
+        }
+        if (tr == 0) {
+            if (!RMS && mean_out != nullptr) mean_out[row] = mu;
+            if (rstd_out != nullptr) rstd_out[row] = rs;
+        }
+        T* yr = y + row * (int64_t)D;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            float g[EPV], b[EPV], o[EPV];
+            unpack<T>(sm.gamma[tr + j * TPR], g);
+            if constexpr (!RMS) unpack<T>(sm.beta[tr + j * TPR], b);
+#pragma unroll
+            for (int e = 0; e < EPV; ++e) {
+                const float z = RMS ? v[j][e] * rs * g[e] : fmaf(v[j][e] * rs, g[e], b[e]);   // v holds x - mean for LayerNorm
+                o[e] = act_fwd<ACT>(z);
+            }
+            st_stream(yr + (size_t)(tr + j * TPR) * EPV, pack<T>(o));
+        }
+        if constexpr (TPR > 32 && RMS) named_barrier(grp + 1, TPR);   // red_a reuse
+    }
+    if (tr == 0 && *sm.abort_flag) {
+        // gave up: let the copies this group still has in flight land before the CTA leaves
+        for (int b = 0; b < stages; ++b) {
+            const int ib = i + b;
+            if (first + (int64_t)ib * stride < rows) mbar_wait_drain(&full[ib % stages], (uint32_t)((ib / stages) & 1));
+        }
     }
 }
 
 // ----------------------------------------------------------------- backward
-template <typename T, int TPR, int VPT, int ACT, bool RMS, bool FAST>
+template <typename T, int TPR, int VPT, int ACT, bool RMS>
 __global__ void __launch_bounds__(kTmaThreads, 1)
 norm_bwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ dy,
                     const T* __restrict__ gamma, const T* __restrict__ beta,
                     const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
                     T* __restrict__ dx, float* __restrict__ partials,
-                    int64_t rows, int D, int tile_rows, int stages,
-                    unsigned int* __restrict__ status) {
+                    int64_t rows, int D, int stages, unsigned int* __restrict__ status) {
     constexpr int EPV = VecTraits<T>::EPV;
     constexpr int RPC = kTmaThreads / TPR;
     constexpr int WPR = (TPR + 31) / 32;
     constexpr int NP = NormPartials<RMS>::N;
     constexpr int COLS = TPR * VPT * EPV;
     static_assert(kTmaThreads % TPR == 0, "row groups must tile the CTA");
-    static_assert(TPR <= 32 || RPC <= 14, "one named barrier per multi-warp row slot");
+    static_assert(TPR <= 32 || RPC <= 14, "one named barrier per multi-warp row group");
 
     extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t row_bytes = (uint32_t)D * sizeof(T);
+    const uint32_t slot_bytes = 2 * row_bytes;                      // a row of x then the same row of dy
     const TmaSmem sm(smem, tma_param_bytes(D, (int)sizeof(T)));
-    const int row_bytes = D * (int)sizeof(T);
-    const uint32_t tile_bytes = (uint32_t)tile_rows * row_bytes;      // one tensor's share of a stage
-    const uint32_t stage_bytes = 2 * tile_bytes;                     // x tile then dy tile
-    const int64_t ntiles = (rows + tile_rows - 1) / tile_rows;
-    tma_setup(sm, x, dy, rows, row_bytes, tile_rows, stages, status, gamma, RMS ? nullptr : beta);
+    tma_setup(sm, RPC, stages, (int)row_bytes, gamma, RMS ? nullptr : beta);
 
-    const int nvec = D / EPV;
-    const int slot = threadIdx.x / TPR;
+    const int grp = threadIdx.x / TPR;
     const int tr = threadIdx.x % TPR;
     const float inv_d = 1.0f / (float)D;
-    const bool has_g = FAST || gamma != nullptr;
-    const bool has_b = !RMS && (FAST || beta != nullptr);
+    uint64_t* full = sm.full + grp * kTmaMaxStages;
+    uint8_t* ring = sm.ring + (size_t)grp * stages * slot_bytes;
+    const uint8_t* src0 = reinterpret_cast<const uint8_t*>(x);
+    const uint8_t* src1 = reinterpret_cast<const uint8_t*>(dy);
+    const int64_t first = (int64_t)blockIdx.x * RPC + grp;
+    const int64_t stride = (int64_t)gridDim.x * RPC;
+    uint64_t policy = 0;
+    if (tr == 0) {
+        policy = policy_evict_first();
+        for (int s = 0; s < stages; ++s) {
+            const int64_t row = first + s * stride;
+            if (row < rows) request_row(&full[s], ring + (size_t)s * slot_bytes, src0, src1, row, row_bytes, policy);
+        }
+    }
 
     float acc_g[VPT][EPV], acc_b[RMS ? 1 : VPT][EPV];
 #pragma unroll
@@ -366,106 +302,98 @@ norm_bwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ dy,
 #pragma unroll
         for (int e = 0; e < EPV; ++e) { acc_g[j][e] = 0.f; if (!RMS) acc_b[j][e] = 0.f; }
 
-    // The saved statistics of the slot's first row in a tile are fetched one tile
-    // ahead, so their global-memory latency never sits in front of a row's maths.
+    // the saved statistics are fetched one row ahead, off the critical path
     float mu_next = 0.f, rs_next = 0.f;
-    {
-        const int64_t row = (int64_t)blockIdx.x * tile_rows + slot;
-        if (row < rows) { if (!RMS) mu_next = __ldg(mean_in + row); rs_next = __ldg(rstd_in + row); }
-    }
-    int k = 0;
-    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++k) {
-        const int s = k % stages;
-        if (threadIdx.x == 0) { sm.poll(); sm.ensure(k); }
-        float mu = mu_next, rs = rs_next;
-        {
-            const int64_t row = (tile + gridDim.x) * tile_rows + slot;
-            if (row < rows) { if (!RMS) mu_next = __ldg(mean_in + row); rs_next = __ldg(rstd_in + row); }
-        }
-        bool ok = mbar_wait_bounded(&sm.full[s], (uint32_t)((k / stages) & 1), sm.abort_flag(), kStatusFullTimeout, status);
-        ok = group_all<TPR>(ok, slot + 1);
-        if (!ok) break;
-        const int64_t r0 = tile * tile_rows;
-        const int nr = (int)((rows - r0 < tile_rows) ? rows - r0 : tile_rows);
-        const uint8_t* stage = sm.ring + (size_t)s * stage_bytes;
+    if (first < rows) { if (!RMS) mu_next = __ldg(mean_in + first); rs_next = __ldg(rstd_in + first); }
 
-        for (int r = slot; r < nr; r += RPC) {
-            const uint4* sx = reinterpret_cast<const uint4*>(stage + (size_t)r * row_bytes);
-            const uint4* sd = reinterpret_cast<const uint4*>(stage + tile_bytes + (size_t)r * row_bytes);
-            const int64_t row = r0 + r;
-            if (r != slot) { mu = RMS ? 0.f : __ldg(mean_in + row); rs = __ldg(rstd_in + row); }
-            float xh[VPT][EPV], gg[VPT][EPV];
-            float s1 = 0.f, s2 = 0.f;
+    int i = 0;
+    for (int64_t row = first; row < rows; row += stride, ++i) {
+        const int s = i % stages;
+        const float mu = mu_next, rs = rs_next;
+        if (row + stride < rows) { if (!RMS) mu_next = __ldg(mean_in + row + stride); rs_next = __ldg(rstd_in + row + stride); }
+        bool ok = mbar_wait_bounded(&full[s], (uint32_t)((i / stages) & 1), sm.abort_flag, kStatusFullTimeout, status);
+        ok = group_all<TPR>(ok, grp + 1);
+        if (!ok) break;
+        const uint4* sx = reinterpret_cast<const uint4*>(ring + (size_t)s * slot_bytes);
+        const uint4* sd = reinterpret_cast<const uint4*>(ring + (size_t)s * slot_bytes + row_bytes);
+        float xh[VPT][EPV], gg[VPT][EPV];
+        float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-            for (int j = 0; j < VPT; ++j) {
-                if (FAST || (tr + j * TPR) < nvec) {
-                    float xv[EPV], dv[EPV], g[EPV], b[EPV];
-                    unpack<T>(sx[tr + j * TPR], xv);
-                    unpack<T>(sd[tr + j * TPR], dv);
-                    if (has_g) unpack<T>(sm.gamma[tr + j * TPR], g);
-                    if (has_b && ACT != NB2_ACT_NONE) unpack<T>(sm.beta[tr + j * TPR], b);
+        for (int j = 0; j < VPT; ++j) {
+            float xv[EPV], dv[EPV], g[EPV], b[EPV];
+            unpack<T>(sx[tr + j * TPR], xv);
+            unpack<T>(sd[tr + j * TPR], dv);
+            unpack<T>(sm.gamma[tr + j * TPR], g);
+            if constexpr (!RMS && ACT != NB2_ACT_NONE) unpack<T>(sm.beta[tr + j * TPR], b);
 #pragma unroll
-                    for (int e = 0; e < EPV; ++e) {
-                        const float h = (xv[e] - mu) * rs;
-                        float dz = dv[e];
-                        if constexpr (ACT != NB2_ACT_NONE) {
-                            float z = h;
-                            if (has_g) z = has_b ? fmaf(z, g[e], b[e]) : z * g[e];
-                            else if (has_b) z += b[e];
-                            dz *= act_grad<ACT>(z);
-                        }
-                        acc_g[j][e] = fmaf(dz, h, acc_g[j][e]);
-                        if constexpr (!RMS) acc_b[j][e] += dz;
-                        const float gv = has_g ? __fmul_rn(dz, g[e]) : dz;   // rounded once: g - mean(g) cancels exactly
-                        s1 += gv;
-                        s2 = fmaf(gv, h, s2);
-                        xh[j][e] = h;
-                        gg[j][e] = gv;
-                    }
+            for (int e = 0; e < EPV; ++e) {
+                const float h = (xv[e] - mu) * rs;
+                float dz = dv[e];
+                if constexpr (ACT != NB2_ACT_NONE) {
+                    const float z = RMS ? h * g[e] : fmaf(h, g[e], b[e]);
+                    dz *= act_grad<ACT>(z);
                 }
+                acc_g[j][e] = fmaf(dz, h, acc_g[j][e]);
+                if constexpr (!RMS) acc_b[j][e] += dz;
+                const float gv = __fmul_rn(dz, g[e]);   // rounded once: g - mean(g) cancels exactly
+                s1 += gv;
+                s2 = fmaf(gv, h, s2);
+                xh[j][e] = h;
+                gg[j][e] = gv;
             }
-            float m1 = 0.f;
-            if constexpr (!RMS) m1 = row_sum<TPR>(s1, sm.red_a + slot * WPR, slot + 1) * inv_d;
-            const float m2 = row_sum<TPR>(s2, sm.red_b + slot * WPR, slot + 1) * inv_d;
-            T* xo = dx + row * (int64_t)D;
-#pragma unroll
-            for (int j = 0; j < VPT; ++j) {
-                if (FAST || (tr + j * TPR) < nvec) {
-                    float o[EPV];
-#pragma unroll
-                    for (int e = 0; e < EPV; ++e) o[e] = rs * (gg[j][e] - m1 - xh[j][e] * m2);
-                    st_stream(xo + (size_t)(tr + j * TPR) * EPV, pack<T>(o));
-                }
-            }
-            if constexpr (TPR > 32 && RMS) named_barrier(slot + 1, TPR);   // red_b reuse
         }
-        __syncwarp();
-        if ((threadIdx.x & 31) == 0) mbar_arrive(&sm.empty[s]);
-        if (threadIdx.x == 0) sm.poll();
+        // after the first reduction every thread of the group is done with the slot
+        float m1 = 0.f, m2;
+        if constexpr (!RMS) {
+            m1 = row_sum<TPR>(s1, sm.red_a + grp * WPR, grp + 1) * inv_d;
+            if (tr == 0) {
+                const int64_t ahead = row + (int64_t)stages * stride;
+                if (ahead < rows) request_row(&full[s], ring + (size_t)s * slot_bytes, src0, src1, ahead, row_bytes, policy);
+            }
+            m2 = row_sum<TPR>(s2, sm.red_b + grp * WPR, grp + 1) * inv_d;
+        } else {
+            m2 = row_sum<TPR>(s2, sm.red_b + grp * WPR, grp + 1) * inv_d;
+            if (tr == 0) {
+                const int64_t ahead = row + (int64_t)stages * stride;
+                if (ahead < rows) request_row(&full[s], ring + (size_t)s * slot_bytes, src0, src1, ahead, row_bytes, policy);
+            }
+        }
+        T* xo = dx + row * (int64_t)D;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            float o[EPV];
+#pragma unroll
+            for (int e = 0; e < EPV; ++e) o[e] = rs * (gg[j][e] - m1 - xh[j][e] * m2);
+            st_stream(xo + (size_t)(tr + j * TPR) * EPV, pack<T>(o));
+        }
+        if constexpr (TPR > 32 && RMS) named_barrier(grp + 1, TPR);   // red_b reuse
+    }
+    if (tr == 0 && *sm.abort_flag) {
+        for (int b = 0; b < stages; ++b) {
+            const int ib = i + b;
+            if (first + (int64_t)ib * stride < rows) mbar_wait_drain(&full[ib % stages], (uint32_t)((ib / stages) & 1));
+        }
     }
 
     if (partials == nullptr) return;
-    // Combine the row slots in a fixed order through shared memory.  The ring is
-    // free for that: after the barrier every warp is past its last tile, and no
-    // copy is in flight (each issued tile was waited for).
+    // Combine the row groups in a fixed order through shared memory.  The rings are
+    // free for that: past the barrier every group has consumed every row it requested.
     float* comb = reinterpret_cast<float*>(sm.ring);
     float* out = partials + (size_t)blockIdx.x * NP * D;
     __syncthreads();
     for (int sl = 0; sl < RPC; ++sl) {
-        if (slot == sl) {
+        if (grp == sl) {
 #pragma unroll
             for (int j = 0; j < VPT; ++j) {
-                if (FAST || (tr + j * TPR) < nvec) {
-                    const int c0 = (tr + j * TPR) * EPV;
+                const int c0 = (tr + j * TPR) * EPV;
 #pragma unroll
-                    for (int e = 0; e < EPV; ++e) {
-                        if (sl == 0) {
-                            comb[c0 + e] = acc_g[j][e];
-                            if constexpr (!RMS) comb[COLS + c0 + e] = acc_b[j][e];
-                        } else {
-                            comb[c0 + e] += acc_g[j][e];
-                            if constexpr (!RMS) comb[COLS + c0 + e] += acc_b[j][e];
-                        }
+                for (int e = 0; e < EPV; ++e) {
+                    if (sl == 0) {
+                        comb[c0 + e] = acc_g[j][e];
+                        if constexpr (!RMS) comb[COLS + c0 + e] = acc_b[j][e];
+                    } else {
+                        comb[c0 + e] += acc_g[j][e];
+                        if constexpr (!RMS) comb[COLS + c0 + e] += acc_b[j][e];
                     }
                 }
             }

@@ -1,0 +1,62 @@
+// Python bindings of the C++ host layer (nott_b200.hpp) so the parity tests can drive the
+// same autograd functions and modules a Nott build would link.  Not a second API: every
+// call forwards to Nott::B200.
+#include <torch/extension.h>
+
+#include "nott_b200.hpp"
+
+namespace nb = Nott::B200;
+
+PYBIND11_MODULE(_nott_b200_host, m) {
+    m.doc() = "libtorch host layer of libnott_b200 (Nott::B200)";
+    m.def("layernorm_act", [](torch::Tensor x, c10::optional<torch::Tensor> w, c10::optional<torch::Tensor> b, double eps,
+                              int64_t act) {
+        return nb::LayerNormActFunction::apply(std::move(x), w, b, eps, act);
+    });
+    m.def("rmsnorm_act", [](torch::Tensor x, c10::optional<torch::Tensor> w, double eps, int64_t act) {
+        return nb::RMSNormActFunction::apply(std::move(x), w, eps, act);
+    });
+    m.def("apply", [](int64_t type, torch::Tensor x) { return nb::apply(static_cast<nb::ActivationType>(type), std::move(x)); });
+    m.def("silu_gate", [](torch::Tensor gate, torch::Tensor up) { return nb::silu_gate(gate, up); });
+    m.def("embedding", [](torch::Tensor weight, torch::Tensor ids) { return nb::EmbeddingFunction::apply(std::move(weight), std::move(ids)); });
+    m.def("rotary_table", [](int64_t S, int64_t hd, double theta, torch::Device device) {
+        return nb::RotaryTable(S, hd, theta, device).table();
+    });
+    m.def("rotary", [](torch::Tensor x, torch::Tensor table) { return nb::RotaryFunction::apply(std::move(x), std::move(table)); });
+
+    // module round trip: construct, run, and expose named parameters (checkpoint key names)
+    m.def("layernorm_module_step", [](int64_t D, double eps, bool affine, int64_t act_type, torch::Tensor x, torch::Tensor dy) {
+        nb::LayerNormOptions opt;
+        opt.eps = eps; opt.elementwise_affine = affine; opt.activation = static_cast<nb::ActivationType>(act_type);
+        nb::LayerNorm mod(D, opt);
+        mod->to(x.device(), x.scalar_type());
+        auto xin = x.clone().requires_grad_(true);
+        auto y = mod->forward(xin);
+        y.backward(dy);
+        std::vector<std::string> names;
+        std::vector<torch::Tensor> out{y.detach(), xin.grad()};
+        for (auto& kv : mod->named_parameters()) { names.push_back(kv.key()); out.push_back(kv.value().grad()); }
+        return std::make_pair(names, out);
+    });
+    m.def("rmsnorm_module_step", [](int64_t D, double eps, bool learnable, int64_t act_type, torch::Tensor x, torch::Tensor dy) {
+        nb::RMSNormOptions opt;
+        opt.eps = eps; opt.learnable = learnable; opt.activation = static_cast<nb::ActivationType>(act_type);
+        nb::RMSNorm mod(D, opt);
+        mod->to(x.device(), x.scalar_type());
+        auto xin = x.clone().requires_grad_(true);
+        auto y = mod->forward(xin);
+        y.backward(dy);
+        std::vector<std::string> names;
+        std::vector<torch::Tensor> out{y.detach(), xin.grad()};
+        for (auto& kv : mod->named_parameters()) { names.push_back(kv.key()); out.push_back(kv.value().grad()); }
+        return std::make_pair(names, out);
+    });
+    m.def("module_errors", []() {
+        // the exception types the reference throws for the same mistakes (mamba.hpp:116-132)
+        std::vector<std::string> seen;
+        try { nb::RMSNorm bad(0, nb::RMSNormOptions{}); } catch (const std::invalid_argument& e) { seen.push_back(e.what()); }
+        try { nb::RMSNorm ok(8, nb::RMSNormOptions{}); ok->forward(torch::Tensor()); } catch (const std::invalid_argument& e) { seen.push_back(e.what()); }
+        try { nb::RMSNorm ok(8, nb::RMSNormOptions{}); ok->forward(torch::zeros({2, 8})); } catch (const std::invalid_argument& e) { seen.push_back(e.what()); }
+        return seen;
+    });
+}

@@ -1,0 +1,472 @@
+// nott_b200.hpp — libtorch host layer over libnott_b200.so.
+//
+// Drop-in counterparts of the pieces of Nott (MoonFlowww/Thot) that sit on the
+// memory-bound row-op path, with the same names, constructor arguments,
+// parameter names and exception types, so a block that holds the reference
+// module can hold this one instead and existing checkpoints keep loading:
+//
+//   Nott::B200::LayerNorm   <- torch::nn::LayerNorm as the blocks build it
+//                              (src/block/details/transformers/classic.hpp:399-404, options :54-57),
+//                              optionally fused with the activation that follows it
+//   Nott::B200::RMSNorm     <- Mamba::Detail::RMSNorm (src/block/details/transformers/mamba.hpp:110-150)
+//   Nott::B200::Embedding   <- torch::nn::Embedding (bert.hpp:126-128, ebt.hpp:94-96)
+//   Nott::B200::apply       <- Nott::Activation::Details::apply (src/activation/apply.hpp:24-57)
+//   Nott::B200::silu_gate   <- `up * torch::silu(gate)` (mamba.hpp:443-446)
+//   Nott::B200::RotaryTable / rotary  (no reference code; belongs between the head
+//                              view and the attention kernel, src/attention/details/head.hpp:70-74)
+//
+// Every op is a torch::autograd::Function whose forward and backward call the
+// extern "C" kernels on the current CUDA stream; outputs come from libtorch's
+// caching allocator; nothing synchronises, so the ops can be captured in the
+// CUDA graphs Nott records around a training step (src/core.hpp:3856-3879).
+// There is no CPU path: a CPU tensor, an unsupported dtype or a missing library
+// raises.  Under CUDA autocast the norms run in fp32, like libtorch's.
+#pragma once
+
+#include <ATen/autocast_mode.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <torch/torch.h>
+
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "../../include/nott_b200.h"
+
+namespace Nott::B200 {
+
+// Same enumerators, same order as Nott::Activation::Type (src/activation/activation.hpp:6-21),
+// so a value converts with a static_cast in either direction.
+enum class ActivationType {
+    Identity, ReLU, Sigmoid, Tanh, LeakyReLU, Softmax, SiLU, GeLU, GLU, SwiGLU, dSiLU, PSiLU, Mish, Swish,
+};
+
+namespace detail {
+
+inline void check(int status, const char* what) {
+    if (status == 0) return;
+    const std::string msg = std::string(what) + ": " + nb2_last_error_string();
+    if (status < 0) throw std::invalid_argument(msg);
+    throw std::runtime_error(msg);
+}
+
+inline int dtype_code(const torch::Tensor& t, const char* what) {
+    if (t.scalar_type() == torch::kFloat32) return NB2_F32;
+    if (t.scalar_type() == torch::kBFloat16) return NB2_BF16;
+    throw std::invalid_argument(std::string(what) + " supports float32 and bfloat16 tensors only.");
+}
+
+inline void require_cuda(const torch::Tensor& t, const char* what) {
+    if (!t.defined()) throw std::invalid_argument(std::string(what) + " requires a defined input tensor.");
+    if (!t.is_cuda()) throw std::invalid_argument(std::string(what) + " runs on CUDA tensors only (there is no CPU fallback).");
+}
+
+inline void* stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+inline const void* ptr_or_null(const torch::Tensor& t) { return t.defined() ? t.data_ptr() : nullptr; }
+
+// which activation the norm kernels can fuse
+inline int fused_act_code(ActivationType type) {
+    switch (type) {
+        case ActivationType::Identity: return NB2_ACT_NONE;
+        case ActivationType::GeLU: return NB2_ACT_GELU;
+        case ActivationType::SiLU:
+        case ActivationType::Swish: return NB2_ACT_SILU;        // swish.hpp:12-17 is x * sigmoid(x)
+        default: return -1;
+    }
+}
+
+inline c10::optional<torch::Tensor> opt(const torch::Tensor& t) {
+    return t.defined() ? c10::optional<torch::Tensor>(t) : c10::nullopt;
+}
+
+inline torch::Tensor param_like(const torch::Tensor& p, const torch::Tensor& x) {
+    if (!p.defined()) return p;
+    return p.scalar_type() == x.scalar_type() ? p.contiguous() : p.to(x.scalar_type()).contiguous();
+}
+
+}  // namespace detail
+
+// ------------------------------------------------------------------ LayerNorm (+act)
+struct LayerNormActFunction : public torch::autograd::Function<LayerNormActFunction> {
+    static torch::Tensor forward(torch::autograd::AutogradContext* ctx, torch::Tensor input,
+                                 c10::optional<torch::Tensor> weight_opt, c10::optional<torch::Tensor> bias_opt,
+                                 double eps, int64_t act) {
+        detail::require_cuda(input, "LayerNorm");
+        const torch::Tensor weight = weight_opt.value_or(torch::Tensor()), bias = bias_opt.value_or(torch::Tensor());
+        const auto D = input.size(-1);
+        auto x = input.contiguous().view({-1, D});
+        const int code = detail::dtype_code(x, "LayerNorm");
+        auto w = detail::param_like(weight, x), b = detail::param_like(bias, x);
+        const auto rows = x.size(0);
+        auto y = torch::empty_like(x);
+        auto stats = torch::empty({2, rows}, x.options().dtype(torch::kFloat32));
+        detail::check(nb2_layernorm_fwd(x.data_ptr(), detail::ptr_or_null(w), detail::ptr_or_null(b), y.data_ptr(),
+                                        stats[0].data_ptr<float>(), stats[1].data_ptr<float>(), rows, D, eps, code,
+                                        (int)act, detail::stream()),
+                      "nb2_layernorm_fwd");
+        ctx->save_for_backward({x, w, b, stats});
+        ctx->saved_data["act"] = act;
+        ctx->saved_data["weight_dtype"] = weight.defined() ? (int64_t)weight.scalar_type() : (int64_t)-1;
+        return y.view(input.sizes());
+    }
+
+    static torch::autograd::tensor_list backward(torch::autograd::AutogradContext* ctx,
+                                                 torch::autograd::tensor_list grads) {
+        auto saved = ctx->get_saved_variables();
+        auto x = saved[0], w = saved[1], b = saved[2], stats = saved[3];
+        const auto act = ctx->saved_data["act"].toInt();
+        const auto rows = x.size(0), D = x.size(1);
+        const int code = detail::dtype_code(x, "LayerNorm backward");
+        auto dy = grads[0].contiguous().view({rows, D});
+        if (dy.scalar_type() != x.scalar_type()) dy = dy.to(x.scalar_type());
+        auto dx = torch::empty_like(x);
+        torch::Tensor dw, db;
+        if (w.defined()) {
+            const auto ws = nb2_workspace_bytes(NB2_WS_NORM_BWD, rows, D, code);
+            auto partials = torch::empty({(int64_t)(ws / 4)}, x.options().dtype(torch::kFloat32));
+            int64_t n = 0;
+            detail::check(nb2_layernorm_bwd(x.data_ptr(), dy.data_ptr(), w.data_ptr(), detail::ptr_or_null(b),
+                                            stats[0].data_ptr<float>(), stats[1].data_ptr<float>(), dx.data_ptr(),
+                                            partials.data_ptr<float>(), &n, rows, D, code, (int)act, detail::stream()),
+                          "nb2_layernorm_bwd");
+            auto sums = torch::zeros({2, D}, x.options().dtype(torch::kFloat32));
+            if (rows > 0)
+                detail::check(nb2_colreduce_partials(partials.data_ptr<float>(), n, 2 * D, sums.data_ptr<float>(),
+                                                     detail::stream()),
+                              "nb2_colreduce_partials");
+            const auto wt = (torch::ScalarType)ctx->saved_data["weight_dtype"].toInt();
+            dw = sums[0].to(wt);
+            if (b.defined()) db = sums[1].to(wt);
+        } else {
+            int64_t n = 0;
+            detail::check(nb2_layernorm_bwd(x.data_ptr(), dy.data_ptr(), nullptr, nullptr, stats[0].data_ptr<float>(),
+                                            stats[1].data_ptr<float>(), dx.data_ptr(), nullptr, &n, rows, D, code,
+                                            (int)act, detail::stream()),
+                          "nb2_layernorm_bwd");
+        }
+        return {dx.view(grads[0].sizes()), dw, db, torch::Tensor(), torch::Tensor()};
+    }
+};
+
+struct LayerNormOptions {
+    double eps{1e-5};                      // classic.hpp:54-57
+    bool elementwise_affine{true};
+    ActivationType activation{ActivationType::Identity};   // fused behind the norm (the layer.forward + apply seam, core.hpp:1927-1934)
+};
+
+class LayerNormImpl : public torch::nn::Module {
+public:
+    LayerNormImpl(std::int64_t normalized_dim, LayerNormOptions options = {})
+        : dim_(normalized_dim), options_(options) {
+        if (dim_ <= 0) throw std::invalid_argument("LayerNorm requires a positive normalized dimension.");
+        if (detail::fused_act_code(options_.activation) < 0)
+            throw std::invalid_argument("LayerNorm can fuse Identity, GeLU, SiLU or Swish only.");
+        if (options_.elementwise_affine) {
+            weight = register_parameter("weight", torch::ones({dim_}));     // same names as torch::nn::LayerNorm
+            bias = register_parameter("bias", torch::zeros({dim_}));
+        }
+    }
+
+    torch::Tensor forward(torch::Tensor input) {
+        if (!input.defined()) throw std::invalid_argument("LayerNorm requires a defined input tensor.");
+        if (input.dim() == 0 || input.size(-1) != dim_)
+            throw std::invalid_argument("LayerNorm expected last dimension " + std::to_string(dim_) + ".");
+        if (at::autocast::is_autocast_enabled(at::kCUDA) && input.scalar_type() != torch::kFloat32)
+            input = input.to(torch::kFloat32);                            // libtorch's autocast policy for layer_norm
+        return LayerNormActFunction::apply(std::move(input), detail::opt(weight), detail::opt(bias), options_.eps,
+                                           (int64_t)detail::fused_act_code(options_.activation));
+    }
+
+    torch::Tensor weight, bias;
+
+private:
+    std::int64_t dim_{};
+    LayerNormOptions options_{};
+};
+TORCH_MODULE(LayerNorm);
+
+// -------------------------------------------------------------------- RMSNorm (+act)
+struct RMSNormActFunction : public torch::autograd::Function<RMSNormActFunction> {
+    static torch::Tensor forward(torch::autograd::AutogradContext* ctx, torch::Tensor input,
+                                 c10::optional<torch::Tensor> weight_opt, double eps, int64_t act) {
+        detail::require_cuda(input, "RMSNorm");
+        const torch::Tensor weight = weight_opt.value_or(torch::Tensor());
+        const auto D = input.size(-1);
+        auto x = input.contiguous().view({-1, D});
+        const int code = detail::dtype_code(x, "RMSNorm");
+        auto w = detail::param_like(weight, x);
+        const auto rows = x.size(0);
+        auto y = torch::empty_like(x);
+        auto rstd = torch::empty({rows}, x.options().dtype(torch::kFloat32));
+        detail::check(nb2_rmsnorm_fwd(x.data_ptr(), detail::ptr_or_null(w), y.data_ptr(), rstd.data_ptr<float>(), rows,
+                                      D, eps, code, (int)act, detail::stream()),
+                      "nb2_rmsnorm_fwd");
+        ctx->save_for_backward({x, w, rstd});
+        ctx->saved_data["act"] = act;
+        ctx->saved_data["weight_dtype"] = weight.defined() ? (int64_t)weight.scalar_type() : (int64_t)-1;
+        return y.view(input.sizes());
+    }
+
+    static torch::autograd::tensor_list backward(torch::autograd::AutogradContext* ctx,
+                                                 torch::autograd::tensor_list grads) {
+        auto saved = ctx->get_saved_variables();
+        auto x = saved[0], w = saved[1], rstd = saved[2];
+        const auto act = ctx->saved_data["act"].toInt();
+        const auto rows = x.size(0), D = x.size(1);
+        const int code = detail::dtype_code(x, "RMSNorm backward");
+        auto dy = grads[0].contiguous().view({rows, D});
+        if (dy.scalar_type() != x.scalar_type()) dy = dy.to(x.scalar_type());
+        auto dx = torch::empty_like(x);
+        torch::Tensor dw;
+        int64_t n = 0;
+        if (w.defined()) {
+            const auto ws = nb2_workspace_bytes(NB2_WS_NORM_BWD, rows, D, code);
+            auto partials = torch::empty({(int64_t)(ws / 4)}, x.options().dtype(torch::kFloat32));
+            detail::check(nb2_rmsnorm_bwd(x.data_ptr(), dy.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(),
+                                          dx.data_ptr(), partials.data_ptr<float>(), &n, rows, D, code, (int)act,
+                                          detail::stream()),
+                          "nb2_rmsnorm_bwd");
+            auto sums = torch::zeros({D}, x.options().dtype(torch::kFloat32));
+            if (rows > 0)
+                detail::check(nb2_colreduce_partials(partials.data_ptr<float>(), n, D, sums.data_ptr<float>(),
+                                                     detail::stream()),
+                              "nb2_colreduce_partials");
+            dw = sums.to((torch::ScalarType)ctx->saved_data["weight_dtype"].toInt());
+        } else {
+            detail::check(nb2_rmsnorm_bwd(x.data_ptr(), dy.data_ptr(), nullptr, rstd.data_ptr<float>(), dx.data_ptr(),
+                                          nullptr, &n, rows, D, code, (int)act, detail::stream()),
+                          "nb2_rmsnorm_bwd");
+        }
+        return {dx.view(grads[0].sizes()), dw, torch::Tensor(), torch::Tensor()};
+    }
+};
+
+struct RMSNormOptions {
+    double eps{1e-6};                      // mamba.hpp:25-28
+    bool learnable{true};
+    ActivationType activation{ActivationType::Identity};
+};
+
+class RMSNormImpl : public torch::nn::Module {
+public:
+    RMSNormImpl(std::int64_t embed_dim, RMSNormOptions options) : embed_dim_(embed_dim), options_(options) {
+        if (embed_dim_ <= 0) throw std::invalid_argument("RMSNorm requires a positive embedding dimension.");
+        if (detail::fused_act_code(options_.activation) < 0)
+            throw std::invalid_argument("RMSNorm can fuse Identity, GeLU, SiLU or Swish only.");
+        if (options_.learnable) weight_ = register_parameter("weight", torch::ones({embed_dim_}));
+    }
+
+    torch::Tensor forward(torch::Tensor input) {
+        if (!input.defined()) throw std::invalid_argument("RMSNorm requires a defined input tensor.");
+        if (input.dim() == 0) throw std::invalid_argument("RMSNorm expects a tensor with at least one dimension.");
+        if (input.size(-1) != embed_dim_)
+            throw std::invalid_argument("RMSNorm expected last dimension " + std::to_string(embed_dim_) + ".");
+        return RMSNormActFunction::apply(std::move(input), detail::opt(weight_), options_.eps,
+                                         (int64_t)detail::fused_act_code(options_.activation));
+    }
+
+private:
+    std::int64_t embed_dim_{};
+    RMSNormOptions options_{};
+    torch::Tensor weight_{};
+};
+TORCH_MODULE(RMSNorm);
+
+// ------------------------------------------------------------------------ activations
+struct ActivationFunction : public torch::autograd::Function<ActivationFunction> {
+    static torch::Tensor forward(torch::autograd::AutogradContext* ctx, torch::Tensor input, int64_t act) {
+        detail::require_cuda(input, "activation");
+        auto x = input.contiguous();
+        auto y = torch::empty_like(x);
+        detail::check(nb2_act_fwd(x.data_ptr(), y.data_ptr(), x.numel(), detail::dtype_code(x, "activation"), (int)act,
+                                  detail::stream()),
+                      "nb2_act_fwd");
+        ctx->save_for_backward({x});
+        ctx->saved_data["act"] = act;
+        return y;
+    }
+    static torch::autograd::tensor_list backward(torch::autograd::AutogradContext* ctx,
+                                                 torch::autograd::tensor_list grads) {
+        auto x = ctx->get_saved_variables()[0];
+        auto dy = grads[0].contiguous();
+        auto dx = torch::empty_like(x);
+        detail::check(nb2_act_bwd(x.data_ptr(), dy.data_ptr(), dx.data_ptr(), x.numel(),
+                                  detail::dtype_code(x, "activation backward"), (int)ctx->saved_data["act"].toInt(),
+                                  detail::stream()),
+                      "nb2_act_bwd");
+        return {dx, torch::Tensor()};
+    }
+};
+
+// out = silu(a) * b on two [.., H] operands whose rows may be strided (unit column stride)
+struct SiluGateFunction : public torch::autograd::Function<SiluGateFunction> {
+    static torch::Tensor forward(torch::autograd::AutogradContext* ctx, torch::Tensor a, torch::Tensor b) {
+        detail::require_cuda(a, "SiLU gate");
+        if (a.dim() != 2 || b.dim() != 2 || a.sizes() != b.sizes() || a.stride(1) != 1 || b.stride(1) != 1)
+            throw std::invalid_argument("SiLU gate expects two [rows, H] operands with unit column stride.");
+        const auto rows = a.size(0), H = a.size(1);
+        auto out = torch::empty({rows, H}, a.options());
+        detail::check(nb2_silu_gate_fwd(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(), H, rows, H,
+                                        detail::dtype_code(a, "SiLU gate"), detail::stream()),
+                      "nb2_silu_gate_fwd");
+        ctx->save_for_backward({a, b});
+        return out;
+    }
+    static torch::autograd::tensor_list backward(torch::autograd::AutogradContext* ctx,
+                                                 torch::autograd::tensor_list grads) {
+        auto saved = ctx->get_saved_variables();
+        auto a = saved[0], b = saved[1];
+        const auto rows = a.size(0), H = a.size(1);
+        auto dy = grads[0].contiguous();
+        auto da = torch::empty({rows, H}, a.options()), db = torch::empty({rows, H}, a.options());
+        detail::check(nb2_silu_gate_bwd(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), dy.data_ptr(), H,
+                                        da.data_ptr(), H, db.data_ptr(), H, rows, H,
+                                        detail::dtype_code(a, "SiLU gate backward"), detail::stream()),
+                      "nb2_silu_gate_bwd");
+        return {da, db};
+    }
+};
+
+// Mamba's gated feed forward: up * silu(gate) (mamba.hpp:443-446)
+inline torch::Tensor silu_gate(const torch::Tensor& gate, const torch::Tensor& up) {
+    const auto H = gate.size(-1);
+    auto out = SiluGateFunction::apply(gate.contiguous().view({-1, H}), up.contiguous().view({-1, H}));
+    return out.view(gate.sizes());
+}
+
+// Nott::Activation::Details::apply for the activations on this path.  GeLU, SiLU, Swish and
+// SwiGLU run the sm_100a kernels; Identity returns its input; every other type is not part of
+// this path and raises (inside Nott, keep dispatching those to the reference's own functors).
+inline torch::Tensor apply(ActivationType type, torch::Tensor input) {
+    switch (type) {
+        case ActivationType::Identity: return input;
+        case ActivationType::GeLU: return ActivationFunction::apply(std::move(input), (int64_t)NB2_ACT_GELU);
+        case ActivationType::SiLU:
+        case ActivationType::Swish: return ActivationFunction::apply(std::move(input), (int64_t)NB2_ACT_SILU);
+        case ActivationType::SwiGLU: {
+            // swiglu.hpp:18-23: chunk(2, -1), silu(first) * second; scalars and odd widths follow the reference
+            if (input.dim() == 0) return input;
+            const auto last = input.size(-1);
+            if (last < 2) return input;
+            if (last % 2 != 0) throw std::invalid_argument("SwiGLU expects an even last dimension on the fused path.");
+            auto flat = input.contiguous().view({-1, last});
+            const auto H = last / 2;
+            auto out = SiluGateFunction::apply(flat.narrow(1, 0, H), flat.narrow(1, H, H));
+            auto shape = input.sizes().vec();
+            shape.back() = H;
+            return out.view(shape);
+        }
+        default:
+            throw std::invalid_argument("Nott::B200::apply covers Identity, GeLU, SiLU, Swish and SwiGLU.");
+    }
+}
+
+// -------------------------------------------------------------------------- embedding
+struct EmbeddingFunction : public torch::autograd::Function<EmbeddingFunction> {
+    static torch::Tensor forward(torch::autograd::AutogradContext* ctx, torch::Tensor weight, torch::Tensor ids) {
+        detail::require_cuda(weight, "Embedding");
+        if (ids.scalar_type() != torch::kInt64 && ids.scalar_type() != torch::kInt32)
+            throw std::invalid_argument("Embedding expects int32 or int64 token ids.");
+        auto w = weight.contiguous();
+        auto flat = ids.contiguous().view({-1});
+        const auto vocab = w.size(0), D = w.size(1);
+        auto out = torch::empty({flat.size(0), D}, w.options());
+        detail::check(nb2_embedding_fwd(w.data_ptr(), flat.data_ptr(), out.data_ptr(), flat.size(0), vocab, D,
+                                        detail::dtype_code(w, "Embedding"),
+                                        flat.scalar_type() == torch::kInt32 ? NB2_I32 : NB2_I64, nullptr,
+                                        detail::stream()),
+                      "nb2_embedding_fwd");
+        ctx->save_for_backward({flat});
+        ctx->saved_data["vocab"] = vocab;
+        auto shape = ids.sizes().vec();
+        shape.push_back(D);
+        return out.view(shape);
+    }
+    static torch::autograd::tensor_list backward(torch::autograd::AutogradContext* ctx,
+                                                 torch::autograd::tensor_list grads) {
+        auto flat = ctx->get_saved_variables()[0];
+        const auto vocab = ctx->saved_data["vocab"].toInt();
+        const auto D = grads[0].size(-1);
+        auto dout = grads[0].contiguous().view({-1, D});
+        const int code = detail::dtype_code(dout, "Embedding backward");
+        auto dtable = torch::empty({vocab, D}, dout.options());
+        const auto ws = nb2_workspace_bytes(NB2_WS_EMBEDDING_BWD, flat.size(0), vocab, code);
+        auto scratch = torch::empty({(int64_t)ws}, dout.options().dtype(torch::kUInt8));
+        detail::check(nb2_embedding_bwd(dout.data_ptr(), flat.data_ptr(), dtable.data_ptr(), flat.size(0), vocab, D, code,
+                                        flat.scalar_type() == torch::kInt32 ? NB2_I32 : NB2_I64, scratch.data_ptr(), ws,
+                                        detail::stream()),
+                      "nb2_embedding_bwd");
+        return {dtable, torch::Tensor()};
+    }
+};
+
+class EmbeddingImpl : public torch::nn::Module {
+public:
+    EmbeddingImpl(std::int64_t num_embeddings, std::int64_t embedding_dim) {
+        if (num_embeddings <= 0 || embedding_dim <= 0)
+            throw std::invalid_argument("Embedding requires positive vocabulary and embedding sizes.");
+        weight = register_parameter("weight", torch::randn({num_embeddings, embedding_dim}));   // N(0,1), as torch::nn::Embedding
+    }
+    torch::Tensor forward(const torch::Tensor& ids) { return EmbeddingFunction::apply(weight, ids); }
+    torch::Tensor weight;
+};
+TORCH_MODULE(Embedding);
+
+// ----------------------------------------------------------------------------- rotary
+// cos/sin of angle(s, i) = pos[s] * theta^(-2i/hd), built once and shared by q, k and the backward
+class RotaryTable {
+public:
+    RotaryTable(std::int64_t seq_len, std::int64_t head_dim, double theta, const torch::Device& device,
+                const torch::Tensor& positions = {})
+        : seq_len_(seq_len), head_dim_(head_dim) {
+        if (head_dim <= 0 || head_dim % 2 != 0) throw std::invalid_argument("Rotary embedding requires an even head dimension.");
+        table_ = torch::empty({seq_len, head_dim / 2, 2}, torch::TensorOptions().dtype(torch::kFloat32).device(device));
+        torch::Tensor pos;
+        if (positions.defined()) pos = positions.to(device, torch::kInt32).contiguous();
+        detail::check(nb2_rope_table(table_.data_ptr<float>(), pos.defined() ? pos.data_ptr<int32_t>() : nullptr, seq_len,
+                                     head_dim, theta, detail::stream()),
+                      "nb2_rope_table");
+    }
+    const torch::Tensor& table() const { return table_; }
+    std::int64_t seq_len() const { return seq_len_; }
+    std::int64_t head_dim() const { return head_dim_; }
+
+private:
+    std::int64_t seq_len_, head_dim_;
+    torch::Tensor table_;
+};
+
+struct RotaryFunction : public torch::autograd::Function<RotaryFunction> {
+    static torch::Tensor forward(torch::autograd::AutogradContext* ctx, torch::Tensor x, torch::Tensor table) {
+        detail::require_cuda(x, "rotary");
+        if (x.dim() != 4 || x.size(1) != table.size(0) || x.size(3) != 2 * table.size(1))
+            throw std::invalid_argument("rotary expects x[B, S, H, hd] and a table built for (S, hd).");
+        auto xc = x.contiguous();
+        auto out = torch::empty_like(xc);
+        detail::check(nb2_rope_apply(xc.data_ptr(), table.data_ptr<float>(), out.data_ptr(), xc.size(0), xc.size(1),
+                                     xc.size(2), xc.size(3), detail::dtype_code(xc, "rotary"), 0, detail::stream()),
+                      "nb2_rope_apply");
+        ctx->save_for_backward({table});
+        return out;
+    }
+    static torch::autograd::tensor_list backward(torch::autograd::AutogradContext* ctx,
+                                                 torch::autograd::tensor_list grads) {
+        auto table = ctx->get_saved_variables()[0];
+        auto dy = grads[0].contiguous();
+        auto dx = torch::empty_like(dy);
+        detail::check(nb2_rope_apply(dy.data_ptr(), table.data_ptr<float>(), dx.data_ptr(), dy.size(0), dy.size(1),
+                                     dy.size(2), dy.size(3), detail::dtype_code(dy, "rotary backward"), 1,
+                                     detail::stream()),
+                      "nb2_rope_apply");
+        return {dx, torch::Tensor()};
+    }
+};
+
+inline torch::Tensor rotary(const torch::Tensor& x, const RotaryTable& table) {
+    return RotaryFunction::apply(x, table.table());
+}
+
+}  // namespace Nott::B200
