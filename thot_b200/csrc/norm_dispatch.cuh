@@ -66,18 +66,15 @@ static inline int64_t norm_bwd_generic_parts(int64_t rows) {
 
 // ---- bulk-async ring kernels: exact-fit shapes only (D == TPR * VPT * EPV), parameters present.
 struct TmaShape { int tpr, vpt; };
-static inline TmaShape tma_bwd_shape_fwddecl(int64_t D, int epv);
-// forward holds 32 elements per thread and row (24 for the 768-wide rows)
+// Both directions hold 4 (fp32) or 2..4 (bf16) 16-byte vectors per thread and row.
+// Forward: 4 vectors for either type (16 fp32 / 32 bf16 elements), measured best on B200.
 static inline TmaShape tma_fwd_shape(int64_t D, int epv) {
-    if (const char* e = getenv("NB2_FWD_EPT")) { if (atoi(e) == 16) return tma_bwd_shape_fwddecl(D, epv); }
-    if (D == 768) return {32, 24 / epv};
+    if (D == 768) return epv == 4 ? TmaShape{64, 3} : TmaShape{32, 3};
     for (int tpr = 32; tpr <= 512; tpr *= 2)
-        if (D == (int64_t)tpr * 32) return {tpr, 32 / epv};
+        if (D == (int64_t)tpr * 4 * epv) return {tpr, 4};
     return {0, 0};
 }
-// backward holds 16 (its accumulators take the registers)
-static inline TmaShape tma_bwd_shape(int64_t D, int epv);
-static inline TmaShape tma_bwd_shape_fwddecl(int64_t D, int epv) { return tma_bwd_shape(D, epv); }
+// Backward: 16 elements per thread (its dgamma/dbeta accumulators take the registers).
 static inline TmaShape tma_bwd_shape(int64_t D, int epv) {
     if (D == 768) return epv == 4 ? TmaShape{64, 3} : TmaShape{32, 3};
     for (int tpr = 32; tpr <= 512; tpr *= 2)
@@ -85,7 +82,7 @@ static inline TmaShape tma_bwd_shape(int64_t D, int epv) {
     return {0, 0};
 }
 // ring depth: every row group gets `stages` row slots; one "layer" (a slot of every
-// group) is 32-64 KiB, and the rings may take what 200 KiB leave after the parameters
+// group) is 16-64 KiB
 struct TmaTiling { int stages; size_t smem; };
 static inline TmaTiling tma_tiling(int64_t D, int elt, int tpr, int nsrc) {
     const int rpc = kTmaThreads / tpr;
@@ -93,9 +90,9 @@ static inline TmaTiling tma_tiling(int64_t D, int elt, int tpr, int nsrc) {
     const size_t fixed = kTmaHeaderBytes + 2 * (size_t)tma_param_bytes((int)D, elt);
     TmaTiling t;
     t.stages = 2;
-    int max_stages = 4;
-    if (const char* e = getenv("NB2_TMA_STAGES")) max_stages = atoi(e);
-    while (t.stages < max_stages && fixed + (size_t)(t.stages + 1) * layer <= 216 * 1024) ++t.stages;
+    // two slots per group already cover the latency (deeper rings measured the same); a third
+    // is taken only while the whole allocation stays small
+    if (fixed + 3 * layer <= 100 * 1024) t.stages = 3;
     t.smem = fixed + t.stages * layer;
     return t;
 }
@@ -106,16 +103,19 @@ static inline int64_t tma_grid(int64_t rows, int tpr, int sms) {
 }
 
 // Should this (norm, direction, dtype, D) use the ring kernels?  Measured on B200 over
-// D in {768 .. 8192}, 2^17 rows: LayerNorm (two statistics passes, erf epilogue) gains
-// from the ring in backward at every width and in forward except for fp32 rows above
-// 8 KiB; RMSNorm is lean enough that plain register-row loads already run at 92-96% of
-// the copy rate, and only its fp32 forward at D >= 2048 gains.
+// D in {768 .. 8192}, 2^17 rows, both families on the same inputs:
+//   LayerNorm backward: ring at every width (fp32 6.2-6.6 TB/s vs 3.9-4.5 register-row).
+//   LayerNorm forward : ring for bf16 and for fp32 rows up to 8 KiB; wider fp32 rows are
+//                       better served by 256-512 threads loading straight into registers.
+//   RMSNorm is lean enough that register-row loads already run at 92-96% of the copy
+//   rate; the ring only wins for rows of 16 KiB and more, and for the bf16 backward.
 static inline bool tma_preferred(bool rms, int64_t D, int elt, bool bwd) {
     const int ov = norm_path_override();
     if (ov == 1) return false;
     if (ov == 2) return true;
-    if (!rms) return bwd ? true : (elt == 2 || D * elt <= 8192);
-    return !bwd && elt == 4 && D >= 2048;
+    const int64_t row_bytes = D * elt;
+    if (!rms) return bwd ? true : (elt == 2 || row_bytes <= 8192);
+    return bwd ? (elt == 2 || row_bytes >= 16384) : (elt == 4 && row_bytes >= 16384);
 }
 // does the ring of this shape fit the SM's shared memory at all
 static inline bool tma_fits(int64_t D, int elt, int tpr, int nsrc) {

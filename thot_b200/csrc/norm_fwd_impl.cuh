@@ -28,24 +28,16 @@ static int launch_fwd_tma(const NormArgs& a) {
 template <typename T, int ACT, bool RMS>
 static int launch_fwd_tma_shape(const NormArgs& a, TmaShape s) {
     constexpr int EPV = VecTraits<T>::EPV;
-    constexpr int V32 = 32 / EPV, V24 = 24 / EPV, V16 = 16 / EPV;
-    if (s.vpt == V24 && s.tpr == 32) return launch_fwd_tma<T, 32, V24, ACT, RMS>(a);
-    if (s.vpt == V16) {           // experiment: 16 elements per thread
-        switch (s.tpr) {
-            case 32:  return launch_fwd_tma<T, 32, V16, ACT, RMS>(a);
-            case 64:  return launch_fwd_tma<T, 64, V16, ACT, RMS>(a);
-            case 128: return launch_fwd_tma<T, 128, V16, ACT, RMS>(a);
-            case 256: return launch_fwd_tma<T, 256, V16, ACT, RMS>(a);
-            case 512: return launch_fwd_tma<T, 512, V16, ACT, RMS>(a);
-            default: break;
-        }
+    if (s.vpt == 3) {
+        if constexpr (EPV == 4) return launch_fwd_tma<T, 64, 3, ACT, RMS>(a);
+        else return launch_fwd_tma<T, 32, 3, ACT, RMS>(a);
     }
     switch (s.tpr) {
-        case 32:  return launch_fwd_tma<T, 32, V32, ACT, RMS>(a);
-        case 64:  return launch_fwd_tma<T, 64, V32, ACT, RMS>(a);
-        case 128: return launch_fwd_tma<T, 128, V32, ACT, RMS>(a);
-        case 256: return launch_fwd_tma<T, 256, V32, ACT, RMS>(a);
-        case 512: return launch_fwd_tma<T, 512, V32, ACT, RMS>(a);
+        case 32:  return launch_fwd_tma<T, 32, 4, ACT, RMS>(a);
+        case 64:  return launch_fwd_tma<T, 64, 4, ACT, RMS>(a);
+        case 128: return launch_fwd_tma<T, 128, 4, ACT, RMS>(a);
+        case 256: return launch_fwd_tma<T, 256, 4, ACT, RMS>(a);
+        case 512: return launch_fwd_tma<T, 512, 4, ACT, RMS>(a);
         default: break;
     }
     set_error("norm fwd: no ring kernel for threads-per-row %d", s.tpr);

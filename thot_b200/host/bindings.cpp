@@ -28,6 +28,7 @@ PYBIND11_MODULE(_nott_b200_host, m) {
     m.def("layernorm_module_step", [](int64_t D, double eps, bool affine, int64_t act_type, torch::Tensor x, torch::Tensor dy) {
         nb::LayerNormOptions opt;
         opt.eps = eps; opt.elementwise_affine = affine; opt.activation = static_cast<nb::ActivationType>(act_type);
+        pybind11::gil_scoped_release no_gil;     // backward() runs the autograd engine
         nb::LayerNorm mod(D, opt);
         mod->to(x.device(), x.scalar_type());
         auto xin = x.clone().requires_grad_(true);
@@ -41,6 +42,7 @@ PYBIND11_MODULE(_nott_b200_host, m) {
     m.def("rmsnorm_module_step", [](int64_t D, double eps, bool learnable, int64_t act_type, torch::Tensor x, torch::Tensor dy) {
         nb::RMSNormOptions opt;
         opt.eps = eps; opt.learnable = learnable; opt.activation = static_cast<nb::ActivationType>(act_type);
+        pybind11::gil_scoped_release no_gil;
         nb::RMSNorm mod(D, opt);
         mod->to(x.device(), x.scalar_type());
         auto xin = x.clone().requires_grad_(true);
