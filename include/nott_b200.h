@@ -128,6 +128,31 @@ int nb2_layernorm_bwd(const void* x, const void* dy, const void* gamma, const vo
                       int64_t rows, int64_t D,
                       int dtype, int act, void* stream);
 
+/*
+ * The same backward for callers that cannot allocate device memory (no
+ * counterpart in the reference, which always allocates through libtorch).
+ * A host that runs under a frozen memory plan, or that is only ever handed its
+ * input and output buffers, has nowhere to get the partials workspace from; here
+ * that scratch is a fixed 4.6 MiB array inside the library image (present on
+ * every GPU that loads the library, for the life of the process).  The call
+ * writes dx and the finished [2, D] fp32 gradients (dgamma row, dbeta row) and
+ * performs no cudaMalloc/cudaFree or any other allocating call.
+ *   - Limit: the shape must satisfy
+ *     nb2_workspace_bytes(NB2_WS_NORM_BWD, rows, D, dtype) <= 296 * 2 * 2048 * 4 + 256,
+ *     which holds for D <= 2048 at any row count (and for wider rows when there
+ *     are few of them); larger shapes return NB2_ERR_WORKSPACE.
+ *   - gamma must be non-NULL.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress); make that first call outside any stream capture.
+ *   - All calls share the one array and it keeps the previous call's contents:
+ *     two calls that overlap on the GPU (different streams) race on it.
+ */
+int nb2_layernorm_bwd_static(const void* x, const void* dy, const void* gamma, const void* beta,
+                             const float* mean, const float* rstd,
+                             void* dx, float* dgamma_dbeta,
+                             int64_t rows, int64_t D,
+                             int dtype, int act, void* stream);
+
 /* ------------------------------------------------------------------ *
  * RMSNorm (+ fused GELU / SiLU)
  * Replaces Nott's RMSNormImpl::forward

@@ -28,6 +28,7 @@ _SIGNATURES = {
     "nb2_workspace_bytes": (c_size_t, [c_int, c_int64, c_int64, c_int]),
     "nb2_layernorm_fwd": (c_int, [c_void_p] * 6 + [c_int64, c_int64, c_double, c_int, c_int, c_void_p]),
     "nb2_layernorm_bwd": (c_int, [c_void_p] * 8 + [POINTER(c_int64), c_int64, c_int64, c_int, c_int, c_void_p]),
+    "nb2_layernorm_bwd_static": (c_int, [c_void_p] * 8 + [c_int64, c_int64, c_int, c_int, c_void_p]),
     "nb2_rmsnorm_fwd": (c_int, [c_void_p] * 4 + [c_int64, c_int64, c_double, c_int, c_int, c_void_p]),
     "nb2_rmsnorm_bwd": (c_int, [c_void_p] * 6 + [POINTER(c_int64), c_int64, c_int64, c_int, c_int, c_void_p]),
     "nb2_colreduce_partials": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
