@@ -210,6 +210,74 @@ def run_reference_arm(args, w: Workload, rank: int, world: int):
     print(json.dumps(line))
 
 
+# ---------------------------------------------------------------- op suite
+def run_suite(args):
+    """`--suite`: every other kernel of the path at BASELINE's configs[2]/[3] sizes, one launch type per
+    entry, CUDA-event timed, algorithmic bytes / time against the measured HBM peak.  One JSON line."""
+    from thot_b200 import abi
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    peaks_file = ROOT / "MEASURED_PEAKS.json"
+    peak = float(json.loads(peaks_file.read_text())["hbm_gbs"]) if peaks_file.exists() else FALLBACK_HBM_GBS
+    results = []
+
+    def timed(name, fn, nbytes, iters=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        sec = e0.elapsed_time(e1) / iters / 1e3
+        results.append({"op": name, "us": sec * 1e6, "algorithmic_bytes": nbytes, "achieved_gbs": nbytes / sec / 1e9,
+                        "frac_of_measured_peak": nbytes / sec / 1e9 / peak, "frac_of_nominal_8000": nbytes / sec / 8e12})
+
+    g = torch.Generator(device=dev).manual_seed(7)
+    bf = torch.bfloat16
+    # configs[2]: RMSNorm bf16 x[16,4096,4096], then out = silu(a) * b for a, b [65536, 11008]
+    rows, D = 65536, 4096
+    x = torch.randn(rows, D, device=dev, generator=g).to(bf); dy = torch.randn(rows, D, device=dev, generator=g).to(bf)
+    w = (1 + 0.02 * torch.randn(D, device=dev, generator=g)).to(bf)
+    y, rstd = abi.rmsnorm_fwd(x, w, 1e-6)
+    timed("rmsnorm_fwd bf16 [65536,4096]", lambda: abi.rmsnorm_fwd(x, w, 1e-6), 2 * rows * D * 2 + 4 * rows)
+    timed("rmsnorm_bwd+reduce bf16 [65536,4096]", lambda: abi.rmsnorm_bwd(x, dy, w, rstd), 3 * rows * D * 2 + 4 * rows)
+    del x, dy, y
+    H = 11008
+    a = torch.randn(rows, H, device=dev, generator=g).to(bf); b = torch.randn(rows, H, device=dev, generator=g).to(bf)
+    d = torch.randn(rows, H, device=dev, generator=g).to(bf)
+    timed("silu_gate_fwd bf16 [65536,11008]", lambda: abi.silu_gate_fwd(a, b), 3 * rows * H * 2, iters=10)
+    da, db = torch.empty_like(a), torch.empty_like(a)
+    timed("silu_gate_bwd bf16 [65536,11008]", lambda: abi.silu_gate_bwd(a, b, d, da, db), 5 * rows * H * 2, iters=10)
+    ab = torch.cat([a[:16384], b[:16384]], dim=1)              # SwiGLU form: halves of one [rows, 2H] tensor
+    timed("silu_gate_fwd bf16 swiglu-strided [16384,2x11008]", lambda: abi.silu_gate_fwd(ab[:, :H], ab[:, H:]), 3 * 16384 * H * 2)
+    del a, b, d, da, db, ab
+    # configs[3]: gather table[32000,4096] bf16, ids int32 [32,2048]; rotary q,k [32,2048,32,128] bf16
+    table = (0.02 * torch.randn(32000, 4096, device=dev, generator=g)).to(bf)
+    ids = torch.randint(0, 32000, (32, 2048), device=dev, generator=g, dtype=torch.int32)
+    timed("embedding_fwd bf16 65536 tokens x 4096", lambda: abi.embedding_fwd(table, ids), 2 * 65536 * 4096 * 2 + 65536 * 4)
+    dout = torch.randn(65536, 4096, device=dev, generator=g).to(bf)
+    timed("embedding_bwd bf16 (zero table + sort + segmented sum)", lambda: abi.embedding_bwd(dout, ids, 32000),
+          65536 * 4096 * 2 + 32000 * 4096 * 2 + 65536 * 4, iters=10)
+    del table, dout
+    q = torch.randn(32, 2048, 32, 128, device=dev, generator=g).to(bf)
+    cs = abi.rope_table(2048, 128)
+    timed("rope_apply bf16 [32,2048,32,128] (one of q, k)", lambda: abi.rope_apply(q, cs), 2 * q.numel() * 2)
+    timed("rope_apply inverse (backward)", lambda: abi.rope_apply(q, cs, inverse=True), 2 * q.numel() * 2)
+    del q
+    n = 32 * 1024 * 1024
+    xf = torch.randn(n, device=dev, generator=g); df = torch.randn(n, device=dev, generator=g)
+    for nm, code in (("gelu", abi.ACT_GELU), ("silu", abi.ACT_SILU)):
+        timed(f"{nm}_fwd fp32 32Mi", lambda: abi.act_fwd(xf, code), 2 * n * 4)
+        timed(f"{nm}_bwd fp32 32Mi", lambda: abi.act_bwd(xf, df, code), 3 * n * 4)
+    abi.device_status()
+    print(json.dumps({"suite": results, "peak_gbs": peak, "unit": "GB/s", "data": "synthetic",
+                      "note": "timings include torch's output allocation from its caching allocator"}))
+
+
 # ------------------------------------------------------------------ our arm
 def main():
     ap = argparse.ArgumentParser()
@@ -220,6 +288,7 @@ def main():
     ap.add_argument("--workload", default="cfg2")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--suite", action="store_true", help="time the other kernels of the path (1 GPU) instead of the step")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -230,6 +299,10 @@ def main():
 
     if args.impl == "reference":
         run_reference_arm(args, w, rank, world)
+        return
+    if args.suite:
+        if rank == 0:
+            run_suite(args)
         return
 
     import torch.distributed as dist
