@@ -85,21 +85,14 @@ __device__ __forceinline__ uint64_t policy_evict_first() {
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
     return p;
 }
-// all threads of a row group (TPR of them) agree on `ok`
+// Has any thread of this row group given up waiting?  The flag is per group and only raised
+// inside a wait, i.e. before the row reduction's barrier, so right after that reduction every
+// thread of the group reads the same value (one warp: made uniform with a vote).
 template <int TPR>
-__device__ __forceinline__ bool group_all(bool ok, int barrier_id) {
-    if constexpr (TPR <= 32) {
-        return __all_sync(0xffffffffu, ok);
-    } else {
-        uint32_t r;
-        asm volatile(
-            "{\n\t.reg .pred p, q;\n\t"
-            "setp.ne.u32 q, %1, 0;\n\t"
-            "bar.red.and.pred p, %2, %3, q;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(r) : "r"((uint32_t)ok), "r"(barrier_id), "r"(TPR) : "memory");
-        return r != 0;
-    }
+__device__ __forceinline__ bool group_gave_up(volatile int* abort_flag) {
+    const bool gave_up = *abort_flag != 0;
+    if constexpr (TPR <= 32) return __any_sync(0xffffffffu, gave_up);
+    else return gave_up;
 }
 
 // Every row group owns a private ring of `stages` row slots.  Its leader thread
@@ -118,7 +111,7 @@ struct TmaSmem {
     uint64_t* full;               // [kTmaMaxGroups][kTmaMaxStages]
     float* red_a;                 // [64]
     float* red_b;                 // [64]
-    volatile int* abort_flag;
+    volatile int* abort_flag;     // [kTmaMaxGroups]: one per row group, raised only by that group's threads
     const uint4* gamma;
     const uint4* beta;
     uint8_t* ring;
@@ -141,7 +134,7 @@ __device__ __forceinline__ void tma_setup(const TmaSmem& sm, int groups, int sta
     if (threadIdx.x == 0) {
         for (int g = 0; g < groups; ++g)
             for (int s = 0; s < stages; ++s) mbar_init(&sm.full[g * kTmaMaxStages + s], 1);
-        *sm.abort_flag = 0;
+        for (int g = 0; g < kTmaMaxGroups; ++g) sm.abort_flag[g] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -181,6 +174,7 @@ norm_fwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const 
     const int tr = threadIdx.x % TPR;
     const float inv_d = 1.0f / (float)D;
     uint64_t* full = sm.full + grp * kTmaMaxStages;
+    volatile int* gave_up = sm.abort_flag + grp;
     uint8_t* ring = sm.ring + (size_t)grp * stages * row_bytes;
     const uint8_t* src = reinterpret_cast<const uint8_t*>(x);
     const int64_t first = (int64_t)blockIdx.x * RPC + grp;
@@ -197,9 +191,10 @@ norm_fwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const 
     int i = 0;
     for (int64_t row = first; row < rows; row += stride, ++i) {
         const int s = i % stages;
-        bool ok = mbar_wait_bounded(&full[s], (uint32_t)((i / stages) & 1), sm.abort_flag, kStatusFullTimeout, status);
-        ok = group_all<TPR>(ok, grp + 1);
-        if (!ok) break;
+        // A wait that gives up raises the group's abort flag.  Leaving here would strand the rest of
+        // the group at the next barrier, so the thread carries on with whatever the slot holds and
+        // the whole group leaves together after the reduction below.
+        mbar_wait_bounded(&full[s], (uint32_t)((i / stages) & 1), gave_up, kStatusFullTimeout, status);
         const uint4* srow = reinterpret_cast<const uint4*>(ring + (size_t)s * row_bytes);
         float v[VPT][EPV];
         float sum = 0.f;
@@ -213,6 +208,7 @@ norm_fwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const 
         // part of the row in registers: the slot is free, request the row `stages` ahead.
         float mu = 0.f, rs;
         const float red0 = row_sum<TPR>(sum, sm.red_a + grp * WPR, grp + 1) * inv_d;
+        if (group_gave_up<TPR>(gave_up)) break;
         if (tr == 0) {
             const int64_t ahead = row + (int64_t)stages * stride;
             if (ahead < rows) request_row(&full[s], ring + (size_t)s * row_bytes, src, nullptr, ahead, row_bytes, policy);
@@ -247,7 +243,7 @@ norm_fwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const 
         }
         if constexpr (TPR > 32 && RMS) named_barrier(grp + 1, TPR);   // red_a reuse
     }
-    if (tr == 0 && *sm.abort_flag) {
+    if (tr == 0 && *gave_up) {
         // gave up: let the copies this group still has in flight land before the CTA leaves
         for (int b = 0; b < stages; ++b) {
             const int ib = i + b;
@@ -282,6 +278,7 @@ norm_bwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ dy,
     const int tr = threadIdx.x % TPR;
     const float inv_d = 1.0f / (float)D;
     uint64_t* full = sm.full + grp * kTmaMaxStages;
+    volatile int* gave_up = sm.abort_flag + grp;
     uint8_t* ring = sm.ring + (size_t)grp * stages * slot_bytes;
     const uint8_t* src0 = reinterpret_cast<const uint8_t*>(x);
     const uint8_t* src1 = reinterpret_cast<const uint8_t*>(dy);
@@ -311,9 +308,8 @@ norm_bwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ dy,
         const int s = i % stages;
         const float mu = mu_next, rs = rs_next;
         if (row + stride < rows) { if (!RMS) mu_next = __ldg(mean_in + row + stride); rs_next = __ldg(rstd_in + row + stride); }
-        bool ok = mbar_wait_bounded(&full[s], (uint32_t)((i / stages) & 1), sm.abort_flag, kStatusFullTimeout, status);
-        ok = group_all<TPR>(ok, grp + 1);
-        if (!ok) break;
+        // see the forward kernel: a thread whose wait gave up stays with its group until the reduction
+        mbar_wait_bounded(&full[s], (uint32_t)((i / stages) & 1), gave_up, kStatusFullTimeout, status);
         const uint4* sx = reinterpret_cast<const uint4*>(ring + (size_t)s * slot_bytes);
         const uint4* sd = reinterpret_cast<const uint4*>(ring + (size_t)s * slot_bytes + row_bytes);
         float xh[VPT][EPV], gg[VPT][EPV];
@@ -346,6 +342,7 @@ norm_bwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ dy,
         float m1 = 0.f, m2;
         if constexpr (!RMS) {
             m1 = row_sum<TPR>(s1, sm.red_a + grp * WPR, grp + 1) * inv_d;
+            if (group_gave_up<TPR>(gave_up)) break;
             if (tr == 0) {
                 const int64_t ahead = row + (int64_t)stages * stride;
                 if (ahead < rows) request_row(&full[s], ring + (size_t)s * slot_bytes, src0, src1, ahead, row_bytes, policy);
@@ -353,6 +350,7 @@ norm_bwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ dy,
             m2 = row_sum<TPR>(s2, sm.red_b + grp * WPR, grp + 1) * inv_d;
         } else {
             m2 = row_sum<TPR>(s2, sm.red_b + grp * WPR, grp + 1) * inv_d;
+            if (group_gave_up<TPR>(gave_up)) break;
             if (tr == 0) {
                 const int64_t ahead = row + (int64_t)stages * stride;
                 if (ahead < rows) request_row(&full[s], ring + (size_t)s * slot_bytes, src0, src1, ahead, row_bytes, policy);
@@ -368,7 +366,7 @@ norm_bwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ dy,
         }
         if constexpr (TPR > 32 && RMS) named_barrier(grp + 1, TPR);   // red_b reuse
     }
-    if (tr == 0 && *sm.abort_flag) {
+    if (tr == 0 && *gave_up) {
         for (int b = 0; b < stages; ++b) {
             const int ib = i + b;
             if (first + (int64_t)ib * stride < rows) mbar_wait_drain(&full[ib % stages], (uint32_t)((ib / stages) & 1));
