@@ -208,7 +208,7 @@ def run_reference_arm(args, w: Workload, rank: int, world: int):
         "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "rows_per_s": sample_rows / sec, "gpu_launches": 0,
     }
-    print(json.dumps(line))
+    _emit(line)
 
 
 # ---------------------------------------------------------------- op suite
@@ -275,12 +275,25 @@ def run_suite(args):
         timed(f"{nm}_fwd fp32 32Mi", lambda: abi.act_fwd(xf, code), 2 * n * 4)
         timed(f"{nm}_bwd fp32 32Mi", lambda: abi.act_bwd(xf, df, code), 3 * n * 4)
     abi.device_status()
-    print(json.dumps({"suite": results, "peak_gbs": peak, "unit": "GB/s", "data": "synthetic",
-                      "note": "timings include torch's output allocation from its caching allocator"}))
+    _emit({"suite": results, "peak_gbs": peak, "unit": "GB/s", "data": "synthetic",
+           "note": "timings include torch's output allocation from its caching allocator"})
 
 
 # ------------------------------------------------------------------ our arm
+def _emit(line: dict) -> None:
+    """The one JSON line goes to the process's original stdout; everything else that libraries
+    print to fd 1 (NCCL's version banner, for one) was redirected to stderr in main()."""
+    os.write(_REAL_STDOUT, (json.dumps(line) + "\n").encode())
+
+
+_REAL_STDOUT = 1
+
+
 def main():
+    global _REAL_STDOUT
+    sys.stdout.flush()
+    _REAL_STDOUT = os.dup(1)
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
@@ -498,7 +511,7 @@ def main():
             "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu, "e2e": e2e,
             "clocks": clocks.summary(), "gpu_launches": 3 * args.steps,
         }
-        print(json.dumps(line))
+        _emit(line)
     if world > 1:
         dist.destroy_process_group()
 
