@@ -13,6 +13,8 @@ colreduce_vec_kernel(const float* __restrict__ partials, int n_partials, int64_t
     __shared__ double red[CR_PL][CR_CL * 4 + 1];
     const int cl = threadIdx.x % CR_CL, pl = threadIdx.x / CR_CL;
     const int64_t c0 = ((int64_t)blockIdx.x * CR_CL + cl) * 4;
+    pdl_release();
+    pdl_wait();
     double acc[4] = {0.0, 0.0, 0.0, 0.0};
     if (c0 < ncols) {
 #pragma unroll 4
@@ -57,7 +59,8 @@ int launch_colreduce(const float* partials, int64_t n_partials, int64_t ncols, f
     if (ncols == 0) return 0;
     if (ncols % 4 == 0 && aligned16(partials)) {
         const int64_t grid = (ncols / 4 + CR_CL - 1) / CR_CL;
-        colreduce_vec_kernel<<<(unsigned)grid, CR_PL * CR_CL, 0, st>>>(partials, (int)n_partials, ncols, out);
+        cudaError_t e = launch_pdl(colreduce_vec_kernel, dim3((unsigned)grid), dim3(CR_PL * CR_CL), 0, st, partials, (int)n_partials, ncols, out);
+        if (e != cudaSuccess) return cuda_status(e, "colreduce launch");
     } else {
         const int64_t grid = (ncols + 31) / 32;
         colreduce_scalar_kernel<<<(unsigned)grid, 256, 0, st>>>(partials, (int)n_partials, ncols, out);

@@ -23,6 +23,26 @@ int  sm_count();           // SMs of the current device (cached per device)
         }                                       \
     } while (0)
 
+// Launch with programmatic stream serialization: the grid may be scheduled while the previous
+// kernel in the stream is still draining, and blocks in pdl_wait() until that kernel has
+// completed and its writes are visible.  Behind a kernel that never signals (any kernel not
+// from this library) this degenerates to the ordinary stream order.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                     cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // -------------------------------------------------------------- device side
@@ -30,6 +50,13 @@ static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t
 template <typename T> struct VecTraits;
 template <> struct VecTraits<float> { static constexpr int EPV = 4; };
 template <> struct VecTraits<__nv_bfloat16> { static constexpr int EPV = 8; };
+
+// Programmatic dependent launch, device side.  pdl_wait(): block until the kernel this one was
+// serialized behind has completed (a no-op for an ordinary launch); every kernel calls it before
+// its first global-memory access.  pdl_release(): let the next kernel of the stream be scheduled
+// onto SMs as this grid's CTAs retire.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // Streaming (evict-first) 16-byte global load/store: every activation byte on
 // this path is touched once per kernel, so it should not displace the affine

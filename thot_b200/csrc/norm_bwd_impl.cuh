@@ -20,9 +20,10 @@ static int launch_bwd_tma(const NormArgs& a, int64_t* n_partials) {
         configured = t.smem;
     }
     const int grid = (int)tma_grid(a.rows, TPR, sm_count());
-    kern<<<grid, kTmaThreads, t.smem, a.stream>>>((const T*)a.x, (const T*)a.dy, (const T*)a.gamma, (const T*)a.beta,
-                                                  a.mean, a.rstd, (T*)a.dx, a.partials, a.rows, (int)a.D,
-                                                  t.stages, device_status_ptr());
+    const cudaError_t e = launch_pdl(kern, dim3(grid), dim3(kTmaThreads), t.smem, a.stream, (const T*)a.x, (const T*)a.dy,
+                                     (const T*)a.gamma, (const T*)a.beta, a.mean, a.rstd, (T*)a.dx, a.partials, a.rows,
+                                     (int)a.D, t.stages, device_status_ptr());
+    if (e != cudaSuccess) return cuda_status(e, "norm_bwd_tma_kernel launch");
     if (n_partials) *n_partials = a.partials ? grid : 0;
     return cuda_status(cudaGetLastError(), "norm_bwd_tma_kernel launch");
 }

@@ -19,9 +19,10 @@ static int launch_fwd_tma(const NormArgs& a) {
         configured = t.smem;
     }
     const int grid = (int)tma_grid(a.rows, TPR, sm_count());
-    kern<<<grid, kTmaThreads, t.smem, a.stream>>>((const T*)a.x, (const T*)a.gamma, (const T*)a.beta, (T*)a.y,
-                                                  a.mean_out, a.rstd_out, a.rows, (int)a.D, a.eps, t.stages,
-                                                  device_status_ptr());
+    const cudaError_t e = launch_pdl(kern, dim3(grid), dim3(kTmaThreads), t.smem, a.stream, (const T*)a.x, (const T*)a.gamma,
+                                     (const T*)a.beta, (T*)a.y, a.mean_out, a.rstd_out, a.rows, (int)a.D, a.eps, t.stages,
+                                     device_status_ptr());
+    if (e != cudaSuccess) return cuda_status(e, "norm_fwd_tma_kernel launch");
     return cuda_status(cudaGetLastError(), "norm_fwd_tma_kernel launch");
 }
 

@@ -168,6 +168,8 @@ norm_fwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const 
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t row_bytes = (uint32_t)D * sizeof(T);
     const TmaSmem sm(smem, tma_param_bytes(D, (int)sizeof(T)));
+    pdl_release();
+    pdl_wait();
     tma_setup(sm, RPC, stages, (int)row_bytes, gamma, RMS ? nullptr : beta);
 
     const int grp = threadIdx.x / TPR;
@@ -272,6 +274,8 @@ norm_bwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ dy,
     const uint32_t row_bytes = (uint32_t)D * sizeof(T);
     const uint32_t slot_bytes = 2 * row_bytes;                      // a row of x then the same row of dy
     const TmaSmem sm(smem, tma_param_bytes(D, (int)sizeof(T)));
+    pdl_release();
+    pdl_wait();
     tma_setup(sm, RPC, stages, (int)row_bytes, gamma, RMS ? nullptr : beta);
 
     const int grp = threadIdx.x / TPR;
