@@ -173,6 +173,35 @@ int nb2_rmsnorm_bwd(const void* x, const void* dy, const void* weight,
                     int64_t rows, int64_t D,
                     int dtype, int act, void* stream);
 
+/* ------------------------------------------------------------------ *
+ * Residual add fused with the norm that follows it.
+ * Replaces the pair `output = residual + attention; norm2_->forward(output)`
+ * (src/block/details/transformers/classic.hpp:442-445; bert.hpp:291-293
+ * post-norm `norm1(residual + attn)`; mamba.hpp:409-415 for RMSNorm):
+ *   sum_out = a + b   (rounded to the tensor dtype, as the reference's sum tensor is)
+ *   y       = norm(sum_out) * gamma (+ beta)
+ * Both are written: the sum is the next residual.  One pass (2 reads, 2 writes)
+ * instead of an add (2 reads, 1 write) plus a norm (1 read, 1 write).  Shapes the
+ * fused kernels do not cover run as add + norm inside the call.
+ * Backward: dx = norm_backward(dy) + dsum, where dsum is the gradient that
+ * reaches the sum through the residual branch (NULL = none); da = db = dx.
+ * `sum` is the forward's sum_out.  Partials / second pass as for nb2_layernorm_bwd.
+ * ------------------------------------------------------------------ */
+int nb2_add_layernorm_fwd(const void* a, const void* b, const void* gamma, const void* beta,
+                          void* sum_out, void* y, float* mean, float* rstd,
+                          int64_t rows, int64_t D, double eps, int dtype, void* stream);
+int nb2_add_layernorm_bwd(const void* sum, const void* dy, const void* dsum, const void* gamma,
+                          const float* mean, const float* rstd,
+                          void* dx, float* partials, int64_t* n_partials_host,
+                          int64_t rows, int64_t D, int dtype, void* stream);
+int nb2_add_rmsnorm_fwd(const void* a, const void* b, const void* weight,
+                        void* sum_out, void* y, float* rstd,
+                        int64_t rows, int64_t D, double eps, int dtype, void* stream);
+int nb2_add_rmsnorm_bwd(const void* sum, const void* dy, const void* dsum, const void* weight,
+                        const float* rstd,
+                        void* dx, float* partials, int64_t* n_partials_host,
+                        int64_t rows, int64_t D, int dtype, void* stream);
+
 /*
  * Second pass: out[c] = sum_p partials[p, c] for c < ncols, summed in fp64 in
  * a fixed order (deterministic), written as fp32.  For LayerNorm ncols = 2*D

@@ -111,3 +111,18 @@ def rope_apply(x, cos_sin, inverse=False):
     lib().orc_rope_apply(_p(x), _p(np.ascontiguousarray(cos_sin, dtype=np.float32)), c_int64(B), c_int64(S),
                          c_int64(H), c_int64(hd), c_int(int(inverse)), _p(out))
     return out
+
+
+def add_norm(kind, a, b, gamma, beta, dy, dsum, eps, bf16=False):
+    """Residual add in front of a norm: `output = residual + attention; norm(output)`
+    (classic.hpp:442-445 LayerNorm, mamba.hpp:409-415 RMSNorm).  The sum is rounded to the
+    tensor dtype before it is normalised, as the reference's sum tensor is.  da == db == dx."""
+    s = (_f32(a).astype(np.float64) + _f32(b).astype(np.float64)).astype(np.float32)   # fp32 add of fp32/bf16 values
+    if bf16:
+        u = s.view(np.uint32).astype(np.uint64)
+        s = (((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16).astype(np.uint32).view(np.float32)
+    r = layernorm_act(s, gamma, beta, dy, eps) if kind == "ln" else rmsnorm_act(s, gamma, dy, eps)
+    out = dict(sum=s, y=r["y"], dgamma=r.get("dgamma", r.get("dweight")), dbeta=r.get("dbeta"))
+    if dy is not None:
+        out["dx"] = r["dx"] + (0.0 if dsum is None else _f32(dsum).astype(np.float64))
+    return out

@@ -218,6 +218,53 @@ int ref_token_embedding(const float* table, const int64_t* ids, const float* dou
     });
 }
 
+// The residual add in front of a norm, as the blocks write it:
+//   `output = residual + attention; norm2_->forward(output)`  (classic.hpp:442-445, LayerNorm)
+//   `output = residual + ...; norm2_->forward(output)`         (mamba.hpp:409-415, Nott's RMSNorm)
+// Returns the sum, the normalised sum, and with dy/dsum the gradients of
+// sum(y*dy) + sum(s*dsum): da (== db) and the parameter gradients.
+int ref_add_norm(int rms, const float* a, const float* b, const float* gamma, const float* beta, const float* dy,
+                 const float* dsum, int64_t rows, int64_t D, double eps, int compute,
+                 float* sum_out, float* y, float* da, float* dgamma, float* dbeta) {
+    return guarded([&] {
+        namespace M = Nott::Block::Details::Transformer::Mamba;
+        const auto dt = compute_type(compute);
+        torch::nn::LayerNorm ln(torch::nn::LayerNormOptions(std::vector<int64_t>{D}).eps(eps));
+        M::RMSNormOptions opt{};
+        opt.eps = eps;
+        M::Detail::RMSNorm rn(D, opt);
+        ln->to(dt);
+        rn->to(dt);
+        {
+            torch::NoGradGuard ng;
+            if (rms) {
+                rn->named_parameters()["weight"].copy_(wrap(gamma, {D}, compute));
+            } else {
+                ln->weight.copy_(wrap(gamma, {D}, compute));
+                ln->bias.copy_(wrap(beta, {D}, compute));
+            }
+        }
+        auto residual = wrap(a, {rows, D}, compute).clone().requires_grad_(dy != nullptr);
+        auto attention = wrap(b, {rows, D}, compute).clone().requires_grad_(dy != nullptr);
+        auto output = residual + attention;
+        auto normed = rms ? rn->forward(output) : ln->forward(output);
+        store(output, sum_out);
+        store(normed, y);
+        if (dy != nullptr) {
+            auto loss = (normed * wrap(dy, {rows, D}, compute)).sum();
+            if (dsum != nullptr) loss = loss + (output * wrap(dsum, {rows, D}, compute)).sum();
+            loss.backward();
+            store(residual.grad(), da);
+            if (rms) {
+                store(rn->named_parameters()["weight"].grad(), dgamma);
+            } else {
+                store(ln->weight.grad(), dgamma);
+                store(ln->bias.grad(), dbeta);
+            }
+        }
+    });
+}
+
 // Times forward + autograd backward of LayerNorm->act (rms == 0) or Nott's
 // RMSNorm->act (rms != 0) on seeded N(0,1) inputs that are built once; only the
 // module calls are inside the clock.  Returns seconds per iteration (mean of

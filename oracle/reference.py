@@ -82,6 +82,19 @@ def rmsnorm_act(x, weight, dy, eps, act=0, compute=0):
     return dict(y=y, dx=dx, dweight=dw, dweight64=dw64)
 
 
+def add_norm(kind, a, b, gamma, beta, dy, dsum, eps, compute=0):
+    a, b, gamma, beta, dy, dsum = map(_f32, (a, b, gamma, beta, dy, dsum))
+    rows, D = a.shape
+    s = np.empty((rows, D), np.float32); y = np.empty((rows, D), np.float32)
+    bwd = dy is not None
+    da = np.empty((rows, D), np.float32) if bwd else None
+    dg = np.empty(D, np.float32) if bwd else None
+    db = np.empty(D, np.float32) if bwd and kind == "ln" else None
+    _chk(lib().ref_add_norm(c_int(1 if kind == "rms" else 0), _p(a), _p(b), _p(gamma), _p(beta), _p(dy), _p(dsum),
+                            c_int64(rows), c_int64(D), c_double(eps), c_int(compute), _p(s), _p(y), _p(da), _p(dg), _p(db)))
+    return dict(sum=s, y=y, da=da, dgamma=dg, dbeta=db)
+
+
 def act(x, dy, act_code, compute=0):
     x, dy = _f32(x), _f32(dy)
     y = np.empty(x.shape, np.float32)

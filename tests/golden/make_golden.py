@@ -97,6 +97,24 @@ def main():
         rec[f"mamba_out_{tag}"], rec[f"mamba_dgate_{tag}"], rec[f"mamba_dup_{tag}"] = m["out"], m["dgate"], m["dup"]
     np.savez(OUT / "silu_gate.npz", **rec)
 
+    # residual add + norm (classic.hpp:442-445 with LayerNorm, mamba.hpp:409-415 with RMSNorm)
+    for name, kind, seed, rows, D, eps, bf16 in (("add_ln_d1024", "ln", 20, 6, 1024, 1e-5, False),
+                                                 ("add_rms_d2048_bf16", "rms", 21, 5, 2048, 1e-6, True)):
+        gen = torch.Generator().manual_seed(seed)
+        a, b = randn(gen, rows, D, bf16=bf16), randn(gen, rows, D, bf16=bf16)
+        gamma = randn(gen, D, scale=0.02, shift=1.0, bf16=bf16)
+        beta = randn(gen, D, scale=0.02, bf16=bf16) if kind == "ln" else None
+        dy, dsum = randn(gen, rows, D, bf16=bf16), randn(gen, rows, D, bf16=bf16)
+        rec = dict(kind=kind, rows=rows, D=D, eps=eps, bf16=bf16, a=a, b=b, gamma=gamma, dy=dy, dsum=dsum)
+        if beta is not None:
+            rec["beta"] = beta
+        for tag, compute in (("f32", 0), ("f64", 1)):
+            r = R.add_norm(kind, a, b, gamma, beta, dy, dsum, eps, compute)
+            for k in ("sum", "y", "da", "dgamma", "dbeta"):
+                if r[k] is not None:
+                    rec[f"{k}_{tag}"] = r[k]
+        np.savez(OUT / f"{name}.npz", **rec)
+
     gen = torch.Generator().manual_seed(12)
     table = randn(gen, 64, 40, scale=0.02)
     ids = torch.randint(0, 64, (3, 9), generator=gen).numpy().astype(np.int64)

@@ -1,0 +1,90 @@
+"""Residual add fused with LayerNorm / RMSNorm (nb2_add_*norm_fwd/bwd) through the C ABI."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import cpu_oracle as O
+from tests import tol
+from tests.gpu_util import bits, check, make, to_dev
+from thot_b200 import abi
+
+pytestmark = pytest.mark.gpu
+
+
+def run(kind, a, b, gamma, beta, dy, dsum, eps):
+    s, y, mean, rstd = abi.add_norm_fwd(kind, a, b, gamma, beta, eps)
+    dx, grads = abi.add_norm_bwd(kind, s, dy, dsum, gamma, mean, rstd)
+    return s, y, dx, grads
+
+
+@pytest.mark.parametrize("name", ["add_ln_d1024", "add_rms_d2048_bf16"])
+def test_golden_reference_outputs(golden_dir, name):
+    z = np.load(golden_dir / f"{name}.npz")
+    g = {k: z[k] for k in z.files}
+    kind = str(g["kind"])
+    dtype = torch.bfloat16 if bool(g["bf16"]) else torch.float32
+    dev = lambda k: to_dev(g[k], dtype) if k in g else None  # noqa: E731
+    s, y, dx, grads = run(kind, dev("a"), dev("b"), dev("gamma"), dev("beta"), dev("dy"), dev("dsum"), float(g["eps"]))
+    if dtype == torch.float32:
+        assert np.array_equal(s.cpu().numpy(), g["sum_f32"])          # one fp32 add: exact
+        check(y, g["y_f32"], "y")
+        check(dx, g["da_f32"], "dx")
+        tol.long_sum_close(grads[0].cpu().numpy(), g["dgamma_f64"], int(g["rows"]), ref32=g["dgamma_f32"])
+        tol.long_sum_close(grads[1].cpu().numpy(), g["dbeta_f64"], int(g["rows"]), ref32=g["dbeta_f32"])
+    else:
+        ob = O.add_norm(kind, g["a"], g["b"], g["gamma"], None, g["dy"], g["dsum"], float(g["eps"]), bf16=True)
+        assert np.array_equal(tol.to_bf16_bits(ob["sum"]), s.view(torch.int16).cpu().numpy().view(np.uint16))
+        check(y, ob["y"], "y")
+        check(dx, ob["dx"], "dx")
+        tol.long_sum_close(grads.cpu().numpy(), ob["dgamma"], int(g["rows"]))
+
+
+# ring-fused shapes, and shapes that compose add + norm inside the call (odd width, ring too large)
+@pytest.mark.parametrize("kind", ["ln", "rms"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,D", [(1, 1024), (700, 768), (3000, 1024), (257, 4096), (33, 513), (64, 8192), (5, 16384)])
+def test_against_oracle(kind, dtype, rows, D):
+    eps = 1e-5 if kind == "ln" else 1e-6
+    a, an = make((rows, D), 1, dtype); b, bn = make((rows, D), 2, dtype)
+    dy, dyn = make((rows, D), 3, dtype); dsum, dsn = make((rows, D), 4, dtype)
+    gamma, gn = make((D,), 5, dtype, 0.02, 1.0)
+    beta, ben = make((D,), 6, dtype, 0.02) if kind == "ln" else (None, None)
+    s, y, dx, grads = run(kind, a, b, gamma, beta, dy, dsum, eps)
+    ref = O.add_norm(kind, an, bn, gn, ben, dyn, dsn, eps, bf16=dtype == torch.bfloat16)
+    if dtype == torch.float32:
+        assert np.array_equal(s.cpu().numpy(), ref["sum"])
+    else:
+        assert np.array_equal(s.view(torch.int16).cpu().numpy().view(np.uint16), tol.to_bf16_bits(ref["sum"]))
+    check(y, ref["y"], "y")
+    if dtype == torch.float32:
+        check(dx, ref["dx"], "dx")
+    else:
+        # Shapes without a fused kernel run norm backward, then an add, and round to bf16 after each,
+        # exactly as the reference's autograd does with bf16 tensors; the fused kernel rounds once.
+        # Either is accepted: within 2 ulp of the once-rounded or of the twice-rounded result.
+        once = tol.bf16_ulp_mask(bits(dx), ref["dx"])
+        norm_only = tol.bf16_bits_to_f32(tol.to_bf16_bits(ref["dx"] - dsn.astype(np.float64)))
+        twice = tol.bf16_ulp_mask(bits(dx), norm_only.astype(np.float64) + dsn)
+        assert (once | twice).all(), f"{(~(once | twice)).sum()} of {once.size} dx elements outside 2 bf16 ulp"
+    if kind == "ln":
+        tol.long_sum_close(grads[0].cpu().numpy(), ref["dgamma"], rows)
+        tol.long_sum_close(grads[1].cpu().numpy(), ref["dbeta"], rows)
+    else:
+        tol.long_sum_close(grads.cpu().numpy(), ref["dgamma"], rows)
+    # no residual gradient: plain norm backward of the sum
+    dx0, _ = abi.add_norm_bwd(kind, s, dy, None, gamma, *abi.add_norm_fwd(kind, a, b, gamma, beta, eps)[2:])
+    ref0 = O.add_norm(kind, an, bn, gn, ben, dyn, None, eps, bf16=dtype == torch.bfloat16)
+    check(dx0, ref0["dx"], "dx without dsum")
+    assert abi.device_status() == 0
+
+
+def test_fused_equals_composed_bitwise_in_fp32():
+    """The fused kernel and (add, then the plain norm kernels) see the same fp32 sum: same bits out."""
+    rows, D = 2048, 1024
+    a, _ = make((rows, D), 11, torch.float32); b, _ = make((rows, D), 12, torch.float32)
+    gamma, _ = make((D,), 13, torch.float32, 0.02, 1.0); beta, _ = make((D,), 14, torch.float32, 0.02)
+    s, y, mean, rstd = abi.add_norm_fwd("ln", a, b, gamma, beta, 1e-5)
+    y2, mean2, rstd2 = abi.layernorm_fwd(a + b, gamma, beta, 1e-5)
+    assert torch.equal(s, a + b) and torch.equal(y, y2) and torch.equal(rstd, rstd2)

@@ -96,3 +96,21 @@ def test_rope_oracle_properties():
     pos = np.array([5, 0, 2], dtype=np.int32)
     cs2 = O.rope_table(3, hd, 10000.0, positions=pos)
     assert np.array_equal(cs2[0], O.rope_table(6, hd)[5]) and np.array_equal(cs2[2], cs[2])
+
+
+@pytest.mark.parametrize("name", ["add_ln_d1024", "add_rms_d2048_bf16"])
+def test_residual_add_norm_oracle_matches_reference(golden_dir, name):
+    g = load(golden_dir, name)
+    kind, bf16 = str(g["kind"]), bool(g["bf16"])
+    o = O.add_norm(kind, g["a"], g["b"], g["gamma"], g.get("beta"), g["dy"], g["dsum"], float(g["eps"]), bf16=False)
+    # the fp32 run of the reference keeps the sum in fp32, so the un-rounded oracle sum is the one to compare
+    assert np.array_equal(o["sum"], g["sum_f32"])
+    tol.fp32_close(o["y"], g["y_f32"])
+    tol.fp32_close(o["dx"], g["da_f32"])
+    np.testing.assert_allclose(o["dx"], g["da_f64"], rtol=2e-6, atol=2e-6)
+    tol.long_sum_close(o["dgamma"], g["dgamma_f64"], int(g["rows"]), ref32=g["dgamma_f32"])
+    if kind == "ln":
+        tol.long_sum_close(o["dbeta"], g["dbeta_f64"], int(g["rows"]), ref32=g["dbeta_f32"])
+    if bf16:   # bf16 tensors: the reference's own sum tensor is a bf16 tensor, i.e. the rounded sum
+        ob = O.add_norm(kind, g["a"], g["b"], g["gamma"], g.get("beta"), g["dy"], g["dsum"], float(g["eps"]), bf16=True)
+        assert np.array_equal(tol.to_bf16_bits(g["sum_f32"]), tol.to_bf16_bits(ob["sum"]))

@@ -86,6 +86,13 @@ def _ordered(bits):
     return np.where(b & 0x8000, -(b & 0x7FFF), b & 0x7FFF)
 
 
+def bf16_ulp_mask(got_bits, ref_values, max_ulp=BF16_MAX_ULP):
+    """Elementwise pass mask of the bf16 rule (2 ulp, or inside the fp32 absolute tolerance)."""
+    d = np.abs(_ordered(got_bits) - _ordered(to_bf16_bits(ref_values)))
+    inside_abs = np.abs(bf16_bits_to_f32(got_bits).astype(np.float64) - np.asarray(ref_values, np.float64)) <= FP32_ATOL
+    return (d <= max_ulp) | inside_abs
+
+
 def bf16_ulp_close(got_bits, ref_values, max_ulp=BF16_MAX_ULP):
     """got_bits: uint16 bf16 patterns; ref_values: fp32/fp64 reference before rounding."""
     ref_bits = to_bf16_bits(ref_values)

@@ -31,6 +31,10 @@ _SIGNATURES = {
     "nb2_layernorm_bwd_static": (c_int, [c_void_p] * 8 + [c_int64, c_int64, c_int, c_int, c_void_p]),
     "nb2_rmsnorm_fwd": (c_int, [c_void_p] * 4 + [c_int64, c_int64, c_double, c_int, c_int, c_void_p]),
     "nb2_rmsnorm_bwd": (c_int, [c_void_p] * 6 + [POINTER(c_int64), c_int64, c_int64, c_int, c_int, c_void_p]),
+    "nb2_add_layernorm_fwd": (c_int, [c_void_p] * 8 + [c_int64, c_int64, c_double, c_int, c_void_p]),
+    "nb2_add_layernorm_bwd": (c_int, [c_void_p] * 8 + [POINTER(c_int64), c_int64, c_int64, c_int, c_void_p]),
+    "nb2_add_rmsnorm_fwd": (c_int, [c_void_p] * 6 + [c_int64, c_int64, c_double, c_int, c_void_p]),
+    "nb2_add_rmsnorm_bwd": (c_int, [c_void_p] * 7 + [POINTER(c_int64), c_int64, c_int64, c_int, c_void_p]),
     "nb2_colreduce_partials": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
     "nb2_act_fwd": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
     "nb2_act_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
@@ -172,6 +176,45 @@ def rmsnorm_bwd(x, dy, weight, rstd, act: int = ACT_NONE, want_param_grads: bool
             out.zero_()
         else:
             check(lib().nb2_colreduce_partials(_p(partials), n.value, D, _p(out), _stream()))
+    return dx, out
+
+
+# ------------------------------------------------------- residual add + norm
+def add_norm_fwd(kind, a, b, gamma, beta, eps: float):
+    """-> (sum, y, mean or None, rstd): y = norm(a + b), sum = a + b."""
+    _dev(a)
+    rows, D = a.shape
+    s, y = torch.empty_like(a), torch.empty_like(a)
+    rstd = torch.empty(rows, dtype=torch.float32, device=a.device)
+    if kind == "ln":
+        mean = torch.empty(rows, dtype=torch.float32, device=a.device)
+        check(lib().nb2_add_layernorm_fwd(_p(a), _p(b), _p(gamma), _p(beta), _p(s), _p(y), _p(mean), _p(rstd), rows, D, eps,
+                                          dtype_code(a.dtype), _stream()))
+        return s, y, mean, rstd
+    check(lib().nb2_add_rmsnorm_fwd(_p(a), _p(b), _p(gamma), _p(s), _p(y), _p(rstd), rows, D, eps, dtype_code(a.dtype), _stream()))
+    return s, y, None, rstd
+
+
+def add_norm_bwd(kind, s, dy, dsum, gamma, mean, rstd):
+    """-> (dx, parameter gradients fp32: [2, D] for "ln", [D] for "rms")."""
+    _dev(s)
+    rows, D = s.shape
+    code = dtype_code(s.dtype)
+    dx = torch.empty_like(s)
+    partials = torch.empty(workspace_bytes(WS_NORM_BWD, rows, D, code) // 4, dtype=torch.float32, device=s.device)
+    n = c_int64(0)
+    if kind == "ln":
+        check(lib().nb2_add_layernorm_bwd(_p(s), _p(dy), _p(dsum), _p(gamma), _p(mean), _p(rstd), _p(dx), _p(partials),
+                                          ctypes.byref(n), rows, D, code, _stream()))
+        out = torch.empty(2, D, dtype=torch.float32, device=s.device)
+    else:
+        check(lib().nb2_add_rmsnorm_bwd(_p(s), _p(dy), _p(dsum), _p(gamma), _p(rstd), _p(dx), _p(partials), ctypes.byref(n),
+                                        rows, D, code, _stream()))
+        out = torch.empty(D, dtype=torch.float32, device=s.device)
+    if rows == 0:
+        out.zero_()
+    else:
+        check(lib().nb2_colreduce_partials(_p(partials), n.value, out.numel(), _p(out), _stream()))
     return dx, out
 
 

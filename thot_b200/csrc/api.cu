@@ -67,7 +67,8 @@ static int require_device() {
 }
 
 static int norm_fwd(bool rms, const void* x, const void* gamma, const void* beta, void* y, float* mean,
-                    float* rstd, int64_t rows, int64_t D, double eps, int dtype, int act, void* stream) {
+                    float* rstd, int64_t rows, int64_t D, double eps, int dtype, int act, void* stream,
+                    const void* res = nullptr, void* sum_out = nullptr) {
     NB2_REQUIRE(dtype_ok(dtype), NB2_ERR_DTYPE, "norm fwd: unknown dtype %d", dtype);
     NB2_REQUIRE(act_ok(act), NB2_ERR_DTYPE, "norm fwd: unknown activation %d", act);
     NB2_REQUIRE(rows >= 0 && D > 0, NB2_ERR_SHAPE, "norm fwd: rows=%lld D=%lld (need rows >= 0, D > 0)", (long long)rows, (long long)D);
@@ -80,13 +81,25 @@ static int norm_fwd(bool rms, const void* x, const void* gamma, const void* beta
     a.x = x; a.gamma = gamma; a.beta = rms ? nullptr : beta; a.y = y;
     a.mean_out = mean; a.rstd_out = rstd; a.rows = rows; a.D = D; a.eps = (float)eps;
     a.act = act; a.rms = rms; a.stream = (cudaStream_t)stream;
-    if (dtype == NB2_F32) return rms ? launch_norm_fwd<float, true>(a) : launch_norm_fwd<float, false>(a);
-    return rms ? launch_norm_fwd<__nv_bfloat16, true>(a) : launch_norm_fwd<__nv_bfloat16, false>(a);
+    a.res = res; a.sum_out = sum_out;
+    auto run = [&](const NormArgs& n) {
+        if (dtype == NB2_F32) return rms ? launch_norm_fwd<float, true>(n) : launch_norm_fwd<float, false>(n);
+        return rms ? launch_norm_fwd<__nv_bfloat16, true>(n) : launch_norm_fwd<__nv_bfloat16, false>(n);
+    };
+    rc = run(a);
+    if (rc == kNotFused) {
+        // no fused residual kernel for this shape: the sum in one pass, the norm of the sum in another
+        rc = launch_add(x, res, sum_out, rows * D, dtype, (cudaStream_t)stream);
+        if (rc != 0) return rc;
+        a.x = sum_out; a.res = nullptr; a.sum_out = nullptr;
+        rc = run(a);
+    }
+    return rc;
 }
 
 static int norm_bwd(bool rms, const void* x, const void* dy, const void* gamma, const void* beta,
                     const float* mean, const float* rstd, void* dx, float* partials, int64_t* n_partials,
-                    int64_t rows, int64_t D, int dtype, int act, void* stream) {
+                    int64_t rows, int64_t D, int dtype, int act, void* stream, const void* dres = nullptr) {
     NB2_REQUIRE(dtype_ok(dtype), NB2_ERR_DTYPE, "norm bwd: unknown dtype %d", dtype);
     NB2_REQUIRE(act_ok(act), NB2_ERR_DTYPE, "norm bwd: unknown activation %d", act);
     NB2_REQUIRE(rows >= 0 && D > 0, NB2_ERR_SHAPE, "norm bwd: rows=%lld D=%lld (need rows >= 0, D > 0)", (long long)rows, (long long)D);
@@ -101,8 +114,19 @@ static int norm_bwd(bool rms, const void* x, const void* dy, const void* gamma, 
     a.x = x; a.dy = dy; a.gamma = gamma; a.beta = rms ? nullptr : beta; a.mean = mean; a.rstd = rstd;
     a.dx = dx; a.partials = partials; a.rows = rows; a.D = D; a.act = act; a.rms = rms;
     a.stream = (cudaStream_t)stream;
-    if (dtype == NB2_F32) return rms ? launch_norm_bwd<float, true>(a, n_partials) : launch_norm_bwd<float, false>(a, n_partials);
-    return rms ? launch_norm_bwd<__nv_bfloat16, true>(a, n_partials) : launch_norm_bwd<__nv_bfloat16, false>(a, n_partials);
+    a.dres = dres;
+    auto run = [&](const NormArgs& n) {
+        if (dtype == NB2_F32) return rms ? launch_norm_bwd<float, true>(n, n_partials) : launch_norm_bwd<float, false>(n, n_partials);
+        return rms ? launch_norm_bwd<__nv_bfloat16, true>(n, n_partials) : launch_norm_bwd<__nv_bfloat16, false>(n, n_partials);
+    };
+    rc = run(a);
+    if (rc == kNotFused) {
+        a.dres = nullptr;
+        rc = run(a);
+        if (rc != 0) return rc;
+        rc = launch_add(dx, dres, dx, rows * D, dtype, (cudaStream_t)stream);
+    }
+    return rc;
 }
 
 }  // namespace nb2
@@ -173,6 +197,29 @@ int nb2_rmsnorm_bwd(const void* x, const void* dy, const void* weight, const flo
                     float* partials, int64_t* n_partials_host, int64_t rows, int64_t D, int dtype, int act,
                     void* stream) {
     return norm_bwd(true, x, dy, weight, nullptr, nullptr, rstd, dx, partials, n_partials_host, rows, D, dtype, act, stream);
+}
+
+int nb2_add_layernorm_fwd(const void* a, const void* b, const void* gamma, const void* beta, void* sum_out, void* y,
+                          float* mean, float* rstd, int64_t rows, int64_t D, double eps, int dtype, void* stream) {
+    NB2_REQUIRE(rows == 0 || (b != nullptr && sum_out != nullptr), NB2_ERR_NULL, "add+layernorm fwd: b or sum_out is NULL");
+    return norm_fwd(false, a, gamma, beta, y, mean, rstd, rows, D, eps, dtype, NB2_ACT_NONE, stream, b, sum_out);
+}
+int nb2_add_layernorm_bwd(const void* sum, const void* dy, const void* dsum, const void* gamma, const float* mean,
+                          const float* rstd, void* dx, float* partials, int64_t* n_partials_host, int64_t rows,
+                          int64_t D, int dtype, void* stream) {
+    return norm_bwd(false, sum, dy, gamma, nullptr, mean, rstd, dx, partials, n_partials_host, rows, D, dtype,
+                    NB2_ACT_NONE, stream, dsum);
+}
+int nb2_add_rmsnorm_fwd(const void* a, const void* b, const void* weight, void* sum_out, void* y, float* rstd,
+                        int64_t rows, int64_t D, double eps, int dtype, void* stream) {
+    NB2_REQUIRE(rows == 0 || (b != nullptr && sum_out != nullptr), NB2_ERR_NULL, "add+rmsnorm fwd: b or sum_out is NULL");
+    return norm_fwd(true, a, weight, nullptr, y, nullptr, rstd, rows, D, eps, dtype, NB2_ACT_NONE, stream, b, sum_out);
+}
+int nb2_add_rmsnorm_bwd(const void* sum, const void* dy, const void* dsum, const void* weight, const float* rstd,
+                        void* dx, float* partials, int64_t* n_partials_host, int64_t rows, int64_t D, int dtype,
+                        void* stream) {
+    return norm_bwd(true, sum, dy, weight, nullptr, nullptr, rstd, dx, partials, n_partials_host, rows, D, dtype,
+                    NB2_ACT_NONE, stream, dsum);
 }
 
 int nb2_colreduce_partials(const float* partials, int64_t n_partials, int64_t ncols, float* out, void* stream) {

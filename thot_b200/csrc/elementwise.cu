@@ -92,6 +92,41 @@ int launch_act(const void* x, const void* dy, void* out, int64_t n, int dtype, i
                : launch_act_a<__nv_bfloat16, false>(x, dy, out, n, act, st);
 }
 
+// ---------------------------------------------------------------- plain add
+// out = a + b (fp32 add, rounded to T): the unfused form of the residual in front of a norm,
+// used for shapes the fused residual kernels do not cover.  out may alias a or b.
+template <typename T>
+__global__ void __launch_bounds__(EW_THREADS)
+add_kernel(const T* a, const T* b, T* out, int64_t n, bool vec) {
+    constexpr int EPV = VecTraits<T>::EPV;
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (int64_t)gridDim.x * blockDim.x;
+    int64_t done = 0;
+    if (vec) {
+        const int64_t nvec = n / EPV;
+        for (int64_t i = tid; i < nvec; i += nth) {
+            float fa[EPV], fb[EPV];
+            unpack<T>(ld_stream(a + i * EPV), fa);
+            unpack<T>(ld_stream(b + i * EPV), fb);
+#pragma unroll
+            for (int e = 0; e < EPV; ++e) fa[e] += fb[e];
+            st_stream(out + i * EPV, pack<T>(fa));
+        }
+        done = nvec * EPV;
+    }
+    for (int64_t i = done + tid; i < n; i += nth) out[i] = from_f32<T>(to_f32(a[i]) + to_f32(b[i]));
+}
+
+int launch_add(const void* a, const void* b, void* out, int64_t n, int dtype, cudaStream_t st) {
+    if (n == 0) return 0;
+    const bool vec = aligned16(a) && aligned16(b) && aligned16(out);
+    int64_t grid = (n / 4 + EW_THREADS - 1) / EW_THREADS + 1;
+    const int64_t cap = (int64_t)sm_count() * 16;
+    if (grid > cap) grid = cap;
+    if (dtype == NB2_F32) add_kernel<float><<<(unsigned)grid, EW_THREADS, 0, st>>>((const float*)a, (const float*)b, (float*)out, n, vec);
+    else add_kernel<__nv_bfloat16><<<(unsigned)grid, EW_THREADS, 0, st>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)out, n, vec);
+    return cuda_status(cudaGetLastError(), "add launch");
+}
+
 // ------------------------------------------------------------------ SiLU gate
 // Rows may be strided (the two halves of a [rows, 2H] SwiGLU input), so the
 // kernel walks (row, column-vector): blockIdx.x picks GATE_ROWS consecutive

@@ -6,6 +6,7 @@
 namespace nb2 {
 
 int launch_act(const void* x, const void* dy, void* out, int64_t n, int dtype, int act, bool bwd, cudaStream_t st);
+int launch_add(const void* a, const void* b, void* out, int64_t n, int dtype, cudaStream_t st);
 int launch_silu_gate(const void* a, int64_t lda, const void* b, int64_t ldb,
                      const void* dy, int64_t lddy, void* o0, int64_t ldo0, void* o1, int64_t ldo1,
                      int64_t rows, int64_t H, int dtype, bool bwd, cudaStream_t st);

@@ -112,19 +112,19 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
 // element has an issue budget of ~35 instructions (fp32) or ~18 (bf16), and the
 // library erff alone costs more than that.  Instead
 //     erfc(|z|/sqrt2) = t * P(t) * exp(-z^2/2),   t = 1 / (1 + p |z|)
-// with a degree-6 P fitted (weighted minimax over |z| <= 9.5) to 6e-9; evaluated
-// in fp32 with the approximate rcp/ex2 units the error is <= 4e-7 on erfc, i.e.
-// <= 7e-8 absolute on GELU(z) and <= 2e-7 on GELU'(z): inside the 1e-6 absolute
-// tolerance with room to spare, in ~14 instructions of which 2 are MUFU.
+// with a degree-5 P fitted (weighted minimax over |z| <= 9.5, weight max(1,|z|)/2)
+// to 9e-8; evaluated in fp32 with the approximate rcp/ex2 units the error is
+// <= 5e-7 on erfc, i.e. <= 1.3e-7 absolute on GELU(z) and <= 2.6e-7 on GELU'(z):
+// inside the 1e-6 absolute tolerance with room to spare, in 13 instructions of
+// which 2 are MUFU.
 constexpr float kInvSqrt2Pi = 0.39894228040143267794f;
-constexpr float kErfcP  = 0.2774544051f;
+constexpr float kErfcP  = 0.3329536741f;
 // half of the fitted coefficients: gelu_half_erfc returns 0.5 * erfc(|z|/sqrt2)
-constexpr float kErfcA1 = 0.5f * 2.3451949666e-01f;
-constexpr float kErfcA2 = 0.5f * 1.0810584440e-01f;
-constexpr float kErfcA3 = 0.5f * 6.0672620911e-01f;
-constexpr float kErfcA4 = 0.5f * -5.7341484387e-01f;
-constexpr float kErfcA5 = 0.5f * 8.4590121047e-01f;
-constexpr float kErfcA6 = 0.5f * -2.2183792820e-01f;
+constexpr float kErfcA1 = 0.5f * 2.4810082281e-01f;
+constexpr float kErfcA2 = 0.5f * 3.9755105569e-01f;
+constexpr float kErfcA3 = 0.5f * -1.5376413303e-01f;
+constexpr float kErfcA4 = 0.5f * 7.2612069805e-01f;
+constexpr float kErfcA5 = 0.5f * -2.1800861308e-01f;
 
 __device__ __forceinline__ float fast_rcp(float x) {
     float r;
@@ -141,8 +141,7 @@ __device__ __forceinline__ void gelu_half_erfc(float z, float& q, float& e) {
     const float az = fabsf(z);
     const float t = fast_rcp(fmaf(kErfcP, az, 1.0f));
     e = fast_ex2(z * z * -0.72134752044448170368f);          // -0.5 * log2(e) * z^2
-    float p = fmaf(kErfcA6, t, kErfcA5);
-    p = fmaf(p, t, kErfcA4);
+    float p = fmaf(kErfcA5, t, kErfcA4);
     p = fmaf(p, t, kErfcA3);
     p = fmaf(p, t, kErfcA2);
     p = fmaf(p, t, kErfcA1);

@@ -6,10 +6,10 @@
 
 namespace nb2 {
 
-template <typename T, int TPR, int VPT, int ACT, bool RMS>
-static int launch_bwd_tma(const NormArgs& a, int64_t* n_partials) {
-    auto kern = norm_bwd_tma_kernel<T, TPR, VPT, ACT, RMS>;
-    const TmaTiling t = tma_tiling(a.D, (int)sizeof(T), TPR, 2);
+template <typename T, int TPR, int VPT, int ACT, bool RMS, bool RES>
+static int launch_bwd_tma_res(const NormArgs& a, int64_t* n_partials) {
+    auto kern = norm_bwd_tma_kernel<T, TPR, VPT, ACT, RMS, RES>;
+    const TmaTiling t = tma_tiling(a.D, (int)sizeof(T), TPR, RES ? 3 : 2);
     NB2_REQUIRE(t.smem <= kTmaMaxSmem, NB2_ERR_SHAPE, "norm ring kernel: %zu bytes of shared memory exceed the SM", t.smem);
     static thread_local size_t configured_all[kMaxDevices] = {};
     size_t& configured = configured_all[current_device_slot()];
@@ -21,11 +21,21 @@ static int launch_bwd_tma(const NormArgs& a, int64_t* n_partials) {
     }
     const int grid = (int)tma_grid(a.rows, TPR, sm_count());
     const cudaError_t e = launch_pdl(kern, dim3(grid), dim3(kTmaThreads), t.smem, a.stream, (const T*)a.x, (const T*)a.dy,
-                                     (const T*)a.gamma, (const T*)a.beta, a.mean, a.rstd, (T*)a.dx, a.partials, a.rows,
-                                     (int)a.D, t.stages, device_status_ptr());
+                                     (const T*)a.dres, (const T*)a.gamma, (const T*)a.beta, a.mean, a.rstd, (T*)a.dx,
+                                     a.partials, a.rows, (int)a.D, t.stages, device_status_ptr());
     if (e != cudaSuccess) return cuda_status(e, "norm_bwd_tma_kernel launch");
     if (n_partials) *n_partials = a.partials ? grid : 0;
-    return cuda_status(cudaGetLastError(), "norm_bwd_tma_kernel launch");
+    return 0;
+}
+
+template <typename T, int TPR, int VPT, int ACT, bool RMS>
+static int launch_bwd_tma(const NormArgs& a, int64_t* n_partials) {
+    if (a.dres != nullptr) {
+        if constexpr (ACT == NB2_ACT_NONE) return launch_bwd_tma_res<T, TPR, VPT, ACT, RMS, true>(a, n_partials);
+        set_error("residual + norm is not fused with an activation");
+        return NB2_ERR_DTYPE;
+    }
+    return launch_bwd_tma_res<T, TPR, VPT, ACT, RMS, false>(a, n_partials);
 }
 
 template <typename T, int ACT, bool RMS>
@@ -66,7 +76,11 @@ static int launch_bwd_act(const NormArgs& a, int64_t* n_partials) {
     constexpr int EPV = VecTraits<T>::EPV;
     if (norm_fast_path_ok<T>(a, bwd_vpt<T>())) {
         const TmaShape s = tma_bwd_shape(a.D, EPV);
-        const bool affine = a.gamma != nullptr && (RMS || a.beta != nullptr);
+        const bool affine = a.gamma != nullptr && (RMS || a.beta != nullptr || ACT == NB2_ACT_NONE);   // beta only enters through act'(z)
+        if (a.dres != nullptr) {
+            if (s.tpr != 0 && affine && tma_fits(a.D, (int)sizeof(T), s.tpr, 3)) return launch_bwd_tma_shape<T, ACT, RMS>(a, s, n_partials);
+            return kNotFused;
+        }
         if (s.tpr != 0 && affine && tma_preferred(RMS, a.D, (int)sizeof(T), true) && tma_fits(a.D, (int)sizeof(T), s.tpr, 2))
             return launch_bwd_tma_shape<T, ACT, RMS>(a, s, n_partials);
         switch (pick_tpr(a.D / EPV, bwd_vpt<T>())) {
@@ -78,6 +92,7 @@ static int launch_bwd_act(const NormArgs& a, int64_t* n_partials) {
             default: break;
         }
     }
+    if (a.dres != nullptr) return kNotFused;
     int64_t need = (a.rows + 7) / 8;
     int64_t cap = (int64_t)sm_count() * 8;
     const int grid = (int)(need < cap ? need : cap);

@@ -14,6 +14,8 @@ struct NormArgs {
     const float* mean; const float* rstd;       // backward inputs
     float* mean_out; float* rstd_out;           // forward outputs
     void* y; void* dx; float* partials;
+    const void* res = nullptr; void* sum_out = nullptr;   // forward: normalise x + res, also write the sum
+    const void* dres = nullptr;                           // backward: dx += dres
     int64_t rows; int64_t D; float eps; int act; bool rms;
     cudaStream_t stream;
 };
@@ -22,6 +24,8 @@ unsigned int* device_status_ptr();              // api.cu: the device status wor
 constexpr int kMaxDevices = 64;
 int current_device_slot();                      // api.cu: cudaGetDevice() folded into [0, kMaxDevices)
 constexpr size_t kTmaMaxSmem = 227 * 1024;
+// launcher result: the shape has no fused residual kernel; the caller composes add + norm instead
+constexpr int kNotFused = -1000;
 
 // Which kernel family to use: 0 = by shape (default), 1 = register-row only,
 // 2 = bulk-async ring wherever the shape fits it.  NB2_NORM_PATH=reg|tma

@@ -5,10 +5,10 @@
 
 namespace nb2 {
 
-template <typename T, int TPR, int VPT, int ACT, bool RMS>
-static int launch_fwd_tma(const NormArgs& a) {
-    auto kern = norm_fwd_tma_kernel<T, TPR, VPT, ACT, RMS>;
-    const TmaTiling t = tma_tiling(a.D, (int)sizeof(T), TPR, 1);
+template <typename T, int TPR, int VPT, int ACT, bool RMS, bool RES>
+static int launch_fwd_tma_res(const NormArgs& a) {
+    auto kern = norm_fwd_tma_kernel<T, TPR, VPT, ACT, RMS, RES>;
+    const TmaTiling t = tma_tiling(a.D, (int)sizeof(T), TPR, RES ? 2 : 1);
     NB2_REQUIRE(t.smem <= kTmaMaxSmem, NB2_ERR_SHAPE, "norm ring kernel: %zu bytes of shared memory exceed the SM", t.smem);
     static thread_local size_t configured_all[kMaxDevices] = {};
     size_t& configured = configured_all[current_device_slot()];
@@ -19,11 +19,23 @@ static int launch_fwd_tma(const NormArgs& a) {
         configured = t.smem;
     }
     const int grid = (int)tma_grid(a.rows, TPR, sm_count());
-    const cudaError_t e = launch_pdl(kern, dim3(grid), dim3(kTmaThreads), t.smem, a.stream, (const T*)a.x, (const T*)a.gamma,
-                                     (const T*)a.beta, (T*)a.y, a.mean_out, a.rstd_out, a.rows, (int)a.D, a.eps, t.stages,
-                                     device_status_ptr());
+    const cudaError_t e = launch_pdl(kern, dim3(grid), dim3(kTmaThreads), t.smem, a.stream, (const T*)a.x, (const T*)a.res,
+                                     (const T*)a.gamma, (const T*)a.beta, (T*)a.sum_out, (T*)a.y, a.mean_out, a.rstd_out,
+                                     a.rows, (int)a.D, a.eps, t.stages, device_status_ptr());
     if (e != cudaSuccess) return cuda_status(e, "norm_fwd_tma_kernel launch");
-    return cuda_status(cudaGetLastError(), "norm_fwd_tma_kernel launch");
+    return 0;
+}
+
+template <typename T, int TPR, int VPT, int ACT, bool RMS>
+static int launch_fwd_tma(const NormArgs& a) {
+    if (a.res != nullptr) {
+        // the residual form is built without a fused activation (the reference norms a residual sum
+        // right before attention or the feed forward, never before an activation)
+        if constexpr (ACT == NB2_ACT_NONE) return launch_fwd_tma_res<T, TPR, VPT, ACT, RMS, true>(a);
+        set_error("residual + norm is not fused with an activation");
+        return NB2_ERR_DTYPE;
+    }
+    return launch_fwd_tma_res<T, TPR, VPT, ACT, RMS, false>(a);
 }
 
 template <typename T, int ACT, bool RMS>
@@ -66,6 +78,10 @@ static int launch_fwd_act(const NormArgs& a) {
     if (norm_fast_path_ok<T>(a, fwd_vpt<T>())) {
         const TmaShape s = tma_fwd_shape(a.D, EPV);
         const bool affine = a.gamma != nullptr && (RMS || a.beta != nullptr);
+        if (a.res != nullptr) {
+            if (s.tpr != 0 && affine && tma_fits(a.D, (int)sizeof(T), s.tpr, 2)) return launch_fwd_tma_shape<T, ACT, RMS>(a, s);
+            return kNotFused;
+        }
         if (s.tpr != 0 && affine && tma_preferred(RMS, a.D, (int)sizeof(T), false) && tma_fits(a.D, (int)sizeof(T), s.tpr, 1))
             return launch_fwd_tma_shape<T, ACT, RMS>(a, s);
         switch (pick_tpr(a.D / EPV, fwd_vpt<T>())) {
@@ -77,6 +93,7 @@ static int launch_fwd_act(const NormArgs& a) {
             default: break;
         }
     }
+    if (a.res != nullptr) return kNotFused;
     int64_t need = (a.rows + 7) / 8;
     int64_t cap = (int64_t)sm_count() * 8;
     const int grid = (int)(need < cap ? need : cap);

@@ -140,23 +140,30 @@ __device__ __forceinline__ void tma_setup(const TmaSmem& sm, int groups, int sta
     __syncthreads();
 }
 
-// group leader: request one row of each source into a slot
+// group leader: request one row of each source (up to three) into a slot, one after the other
 __device__ __forceinline__ void request_row(uint64_t* bar, uint8_t* slot, const uint8_t* src0, const uint8_t* src1,
-                                            int64_t row, uint32_t row_bytes, uint64_t policy) {
-    mbar_arrive_expect_tx(bar, src1 != nullptr ? 2 * row_bytes : row_bytes);
+                                            const uint8_t* src2, int64_t row, uint32_t row_bytes, uint64_t policy) {
+    const uint32_t nsrc = 1u + (src1 != nullptr) + (src2 != nullptr);
+    mbar_arrive_expect_tx(bar, nsrc * row_bytes);
     for (uint32_t off = 0; off < row_bytes; off += kBulkChunk) {
         const uint32_t n = row_bytes - off < kBulkChunk ? row_bytes - off : kBulkChunk;
         bulk_g2s(slot + off, src0 + row * (int64_t)row_bytes + off, n, bar, policy);
         if (src1 != nullptr) bulk_g2s(slot + row_bytes + off, src1 + row * (int64_t)row_bytes + off, n, bar, policy);
+        if (src2 != nullptr) bulk_g2s(slot + 2 * row_bytes + off, src2 + row * (int64_t)row_bytes + off, n, bar, policy);
     }
 }
 
 // ------------------------------------------------------------------ forward
 // D == TPR * VPT * EPV exactly and the affine parameters are present (the host
 // checks both), so the inner loops carry no predicates.
-template <typename T, int TPR, int VPT, int ACT, bool RMS>
+// RES: the normalised row is x + res (the residual add in front of a norm,
+// src/block/details/transformers/classic.hpp:442-445, mamba.hpp:409-415); the sum, rounded
+// to T as the reference's own `residual + attention` tensor would be, is also written out
+// because it is the next residual.
+template <typename T, int TPR, int VPT, int ACT, bool RMS, bool RES>
 __global__ void __launch_bounds__(kTmaThreads, 1)
-norm_fwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
+norm_fwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __restrict__ gamma,
+                    const T* __restrict__ beta, T* __restrict__ sum_out,
                     T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
                     int64_t rows, int D, float eps, int stages, unsigned int* __restrict__ status) {
     constexpr int EPV = VecTraits<T>::EPV;
@@ -177,8 +184,10 @@ norm_fwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const 
     const float inv_d = 1.0f / (float)D;
     uint64_t* full = sm.full + grp * kTmaMaxStages;
     volatile int* gave_up = sm.abort_flag + grp;
-    uint8_t* ring = sm.ring + (size_t)grp * stages * row_bytes;
+    const uint32_t slot_bytes = RES ? 2 * row_bytes : row_bytes;     // a row of x, then the same row of res
+    uint8_t* ring = sm.ring + (size_t)grp * stages * slot_bytes;
     const uint8_t* src = reinterpret_cast<const uint8_t*>(x);
+    const uint8_t* src_res = RES ? reinterpret_cast<const uint8_t*>(res) : nullptr;
     const int64_t first = (int64_t)blockIdx.x * RPC + grp;
     const int64_t stride = (int64_t)gridDim.x * RPC;
     uint64_t policy = 0;
@@ -186,7 +195,7 @@ norm_fwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const 
         policy = policy_evict_first();
         for (int s = 0; s < stages; ++s) {
             const int64_t row = first + s * stride;
-            if (row < rows) request_row(&full[s], ring + (size_t)s * row_bytes, src, nullptr, row, row_bytes, policy);
+            if (row < rows) request_row(&full[s], ring + (size_t)s * slot_bytes, src, src_res, nullptr, row, row_bytes, policy);
         }
     }
 
@@ -197,12 +206,21 @@ norm_fwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const 
         // the group at the next barrier, so the thread carries on with whatever the slot holds and
         // the whole group leaves together after the reduction below.
         mbar_wait_bounded(&full[s], (uint32_t)((i / stages) & 1), gave_up, kStatusFullTimeout, status);
-        const uint4* srow = reinterpret_cast<const uint4*>(ring + (size_t)s * row_bytes);
+        const uint4* srow = reinterpret_cast<const uint4*>(ring + (size_t)s * slot_bytes);
         float v[VPT][EPV];
         float sum = 0.f;
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
             unpack<T>(srow[tr + j * TPR], v[j]);
+            if constexpr (RES) {
+                float r[EPV];
+                unpack<T>(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(srow) + row_bytes)[tr + j * TPR], r);
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) v[j][e] += r[e];
+                const uint4 packed = pack<T>(v[j]);
+                st_stream(sum_out + row * (int64_t)D + (size_t)(tr + j * TPR) * EPV, packed);
+                unpack<T>(packed, v[j]);                        // normalise what was stored (matters for bf16)
+            }
 #pragma unroll
             for (int e = 0; e < EPV; ++e) sum += RMS ? v[j][e] * v[j][e] : v[j][e];
         }
@@ -213,7 +231,7 @@ norm_fwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const 
         if (group_gave_up<TPR>(gave_up)) break;
         if (tr == 0) {
             const int64_t ahead = row + (int64_t)stages * stride;
-            if (ahead < rows) request_row(&full[s], ring + (size_t)s * row_bytes, src, nullptr, ahead, row_bytes, policy);
+            if (ahead < rows) request_row(&full[s], ring + (size_t)s * slot_bytes, src, src_res, nullptr, ahead, row_bytes, policy);
         }
         if constexpr (RMS) {
             rs = rsqrtf(red0 + eps);
@@ -255,9 +273,11 @@ norm_fwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const 
 }
 
 // ----------------------------------------------------------------- backward
-template <typename T, int TPR, int VPT, int ACT, bool RMS>
+// RES: dx = (norm backward of dy) + dres, the gradient that reaches the normalised tensor
+// through the residual branch as well; one pass instead of a backward plus an add.
+template <typename T, int TPR, int VPT, int ACT, bool RMS, bool RES>
 __global__ void __launch_bounds__(kTmaThreads, 1)
-norm_bwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ dy,
+norm_bwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T* __restrict__ dres,
                     const T* __restrict__ gamma, const T* __restrict__ beta,
                     const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
                     T* __restrict__ dx, float* __restrict__ partials,
@@ -272,7 +292,7 @@ norm_bwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ dy,
 
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t row_bytes = (uint32_t)D * sizeof(T);
-    const uint32_t slot_bytes = 2 * row_bytes;                      // a row of x then the same row of dy
+    const uint32_t slot_bytes = (RES ? 3 : 2) * row_bytes;          // a row of x, of dy (and of dres)
     const TmaSmem sm(smem, tma_param_bytes(D, (int)sizeof(T)));
     pdl_release();
     pdl_wait();
@@ -286,6 +306,7 @@ norm_bwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ dy,
     uint8_t* ring = sm.ring + (size_t)grp * stages * slot_bytes;
     const uint8_t* src0 = reinterpret_cast<const uint8_t*>(x);
     const uint8_t* src1 = reinterpret_cast<const uint8_t*>(dy);
+    const uint8_t* src2 = RES ? reinterpret_cast<const uint8_t*>(dres) : nullptr;
     const int64_t first = (int64_t)blockIdx.x * RPC + grp;
     const int64_t stride = (int64_t)gridDim.x * RPC;
     uint64_t policy = 0;
@@ -293,7 +314,7 @@ norm_bwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ dy,
         policy = policy_evict_first();
         for (int s = 0; s < stages; ++s) {
             const int64_t row = first + s * stride;
-            if (row < rows) request_row(&full[s], ring + (size_t)s * slot_bytes, src0, src1, row, row_bytes, policy);
+            if (row < rows) request_row(&full[s], ring + (size_t)s * slot_bytes, src0, src1, src2, row, row_bytes, policy);
         }
     }
 
@@ -347,17 +368,17 @@ norm_bwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ dy,
         if constexpr (!RMS) {
             m1 = row_sum<TPR>(s1, sm.red_a + grp * WPR, grp + 1) * inv_d;
             if (group_gave_up<TPR>(gave_up)) break;
-            if (tr == 0) {
+            if (!RES && tr == 0) {
                 const int64_t ahead = row + (int64_t)stages * stride;
-                if (ahead < rows) request_row(&full[s], ring + (size_t)s * slot_bytes, src0, src1, ahead, row_bytes, policy);
+                if (ahead < rows) request_row(&full[s], ring + (size_t)s * slot_bytes, src0, src1, src2, ahead, row_bytes, policy);
             }
             m2 = row_sum<TPR>(s2, sm.red_b + grp * WPR, grp + 1) * inv_d;
         } else {
             m2 = row_sum<TPR>(s2, sm.red_b + grp * WPR, grp + 1) * inv_d;
             if (group_gave_up<TPR>(gave_up)) break;
-            if (tr == 0) {
+            if (!RES && tr == 0) {
                 const int64_t ahead = row + (int64_t)stages * stride;
-                if (ahead < rows) request_row(&full[s], ring + (size_t)s * slot_bytes, src0, src1, ahead, row_bytes, policy);
+                if (ahead < rows) request_row(&full[s], ring + (size_t)s * slot_bytes, src0, src1, src2, ahead, row_bytes, policy);
             }
         }
         T* xo = dx + row * (int64_t)D;
@@ -366,9 +387,25 @@ norm_bwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ dy,
             float o[EPV];
 #pragma unroll
             for (int e = 0; e < EPV; ++e) o[e] = rs * (gg[j][e] - m1 - xh[j][e] * m2);
+            if constexpr (RES) {
+                float r[EPV];
+                unpack<T>(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(sx) + 2 * row_bytes)[tr + j * TPR], r);
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) o[e] += r[e];
+            }
             st_stream(xo + (size_t)(tr + j * TPR) * EPV, pack<T>(o));
         }
-        if constexpr (TPR > 32 && RMS) named_barrier(grp + 1, TPR);   // red_b reuse
+        if constexpr (RES) {
+            // dres is read from the slot at the very end, so the slot is recycled here, not after
+            // the first reduction: the whole group must be past its reads first.
+            if constexpr (TPR > 32) named_barrier(grp + 1, TPR); else __syncwarp();
+            if (tr == 0) {
+                const int64_t ahead = row + (int64_t)stages * stride;
+                if (ahead < rows) request_row(&full[s], ring + (size_t)s * slot_bytes, src0, src1, src2, ahead, row_bytes, policy);
+            }
+        } else {
+            if constexpr (TPR > 32 && RMS) named_barrier(grp + 1, TPR);   // red_b reuse
+        }
     }
     if (tr == 0 && *gave_up) {
         for (int b = 0; b < stages; ++b) {
