@@ -246,7 +246,20 @@ def run_suite(args):
     y, rstd = abi.rmsnorm_fwd(x, w, 1e-6)
     timed("rmsnorm_fwd bf16 [65536,4096]", lambda: abi.rmsnorm_fwd(x, w, 1e-6), 2 * rows * D * 2 + 4 * rows)
     timed("rmsnorm_bwd+reduce bf16 [65536,4096]", lambda: abi.rmsnorm_bwd(x, dy, w, rstd), 3 * rows * D * 2 + 4 * rows)
-    del x, dy, y
+    # residual add + RMSNorm at the same shape (mamba.hpp:409-415), against add + norm as two passes
+    r = torch.randn(rows, D, device=dev, generator=g).to(bf)
+    sm_, yy, _, rs2 = abi.add_norm_fwd("rms", x, r, w, None, 1e-6)
+    timed("add+rmsnorm_fwd bf16 [65536,4096] (2 reads, 2 writes)", lambda: abi.add_norm_fwd("rms", x, r, w, None, 1e-6),
+          4 * rows * D * 2 + 4 * rows)
+    timed("add+rmsnorm_bwd+reduce bf16 [65536,4096] (3 reads, 1 write)", lambda: abi.add_norm_bwd("rms", sm_, dy, r, w, None, rs2),
+          4 * rows * D * 2 + 4 * rows)
+    del x, dy, y, r, sm_, yy
+    xf32 = torch.randn(32768, 1024, device=dev, generator=g); rf32 = torch.randn(32768, 1024, device=dev, generator=g)
+    gf = torch.ones(1024, device=dev); bf_ = torch.zeros(1024, device=dev)
+    s32, y32, m32, r32 = abi.add_norm_fwd("ln", xf32, rf32, gf, bf_, 1e-5)
+    timed("add+layernorm_fwd fp32 [32768,1024]", lambda: abi.add_norm_fwd("ln", xf32, rf32, gf, bf_, 1e-5), 4 * 32768 * 1024 * 4)
+    timed("add+layernorm_bwd+reduce fp32 [32768,1024]", lambda: abi.add_norm_bwd("ln", s32, xf32, rf32, gf, m32, r32), 4 * 32768 * 1024 * 4)
+    del xf32, rf32, s32, y32
     H = 11008
     a = torch.randn(rows, H, device=dev, generator=g).to(bf); b = torch.randn(rows, H, device=dev, generator=g).to(bf)
     d = torch.randn(rows, H, device=dev, generator=g).to(bf)

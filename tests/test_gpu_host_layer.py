@@ -134,3 +134,30 @@ def test_autocast_runs_layernorm_in_fp32(host):
     with torch.autocast("cuda", dtype=torch.bfloat16):
         names, out = host.layernorm_module_step(256, 1e-5, True, ACT["Identity"], x.float(), dy)
     assert out[0].dtype == torch.float32
+
+
+@pytest.mark.parametrize("rms", [False, True])
+def test_residual_add_norm_autograd(host, rms):
+    dtype = torch.float32
+    a, an = make((3, 50, 1024), 21, dtype); b, bn = make((3, 50, 1024), 22, dtype)
+    w, wn = make((1024,), 23, dtype, 0.02, 1.0); bias, biasn = make((1024,), 24, dtype, 0.02)
+    dy, dyn = make((3, 50, 1024), 25, dtype); ds, dsn = make((3, 50, 1024), 26, dtype)
+    a.requires_grad_(True); b.requires_grad_(True); w.requires_grad_(True); bias.requires_grad_(True)
+    s, y = host.add_norm(a, b, w, None if rms else bias, 1e-6 if rms else 1e-5, rms)
+    ((y * dy).sum() + (s * ds).sum()).backward()
+    ref = O.add_norm("rms" if rms else "ln", an.reshape(-1, 1024), bn.reshape(-1, 1024), wn, None if rms else biasn,
+                     dyn.reshape(-1, 1024), dsn.reshape(-1, 1024), 1e-6 if rms else 1e-5)
+    assert torch.equal(s.detach(), a.detach() + b.detach())
+    check(y.detach().reshape(-1, 1024), ref["y"], "y")
+    check(a.grad.reshape(-1, 1024), ref["dx"], "da")
+    assert torch.equal(a.grad, b.grad)
+    tol.long_sum_close(w.grad.cpu().numpy(), ref["dgamma"], 150)
+    if not rms:
+        tol.long_sum_close(bias.grad.cpu().numpy(), ref["dbeta"], 150)
+    # only the normalised output is used downstream: the residual gradient is absent
+    a2 = a.detach().clone().requires_grad_(True)
+    s2, y2 = host.add_norm(a2, b.detach(), w.detach(), None if rms else bias.detach(), 1e-6 if rms else 1e-5, rms)
+    y2.backward(dy)
+    ref2 = O.add_norm("rms" if rms else "ln", an.reshape(-1, 1024), bn.reshape(-1, 1024), wn, None if rms else biasn,
+                      dyn.reshape(-1, 1024), None, 1e-6 if rms else 1e-5)
+    check(a2.grad.reshape(-1, 1024), ref2["dx"], "da without residual gradient")

@@ -16,6 +16,9 @@ PYBIND11_MODULE(_nott_b200_host, m) {
     m.def("rmsnorm_act", [](torch::Tensor x, c10::optional<torch::Tensor> w, double eps, int64_t act) {
         return nb::RMSNormActFunction::apply(std::move(x), w, eps, act);
     });
+    m.def("add_norm", [](torch::Tensor a, torch::Tensor b, torch::Tensor w, c10::optional<torch::Tensor> bias, double eps, bool rms) {
+        return nb::AddNormFunction::apply(std::move(a), std::move(b), std::move(w), bias, eps, rms);
+    });
     m.def("apply", [](int64_t type, torch::Tensor x) { return nb::apply(static_cast<nb::ActivationType>(type), std::move(x)); });
     m.def("silu_gate", [](torch::Tensor gate, torch::Tensor up) { return nb::silu_gate(gate, up); });
     m.def("embedding", [](torch::Tensor weight, torch::Tensor ids) { return nb::EmbeddingFunction::apply(std::move(weight), std::move(ids)); });

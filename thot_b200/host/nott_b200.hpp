@@ -10,6 +10,8 @@
 //                              optionally fused with the activation that follows it
 //   Nott::B200::RMSNorm     <- Mamba::Detail::RMSNorm (src/block/details/transformers/mamba.hpp:110-150)
 //   Nott::B200::Embedding   <- torch::nn::Embedding (bert.hpp:126-128, ebt.hpp:94-96)
+//   LayerNorm/RMSNorm::forward_residual <- `output = residual + branch; norm(output)` in one pass
+//                              (classic.hpp:442-445, bert.hpp:291-293, mamba.hpp:409-415)
 //   Nott::B200::apply       <- Nott::Activation::Details::apply (src/activation/apply.hpp:24-57)
 //   Nott::B200::silu_gate   <- `up * torch::silu(gate)` (mamba.hpp:443-446)
 //   Nott::B200::RotaryTable / rotary  (no reference code; belongs between the head
@@ -88,6 +90,80 @@ inline torch::Tensor param_like(const torch::Tensor& p, const torch::Tensor& x) 
 }
 
 }  // namespace detail
+
+// ------------------------------------------------------- residual add + norm, one pass
+// `output = residual + attention; norm2_->forward(output)` (classic.hpp:442-445, bert.hpp:291-293,
+// mamba.hpp:409-415) as one autograd node with two outputs: the sum (the next residual) and its
+// normalisation.  rms == false: LayerNorm (weight, bias); rms == true: RMSNorm (weight).
+struct AddNormFunction : public torch::autograd::Function<AddNormFunction> {
+    static torch::autograd::tensor_list forward(torch::autograd::AutogradContext* ctx, torch::Tensor a, torch::Tensor b,
+                                                torch::Tensor weight, c10::optional<torch::Tensor> bias_opt, double eps,
+                                                bool rms) {
+        detail::require_cuda(a, "residual add + norm");
+        if (!b.defined() || a.sizes() != b.sizes() || a.scalar_type() != b.scalar_type())
+            throw std::invalid_argument("residual add + norm expects two tensors of the same shape and dtype.");
+        if (!weight.defined()) throw std::invalid_argument("residual add + norm requires the norm's weight.");
+        const auto D = a.size(-1);
+        auto x = a.contiguous().view({-1, D}), r = b.contiguous().view({-1, D});
+        const int code = detail::dtype_code(x, "residual add + norm");
+        auto w = detail::param_like(weight, x);
+        auto bias = detail::param_like(bias_opt.value_or(torch::Tensor()), x);
+        if (!rms && !bias.defined()) throw std::invalid_argument("residual add + LayerNorm requires the bias.");
+        const auto rows = x.size(0);
+        auto sum = torch::empty_like(x), y = torch::empty_like(x);
+        auto stats = torch::empty({2, rows}, x.options().dtype(torch::kFloat32));
+        if (rms)
+            detail::check(nb2_add_rmsnorm_fwd(x.data_ptr(), r.data_ptr(), w.data_ptr(), sum.data_ptr(), y.data_ptr(),
+                                              stats[1].data_ptr<float>(), rows, D, eps, code, detail::stream()),
+                          "nb2_add_rmsnorm_fwd");
+        else
+            detail::check(nb2_add_layernorm_fwd(x.data_ptr(), r.data_ptr(), w.data_ptr(), bias.data_ptr(), sum.data_ptr(),
+                                                y.data_ptr(), stats[0].data_ptr<float>(), stats[1].data_ptr<float>(), rows,
+                                                D, eps, code, detail::stream()),
+                          "nb2_add_layernorm_fwd");
+        ctx->save_for_backward({sum, w, stats});
+        ctx->saved_data["rms"] = rms;
+        ctx->saved_data["has_bias"] = bias.defined();
+        ctx->saved_data["weight_dtype"] = (int64_t)weight.scalar_type();
+        return {sum.view(a.sizes()), y.view(a.sizes())};
+    }
+
+    static torch::autograd::tensor_list backward(torch::autograd::AutogradContext* ctx,
+                                                 torch::autograd::tensor_list grads) {
+        auto saved = ctx->get_saved_variables();
+        auto sum = saved[0], w = saved[1], stats = saved[2];
+        const bool rms = ctx->saved_data["rms"].toBool();
+        const auto rows = sum.size(0), D = sum.size(1);
+        const int code = detail::dtype_code(sum, "residual add + norm backward");
+        torch::Tensor dsum, dy;
+        if (grads[0].defined()) dsum = grads[0].contiguous().view({rows, D}).to(sum.scalar_type());
+        dy = grads[1].defined() ? grads[1].contiguous().view({rows, D}).to(sum.scalar_type()) : torch::zeros_like(sum);
+        auto dx = torch::empty_like(sum);
+        const auto ws = nb2_workspace_bytes(NB2_WS_NORM_BWD, rows, D, code);
+        auto partials = torch::empty({(int64_t)(ws / 4)}, sum.options().dtype(torch::kFloat32));
+        const int64_t ncols = rms ? D : 2 * D;
+        auto sums = torch::zeros({ncols}, sum.options().dtype(torch::kFloat32));
+        int64_t n = 0;
+        if (rms)
+            detail::check(nb2_add_rmsnorm_bwd(sum.data_ptr(), dy.data_ptr(), detail::ptr_or_null(dsum), w.data_ptr(),
+                                              stats[1].data_ptr<float>(), dx.data_ptr(), partials.data_ptr<float>(), &n,
+                                              rows, D, code, detail::stream()),
+                          "nb2_add_rmsnorm_bwd");
+        else
+            detail::check(nb2_add_layernorm_bwd(sum.data_ptr(), dy.data_ptr(), detail::ptr_or_null(dsum), w.data_ptr(),
+                                                stats[0].data_ptr<float>(), stats[1].data_ptr<float>(), dx.data_ptr(),
+                                                partials.data_ptr<float>(), &n, rows, D, code, detail::stream()),
+                          "nb2_add_layernorm_bwd");
+        if (rows > 0)
+            detail::check(nb2_colreduce_partials(partials.data_ptr<float>(), n, ncols, sums.data_ptr<float>(), detail::stream()),
+                          "nb2_colreduce_partials");
+        const auto wt = (torch::ScalarType)ctx->saved_data["weight_dtype"].toInt();
+        auto shaped = dx.view(grads[1].defined() ? grads[1].sizes() : grads[0].sizes());
+        torch::Tensor dw = rms ? sums.to(wt) : sums.narrow(0, 0, D).to(wt);
+        torch::Tensor db = (!rms && ctx->saved_data["has_bias"].toBool()) ? sums.narrow(0, D, D).to(wt) : torch::Tensor();
+        return {shaped, shaped, dw, db, torch::Tensor(), torch::Tensor()};
+    }
+};
 
 // ------------------------------------------------------------------ LayerNorm (+act)
 struct LayerNormActFunction : public torch::autograd::Function<LayerNormActFunction> {
@@ -180,6 +256,14 @@ public:
                                            (int64_t)detail::fused_act_code(options_.activation));
     }
 
+    // (residual + branch, norm(residual + branch)) in one pass; the module must be affine and unfused
+    std::pair<torch::Tensor, torch::Tensor> forward_residual(torch::Tensor residual, torch::Tensor branch) {
+        if (!options_.elementwise_affine || options_.activation != ActivationType::Identity)
+            throw std::invalid_argument("LayerNorm::forward_residual needs an affine module without a fused activation.");
+        auto out = AddNormFunction::apply(std::move(residual), std::move(branch), weight, detail::opt(bias), options_.eps, false);
+        return {out[0], out[1]};
+    }
+
     torch::Tensor weight, bias;
 
 private:
@@ -266,6 +350,13 @@ public:
             throw std::invalid_argument("RMSNorm expected last dimension " + std::to_string(embed_dim_) + ".");
         return RMSNormActFunction::apply(std::move(input), detail::opt(weight_), options_.eps,
                                          (int64_t)detail::fused_act_code(options_.activation));
+    }
+
+    std::pair<torch::Tensor, torch::Tensor> forward_residual(torch::Tensor residual, torch::Tensor branch) {
+        if (!options_.learnable || options_.activation != ActivationType::Identity)
+            throw std::invalid_argument("RMSNorm::forward_residual needs a learnable module without a fused activation.");
+        auto out = AddNormFunction::apply(std::move(residual), std::move(branch), weight_, c10::nullopt, options_.eps, true);
+        return {out[0], out[1]};
     }
 
 private:
