@@ -277,6 +277,20 @@ def run_suite(args):
     timed("embedding_bwd bf16 (zero table + sort + segmented sum)", lambda: abi.embedding_bwd(dout, ids, 32000),
           65536 * 4096 * 2 + 32000 * 4096 * 2 + 65536 * 4, iters=10)
     del table, dout
+    # BERT front end (bert.hpp:155-194): vocab 30522, D 768, ids [256, 512]
+    Bb, Sb, Db = 256, 512, 768
+    wordt = (0.02 * torch.randn(30522, Db, device=dev, generator=g)).to(bf)
+    post = (0.02 * torch.randn(512, Db, device=dev, generator=g)).to(bf); typt = (0.02 * torch.randn(2, Db, device=dev, generator=g)).to(bf)
+    gb, bb = torch.ones(Db, device=dev).to(bf), torch.zeros(Db, device=dev).to(bf)
+    idb = torch.randint(0, 30522, (Bb, Sb), device=dev, generator=g)
+    yb, sb, mb, rb = abi.bert_embedding_ln_fwd(wordt, post, typt, idb, gb, bb)
+    timed("bert_embedding+layernorm_fwd bf16 [256,512,768] (training: also writes the sum)",
+          lambda: abi.bert_embedding_ln_fwd(wordt, post, typt, idb, gb, bb), 3 * Bb * Sb * Db * 2 + Bb * Sb * 8)
+    timed("bert_embedding+layernorm_fwd bf16 [256,512,768] (inference)",
+          lambda: abi.bert_embedding_ln_fwd(wordt, post, typt, idb, gb, bb, want_backward=False), 2 * Bb * Sb * Db * 2 + Bb * Sb * 8)
+    timed("bert_embedding+layernorm_bwd bf16 (LN bwd + 3 table gradients)",
+          lambda: abi.bert_embedding_ln_bwd(sb, yb, idb, gb, mb, rb, 30522, pos_rows=512), 4 * Bb * Sb * Db * 2 + 30522 * Db * 2, iters=10)
+    del wordt, yb, sb
     q = torch.randn(32, 2048, 32, 128, device=dev, generator=g).to(bf)
     cs = abi.rope_table(2048, 128)
     timed("rope_apply bf16 [32,2048,32,128] (one of q, k)", lambda: abi.rope_apply(q, cs), 2 * q.numel() * 2)

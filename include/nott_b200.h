@@ -67,7 +67,8 @@ enum {
 enum {
     NB2_WS_NORM_BWD = 0,      /* per-CTA dgamma/dbeta (or dweight) partials */
     NB2_WS_EMBEDDING_BWD = 1, /* sort keys + radix-sort temporary           */
-    NB2_WS_ROPE_TABLE = 2     /* cos/sin table [S, hd/2, 2] fp32            */
+    NB2_WS_ROPE_TABLE = 2,    /* cos/sin table [S, hd/2, 2] fp32            */
+    NB2_WS_BERT_EMBEDDING_BWD = 3 /* norm partials + type-row sums + sort scratch */
 };
 
 int nb2_abi_version(void);
@@ -92,6 +93,7 @@ int nb2_device_status(unsigned int* status_host, int clear);
  *   NB2_WS_NORM_BWD      : a = rows, b = D            -> partials buffer
  *   NB2_WS_EMBEDDING_BWD : a = tokens, b = vocab rows -> sort scratch
  *   NB2_WS_ROPE_TABLE    : a = seq_len, b = head_dim  -> cos/sin table
+ *   NB2_WS_BERT_EMBEDDING_BWD : a = tokens (B*S), b = (vocab << 32) | D
  * Returns 0 for unknown `op`.
  */
 size_t nb2_workspace_bytes(int op, int64_t a, int64_t b, int dtype);
@@ -262,6 +264,39 @@ int nb2_embedding_bwd(const void* dout, const void* ids, void* dtable,
                       int64_t tokens, int64_t vocab, int64_t D,
                       int dtype, int index_type,
                       void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------ *
+ * BERT's embedding front end in one pass:
+ *   y[b,s,:] = LayerNorm( word[ids[b,s],:] + pos[s,:] + type[0,:] ) * gamma + beta
+ * Replaces BertEmbeddingImpl::forward
+ * (src/block/details/transformers/bert.hpp:155-194: word gather :162-163,
+ * position gather of arange(S) :176-181, token-type gather of zeros :183-187,
+ * LayerNorm with eps 1e-12 :143-146,189; dropout is left to the caller).
+ * pos ([>= S, D]) and type ([>= 1, D]) may be NULL (the reference's
+ * use_position_embeddings / use_token_type switches).  sum_out ([B*S, D], the
+ * pre-norm sum rounded to the tensor dtype) may be NULL for inference; the
+ * backward needs it, with mean and rstd.  Bad ids behave as in
+ * nb2_embedding_fwd (zero word row + status word).
+ * Backward: dsum = LayerNorm backward of dy (written to the caller's
+ * [B*S, D] buffer), dword = deterministic scatter-add of dsum by id, dpos[s] =
+ * sum over the batch of dsum[:, s] (rows >= S of the pos_rows-row gradient are
+ * zeroed), dtype0 = sum of all dsum rows (gradient of type row 0; other rows
+ * of that table receive none), dgamma_dbeta [2, D] fp32.  dpos / dtype0 may be
+ * NULL.  workspace: nb2_workspace_bytes(NB2_WS_BERT_EMBEDDING_BWD, B*S,
+ * (vocab << 32) | D, dtype).
+ * ------------------------------------------------------------------ */
+int nb2_bert_embedding_ln_fwd(const void* word, const void* pos, const void* type, const void* ids,
+                              const void* gamma, const void* beta,
+                              void* sum_out, void* y, float* mean, float* rstd,
+                              int64_t B, int64_t S, int64_t vocab, int64_t D, double eps,
+                              int dtype, int index_type, int64_t* status, void* stream);
+int nb2_bert_embedding_ln_bwd(const void* sum, const void* dy, const void* ids, const void* gamma,
+                              const float* mean, const float* rstd,
+                              void* dsum, void* dword, void* dpos, int64_t pos_rows, void* dtype0,
+                              float* dgamma_dbeta,
+                              int64_t B, int64_t S, int64_t vocab, int64_t D,
+                              int dtype, int index_type,
+                              void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------ *
  * Rotary embedding, rotate-half pairing (i, i + hd/2).  The reference has no

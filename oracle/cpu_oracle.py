@@ -126,3 +126,43 @@ def add_norm(kind, a, b, gamma, beta, dy, dsum, eps, bf16=False):
     if dy is not None:
         out["dx"] = r["dx"] + (0.0 if dsum is None else _f32(dsum).astype(np.float64))
     return out
+
+
+def bert_embedding(word, pos, type_table, gamma, beta, ids, dy=None, eps=1e-12, bf16=False):
+    """BertEmbeddingImpl::forward (src/block/details/transformers/bert.hpp:155-194): word gather by
+    id, position gather of arange(S), token-type gather of zeros (row 0), sum, LayerNorm(eps 1e-12).
+    With dy: gradients of the three tables (type: row 0 only) and of gamma/beta."""
+    word = _f32(word)
+    ids = np.ascontiguousarray(ids, dtype=np.int64)
+    B, S = ids.shape
+    vocab, D = word.shape
+    # the three rows are added one after the other in fp32, as tensor adds are
+    s = word[ids.reshape(-1)].astype(np.float32)
+    if pos is not None:
+        s = (s + np.tile(_f32(pos)[:S], (B, 1))).astype(np.float32)
+    if type_table is not None:
+        s = (s + _f32(type_table)[0]).astype(np.float32)
+    if bf16:
+        s = _round_bf16(s)
+    r = layernorm_act(s, gamma, beta, None if dy is None else _f32(dy).reshape(B * S, D), eps)
+    out = dict(sum=s, y=r["y"].reshape(B, S, D), dgamma=r["dgamma"], dbeta=r["dbeta"])
+    if dy is not None:
+        dx = r["dx"]
+        if bf16:      # the gradient of the sum is itself a bf16 tensor before it is scattered / reduced
+            dx = _round_bf16(dx.astype(np.float32)).astype(np.float64)
+        out["dsum"] = dx
+        out["dword"] = _scatter_rows(dx, ids.reshape(-1), vocab)
+        out["dpos"] = dx.reshape(B, S, D).sum(axis=0)
+        out["dtype0"] = dx.sum(axis=0)
+    return out
+
+
+def _round_bf16(a):
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    return (((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16).astype(np.uint32).view(np.float32)
+
+
+def _scatter_rows(dx, ids, vocab):
+    out = np.zeros((vocab, dx.shape[1]))
+    np.add.at(out, ids, dx)
+    return out

@@ -14,6 +14,8 @@
 //   - torch::nn::LayerNorm built the way the blocks build it
 //     src/block/details/transformers/classic.hpp:399-404 (options :54-57)
 //   - EBT TokenEmbedding (nn::Embedding gather)   src/block/details/transformers/ebt.hpp:81-160
+//   - BertEmbedding (word + position + type gathers, LayerNorm eps 1e-12)
+//                                                 src/block/details/transformers/bert.hpp:116-204
 //
 // Buffers are always fp32 (or int64 ids) on the host; `compute` picks the dtype
 // the modules run in: 0 = fp32, 1 = fp64 (arbiter for long sums), 2 = native
@@ -28,6 +30,15 @@
 #include "src/activation/apply.hpp"
 #include "src/block/details/transformers/mamba.hpp"
 #include "src/block/details/transformers/ebt.hpp"
+
+// bert.hpp pulls in src/layer/details/recurrent.hpp, which calls an overload of
+// at::Context::setFloat32Precision that libtorch 2.11 no longer has (four lines that set
+// TF32 flags for CUDA RNNs; nothing on this path).  The macro neutralises those calls.
+#include <ATen/cuda/CUDAContext.h>
+#include <torch/cuda.h>
+#define setFloat32Precision(a, b, c) benchmarkCuDNN()
+#include "src/block/details/transformers/bert.hpp"
+#undef setFloat32Precision
 
 namespace {
 
@@ -261,6 +272,46 @@ int ref_add_norm(int rms, const float* a, const float* b, const float* gamma, co
                 store(ln->weight.grad(), dgamma);
                 store(ln->bias.grad(), dbeta);
             }
+        }
+    });
+}
+
+// BertEmbeddingImpl::forward (bert.hpp:155-194), dropout 0.  Tables are given in fp32; gradients of
+// all three tables and of the LayerNorm parameters come back (type table: [type_vocab, D]).
+int ref_bert_embedding(const float* word, const float* pos, const float* type, const float* gamma, const float* beta,
+                       const int64_t* ids, const float* dy, int64_t B, int64_t S, int64_t vocab, int64_t max_pos,
+                       int64_t type_vocab, int64_t D, int compute,
+                       float* y, float* dword, float* dpos, float* dtype, float* dgamma, float* dbeta) {
+    return guarded([&] {
+        namespace Bt = Nott::Block::Details::Transformer::Bert;
+        Bt::EmbeddingOptions opt{};
+        opt.vocab_size = vocab;
+        opt.type_vocab_size = type_vocab;
+        opt.max_position_embeddings = max_pos;
+        opt.dropout = 0.0;
+        opt.use_token_type = type != nullptr;
+        opt.use_position_embeddings = pos != nullptr;
+        Bt::Detail::BertEmbedding emb(D, opt);
+        emb->to(compute_type(compute));
+        auto params = emb->named_parameters();
+        {
+            torch::NoGradGuard ng;
+            params["word_embeddings.weight"].copy_(wrap(word, {vocab, D}, compute));
+            if (pos) params["position_embeddings.weight"].copy_(wrap(pos, {max_pos, D}, compute));
+            if (type) params["token_type_embeddings.weight"].copy_(wrap(type, {type_vocab, D}, compute));
+            params["layer_norm.weight"].copy_(wrap(gamma, {D}, compute));
+            params["layer_norm.bias"].copy_(wrap(beta, {D}, compute));
+        }
+        auto idt = torch::from_blob(const_cast<int64_t*>(ids), {B, S}, torch::kInt64);
+        auto out = emb->forward(idt);
+        store(out, y);
+        if (dy != nullptr) {
+            out.backward(wrap(dy, {B, S, D}, compute));
+            store(params["word_embeddings.weight"].grad(), dword);
+            if (pos) store(params["position_embeddings.weight"].grad(), dpos);
+            if (type) store(params["token_type_embeddings.weight"].grad(), dtype);
+            store(params["layer_norm.weight"].grad(), dgamma);
+            store(params["layer_norm.bias"].grad(), dbeta);
         }
     });
 }

@@ -95,6 +95,26 @@ def add_norm(kind, a, b, gamma, beta, dy, dsum, eps, compute=0):
     return dict(sum=s, y=y, da=da, dgamma=dg, dbeta=db)
 
 
+def bert_embedding(word, pos, type_table, gamma, beta, ids, dy=None, compute=0):
+    word, pos, type_table, gamma, beta, dy = map(_f32, (word, pos, type_table, gamma, beta, dy))
+    ids = np.ascontiguousarray(ids, dtype=np.int64)
+    B, S = ids.shape
+    vocab, D = word.shape
+    max_pos = pos.shape[0] if pos is not None else 0
+    tv = type_table.shape[0] if type_table is not None else 0
+    y = np.empty((B, S, D), np.float32)
+    bwd = dy is not None
+    dword = np.empty((vocab, D), np.float32) if bwd else None
+    dpos = np.empty((max_pos, D), np.float32) if bwd and pos is not None else None
+    dtype = np.empty((tv, D), np.float32) if bwd and type_table is not None else None
+    dg = np.empty(D, np.float32) if bwd else None
+    db = np.empty(D, np.float32) if bwd else None
+    _chk(lib().ref_bert_embedding(_p(word), _p(pos), _p(type_table), _p(gamma), _p(beta), _p(ids), _p(dy), c_int64(B), c_int64(S),
+                                  c_int64(vocab), c_int64(max_pos), c_int64(tv), c_int64(D), c_int(compute),
+                                  _p(y), _p(dword), _p(dpos), _p(dtype), _p(dg), _p(db)))
+    return dict(y=y, dword=dword, dpos=dpos, dtype=dtype, dgamma=dg, dbeta=db)
+
+
 def act(x, dy, act_code, compute=0):
     x, dy = _f32(x), _f32(dy)
     y = np.empty(x.shape, np.float32)

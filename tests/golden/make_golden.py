@@ -115,6 +115,20 @@ def main():
                     rec[f"{k}_{tag}"] = r[k]
         np.savez(OUT / f"{name}.npz", **rec)
 
+    # BertEmbedding: word + position + type gathers and LayerNorm eps 1e-12 (bert.hpp:116-204)
+    gen = torch.Generator().manual_seed(30)
+    vocab, max_pos, tv, D, B, S = 50, 16, 2, 96, 3, 7
+    word, pos, typ = randn(gen, vocab, D, scale=0.02), randn(gen, max_pos, D, scale=0.02), randn(gen, tv, D, scale=0.02)
+    gamma, beta = randn(gen, D, scale=0.02, shift=1.0), randn(gen, D, scale=0.02)
+    ids = torch.randint(0, vocab, (B, S), generator=gen).numpy().astype(np.int64)
+    dy = randn(gen, B, S, D)
+    rec = dict(word=word, pos=pos, type=typ, gamma=gamma, beta=beta, ids=ids, dy=dy)
+    for tag, compute in (("f32", 0), ("f64", 1)):
+        r = R.bert_embedding(word, pos, typ, gamma, beta, ids, dy, compute)
+        for k, v in r.items():
+            rec[f"{k}_{tag}"] = v
+    np.savez(OUT / "bert_embedding.npz", **rec)
+
     gen = torch.Generator().manual_seed(12)
     table = randn(gen, 64, 40, scale=0.02)
     ids = torch.randint(0, 64, (3, 9), generator=gen).numpy().astype(np.int64)

@@ -114,3 +114,18 @@ def test_residual_add_norm_oracle_matches_reference(golden_dir, name):
     if bf16:   # bf16 tensors: the reference's own sum tensor is a bf16 tensor, i.e. the rounded sum
         ob = O.add_norm(kind, g["a"], g["b"], g["gamma"], g.get("beta"), g["dy"], g["dsum"], float(g["eps"]), bf16=True)
         assert np.array_equal(tol.to_bf16_bits(g["sum_f32"]), tol.to_bf16_bits(ob["sum"]))
+
+
+def test_bert_embedding_oracle_matches_reference_module(golden_dir):
+    g = load(golden_dir, "bert_embedding")
+    o = O.bert_embedding(g["word"], g["pos"], g["type"], g["gamma"], g["beta"], g["ids"], g["dy"])
+    # eps = 1e-12 and table values ~0.02: rstd ~ 35, so the outputs are O(1) and the usual tolerance applies
+    tol.fp32_close(o["y"], g["y_f32"], rtol=2e-5, atol=2e-6)
+    np.testing.assert_allclose(o["y"], g["y_f64"], rtol=2e-6, atol=2e-6)
+    np.testing.assert_allclose(o["dword"], g["dword_f64"], rtol=1e-5, atol=1e-4)
+    np.testing.assert_allclose(o["dpos"], g["dpos_f64"][:7], rtol=1e-5, atol=1e-4)
+    assert not g["dpos_f64"][7:].any()                       # positions beyond S get no gradient
+    np.testing.assert_allclose(o["dtype0"], g["dtype_f64"][0], rtol=1e-5, atol=1e-4)
+    assert not g["dtype_f64"][1].any()                       # token types are always 0 (bert.hpp:184)
+    tol.long_sum_close(o["dgamma"], g["dgamma_f64"], 21, ref32=g["dgamma_f32"])
+    tol.long_sum_close(o["dbeta"], g["dbeta_f64"], 21, ref32=g["dbeta_f32"])

@@ -16,7 +16,7 @@ import torch
 F32, BF16 = 0, 1
 ACT_NONE, ACT_GELU, ACT_SILU = 0, 1, 2
 I32, I64 = 0, 1
-WS_NORM_BWD, WS_EMBEDDING_BWD, WS_ROPE_TABLE = 0, 1, 2
+WS_NORM_BWD, WS_EMBEDDING_BWD, WS_ROPE_TABLE, WS_BERT_EMBEDDING_BWD = 0, 1, 2, 3
 
 LIB_PATH = Path(__file__).resolve().parent / "libnott_b200.so"
 
@@ -44,6 +44,9 @@ _SIGNATURES = {
     "nb2_embedding_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "nb2_embedding_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int,
                                   c_void_p, c_size_t, c_void_p]),
+    "nb2_bert_embedding_ln_fwd": (c_int, [c_void_p] * 10 + [c_int64, c_int64, c_int64, c_int64, c_double, c_int, c_int, c_void_p, c_void_p]),
+    "nb2_bert_embedding_ln_bwd": (c_int, [c_void_p] * 9 + [c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_int,
+                                          c_void_p, c_size_t, c_void_p]),
     "nb2_rope_table": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_double, c_void_p]),
     "nb2_rope_apply": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_void_p]),
     "nb2_host_ctx_create": (c_int, [POINTER(c_void_p), c_int64, c_int64, c_int, c_int64]),
@@ -290,6 +293,41 @@ def embedding_bwd(dout, ids, vocab: int):
     check(lib().nb2_embedding_bwd(_p(d2), _p(flat), _p(dtable), flat.numel(), vocab, D, dtype_code(dout.dtype),
                                   _index_code(ids), _p(ws), ws_bytes, _stream()))
     return dtable
+
+
+def bert_embedding_ln_fwd(word, pos, type_table, ids, gamma, beta, eps: float = 1e-12, want_backward: bool = True, status=None):
+    """ids [B, S] -> (y [B, S, D], sum or None, mean or None, rstd or None)."""
+    _dev(word)
+    B, S = ids.shape
+    vocab, D = word.shape
+    y = torch.empty(B, S, D, dtype=word.dtype, device=word.device)
+    ssum = torch.empty(B * S, D, dtype=word.dtype, device=word.device) if want_backward else None
+    mean = torch.empty(B * S, dtype=torch.float32, device=word.device) if want_backward else None
+    rstd = torch.empty(B * S, dtype=torch.float32, device=word.device) if want_backward else None
+    check(lib().nb2_bert_embedding_ln_fwd(_p(word), _p(pos), _p(type_table), _p(ids.contiguous()), _p(gamma), _p(beta), _p(ssum),
+                                          _p(y), _p(mean), _p(rstd), B, S, vocab, D, eps, dtype_code(word.dtype),
+                                          _index_code(ids), _p(status), _stream()))
+    return y, ssum, mean, rstd
+
+
+def bert_embedding_ln_bwd(ssum, dy, ids, gamma, mean, rstd, vocab: int, pos_rows: int = 0, want_type: bool = True):
+    """-> (dword [vocab, D], dpos [pos_rows, D] or None, dtype0 [D] or None, dgamma_dbeta [2, D] fp32,
+    dsum [B*S, D]: the gradient of the pre-norm sum, from which the three table gradients are formed)."""
+    _dev(ssum)
+    B, S = ids.shape
+    D = ssum.shape[-1]
+    code = dtype_code(ssum.dtype)
+    dsum = torch.empty_like(ssum)
+    dword = torch.empty(vocab, D, dtype=ssum.dtype, device=ssum.device)
+    dpos = torch.empty(pos_rows, D, dtype=ssum.dtype, device=ssum.device) if pos_rows else None
+    dtype0 = torch.empty(D, dtype=ssum.dtype, device=ssum.device) if want_type else None
+    grads = torch.empty(2, D, dtype=torch.float32, device=ssum.device)
+    ws_bytes = workspace_bytes(WS_BERT_EMBEDDING_BWD, B * S, (vocab << 32) | D, code)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=ssum.device)
+    check(lib().nb2_bert_embedding_ln_bwd(_p(ssum), _p(dy.reshape(B * S, D)), _p(ids.contiguous()), _p(gamma), _p(mean), _p(rstd),
+                                          _p(dsum), _p(dword), _p(dpos), pos_rows, _p(dtype0), _p(grads), B, S, vocab, D, code,
+                                          _index_code(ids), _p(ws), ws_bytes, _stream()))
+    return dword, dpos, dtype0, grads, dsum
 
 
 # --------------------------------------------------------------------- rope

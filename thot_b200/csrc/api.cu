@@ -175,6 +175,14 @@ size_t nb2_workspace_bytes(int op, int64_t a, int64_t b, int dtype) {
             return (size_t)parts * 2 * (size_t)b * sizeof(float) + 256;
         }
         case NB2_WS_EMBEDDING_BWD: return embedding_bwd_workspace(a, b);
+        case NB2_WS_BERT_EMBEDDING_BWD: {
+            // a = tokens, b = vocab << 32 | D
+            const int64_t vocab = b >> 32, D = b & 0xffffffffLL;
+            if (a < 0 || vocab <= 0 || D <= 0) return 0;
+            const size_t norm_ws = (nb2_workspace_bytes(NB2_WS_NORM_BWD, a, D, dtype) + 255) & ~(size_t)255;
+            const size_t type_ws = ((size_t)257 * D * sizeof(float) + 255) & ~(size_t)255;
+            return norm_ws + type_ws + embedding_bwd_workspace(a, vocab) + 512;
+        }
         case NB2_WS_ROPE_TABLE: return a > 0 && b > 1 ? (size_t)a * (size_t)(b / 2) * 2 * sizeof(float) : 0;
         default: return 0;
     }
@@ -295,6 +303,66 @@ int nb2_embedding_bwd(const void* dout, const void* ids, void* dtable, int64_t t
     int rc = require_device();
     if (rc != 0) return rc;
     return launch_embedding_bwd(dout, ids, dtable, tokens, vocab, D, dtype, index_type, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+int nb2_bert_embedding_ln_fwd(const void* word, const void* pos, const void* type, const void* ids, const void* gamma,
+                              const void* beta, void* sum_out, void* y, float* mean, float* rstd, int64_t B, int64_t S,
+                              int64_t vocab, int64_t D, double eps, int dtype, int index_type, int64_t* status,
+                              void* stream) {
+    NB2_REQUIRE(dtype_ok(dtype) && idx_ok(index_type), NB2_ERR_DTYPE, "bert embedding fwd: dtype=%d index_type=%d", dtype, index_type);
+    NB2_REQUIRE(B >= 0 && S >= 0 && vocab > 0 && D > 0 && D < ((int64_t)1 << 31), NB2_ERR_SHAPE,
+                "bert embedding fwd: B=%lld S=%lld vocab=%lld D=%lld", (long long)B, (long long)S, (long long)vocab, (long long)D);
+    if (B == 0 || S == 0) return 0;
+    NB2_REQUIRE(word && ids && gamma && beta && y, NB2_ERR_NULL, "bert embedding fwd: word, ids, gamma, beta and y must be non-NULL");
+    int rc = require_device();
+    if (rc != 0) return rc;
+    return launch_bert_embed_ln_fwd(word, pos, type, ids, gamma, beta, sum_out, y, mean, rstd, B, S, vocab, D, (float)eps,
+                                    dtype, index_type, status, (cudaStream_t)stream);
+}
+
+int nb2_bert_embedding_ln_bwd(const void* sum, const void* dy, const void* ids, const void* gamma, const float* mean,
+                              const float* rstd, void* dsum, void* dword, void* dpos, int64_t pos_rows, void* dtype0,
+                              float* dgamma_dbeta, int64_t B, int64_t S, int64_t vocab, int64_t D, int dtype,
+                              int index_type, void* workspace, size_t workspace_bytes, void* stream) {
+    NB2_REQUIRE(dtype_ok(dtype) && idx_ok(index_type), NB2_ERR_DTYPE, "bert embedding bwd: dtype=%d index_type=%d", dtype, index_type);
+    NB2_REQUIRE(B >= 0 && S >= 0 && vocab > 0 && D > 0 && pos_rows >= (dpos ? S : 0), NB2_ERR_SHAPE,
+                "bert embedding bwd: B=%lld S=%lld vocab=%lld D=%lld pos_rows=%lld", (long long)B, (long long)S,
+                (long long)vocab, (long long)D, (long long)pos_rows);
+    NB2_REQUIRE(sum && dy && ids && gamma && mean && rstd && dsum && dword && dgamma_dbeta && workspace, NB2_ERR_NULL,
+                "bert embedding bwd: a required pointer is NULL");
+    const int64_t tokens = B * S;
+    const size_t need = nb2_workspace_bytes(NB2_WS_BERT_EMBEDDING_BWD, tokens, vocab * ((int64_t)1 << 32) + D, dtype);
+    NB2_REQUIRE(workspace_bytes >= need, NB2_ERR_WORKSPACE, "bert embedding bwd: workspace %zu < required %zu", workspace_bytes, need);
+    int rc = require_device();
+    if (rc != 0) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t elt = dtype == NB2_F32 ? 4 : 2;
+    // workspace: [norm partials | 257 * D floats for the token-type sum | embedding sort scratch]
+    uint8_t* base = (uint8_t*)(((uintptr_t)workspace + 255) & ~(uintptr_t)255);
+    const size_t norm_ws = (nb2_workspace_bytes(NB2_WS_NORM_BWD, tokens, D, dtype) + 255) & ~(size_t)255;
+    float* partials = (float*)base;
+    float* type_scratch = (float*)(base + norm_ws);
+    const size_t type_ws = ((size_t)257 * D * sizeof(float) + 255) & ~(size_t)255;
+    void* sort_ws = base + norm_ws + type_ws;
+    const size_t sort_bytes = embedding_bwd_workspace(tokens, vocab);
+    if (dpos != nullptr) {
+        rc = cuda_status(cudaMemsetAsync(dpos, 0, (size_t)pos_rows * D * elt, st), "bert embedding bwd: clearing the position gradient");
+        if (rc != 0) return rc;
+    }
+    if (tokens == 0) {
+        rc = cuda_status(cudaMemsetAsync(dword, 0, (size_t)vocab * D * elt, st), "bert embedding bwd memset");
+        if (rc == 0) rc = cuda_status(cudaMemsetAsync(dgamma_dbeta, 0, (size_t)2 * D * 4, st), "bert embedding bwd memset");
+        if (rc == 0 && dtype0) rc = cuda_status(cudaMemsetAsync(dtype0, 0, (size_t)D * elt, st), "bert embedding bwd memset");
+        return rc;
+    }
+    int64_t n = 0;
+    rc = nb2_layernorm_bwd(sum, dy, gamma, nullptr, mean, rstd, dsum, partials, &n, tokens, D, dtype, NB2_ACT_NONE, stream);
+    if (rc != 0) return rc;
+    rc = nb2_colreduce_partials(partials, n, 2 * D, dgamma_dbeta, stream);
+    if (rc != 0) return rc;
+    rc = launch_embedding_bwd(dsum, ids, dword, tokens, vocab, D, dtype, index_type, sort_ws, sort_bytes, st);
+    if (rc != 0) return rc;
+    return launch_bert_embed_table_grads(dsum, dpos, dtype0, type_scratch, B, S, D, dtype, st);
 }
 
 int nb2_rope_table(float* cos_sin, const int32_t* positions, int64_t S, int64_t hd, double theta, void* stream) {

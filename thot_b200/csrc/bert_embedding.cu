@@ -1,0 +1,267 @@
+// BERT's embedding front end in one pass: word + position + token-type rows summed and
+// LayerNorm'ed per token.
+//
+// Reference: BertEmbeddingImpl::forward (src/block/details/transformers/bert.hpp:155-194):
+//   embeddings = word_embeddings(ids)                         (:162-163, ids int64 [B, S])
+//   embeddings += position_embeddings(arange(S) per batch)    (:176-181)
+//   embeddings += token_type_embeddings(zeros)                (:183-187: always row 0)
+//   embeddings  = layer_norm(embeddings)  eps = 1e-12         (:143-146, :189)
+// which libtorch runs as three gathers, two adds and a LayerNorm: 6 passes over [B*S, D].
+// Here: one gather-read of the word row per token (the position rows are shared by the batch
+// and stay in L2, the type row in L1), one write of the output, optionally one of the sum
+// (the backward's LayerNorm input).
+#include "launchers.h"
+#include "norm_kernels.cuh"
+
+namespace nb2 {
+
+template <typename I> __device__ __forceinline__ int64_t load_token(const void* ids, int64_t t) {
+    return (int64_t)reinterpret_cast<const I*>(ids)[t];
+}
+
+template <typename T, typename I, int TPR, int VPT>
+__global__ void __launch_bounds__((TPR > 256 ? TPR : 256), (TPR > 256 ? 1 : 2))
+bert_embed_ln_fwd_kernel(const T* __restrict__ word, const T* __restrict__ pos, const T* __restrict__ type,
+                         const void* __restrict__ ids, const T* __restrict__ gamma, const T* __restrict__ beta,
+                         T* __restrict__ sum_out, T* __restrict__ y, float* __restrict__ mean_out,
+                         float* __restrict__ rstd_out, int64_t tokens, int64_t S, int64_t vocab, int D, float eps,
+                         int64_t* __restrict__ status) {
+    constexpr int EPV = VecTraits<T>::EPV;
+    constexpr int THREADS = (TPR > 256 ? TPR : 256);
+    constexpr int RPC = THREADS / TPR;
+    constexpr int WPR = (TPR + 31) / 32;
+    __shared__ float red_a[RPC][WPR], red_b[RPC][WPR];
+    const int nvec = D / EPV;
+    const int slot = threadIdx.x / TPR, tr = threadIdx.x % TPR;
+    const float inv_d = 1.0f / (float)D;
+    pdl_release();
+    pdl_wait();
+
+    uint4 gpk[VPT], bpk[VPT], tpk[VPT];
+    bool valid[VPT];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        valid[j] = (tr + j * TPR) < nvec;
+        if (valid[j]) {
+            gpk[j] = ld_param(gamma + (size_t)(tr + j * TPR) * EPV);
+            bpk[j] = ld_param(beta + (size_t)(tr + j * TPR) * EPV);
+            if (type != nullptr) tpk[j] = ld_param(type + (size_t)(tr + j * TPR) * EPV);     // row 0
+        }
+    }
+    const int64_t stride = (int64_t)gridDim.x * RPC;
+    for (int64_t t = (int64_t)blockIdx.x * RPC + slot; t < tokens; t += stride) {
+        const int64_t id = load_token<I>(ids, t);
+        const bool ok = id >= 0 && id < vocab;
+        if (!ok && tr == 0 && status != nullptr) { status[0] = 1; status[1] = t; }
+        const T* wrow = word + (ok ? id : 0) * (int64_t)D;
+        const T* prow = pos != nullptr ? pos + (t % S) * (int64_t)D : nullptr;
+        float v[VPT][EPV];
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            if (valid[j]) {
+                const size_t off = (size_t)(tr + j * TPR) * EPV;
+                if (ok) unpack<T>(__ldg(reinterpret_cast<const uint4*>(wrow + off)), v[j]);
+                else {
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e) v[j][e] = 0.f;
+                }
+                float a[EPV];
+                if (prow != nullptr) {
+                    unpack<T>(__ldg(reinterpret_cast<const uint4*>(prow + off)), a);
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e) v[j][e] += a[e];
+                }
+                if (type != nullptr) {
+                    unpack<T>(tpk[j], a);
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e) v[j][e] += a[e];
+                }
+                const uint4 packed = pack<T>(v[j]);                       // the sum as a tensor of dtype T
+                if (sum_out != nullptr) st_stream(sum_out + t * (int64_t)D + off, packed);
+                unpack<T>(packed, v[j]);
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) sum += v[j][e];
+            }
+        }
+        const float mu = row_sum<TPR>(sum, red_a[slot], slot + 1) * inv_d;
+        float q = 0.f;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j)
+            if (valid[j]) {
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) { v[j][e] -= mu; q = fmaf(v[j][e], v[j][e], q); }
+            }
+        const float rs = rsqrtf(row_sum<TPR>(q, red_b[slot], slot + 1) * inv_d + eps);
+        if (tr == 0) {
+            if (mean_out != nullptr) mean_out[t] = mu;
+            if (rstd_out != nullptr) rstd_out[t] = rs;
+        }
+#pragma unroll
+        for (int j = 0; j < VPT; ++j)
+            if (valid[j]) {
+                float g[EPV], b[EPV], o[EPV];
+                unpack<T>(gpk[j], g);
+                unpack<T>(bpk[j], b);
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) o[e] = fmaf(v[j][e] * rs, g[e], b[e]);
+                st_stream(y + t * (int64_t)D + (size_t)(tr + j * TPR) * EPV, pack<T>(o));
+            }
+    }
+}
+
+// any width / alignment: one warp per token, scalar
+template <typename T, typename I>
+__global__ void __launch_bounds__(256)
+bert_embed_ln_fwd_generic(const T* __restrict__ word, const T* __restrict__ pos, const T* __restrict__ type,
+                          const void* __restrict__ ids, const T* __restrict__ gamma, const T* __restrict__ beta,
+                          T* __restrict__ sum_out, T* __restrict__ y, float* __restrict__ mean_out,
+                          float* __restrict__ rstd_out, int64_t tokens, int64_t S, int64_t vocab, int64_t D, float eps,
+                          int64_t* __restrict__ status) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
+    const float inv_d = 1.0f / (float)D;
+    for (int64_t t = warp; t < tokens; t += nwarps) {
+        const int64_t id = load_token<I>(ids, t);
+        const bool ok = id >= 0 && id < vocab;
+        if (!ok && lane == 0 && status != nullptr) { status[0] = 1; status[1] = t; }
+        auto value = [&](int64_t c) {
+            float v = ok ? to_f32(word[id * D + c]) : 0.f;
+            if (pos != nullptr) v += to_f32(pos[(t % S) * D + c]);
+            if (type != nullptr) v += to_f32(type[c]);
+            return to_f32(from_f32<T>(v));
+        };
+        float s = 0.f;
+        for (int64_t c = lane; c < D; c += 32) s += value(c);
+        const float mu = warp_sum(s) * inv_d;
+        float q = 0.f;
+        for (int64_t c = lane; c < D; c += 32) { const float d = value(c) - mu; q = fmaf(d, d, q); }
+        const float rs = rsqrtf(warp_sum(q) * inv_d + eps);
+        if (lane == 0) {
+            if (mean_out != nullptr) mean_out[t] = mu;
+            if (rstd_out != nullptr) rstd_out[t] = rs;
+        }
+        for (int64_t c = lane; c < D; c += 32) {
+            const float v = value(c);
+            if (sum_out != nullptr) sum_out[t * D + c] = from_f32<T>(v);
+            y[t * D + c] = from_f32<T>(fmaf((v - mu) * rs, to_f32(gamma[c]), to_f32(beta[c])));
+        }
+    }
+}
+
+// dpos[s, :] = sum_b dsum[b, s, :]  (fp32 accumulation, rounded once)
+template <typename T>
+__global__ void __launch_bounds__(256)
+batch_sum_kernel(const T* __restrict__ dsum, T* __restrict__ dpos, int64_t B, int64_t S, int64_t D) {
+    const int64_t total = S * D;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        float acc = 0.f;
+        for (int64_t b = 0; b < B; ++b) acc += to_f32(dsum[b * total + i]);
+        dpos[i] = from_f32<T>(acc);
+    }
+}
+// per-CTA column sums of a [rows, D] tensor into fp32 partials [gridDim.x, D] (for the token-type row)
+template <typename T>
+__global__ void __launch_bounds__(256)
+column_partials_kernel(const T* __restrict__ x, float* __restrict__ partials, int64_t rows, int64_t D, int64_t rows_per_cta) {
+    const int64_t r0 = (int64_t)blockIdx.x * rows_per_cta;
+    const int64_t r1 = r0 + rows_per_cta < rows ? r0 + rows_per_cta : rows;
+    for (int64_t c = threadIdx.x; c < D; c += blockDim.x) {
+        float acc = 0.f;
+        for (int64_t r = r0; r < r1; ++r) acc += to_f32(x[r * D + c]);
+        partials[(size_t)blockIdx.x * D + c] = acc;
+    }
+}
+__global__ void __launch_bounds__(256)
+cast_row_kernel(const float* __restrict__ src, void* __restrict__ dst, int64_t n, int bf16) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    if (bf16) reinterpret_cast<__nv_bfloat16*>(dst)[i] = __float2bfloat16_rn(src[i]);
+    else reinterpret_cast<float*>(dst)[i] = src[i];
+}
+
+template <typename T, typename I>
+static int launch_fwd_ti(const void* word, const void* pos, const void* type, const void* ids, const void* gamma,
+                         const void* beta, void* sum_out, void* y, float* mean, float* rstd, int64_t tokens, int64_t S,
+                         int64_t vocab, int64_t D, float eps, int64_t* status, cudaStream_t st) {
+    constexpr int EPV = VecTraits<T>::EPV;
+    const bool aligned = aligned16(word) && aligned16(y) && aligned16(gamma) && aligned16(beta) &&
+                         (pos == nullptr || aligned16(pos)) && (type == nullptr || aligned16(type)) &&
+                         (sum_out == nullptr || aligned16(sum_out));
+    constexpr int VPT = 16 / EPV;                     // 16 elements per thread and token for either type
+    const int tpr = (D % EPV == 0 && aligned) ? pick_tpr(D / EPV, VPT) : 0;
+    const int sms = sm_count();
+#define NB2_BERT_LAUNCH(TPR_)                                                                                     \
+    {                                                                                                             \
+        constexpr int THREADS = (TPR_ > 256 ? TPR_ : 256);                                                        \
+        constexpr int RPC = THREADS / TPR_;                                                                        \
+        int64_t need = (tokens + RPC - 1) / RPC, cap = (int64_t)sms * (TPR_ > 256 ? 1 : 2);                       \
+        const cudaError_t e = launch_pdl(bert_embed_ln_fwd_kernel<T, I, TPR_, VPT>, dim3((unsigned)(need < cap ? need : cap)), \
+                                         dim3(THREADS), 0, st, (const T*)word, (const T*)pos, (const T*)type, ids, \
+                                         (const T*)gamma, (const T*)beta, (T*)sum_out, (T*)y, mean, rstd, tokens, S, \
+                                         vocab, (int)D, eps, status);                                             \
+        return cuda_status(e, "bert embedding + layernorm launch");                                               \
+    }
+    switch (tpr) {
+        case 32: NB2_BERT_LAUNCH(32)
+        case 64: NB2_BERT_LAUNCH(64)
+        case 128: NB2_BERT_LAUNCH(128)
+        case 256: NB2_BERT_LAUNCH(256)
+        case 512: NB2_BERT_LAUNCH(512)
+        default: break;
+    }
+#undef NB2_BERT_LAUNCH
+    int64_t need = (tokens + 7) / 8, cap = (int64_t)sms * 8;
+    bert_embed_ln_fwd_generic<T, I><<<(unsigned)(need < cap ? need : cap), 256, 0, st>>>(
+        (const T*)word, (const T*)pos, (const T*)type, ids, (const T*)gamma, (const T*)beta, (T*)sum_out, (T*)y, mean,
+        rstd, tokens, S, vocab, D, eps, status);
+    return cuda_status(cudaGetLastError(), "bert embedding + layernorm (any width) launch");
+}
+
+int launch_bert_embed_ln_fwd(const void* word, const void* pos, const void* type, const void* ids, const void* gamma,
+                             const void* beta, void* sum_out, void* y, float* mean, float* rstd, int64_t B, int64_t S,
+                             int64_t vocab, int64_t D, float eps, int dtype, int index_type, int64_t* status,
+                             cudaStream_t st) {
+    const int64_t tokens = B * S;
+    if (dtype == NB2_F32)
+        return index_type == NB2_I32
+                   ? launch_fwd_ti<float, int32_t>(word, pos, type, ids, gamma, beta, sum_out, y, mean, rstd, tokens, S, vocab, D, eps, status, st)
+                   : launch_fwd_ti<float, int64_t>(word, pos, type, ids, gamma, beta, sum_out, y, mean, rstd, tokens, S, vocab, D, eps, status, st);
+    return index_type == NB2_I32
+               ? launch_fwd_ti<__nv_bfloat16, int32_t>(word, pos, type, ids, gamma, beta, sum_out, y, mean, rstd, tokens, S, vocab, D, eps, status, st)
+               : launch_fwd_ti<__nv_bfloat16, int64_t>(word, pos, type, ids, gamma, beta, sum_out, y, mean, rstd, tokens, S, vocab, D, eps, status, st);
+}
+
+// dpos (first S rows; the caller zeroed the rest) and dtype0 from dsum [B, S, D]
+int launch_bert_embed_table_grads(const void* dsum, void* dpos, void* dtype0, float* scratch /* [257 * D] */,
+                                  int64_t B, int64_t S, int64_t D, int dtype, cudaStream_t st) {
+    const int64_t total = S * D, tokens = B * S;
+    if (tokens == 0 || D == 0) return 0;
+    if (dpos != nullptr) {
+        int64_t grid = (total + 255) / 256;
+        const int64_t cap = (int64_t)sm_count() * 16;
+        if (grid > cap) grid = cap;
+        if (dtype == NB2_F32) batch_sum_kernel<float><<<(unsigned)grid, 256, 0, st>>>((const float*)dsum, (float*)dpos, B, S, D);
+        else batch_sum_kernel<__nv_bfloat16><<<(unsigned)grid, 256, 0, st>>>((const __nv_bfloat16*)dsum, (__nv_bfloat16*)dpos, B, S, D);
+        int rc = cuda_status(cudaGetLastError(), "bert position gradient launch");
+        if (rc != 0) return rc;
+    }
+    if (dtype0 != nullptr) {
+        int64_t parts = (tokens + 255) / 256;
+        if (parts > 256) parts = 256;
+        const int64_t rows_per = (tokens + parts - 1) / parts;
+        if (dtype == NB2_F32) column_partials_kernel<float><<<(unsigned)parts, 256, 0, st>>>((const float*)dsum, scratch, tokens, D, rows_per);
+        else column_partials_kernel<__nv_bfloat16><<<(unsigned)parts, 256, 0, st>>>((const __nv_bfloat16*)dsum, scratch, tokens, D, rows_per);
+        int rc = cuda_status(cudaGetLastError(), "bert token-type partials launch");
+        if (rc != 0) return rc;
+        float* total_row = scratch + (size_t)256 * D;
+        rc = launch_colreduce(scratch, parts, D, total_row, st);
+        if (rc != 0) return rc;
+        cast_row_kernel<<<(unsigned)((D + 255) / 256), 256, 0, st>>>(total_row, dtype0, D, dtype == NB2_BF16);
+        return cuda_status(cudaGetLastError(), "bert token-type gradient launch");
+    }
+    return 0;
+}
+
+}  // namespace nb2

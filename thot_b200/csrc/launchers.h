@@ -16,6 +16,12 @@ int launch_embedding_fwd(const void* table, const void* ids, void* out, int64_t 
 size_t embedding_bwd_workspace(int64_t tokens, int64_t vocab);
 int launch_embedding_bwd(const void* dout, const void* ids, void* dtable, int64_t tokens, int64_t vocab,
                          int64_t D, int dtype, int index_type, void* ws, size_t ws_bytes, cudaStream_t st);
+int launch_bert_embed_ln_fwd(const void* word, const void* pos, const void* type, const void* ids, const void* gamma,
+                             const void* beta, void* sum_out, void* y, float* mean, float* rstd, int64_t B, int64_t S,
+                             int64_t vocab, int64_t D, float eps, int dtype, int index_type, int64_t* status,
+                             cudaStream_t st);
+int launch_bert_embed_table_grads(const void* dsum, void* dpos, void* dtype0, float* scratch, int64_t B, int64_t S,
+                                  int64_t D, int dtype, cudaStream_t st);
 int launch_rope_table(float* cos_sin, const int32_t* positions, int64_t S, int64_t hd, double theta, cudaStream_t st);
 int launch_rope_apply(const void* x, const float* cos_sin, void* out, int64_t B, int64_t S, int64_t H,
                       int64_t hd, int dtype, bool inverse, cudaStream_t st);

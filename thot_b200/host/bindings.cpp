@@ -56,6 +56,25 @@ PYBIND11_MODULE(_nott_b200_host, m) {
         for (auto& kv : mod->named_parameters()) { names.push_back(kv.key()); out.push_back(kv.value().grad()); }
         return std::make_pair(names, out);
     });
+    m.def("bert_embedding_module_step", [](int64_t D, int64_t vocab, int64_t type_vocab, int64_t max_pos, torch::Tensor ids,
+                                           torch::Tensor dy, std::vector<torch::Tensor> values) {
+        pybind11::gil_scoped_release no_gil;
+        nb::BertEmbeddingOptions opt;
+        opt.vocab_size = vocab; opt.type_vocab_size = type_vocab; opt.max_position_embeddings = max_pos; opt.dropout = 0.0;
+        nb::BertEmbedding mod(D, opt);
+        mod->to(dy.device(), dy.scalar_type());
+        std::vector<std::string> names;
+        {
+            torch::NoGradGuard ng;
+            size_t i = 0;
+            for (auto& kv : mod->named_parameters()) { names.push_back(kv.key()); if (i < values.size()) kv.value().copy_(values[i]); ++i; }
+        }
+        auto y = mod->forward(ids);
+        y.backward(dy);
+        std::vector<torch::Tensor> out{y.detach()};
+        for (auto& kv : mod->named_parameters()) out.push_back(kv.value().grad());
+        return std::make_pair(names, out);
+    });
     m.def("module_errors", []() {
         // the exception types the reference throws for the same mistakes (mamba.hpp:116-132)
         std::vector<std::string> seen;

@@ -9,6 +9,7 @@
 //                              (src/block/details/transformers/classic.hpp:399-404, options :54-57),
 //                              optionally fused with the activation that follows it
 //   Nott::B200::RMSNorm     <- Mamba::Detail::RMSNorm (src/block/details/transformers/mamba.hpp:110-150)
+//   Nott::B200::BertEmbedding <- Bert::Detail::BertEmbedding (bert.hpp:116-204): gathers + LayerNorm in one pass
 //   Nott::B200::Embedding   <- torch::nn::Embedding (bert.hpp:126-128, ebt.hpp:94-96)
 //   LayerNorm/RMSNorm::forward_residual <- `output = residual + branch; norm(output)` in one pass
 //                              (classic.hpp:442-445, bert.hpp:291-293, mamba.hpp:409-415)
@@ -505,6 +506,111 @@ public:
     torch::Tensor weight;
 };
 TORCH_MODULE(Embedding);
+
+// ------------------------------------------------------------------- BERT embedding
+// BertEmbeddingImpl (src/block/details/transformers/bert.hpp:116-204) as one forward kernel and one
+// fused backward: word[ids] + position[arange(S)] + token_type[0], LayerNorm(eps 1e-12), dropout.
+struct BertEmbeddingFunction : public torch::autograd::Function<BertEmbeddingFunction> {
+    static torch::Tensor forward(torch::autograd::AutogradContext* ctx, torch::Tensor ids, torch::Tensor word,
+                                 c10::optional<torch::Tensor> pos_opt, c10::optional<torch::Tensor> type_opt,
+                                 torch::Tensor gamma, torch::Tensor beta, double eps) {
+        detail::require_cuda(word, "BERT embeddings");
+        if (ids.dim() != 2 || (ids.scalar_type() != torch::kInt64 && ids.scalar_type() != torch::kInt32))
+            throw std::invalid_argument("BERT embeddings expect [batch, sequence] int32 or int64 token ids.");
+        const int code = detail::dtype_code(word, "BERT embeddings");
+        auto w = word.contiguous();
+        auto pos = detail::param_like(pos_opt.value_or(torch::Tensor()), w);
+        auto type = detail::param_like(type_opt.value_or(torch::Tensor()), w);
+        auto g = detail::param_like(gamma, w), b = detail::param_like(beta, w);
+        const auto B = ids.size(0), S = ids.size(1), vocab = w.size(0), D = w.size(1);
+        if (pos.defined() && pos.size(0) < S) throw std::invalid_argument("BERT embeddings: sequence longer than max_position_embeddings.");
+        auto idc = ids.contiguous();
+        auto y = torch::empty({B, S, D}, w.options());
+        auto sum = torch::empty({B * S, D}, w.options());
+        auto stats = torch::empty({2, B * S}, w.options().dtype(torch::kFloat32));
+        detail::check(nb2_bert_embedding_ln_fwd(w.data_ptr(), detail::ptr_or_null(pos), detail::ptr_or_null(type), idc.data_ptr(),
+                                                g.data_ptr(), b.data_ptr(), sum.data_ptr(), y.data_ptr(),
+                                                stats[0].data_ptr<float>(), stats[1].data_ptr<float>(), B, S, vocab, D, eps, code,
+                                                idc.scalar_type() == torch::kInt32 ? NB2_I32 : NB2_I64, nullptr, detail::stream()),
+                      "nb2_bert_embedding_ln_fwd");
+        ctx->save_for_backward({sum, idc, g, stats});
+        ctx->saved_data["vocab"] = vocab;
+        ctx->saved_data["pos_rows"] = pos.defined() ? pos.size(0) : (int64_t)0;
+        ctx->saved_data["type_rows"] = type.defined() ? type.size(0) : (int64_t)0;
+        return y;
+    }
+    static torch::autograd::tensor_list backward(torch::autograd::AutogradContext* ctx, torch::autograd::tensor_list grads) {
+        auto saved = ctx->get_saved_variables();
+        auto sum = saved[0], ids = saved[1], g = saved[2], stats = saved[3];
+        const auto B = ids.size(0), S = ids.size(1), D = sum.size(1);
+        const auto vocab = ctx->saved_data["vocab"].toInt(), pos_rows = ctx->saved_data["pos_rows"].toInt(),
+                   type_rows = ctx->saved_data["type_rows"].toInt();
+        const int code = detail::dtype_code(sum, "BERT embeddings backward");
+        auto dy = grads[0].contiguous().to(sum.scalar_type());
+        auto dsum = torch::empty_like(sum);
+        auto dword = torch::empty({vocab, D}, sum.options());
+        torch::Tensor dpos, dtype;
+        if (pos_rows > 0) dpos = torch::empty({pos_rows, D}, sum.options());
+        if (type_rows > 0) dtype = torch::zeros({type_rows, D}, sum.options());       // rows other than 0 get no gradient
+        auto sums = torch::empty({2, D}, sum.options().dtype(torch::kFloat32));
+        const auto ws = nb2_workspace_bytes(NB2_WS_BERT_EMBEDDING_BWD, B * S, (vocab << 32) | D, code);
+        auto scratch = torch::empty({(int64_t)ws}, sum.options().dtype(torch::kUInt8));
+        detail::check(nb2_bert_embedding_ln_bwd(sum.data_ptr(), dy.data_ptr(), ids.data_ptr(), g.data_ptr(),
+                                                stats[0].data_ptr<float>(), stats[1].data_ptr<float>(), dsum.data_ptr(),
+                                                dword.data_ptr(), dpos.defined() ? dpos.data_ptr() : nullptr, pos_rows,
+                                                type_rows > 0 ? dtype.data_ptr() : nullptr, sums.data_ptr<float>(), B, S, vocab, D,
+                                                code, ids.scalar_type() == torch::kInt32 ? NB2_I32 : NB2_I64, scratch.data_ptr(),
+                                                ws, detail::stream()),
+                      "nb2_bert_embedding_ln_bwd");
+        return {torch::Tensor(), dword, dpos, dtype, sums[0].to(g.scalar_type()), sums[1].to(g.scalar_type()), torch::Tensor()};
+    }
+};
+
+struct BertEmbeddingOptions {            // bert.hpp:50-57
+    std::int64_t vocab_size{30522};
+    std::int64_t type_vocab_size{2};
+    std::int64_t max_position_embeddings{512};
+    double dropout{0.1};
+    bool use_token_type{true};
+    bool use_position_embeddings{true};
+};
+
+class BertEmbeddingImpl : public torch::nn::Module {
+public:
+    BertEmbeddingImpl(std::int64_t embed_dim, BertEmbeddingOptions options) : embed_dim_(embed_dim), options_(options) {
+        if (embed_dim_ <= 0) throw std::invalid_argument("BERT embeddings require a positive embedding dimension.");
+        if (options_.vocab_size <= 0) throw std::invalid_argument("BERT embeddings on this path require a vocabulary.");
+        // same submodule and parameter names as the reference: word_embeddings.weight, ..., layer_norm.bias
+        word_embeddings_ = register_module("word_embeddings", Embedding(options_.vocab_size, embed_dim_));
+        if (options_.use_token_type && options_.type_vocab_size > 0)
+            token_type_embeddings_ = register_module("token_type_embeddings", Embedding(options_.type_vocab_size, embed_dim_));
+        if (options_.use_position_embeddings && options_.max_position_embeddings > 0)
+            position_embeddings_ = register_module("position_embeddings", Embedding(options_.max_position_embeddings, embed_dim_));
+        LayerNormOptions norm;
+        norm.eps = 1e-12;                                                     // hard-coded in the reference (bert.hpp:143-146)
+        layer_norm_ = register_module("layer_norm", LayerNorm(embed_dim_, norm));
+        if (options_.dropout > 0.0) dropout_ = register_module("dropout", torch::nn::Dropout(torch::nn::DropoutOptions(options_.dropout)));
+    }
+
+    torch::Tensor forward(torch::Tensor input) {
+        if (!input.defined()) return input;
+        torch::Tensor out = BertEmbeddingFunction::apply(
+            std::move(input), word_embeddings_->weight,
+            position_embeddings_ ? detail::opt(position_embeddings_->weight) : c10::nullopt,
+            token_type_embeddings_ ? detail::opt(token_type_embeddings_->weight) : c10::nullopt, layer_norm_->weight,
+            layer_norm_->bias, 1e-12);
+        if (dropout_) out = dropout_->forward(out);
+        return out;
+    }
+
+private:
+    std::int64_t embed_dim_{};
+    BertEmbeddingOptions options_{};
+    Embedding word_embeddings_{nullptr}, token_type_embeddings_{nullptr}, position_embeddings_{nullptr};
+    LayerNorm layer_norm_{nullptr};
+    torch::nn::Dropout dropout_{nullptr};
+};
+TORCH_MODULE(BertEmbedding);
 
 // ----------------------------------------------------------------------------- rotary
 // cos/sin of angle(s, i) = pos[s] * theta^(-2i/hd), built once and shared by q, k and the backward
