@@ -93,7 +93,7 @@ int nb2_device_status(unsigned int* status_host, int clear);
  *   NB2_WS_NORM_BWD      : a = rows, b = D            -> partials buffer
  *   NB2_WS_EMBEDDING_BWD : a = tokens, b = vocab rows -> sort scratch
  *   NB2_WS_ROPE_TABLE    : a = seq_len, b = head_dim  -> cos/sin table
- *   NB2_WS_BERT_EMBEDDING_BWD : a = tokens (B*S), b = (vocab << 32) | D
+ *   NB2_WS_BERT_EMBEDDING_BWD : a = (B << 32) | S, b = (vocab << 32) | D
  * Returns 0 for unknown `op`.
  */
 size_t nb2_workspace_bytes(int op, int64_t a, int64_t b, int dtype);
@@ -282,8 +282,8 @@ int nb2_embedding_bwd(const void* dout, const void* ids, void* dtable,
  * sum over the batch of dsum[:, s] (rows >= S of the pos_rows-row gradient are
  * zeroed), dtype0 = sum of all dsum rows (gradient of type row 0; other rows
  * of that table receive none), dgamma_dbeta [2, D] fp32.  dpos / dtype0 may be
- * NULL.  workspace: nb2_workspace_bytes(NB2_WS_BERT_EMBEDDING_BWD, B*S,
- * (vocab << 32) | D, dtype).
+ * NULL.  workspace: nb2_workspace_bytes(NB2_WS_BERT_EMBEDDING_BWD,
+ * (B << 32) | S, (vocab << 32) | D, dtype).
  * ------------------------------------------------------------------ */
 int nb2_bert_embedding_ln_fwd(const void* word, const void* pos, const void* type, const void* ids,
                               const void* gamma, const void* beta,

@@ -322,7 +322,7 @@ def bert_embedding_ln_bwd(ssum, dy, ids, gamma, mean, rstd, vocab: int, pos_rows
     dpos = torch.empty(pos_rows, D, dtype=ssum.dtype, device=ssum.device) if pos_rows else None
     dtype0 = torch.empty(D, dtype=ssum.dtype, device=ssum.device) if want_type else None
     grads = torch.empty(2, D, dtype=torch.float32, device=ssum.device)
-    ws_bytes = workspace_bytes(WS_BERT_EMBEDDING_BWD, B * S, (vocab << 32) | D, code)
+    ws_bytes = workspace_bytes(WS_BERT_EMBEDDING_BWD, (B << 32) | S, (vocab << 32) | D, code)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=ssum.device)
     check(lib().nb2_bert_embedding_ln_bwd(_p(ssum), _p(dy.reshape(B * S, D)), _p(ids.contiguous()), _p(gamma), _p(mean), _p(rstd),
                                           _p(dsum), _p(dword), _p(dpos), pos_rows, _p(dtype0), _p(grads), B, S, vocab, D, code,

@@ -176,12 +176,13 @@ size_t nb2_workspace_bytes(int op, int64_t a, int64_t b, int dtype) {
         }
         case NB2_WS_EMBEDDING_BWD: return embedding_bwd_workspace(a, b);
         case NB2_WS_BERT_EMBEDDING_BWD: {
-            // a = tokens, b = vocab << 32 | D
-            const int64_t vocab = b >> 32, D = b & 0xffffffffLL;
+            // a = B << 32 | S, b = vocab << 32 | D
+            const int64_t B = a >> 32, S = a & 0xffffffffLL, vocab = b >> 32, D = b & 0xffffffffLL;
             if (a < 0 || vocab <= 0 || D <= 0) return 0;
-            const size_t norm_ws = (nb2_workspace_bytes(NB2_WS_NORM_BWD, a, D, dtype) + 255) & ~(size_t)255;
-            const size_t type_ws = ((size_t)257 * D * sizeof(float) + 255) & ~(size_t)255;
-            return norm_ws + type_ws + embedding_bwd_workspace(a, vocab) + 512;
+            const int64_t tokens = B * S;
+            const size_t norm_ws = (nb2_workspace_bytes(NB2_WS_NORM_BWD, tokens, D, dtype) + 255) & ~(size_t)255;
+            const size_t type_ws = ((size_t)(S + 1) * D * sizeof(float) + 255) & ~(size_t)255;
+            return norm_ws + type_ws + embedding_bwd_workspace(tokens, vocab) + 512;
         }
         case NB2_WS_ROPE_TABLE: return a > 0 && b > 1 ? (size_t)a * (size_t)(b / 2) * 2 * sizeof(float) : 0;
         default: return 0;
@@ -325,24 +326,25 @@ int nb2_bert_embedding_ln_bwd(const void* sum, const void* dy, const void* ids, 
                               float* dgamma_dbeta, int64_t B, int64_t S, int64_t vocab, int64_t D, int dtype,
                               int index_type, void* workspace, size_t workspace_bytes, void* stream) {
     NB2_REQUIRE(dtype_ok(dtype) && idx_ok(index_type), NB2_ERR_DTYPE, "bert embedding bwd: dtype=%d index_type=%d", dtype, index_type);
-    NB2_REQUIRE(B >= 0 && S >= 0 && vocab > 0 && D > 0 && pos_rows >= (dpos ? S : 0), NB2_ERR_SHAPE,
+    NB2_REQUIRE(B >= 0 && S >= 0 && B < ((int64_t)1 << 31) && S < ((int64_t)1 << 31) && vocab > 0 && D > 0 &&
+                    D < ((int64_t)1 << 31) && pos_rows >= (dpos ? S : 0), NB2_ERR_SHAPE,
                 "bert embedding bwd: B=%lld S=%lld vocab=%lld D=%lld pos_rows=%lld", (long long)B, (long long)S,
                 (long long)vocab, (long long)D, (long long)pos_rows);
     NB2_REQUIRE(sum && dy && ids && gamma && mean && rstd && dsum && dword && dgamma_dbeta && workspace, NB2_ERR_NULL,
                 "bert embedding bwd: a required pointer is NULL");
     const int64_t tokens = B * S;
-    const size_t need = nb2_workspace_bytes(NB2_WS_BERT_EMBEDDING_BWD, tokens, vocab * ((int64_t)1 << 32) + D, dtype);
+    const size_t need = nb2_workspace_bytes(NB2_WS_BERT_EMBEDDING_BWD, B * ((int64_t)1 << 32) + S, vocab * ((int64_t)1 << 32) + D, dtype);
     NB2_REQUIRE(workspace_bytes >= need, NB2_ERR_WORKSPACE, "bert embedding bwd: workspace %zu < required %zu", workspace_bytes, need);
     int rc = require_device();
     if (rc != 0) return rc;
     cudaStream_t st = (cudaStream_t)stream;
     const size_t elt = dtype == NB2_F32 ? 4 : 2;
-    // workspace: [norm partials | 257 * D floats for the token-type sum | embedding sort scratch]
+    // workspace: [norm partials | (S + 1) * D floats for the token-type sum | embedding sort scratch]
     uint8_t* base = (uint8_t*)(((uintptr_t)workspace + 255) & ~(uintptr_t)255);
     const size_t norm_ws = (nb2_workspace_bytes(NB2_WS_NORM_BWD, tokens, D, dtype) + 255) & ~(size_t)255;
     float* partials = (float*)base;
     float* type_scratch = (float*)(base + norm_ws);
-    const size_t type_ws = ((size_t)257 * D * sizeof(float) + 255) & ~(size_t)255;
+    const size_t type_ws = ((size_t)(S + 1) * D * sizeof(float) + 255) & ~(size_t)255;
     void* sort_ws = base + norm_ws + type_ws;
     const size_t sort_bytes = embedding_bwd_workspace(tokens, vocab);
     if (dpos != nullptr) {

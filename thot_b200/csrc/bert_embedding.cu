@@ -48,27 +48,43 @@ bert_embed_ln_fwd_kernel(const T* __restrict__ word, const T* __restrict__ pos, 
             if (type != nullptr) tpk[j] = ld_param(type + (size_t)(tr + j * TPR) * EPV);     // row 0
         }
     }
+    // Software pipeline over this slot's tokens: the id is read two tokens ahead and the word and
+    // position rows one token ahead, so neither the id -> row dependency nor the row's HBM latency
+    // sits in front of a token's arithmetic.
     const int64_t stride = (int64_t)gridDim.x * RPC;
-    for (int64_t t = (int64_t)blockIdx.x * RPC + slot; t < tokens; t += stride) {
-        const int64_t id = load_token<I>(ids, t);
+    int64_t t = (int64_t)blockIdx.x * RPC + slot;
+    int64_t id_cur = t < tokens ? load_token<I>(ids, t) : 0;
+    int64_t id_nxt = t + stride < tokens ? load_token<I>(ids, t + stride) : 0;
+    uint4 wcur[VPT], pcur[VPT];
+    auto fetch = [&](int64_t tok, int64_t id, uint4* w, uint4* p) {
+        const bool ok = id >= 0 && id < vocab;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            if (valid[j]) {
+                const size_t off = (size_t)(tr + j * TPR) * EPV;
+                w[j] = ok ? __ldg(reinterpret_cast<const uint4*>(word + id * (int64_t)D + off)) : make_uint4(0u, 0u, 0u, 0u);
+                if (pos != nullptr) p[j] = __ldg(reinterpret_cast<const uint4*>(pos + (tok % S) * (int64_t)D + off));
+            }
+        }
+    };
+    if (t < tokens) fetch(t, id_cur, wcur, pcur);
+    for (; t < tokens; t += stride) {
+        const int64_t id = id_cur;
         const bool ok = id >= 0 && id < vocab;
         if (!ok && tr == 0 && status != nullptr) { status[0] = 1; status[1] = t; }
-        const T* wrow = word + (ok ? id : 0) * (int64_t)D;
-        const T* prow = pos != nullptr ? pos + (t % S) * (int64_t)D : nullptr;
+        uint4 wnxt[VPT], pnxt[VPT];
+        const int64_t id_after = t + 2 * stride < tokens ? load_token<I>(ids, t + 2 * stride) : 0;
+        if (t + stride < tokens) fetch(t + stride, id_nxt, wnxt, pnxt);
         float v[VPT][EPV];
         float sum = 0.f;
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
             if (valid[j]) {
                 const size_t off = (size_t)(tr + j * TPR) * EPV;
-                if (ok) unpack<T>(__ldg(reinterpret_cast<const uint4*>(wrow + off)), v[j]);
-                else {
-#pragma unroll
-                    for (int e = 0; e < EPV; ++e) v[j][e] = 0.f;
-                }
+                unpack<T>(wcur[j], v[j]);                      // zeros for an id outside the table
                 float a[EPV];
-                if (prow != nullptr) {
-                    unpack<T>(__ldg(reinterpret_cast<const uint4*>(prow + off)), a);
+                if (pos != nullptr) {
+                    unpack<T>(pcur[j], a);
 #pragma unroll
                     for (int e = 0; e < EPV; ++e) v[j][e] += a[e];
                 }
@@ -84,6 +100,10 @@ bert_embed_ln_fwd_kernel(const T* __restrict__ word, const T* __restrict__ pos, 
                 for (int e = 0; e < EPV; ++e) sum += v[j][e];
             }
         }
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) { wcur[j] = wnxt[j]; pcur[j] = pnxt[j]; }
+        id_cur = id_nxt;
+        id_nxt = id_after;
         const float mu = row_sum<TPR>(sum, red_a[slot], slot + 1) * inv_d;
         float q = 0.f;
 #pragma unroll
@@ -150,27 +170,19 @@ bert_embed_ln_fwd_generic(const T* __restrict__ word, const T* __restrict__ pos,
     }
 }
 
-// dpos[s, :] = sum_b dsum[b, s, :]  (fp32 accumulation, rounded once)
+// dpos[s, :] = sum_b dsum[b, s, :]  (fp32 accumulation, rounded once); the unrounded sums also go
+// to `acc_out` ([S, D] fp32) when the token-type gradient (their sum over s) is wanted, so dsum is
+// read once for both.
 template <typename T>
 __global__ void __launch_bounds__(256)
-batch_sum_kernel(const T* __restrict__ dsum, T* __restrict__ dpos, int64_t B, int64_t S, int64_t D) {
+batch_sum_kernel(const T* __restrict__ dsum, T* __restrict__ dpos, float* __restrict__ acc_out, int64_t B, int64_t S, int64_t D) {
     const int64_t total = S * D;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         float acc = 0.f;
+#pragma unroll 4
         for (int64_t b = 0; b < B; ++b) acc += to_f32(dsum[b * total + i]);
-        dpos[i] = from_f32<T>(acc);
-    }
-}
-// per-CTA column sums of a [rows, D] tensor into fp32 partials [gridDim.x, D] (for the token-type row)
-template <typename T>
-__global__ void __launch_bounds__(256)
-column_partials_kernel(const T* __restrict__ x, float* __restrict__ partials, int64_t rows, int64_t D, int64_t rows_per_cta) {
-    const int64_t r0 = (int64_t)blockIdx.x * rows_per_cta;
-    const int64_t r1 = r0 + rows_per_cta < rows ? r0 + rows_per_cta : rows;
-    for (int64_t c = threadIdx.x; c < D; c += blockDim.x) {
-        float acc = 0.f;
-        for (int64_t r = r0; r < r1; ++r) acc += to_f32(x[r * D + c]);
-        partials[(size_t)blockIdx.x * D + c] = acc;
+        if (dpos != nullptr) dpos[i] = from_f32<T>(acc);
+        if (acc_out != nullptr) acc_out[i] = acc;
     }
 }
 __global__ void __launch_bounds__(256)
@@ -233,35 +245,25 @@ int launch_bert_embed_ln_fwd(const void* word, const void* pos, const void* type
                : launch_fwd_ti<__nv_bfloat16, int64_t>(word, pos, type, ids, gamma, beta, sum_out, y, mean, rstd, tokens, S, vocab, D, eps, status, st);
 }
 
-// dpos (first S rows; the caller zeroed the rest) and dtype0 from dsum [B, S, D]
-int launch_bert_embed_table_grads(const void* dsum, void* dpos, void* dtype0, float* scratch /* [257 * D] */,
-                                  int64_t B, int64_t S, int64_t D, int dtype, cudaStream_t st) {
-    const int64_t total = S * D, tokens = B * S;
-    if (tokens == 0 || D == 0) return 0;
-    if (dpos != nullptr) {
-        int64_t grid = (total + 255) / 256;
-        const int64_t cap = (int64_t)sm_count() * 16;
-        if (grid > cap) grid = cap;
-        if (dtype == NB2_F32) batch_sum_kernel<float><<<(unsigned)grid, 256, 0, st>>>((const float*)dsum, (float*)dpos, B, S, D);
-        else batch_sum_kernel<__nv_bfloat16><<<(unsigned)grid, 256, 0, st>>>((const __nv_bfloat16*)dsum, (__nv_bfloat16*)dpos, B, S, D);
-        int rc = cuda_status(cudaGetLastError(), "bert position gradient launch");
-        if (rc != 0) return rc;
-    }
-    if (dtype0 != nullptr) {
-        int64_t parts = (tokens + 255) / 256;
-        if (parts > 256) parts = 256;
-        const int64_t rows_per = (tokens + parts - 1) / parts;
-        if (dtype == NB2_F32) column_partials_kernel<float><<<(unsigned)parts, 256, 0, st>>>((const float*)dsum, scratch, tokens, D, rows_per);
-        else column_partials_kernel<__nv_bfloat16><<<(unsigned)parts, 256, 0, st>>>((const __nv_bfloat16*)dsum, scratch, tokens, D, rows_per);
-        int rc = cuda_status(cudaGetLastError(), "bert token-type partials launch");
-        if (rc != 0) return rc;
-        float* total_row = scratch + (size_t)256 * D;
-        rc = launch_colreduce(scratch, parts, D, total_row, st);
-        if (rc != 0) return rc;
-        cast_row_kernel<<<(unsigned)((D + 255) / 256), 256, 0, st>>>(total_row, dtype0, D, dtype == NB2_BF16);
-        return cuda_status(cudaGetLastError(), "bert token-type gradient launch");
-    }
-    return 0;
+// dpos (first S rows; the caller zeroed the rest) and dtype0 from dsum [B, S, D].
+// scratch: (S + 1) * D floats.
+int launch_bert_embed_table_grads(const void* dsum, void* dpos, void* dtype0, float* scratch, int64_t B, int64_t S,
+                                  int64_t D, int dtype, cudaStream_t st) {
+    const int64_t total = S * D;
+    if (B * S == 0 || D == 0 || (dpos == nullptr && dtype0 == nullptr)) return 0;
+    int64_t grid = (total + 255) / 256;
+    const int64_t cap = (int64_t)sm_count() * 16;
+    if (grid > cap) grid = cap;
+    float* acc = dtype0 != nullptr ? scratch : nullptr;
+    if (dtype == NB2_F32) batch_sum_kernel<float><<<(unsigned)grid, 256, 0, st>>>((const float*)dsum, (float*)dpos, acc, B, S, D);
+    else batch_sum_kernel<__nv_bfloat16><<<(unsigned)grid, 256, 0, st>>>((const __nv_bfloat16*)dsum, (__nv_bfloat16*)dpos, acc, B, S, D);
+    int rc = cuda_status(cudaGetLastError(), "bert position gradient launch");
+    if (rc != 0 || dtype0 == nullptr) return rc;
+    float* total_row = scratch + (size_t)S * D;
+    rc = launch_colreduce(scratch, S, D, total_row, st);          // sum over positions, fp64, fixed order
+    if (rc != 0) return rc;
+    cast_row_kernel<<<(unsigned)((D + 255) / 256), 256, 0, st>>>(total_row, dtype0, D, dtype == NB2_BF16);
+    return cuda_status(cudaGetLastError(), "bert token-type gradient launch");
 }
 
 }  // namespace nb2

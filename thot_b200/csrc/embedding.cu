@@ -97,10 +97,10 @@ int launch_embedding_fwd(const void* table, const void* ids, void* out, int64_t 
 }
 
 // ------------------------------------------------------------------ backward
-// keys = (id << 32 | t) radix-sorted, so equal ids are contiguous and ordered by
-// t; one CTA per run start sums its run in fp32 in that order.  No atomics: the
+// keys = (id << 32 | t) radix-sorted by id, so equal ids are contiguous and ordered by t;
+// one CTA per table row sums that row's run in fp32 in that order.  No atomics: the
 // result is bit-reproducible.  Ids outside [0, vocab) get the key id = vocab and
-// are skipped.
+// belong to no row.
 template <typename I>
 __global__ void __launch_bounds__(256)
 embedding_keys_kernel(const void* __restrict__ ids, uint64_t* __restrict__ keys, int64_t tokens, int64_t vocab) {
@@ -111,39 +111,70 @@ embedding_keys_kernel(const void* __restrict__ ids, uint64_t* __restrict__ keys,
     keys[t] = ((uint64_t)id << 32) | (uint64_t)(uint32_t)t;
 }
 
+// row_start[v] = first sorted position whose id is v, or -1 (the array is preset to -1)
+__global__ void __launch_bounds__(256)
+embedding_row_start_kernel(const uint64_t* __restrict__ keys, int32_t* __restrict__ row_start, int64_t tokens, int64_t vocab) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= tokens) return;
+    const int64_t id = (int64_t)(keys[i] >> 32);
+    if (id < vocab && (i == 0 || (int64_t)(keys[i - 1] >> 32) != id)) row_start[id] = (int32_t)i;
+}
+
+// One CTA per table row v: sum the dout rows of v's run of sorted keys in fp32 in ascending t, or
+// write zeros when no token used the row.  Every row of dtable is written exactly once, so no
+// separate clearing pass is needed.
 template <typename T>
 __global__ void __launch_bounds__(128)
-embedding_bwd_kernel(const T* __restrict__ dout, const uint64_t* __restrict__ keys, T* __restrict__ dtable,
+embedding_bwd_kernel(const T* __restrict__ dout, const uint64_t* __restrict__ keys,
+                     const int32_t* __restrict__ row_start, T* __restrict__ dtable,
                      int64_t tokens, int64_t vocab, int64_t D, bool vec) {
     constexpr int EPV = VecTraits<T>::EPV;
-    for (int64_t i = blockIdx.x; i < tokens; i += gridDim.x) {
-        const uint64_t k0 = keys[i];
-        const int64_t id = (int64_t)(k0 >> 32);
-        if (id >= vocab) continue;
-        if (i > 0 && (int64_t)(keys[i - 1] >> 32) == id) continue;   // not a run start
-        T* dst = dtable + id * D;
+    for (int64_t v = blockIdx.x; v < vocab; v += gridDim.x) {
+        const int32_t rs = __ldg(row_start + v);
+        const int64_t i = rs < 0 ? tokens : (int64_t)rs;        // no run: the loops below add nothing
+        T* dst = dtable + v * D;
         if (vec) {
-            for (int64_t v = threadIdx.x; v < D / EPV; v += blockDim.x) {
-                float acc[EPV];
+            // up to 4 column vectors per thread are in flight for every token of the run
+            const int64_t nvec = D / EPV;
+            for (int64_t c0 = threadIdx.x; c0 < nvec; c0 += 4 * (int64_t)blockDim.x) {
+                float acc[4][EPV];
 #pragma unroll
-                for (int e = 0; e < EPV; ++e) acc[e] = 0.f;
+                for (int u = 0; u < 4; ++u)
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e) acc[u][e] = 0.f;
                 for (int64_t j = i; j < tokens; ++j) {
                     const uint64_t kj = keys[j];
-                    if ((int64_t)(kj >> 32) != id) break;
-                    const int64_t t = (int64_t)(kj & 0xffffffffu);
-                    float f[EPV];
-                    unpack<T>(ld_stream(dout + t * D + v * EPV), f);
+                    if ((int64_t)(kj >> 32) != v) break;
+                    const T* src = dout + (int64_t)(kj & 0xffffffffu) * D;
+                    uint4 r[4];
 #pragma unroll
-                    for (int e = 0; e < EPV; ++e) acc[e] += f[e];
+                    for (int u = 0; u < 4; ++u) {
+                        const int64_t c = c0 + u * (int64_t)blockDim.x;
+                        if (c < nvec) r[u] = ld_stream(src + c * EPV);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int64_t c = c0 + u * (int64_t)blockDim.x;
+                        if (c < nvec) {
+                            float f[EPV];
+                            unpack<T>(r[u], f);
+#pragma unroll
+                            for (int e = 0; e < EPV; ++e) acc[u][e] += f[e];
+                        }
+                    }
                 }
-                *reinterpret_cast<uint4*>(dst + v * EPV) = pack<T>(acc);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int64_t c = c0 + u * (int64_t)blockDim.x;
+                    if (c < nvec) st_stream(dst + c * EPV, pack<T>(acc[u]));
+                }
             }
         } else {
             for (int64_t c = threadIdx.x; c < D; c += blockDim.x) {
                 float acc = 0.f;
                 for (int64_t j = i; j < tokens; ++j) {
                     const uint64_t kj = keys[j];
-                    if ((int64_t)(kj >> 32) != id) break;
+                    if ((int64_t)(kj >> 32) != v) break;
                     acc += to_f32(dout[(int64_t)(kj & 0xffffffffu) * D + c]);
                 }
                 dst[c] = from_f32<T>(acc);
@@ -152,16 +183,20 @@ embedding_bwd_kernel(const T* __restrict__ dout, const uint64_t* __restrict__ ke
     }
 }
 
+// The radix sort only has to order the id half of the keys: it is stable and the keys are built in
+// ascending t, so equal ids keep ascending t.  Bits [32, 32 + bits(vocab)) -> two 8-bit passes for
+// a 32k vocabulary instead of six over the whole key.
 static int key_bits(int64_t vocab) {
     int b = 1;
     while (((int64_t)1 << b) <= vocab && b < 31) ++b;   // ids 0..vocab inclusive (sentinel)
     return 32 + b;
 }
+constexpr int kKeyBeginBit = 32;
 
 static size_t cub_temp_bytes(int64_t tokens, int64_t vocab) {
     size_t bytes = 0;
     cub::DeviceRadixSort::SortKeys(nullptr, bytes, (const uint64_t*)nullptr, (uint64_t*)nullptr,
-                                   (int)tokens, 0, key_bits(vocab));
+                                   (int)tokens, kKeyBeginBit, key_bits(vocab));
     return bytes;
 }
 
@@ -169,14 +204,15 @@ static size_t round256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 size_t embedding_bwd_workspace(int64_t tokens, int64_t vocab) {
     if (tokens <= 0) return 256;
-    return 2 * round256((size_t)tokens * 8) + round256(cub_temp_bytes(tokens, vocab)) + 256;
+    return 2 * round256((size_t)tokens * 8) + round256(cub_temp_bytes(tokens, vocab)) + round256((size_t)vocab * 4) + 256;
 }
 
 int launch_embedding_bwd(const void* dout, const void* ids, void* dtable, int64_t tokens, int64_t vocab,
                          int64_t D, int dtype, int index_type, void* ws, size_t ws_bytes, cudaStream_t st) {
     const int elt = dtype == NB2_F32 ? 4 : 2;
-    int rc = cuda_status(cudaMemsetAsync(dtable, 0, (size_t)vocab * D * elt, st), "embedding bwd memset");
-    if (rc != 0 || tokens == 0 || D == 0) return rc;
+    if (tokens == 0 || D == 0)       // nothing to sum: the gradient is all zeros
+        return cuda_status(cudaMemsetAsync(dtable, 0, (size_t)vocab * D * elt, st), "embedding bwd memset");
+    int rc = 0;
     NB2_REQUIRE(tokens < ((int64_t)1 << 31), NB2_ERR_SHAPE, "embedding bwd: %lld tokens exceed 2^31-1", (long long)tokens);
     NB2_REQUIRE(ws != nullptr, NB2_ERR_NULL, "embedding bwd: workspace is NULL");
     NB2_REQUIRE(ws_bytes >= embedding_bwd_workspace(tokens, vocab), NB2_ERR_WORKSPACE,
@@ -186,23 +222,29 @@ int launch_embedding_bwd(const void* dout, const void* ids, void* dtable, int64_
     uint64_t* keys_out = (uint64_t*)(base + round256((size_t)tokens * 8));
     void* temp = base + 2 * round256((size_t)tokens * 8);
     size_t temp_bytes = cub_temp_bytes(tokens, vocab);
+    int32_t* row_start = (int32_t*)((uint8_t*)temp + round256(temp_bytes));
 
     const unsigned kgrid = (unsigned)((tokens + 255) / 256);
     if (index_type == NB2_I32) embedding_keys_kernel<int32_t><<<kgrid, 256, 0, st>>>(ids, keys_in, tokens, vocab);
     else                       embedding_keys_kernel<int64_t><<<kgrid, 256, 0, st>>>(ids, keys_in, tokens, vocab);
     rc = cuda_status(cudaGetLastError(), "embedding keys launch");
     if (rc != 0) return rc;
-    rc = cuda_status(cub::DeviceRadixSort::SortKeys(temp, temp_bytes, keys_in, keys_out, (int)tokens, 0,
+    rc = cuda_status(cub::DeviceRadixSort::SortKeys(temp, temp_bytes, keys_in, keys_out, (int)tokens, kKeyBeginBit,
                                                     key_bits(vocab), st), "embedding key sort");
     if (rc != 0) return rc;
+    rc = cuda_status(cudaMemsetAsync(row_start, 0xff, (size_t)vocab * 4, st), "embedding row-start preset");
+    if (rc != 0) return rc;
+    embedding_row_start_kernel<<<kgrid, 256, 0, st>>>(keys_out, row_start, tokens, vocab);
+    rc = cuda_status(cudaGetLastError(), "embedding row-start launch");
+    if (rc != 0) return rc;
     const bool vec = (D * elt) % 16 == 0 && aligned16(dout) && aligned16(dtable);
-    int64_t grid = tokens;
+    int64_t grid = vocab;
     const int64_t cap = (int64_t)sm_count() * 64;
     if (grid > cap) grid = cap;
     if (dtype == NB2_F32)
-        embedding_bwd_kernel<float><<<(unsigned)grid, 128, 0, st>>>((const float*)dout, keys_out, (float*)dtable, tokens, vocab, D, vec);
+        embedding_bwd_kernel<float><<<(unsigned)grid, 128, 0, st>>>((const float*)dout, keys_out, row_start, (float*)dtable, tokens, vocab, D, vec);
     else
-        embedding_bwd_kernel<__nv_bfloat16><<<(unsigned)grid, 128, 0, st>>>((const __nv_bfloat16*)dout, keys_out, (__nv_bfloat16*)dtable, tokens, vocab, D, vec);
+        embedding_bwd_kernel<__nv_bfloat16><<<(unsigned)grid, 128, 0, st>>>((const __nv_bfloat16*)dout, keys_out, row_start, (__nv_bfloat16*)dtable, tokens, vocab, D, vec);
     return cuda_status(cudaGetLastError(), "embedding bwd launch");
 }
 

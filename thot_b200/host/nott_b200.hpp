@@ -553,7 +553,7 @@ struct BertEmbeddingFunction : public torch::autograd::Function<BertEmbeddingFun
         if (pos_rows > 0) dpos = torch::empty({pos_rows, D}, sum.options());
         if (type_rows > 0) dtype = torch::zeros({type_rows, D}, sum.options());       // rows other than 0 get no gradient
         auto sums = torch::empty({2, D}, sum.options().dtype(torch::kFloat32));
-        const auto ws = nb2_workspace_bytes(NB2_WS_BERT_EMBEDDING_BWD, B * S, (vocab << 32) | D, code);
+        const auto ws = nb2_workspace_bytes(NB2_WS_BERT_EMBEDDING_BWD, (B << 32) | S, (vocab << 32) | D, code);
         auto scratch = torch::empty({(int64_t)ws}, sum.options().dtype(torch::kUInt8));
         detail::check(nb2_bert_embedding_ln_bwd(sum.data_ptr(), dy.data_ptr(), ids.data_ptr(), g.data_ptr(),
                                                 stats[0].data_ptr<float>(), stats[1].data_ptr<float>(), dsum.data_ptr(),
