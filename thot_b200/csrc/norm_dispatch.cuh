@@ -88,8 +88,8 @@ static inline TmaShape tma_bwd_shape(int64_t D, int epv) {
 // ring depth: every row group gets `stages` row slots; one "layer" (a slot of every
 // group) is 16-64 KiB
 struct TmaTiling { int stages; size_t smem; };
-static inline TmaTiling tma_tiling(int64_t D, int elt, int tpr, int nsrc) {
-    const int rpc = kTmaThreads / tpr;
+static inline TmaTiling tma_tiling(int64_t D, int elt, int tpr, int nsrc, int threads = kTmaThreads) {
+    const int rpc = threads / tpr;
     const size_t layer = (size_t)rpc * D * elt * nsrc;
     const size_t fixed = kTmaHeaderBytes + 2 * (size_t)tma_param_bytes((int)D, elt);
     TmaTiling t;
@@ -100,8 +100,8 @@ static inline TmaTiling tma_tiling(int64_t D, int elt, int tpr, int nsrc) {
     t.smem = fixed + t.stages * layer;
     return t;
 }
-static inline int64_t tma_grid(int64_t rows, int tpr, int sms) {
-    const int rpc = kTmaThreads / tpr;
+static inline int64_t tma_grid(int64_t rows, int tpr, int sms, int threads = kTmaThreads) {
+    const int rpc = threads / tpr;
     const int64_t need = (rows + rpc - 1) / rpc;
     return need < sms ? (need < 1 ? 1 : need) : sms;
 }
@@ -109,8 +109,8 @@ static inline int64_t tma_grid(int64_t rows, int tpr, int sms) {
 // Should this (norm, direction, dtype, D) use the ring kernels?  Measured on B200 over
 // D in {768 .. 8192}, 2^17 rows, both families on the same inputs:
 //   LayerNorm backward: ring at every width (fp32 6.2-6.6 TB/s vs 3.9-4.5 register-row).
-//   LayerNorm forward : ring for bf16 and for fp32 rows up to 8 KiB; wider fp32 rows are
-//                       better served by 256-512 threads loading straight into registers.
+//   LayerNorm forward : ring for bf16 and for fp32 rows up to 16 KiB; wider fp32 rows are
+//                       better served by 512 threads loading straight into registers.
 //   RMSNorm is lean enough that register-row loads already run at 92-96% of the copy
 //   rate; the ring only wins for rows of 16 KiB and more, and for the bf16 backward.
 static inline bool tma_preferred(bool rms, int64_t D, int elt, bool bwd) {
@@ -118,12 +118,17 @@ static inline bool tma_preferred(bool rms, int64_t D, int elt, bool bwd) {
     if (ov == 1) return false;
     if (ov == 2) return true;
     const int64_t row_bytes = D * elt;
-    if (!rms) return bwd ? true : (elt == 2 || row_bytes <= 8192);
+    if (!rms) return bwd ? true : (elt == 2 || row_bytes <= 16384);
     return bwd ? (elt == 2 || row_bytes >= 16384) : (elt == 4 && row_bytes >= 16384);
 }
 // does the ring of this shape fit the SM's shared memory at all
-static inline bool tma_fits(int64_t D, int elt, int tpr, int nsrc) {
-    return tma_tiling(D, elt, tpr, nsrc).smem <= kTmaMaxSmem;
+// Forward CTAs: 16 warps, or 24 for rows of 8 KiB and more (measured on B200: +5-8% at D = 4096
+// in both types, -10% at D = 1024; the forward needs ~72 registers, so 24 warps still fit).
+static inline int fwd_threads(int tpr, int64_t row_bytes) {
+    return (row_bytes >= 8192 && (tpr == 128 || tpr == 256)) ? 768 : 512;
+}
+static inline bool tma_fits(int64_t D, int elt, int tpr, int nsrc, int threads = kTmaThreads) {
+    return tma_tiling(D, elt, tpr, nsrc, threads).smem <= kTmaMaxSmem;
 }
 
 template <typename T, bool RMS> int launch_norm_fwd(const NormArgs& a);

@@ -5,10 +5,10 @@
 
 namespace nb2 {
 
-template <typename T, int TPR, int VPT, int ACT, bool RMS, bool RES>
-static int launch_fwd_tma_res(const NormArgs& a) {
-    auto kern = norm_fwd_tma_kernel<T, TPR, VPT, ACT, RMS, RES>;
-    const TmaTiling t = tma_tiling(a.D, (int)sizeof(T), TPR, RES ? 2 : 1);
+template <typename T, int TPR, int VPT, int ACT, bool RMS, bool RES, int NT>
+static int launch_fwd_tma_nt(const NormArgs& a) {
+    auto kern = norm_fwd_tma_kernel<T, TPR, VPT, ACT, RMS, RES, NT>;
+    const TmaTiling t = tma_tiling(a.D, (int)sizeof(T), TPR, RES ? 2 : 1, NT);
     NB2_REQUIRE(t.smem <= kTmaMaxSmem, NB2_ERR_SHAPE, "norm ring kernel: %zu bytes of shared memory exceed the SM", t.smem);
     static thread_local size_t configured_all[kMaxDevices] = {};
     size_t& configured = configured_all[current_device_slot()];
@@ -18,12 +18,20 @@ static int launch_fwd_tma_res(const NormArgs& a) {
         if (rc != 0) return rc;
         configured = t.smem;
     }
-    const int grid = (int)tma_grid(a.rows, TPR, sm_count());
-    const cudaError_t e = launch_pdl(kern, dim3(grid), dim3(kTmaThreads), t.smem, a.stream, (const T*)a.x, (const T*)a.res,
+    const int grid = (int)tma_grid(a.rows, TPR, sm_count(), NT);
+    const cudaError_t e = launch_pdl(kern, dim3(grid), dim3(NT), t.smem, a.stream, (const T*)a.x, (const T*)a.res,
                                      (const T*)a.gamma, (const T*)a.beta, (T*)a.sum_out, (T*)a.y, a.mean_out, a.rstd_out,
                                      a.rows, (int)a.D, a.eps, t.stages, device_status_ptr());
     if (e != cudaSuccess) return cuda_status(e, "norm_fwd_tma_kernel launch");
     return 0;
+}
+
+template <typename T, int TPR, int VPT, int ACT, bool RMS, bool RES>
+static int launch_fwd_tma_res(const NormArgs& a) {
+    if constexpr ((TPR == 128 || TPR == 256) && !RES) {
+        if (fwd_threads(TPR, a.D * (int64_t)sizeof(T)) == 768) return launch_fwd_tma_nt<T, TPR, VPT, ACT, RMS, RES, 768>(a);
+    }
+    return launch_fwd_tma_nt<T, TPR, VPT, ACT, RMS, RES, 512>(a);
 }
 
 template <typename T, int TPR, int VPT, int ACT, bool RMS>
@@ -82,7 +90,7 @@ static int launch_fwd_act(const NormArgs& a) {
             if (s.tpr != 0 && affine && tma_fits(a.D, (int)sizeof(T), s.tpr, 2)) return launch_fwd_tma_shape<T, ACT, RMS>(a, s);
             return kNotFused;
         }
-        if (s.tpr != 0 && affine && tma_preferred(RMS, a.D, (int)sizeof(T), false) && tma_fits(a.D, (int)sizeof(T), s.tpr, 1))
+        if (s.tpr != 0 && affine && tma_preferred(RMS, a.D, (int)sizeof(T), false) && tma_fits(a.D, (int)sizeof(T), s.tpr, 1, fwd_threads(s.tpr, a.D * (int64_t)sizeof(T))))
             return launch_fwd_tma_shape<T, ACT, RMS>(a, s);
         switch (pick_tpr(a.D / EPV, fwd_vpt<T>())) {
             case 32:  return launch_fwd_cfg<T, 32, ACT, RMS>(a);

@@ -100,11 +100,11 @@ __device__ __forceinline__ bool group_gave_up(volatile int* abort_flag) {
 // row into registers, i.e. before the row's arithmetic, so the copies of the next
 // rows overlap all of it.  Groups never wait for one another.
 //
-// Shared memory: header (full barriers [16 groups][8 stages], reduction scratch,
+// Shared memory: header (full barriers [24 groups][8 stages], reduction scratch,
 // abort flag), then gamma and beta (a per-row global load of the parameters would
 // sit on the critical path of every row even when it hits L1), then the rings.
-constexpr int kTmaMaxGroups = 16;
-constexpr int kTmaHeaderBytes = 2048;
+constexpr int kTmaMaxGroups = 24;
+constexpr int kTmaHeaderBytes = 3072;
 __host__ __device__ inline int tma_param_bytes(int D, int elt) { return (D * elt + 1023) & ~1023; }
 
 struct TmaSmem {
@@ -117,8 +117,8 @@ struct TmaSmem {
     uint8_t* ring;
     __device__ __forceinline__ TmaSmem(uint8_t* smem, int param_bytes)
         : full(reinterpret_cast<uint64_t*>(smem)),
-          red_a(reinterpret_cast<float*>(smem + 1024)), red_b(reinterpret_cast<float*>(smem + 1280)),
-          abort_flag(reinterpret_cast<volatile int*>(smem + 1536)),
+          red_a(reinterpret_cast<float*>(smem + 1536)), red_b(reinterpret_cast<float*>(smem + 1792)),
+          abort_flag(reinterpret_cast<volatile int*>(smem + 2048)),
           gamma(reinterpret_cast<const uint4*>(smem + kTmaHeaderBytes)),
           beta(reinterpret_cast<const uint4*>(smem + kTmaHeaderBytes + param_bytes)),
           ring(smem + kTmaHeaderBytes + 2 * param_bytes) {}
@@ -160,16 +160,16 @@ __device__ __forceinline__ void request_row(uint64_t* bar, uint8_t* slot, const 
 // src/block/details/transformers/classic.hpp:442-445, mamba.hpp:409-415); the sum, rounded
 // to T as the reference's own `residual + attention` tensor would be, is also written out
 // because it is the next residual.
-template <typename T, int TPR, int VPT, int ACT, bool RMS, bool RES>
-__global__ void __launch_bounds__(kTmaThreads, 1)
+template <typename T, int TPR, int VPT, int ACT, bool RMS, bool RES, int NT>
+__global__ void __launch_bounds__(NT, 1)
 norm_fwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __restrict__ gamma,
                     const T* __restrict__ beta, T* __restrict__ sum_out,
                     T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
                     int64_t rows, int D, float eps, int stages, unsigned int* __restrict__ status) {
     constexpr int EPV = VecTraits<T>::EPV;
-    constexpr int RPC = kTmaThreads / TPR;        // row groups
+    constexpr int RPC = NT / TPR;                 // row groups
     constexpr int WPR = (TPR + 31) / 32;
-    static_assert(kTmaThreads % TPR == 0, "row groups must tile the CTA");
+    static_assert(NT % TPR == 0 && RPC <= kTmaMaxGroups, "row groups must tile the CTA");
     static_assert(TPR <= 32 || RPC <= 14, "one named barrier per multi-warp row group");
 
     extern __shared__ __align__(1024) uint8_t smem[];
