@@ -306,6 +306,75 @@ def run_suite(args):
            "note": "timings include torch's output allocation from its caching allocator"})
 
 
+# ------------------------------------------------------------ cfg5 sweep
+def run_sweep(args, rank, world, local):
+    """`--sweep`: BASELINE configs[4] in one go: LayerNorm->GELU and RMSNorm->SiLU, fp32 and bf16,
+    D in {768, 1024, 2048, 4096, 8192}, 2^20 rows split evenly over the ranks (strong scaling),
+    forward / backward(+partial reduce, + NCCL allreduce for N > 1) timed separately with CUDA
+    events, max over ranks.  One JSON line."""
+    import torch.distributed as dist
+    from thot_b200 import abi
+    from thot_b200.sharding import allreduce_param_grads, row_shard
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    peaks_file = ROOT / "MEASURED_PEAKS.json"
+    peak = float(json.loads(peaks_file.read_text())["hbm_gbs"]) if peaks_file.exists() else FALLBACK_HBM_GBS
+    total_rows = 1 << 20
+    _, rows = row_shard(total_rows, world, rank)
+    iters = max(3, min(args.steps, 10))
+    out = []
+    for kind, act, eps in (("ln", abi.ACT_GELU, 1e-5), ("rms", abi.ACT_SILU, 1e-6)):
+        for dt, name in ((torch.float32, "fp32"), (torch.bfloat16, "bf16")):
+            for D in (768, 1024, 2048, 4096, 8192):
+                gen = torch.Generator(device=dev).manual_seed(rank)
+                x = torch.randn(rows, D, device=dev, generator=gen).to(dt)
+                dy = torch.randn(rows, D, device=dev, generator=gen).to(dt)
+                g = (1 + 0.02 * torch.randn(D, device=dev, generator=gen)).to(dt)
+                b = (0.02 * torch.randn(D, device=dev, generator=gen)).to(dt)
+                elt = x.element_size()
+                if kind == "ln":
+                    y, mean, rstd = abi.layernorm_fwd(x, g, b, eps, act)
+                    f = lambda: abi.layernorm_fwd(x, g, b, eps, act)
+                    bw = lambda: allreduce_param_grads(abi.layernorm_bwd(x, dy, g, b, mean, rstd, act)[1].view(-1))
+                else:
+                    y, rstd = abi.rmsnorm_fwd(x, g, eps, act)
+                    f = lambda: abi.rmsnorm_fwd(x, g, eps, act)
+                    bw = lambda: allreduce_param_grads(abi.rmsnorm_bwd(x, dy, g, rstd, act)[1])
+                res = {}
+                for tag, fn, nbytes in (("fwd", f, 2 * rows * D * elt), ("bwd", bw, 3 * rows * D * elt)):
+                    for _ in range(2):
+                        fn()
+                    if world > 1:
+                        dist.barrier()
+                    torch.cuda.synchronize()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    for _ in range(iters):
+                        fn()
+                    e1.record()
+                    torch.cuda.synchronize()
+                    ms = e0.elapsed_time(e1) / iters
+                    if world > 1:
+                        t = torch.tensor([ms], device=dev)
+                        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                        ms = float(t.item())
+                    res[tag] = {"ms": ms, "gbs": nbytes * world / ms / 1e6, "frac_of_measured_per_gpu": nbytes / ms / 1e6 / peak}
+                out.append({"op": "LayerNorm->GELU" if kind == "ln" else "RMSNorm->SiLU", "dtype": name, "D": D,
+                            "rows_total": total_rows, "rows_per_s_fwd_bwd": total_rows / ((res["fwd"]["ms"] + res["bwd"]["ms"]) / 1e3),
+                            **{f"{k}_{m}": v[m] for k, v in res.items() for m in v}})
+                del x, dy, y
+    abi.device_status()
+    if rank == 0:
+        _emit({"sweep": out, "n_gpus": world, "peak_gbs": peak, "scaling": "strong", "data": "synthetic",
+               "note": "backward includes the partial reduce, torch's output allocation and, for N > 1, the NCCL allreduce"})
+    if world > 1:
+        dist.destroy_process_group()
+
+
 # ------------------------------------------------------------------ our arm
 def _emit(line: dict) -> None:
     """The one JSON line goes to the process's original stdout; everything else that libraries
@@ -329,6 +398,7 @@ def main():
     ap.add_argument("--workload", default="cfg2")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--sweep", action="store_true", help="BASELINE configs[4]: 2^20 rows x D sweep, both norms, both dtypes")
     ap.add_argument("--suite", action="store_true", help="time the other kernels of the path (1 GPU) instead of the step")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -344,6 +414,9 @@ def main():
     if args.suite:
         if rank == 0:
             run_suite(args)
+        return
+    if args.sweep:
+        run_sweep(args, rank, world, local)
         return
 
     import torch.distributed as dist

@@ -199,6 +199,18 @@ norm_fwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ res, const T*
         }
     }
 
+    // 16-warp CTAs have the registers to keep this thread's gamma/beta columns for the whole
+    // kernel; 24-warp CTAs read them from shared memory per row.
+    constexpr bool PREG = NT <= 512;
+    uint4 gpk[PREG ? VPT : 1], bpk[PREG ? VPT : 1];
+    if constexpr (PREG) {
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            gpk[j] = sm.gamma[tr + j * TPR];
+            if constexpr (!RMS) bpk[j] = sm.beta[tr + j * TPR];
+        }
+    }
+
     int i = 0;
     for (int64_t row = first; row < rows; row += stride, ++i) {
         const int s = i % stages;
@@ -252,8 +264,8 @@ norm_fwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ res, const T*
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
             float g[EPV], b[EPV], o[EPV];
-            unpack<T>(sm.gamma[tr + j * TPR], g);
-            if constexpr (!RMS) unpack<T>(sm.beta[tr + j * TPR], b);
+            unpack<T>(PREG ? gpk[j] : sm.gamma[tr + j * TPR], g);
+            if constexpr (!RMS) unpack<T>(PREG ? bpk[j] : sm.beta[tr + j * TPR], b);
 #pragma unroll
             for (int e = 0; e < EPV; ++e) {
                 const float z = RMS ? v[j][e] * rs * g[e] : fmaf(v[j][e] * rs, g[e], b[e]);   // v holds x - mean for LayerNorm
