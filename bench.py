@@ -44,7 +44,7 @@ class Workload:
         if spec == "cfg2":
             self.kind, self.dtype, self.D = "ln", torch.float32, 1024
             self.rows_per_rank, self.scaling = 32 * 1024, "weak"
-            self.name = "LayerNorm->GELU(erf) fwd+bwd fp32 x[32,1024,1024] per GPU (BASELINE configs[1])"
+            self.name = "LayerNorm->GELU(erf) fwd+bwd fp32 x[32,1024,1024] per GPU (the headline configuration)"
         elif spec.startswith("cfg5:"):
             _, kind, dt, D = spec.split(":")
             self.kind, self.D = kind, int(D)
@@ -53,7 +53,7 @@ class Workload:
             if total % world:
                 raise SystemExit("cfg5 needs a world size that divides 2^20")
             self.rows_per_rank, self.scaling = total // world, "strong"
-            self.name = f"{'LayerNorm->GELU' if kind == 'ln' else 'RMSNorm->SiLU'} fwd+bwd {dt} 2^20 rows x D={D} (BASELINE configs[4])"
+            self.name = f"{'LayerNorm->GELU' if kind == 'ln' else 'RMSNorm->SiLU'} fwd+bwd {dt} 2^20 rows x D={D} (whole-box sweep configuration)"
         else:
             raise SystemExit(f"unknown workload {spec}")
         self.act = 1 if self.kind == "ln" else 2          # GELU behind LayerNorm, SiLU behind RMSNorm
@@ -213,7 +213,7 @@ def run_reference_arm(args, w: Workload, rank: int, world: int):
 
 # ---------------------------------------------------------------- op suite
 def run_suite(args):
-    """`--suite`: every other kernel of the path at BASELINE's configs[2]/[3] sizes, one launch type per
+    """`--suite`: every other kernel of the path at the benchmark's RMSNorm/gate and gather/rotary configuration sizes, one launch type per
     entry, CUDA-event timed, algorithmic bytes / time against the measured HBM peak.  One JSON line."""
     from thot_b200 import abi
 
@@ -308,7 +308,7 @@ def run_suite(args):
 
 # ------------------------------------------------------------ cfg5 sweep
 def run_sweep(args, rank, world, local):
-    """`--sweep`: BASELINE configs[4] in one go: LayerNorm->GELU and RMSNorm->SiLU, fp32 and bf16,
+    """`--sweep`: the whole-box sweep configuration in one go: LayerNorm->GELU and RMSNorm->SiLU, fp32 and bf16,
     D in {768, 1024, 2048, 4096, 8192}, 2^20 rows split evenly over the ranks (strong scaling),
     forward / backward(+partial reduce, + NCCL allreduce for N > 1) timed separately with CUDA
     events, max over ranks.  One JSON line."""
@@ -398,7 +398,7 @@ def main():
     ap.add_argument("--workload", default="cfg2")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--sweep", action="store_true", help="BASELINE configs[4]: 2^20 rows x D sweep, both norms, both dtypes")
+    ap.add_argument("--sweep", action="store_true", help="whole-box sweep: 2^20 rows x D in {768..8192}, both norms, both dtypes")
     ap.add_argument("--suite", action="store_true", help="time the other kernels of the path (1 GPU) instead of the step")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
