@@ -57,6 +57,19 @@ def test_embedding_bad_ids_do_not_fault():
     assert float(dt.sum()) == 2 * 64
 
 
+def test_embedding_bad_ids_with_wide_rows():
+    """Rows of 1 KiB and more go through the copy-engine gather; a bad id there is a zero row too."""
+    table, _ = make((32, 2048), 2, torch.bfloat16)
+    ids = torch.tensor([5, -1, 31, 32, 0, 7, 7, 40, 1], dtype=torch.int32).cuda()
+    status = torch.zeros(2, dtype=torch.int64, device="cuda")
+    out = abi.embedding_fwd(table, ids, status)
+    assert status[0].item() == 1
+    good = (ids >= 0) & (ids < 32)
+    assert torch.equal(out[good], table[ids[good].long()])
+    assert float(out[~good].float().abs().sum()) == 0.0
+    assert abi.device_status() == 0
+
+
 def test_config4_embedding_full_size_bit_exact():
     """table[32000,4096] bf16 ~N(0,0.02), int32 ids [32,2048] uniform."""
     torch.manual_seed(0)

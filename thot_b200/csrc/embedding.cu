@@ -6,6 +6,7 @@
 // dtable[v,:] = sum_{t: ids[t]==v} dout[t,:].
 #include <cub/device/device_radix_sort.cuh>
 #include "launchers.h"
+#include "norm_tma_kernels.cuh"     // mbarrier / cp.async.bulk helpers
 
 namespace nb2 {
 
@@ -69,6 +70,93 @@ embedding_fwd_kernel(const uint8_t* __restrict__ table, const void* __restrict__
     }
 }
 
+// Copy-engine gather: one warp per CTA, whose first lane drives a private ring of row slots.
+// A table row travels HBM -> shared memory -> HBM as two bulk copies (cp.async.bulk, this CTA only)
+// and never touches a register; the other lanes only help with the rare zero row of a bad id.
+// Slot reuse waits for the outgoing copy to have read the slot (bulk-group wait), the incoming
+// copy completes on the slot's mbarrier; both waits are bounded like every wait in this library.
+constexpr int EMB_RING = 4;
+__device__ __forceinline__ void bulk_s2g(void* dst, const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+template <typename I>
+__global__ void __launch_bounds__(32)
+embedding_fwd_bulk_kernel(const uint8_t* __restrict__ table, const void* __restrict__ ids, uint8_t* __restrict__ out,
+                          int64_t tokens, int64_t vocab, uint32_t row_bytes, int64_t* __restrict__ status,
+                          unsigned int* __restrict__ dev_status) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+    volatile int* gave_up = reinterpret_cast<volatile int*>(smem + 64);
+    uint8_t* ring = smem + 128;
+    const int lane = threadIdx.x;
+    pdl_release();
+    pdl_wait();
+    if (lane == 0) {
+        for (int s = 0; s < EMB_RING; ++s) mbar_init(&full[s], 1);
+        *gave_up = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    const int64_t first = blockIdx.x, stride = gridDim.x;
+    const uint64_t policy = policy_evict_first();
+    // a token whose id is outside the table is not requested; its output row is zero-filled
+    auto request = [&](int k) {
+        const int64_t t = first + (int64_t)k * stride;
+        if (t >= tokens) return;
+        const int64_t id = load_id<I>(ids, t);
+        if (id < 0 || id >= vocab) return;
+        const int s = k % EMB_RING;
+        mbar_arrive_expect_tx(&full[s], row_bytes);
+        for (uint32_t off = 0; off < row_bytes; off += kBulkChunk) {
+            const uint32_t n = row_bytes - off < kBulkChunk ? row_bytes - off : kBulkChunk;
+            bulk_g2s(ring + (size_t)s * row_bytes + off, table + id * (int64_t)row_bytes + off, n, &full[s], policy);
+        }
+    };
+    if (lane == 0)
+        for (int k = 0; k < EMB_RING; ++k) request(k);
+    int k = 0;
+    uint32_t parity = 0;                               // bit s: parity of slot s's next completed load
+    for (int64_t t = first; t < tokens; t += stride, ++k) {
+        const int s = k % EMB_RING;
+        const int64_t id = load_id<I>(ids, t);
+        const bool ok = id >= 0 && id < vocab;          // uniform over the warp
+        if (ok) {
+            if (lane == 0) {
+                if (mbar_wait_bounded(&full[s], (parity >> s) & 1u, gave_up, kStatusFullTimeout, dev_status)) {
+                    bulk_s2g(out + t * (int64_t)row_bytes, ring + (size_t)s * row_bytes, row_bytes);
+                    bulk_commit();
+                    bulk_wait_read_all();                // the slot may be overwritten once the copy out has read it
+                }
+            }
+            parity ^= 1u << s;
+        } else {
+            if (lane == 0 && status != nullptr) { status[0] = 1; status[1] = t; }
+            for (uint32_t off = lane * 16; off < row_bytes; off += 32 * 16)
+                *reinterpret_cast<uint4*>(out + t * (int64_t)row_bytes + off) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        if (__shfl_sync(0xffffffffu, *gave_up, 0)) break;
+        if (lane == 0) request(k + EMB_RING);
+    }
+    if (lane == 0) {
+        bulk_wait_all();                                 // outgoing copies done before the CTA's shared memory goes away
+        if (*gave_up) {
+            // copies still inbound into the ring must land before the CTA leaves
+            for (int b = 0; b < EMB_RING; ++b) {
+                const int kb = k + b;
+                const int64_t t = first + (int64_t)kb * stride;
+                if (t < tokens) {
+                    const int64_t id = load_id<I>(ids, t);
+                    if (id >= 0 && id < vocab) mbar_wait_drain(&full[kb % EMB_RING], (parity >> (kb % EMB_RING)) & 1u);
+                }
+            }
+        }
+    }
+}
+
 template <typename I>
 static int launch_emb_fwd_i(const void* table, const void* ids, void* out, int64_t tokens, int64_t vocab,
                             int64_t D, int dtype, int64_t* status, cudaStream_t st) {
@@ -76,6 +164,27 @@ static int launch_emb_fwd_i(const void* table, const void* ids, void* out, int64
     const int elt = dtype == NB2_F32 ? 4 : 2;
     const int64_t row_bytes = D * elt;
     const bool vec_ok = (row_bytes % 16 == 0) && aligned16(table) && aligned16(out);
+    if (vec_ok && row_bytes >= 1024 && row_bytes <= 48 * 1024) {
+        // rows of 1-48 KiB: the copy engine moves them; smaller rows are cheaper through registers
+        auto kern = embedding_fwd_bulk_kernel<I>;
+        const size_t smem = 128 + (size_t)EMB_RING * row_bytes;
+        static thread_local size_t configured_all[kMaxDevices] = {};
+        size_t& configured = configured_all[current_device_slot()];
+        if (smem > configured) {
+            int rc = cuda_status(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                                 "embedding_fwd_bulk_kernel shared memory");
+            if (rc != 0) return rc;
+            configured = smem;
+        }
+        int per_sm = (int)((200 * 1024) / (smem + 1024));
+        if (per_sm > 16) per_sm = 16;
+        if (per_sm < 1) per_sm = 1;
+        int64_t g = (int64_t)sm_count() * per_sm;
+        if (g > tokens) g = tokens;
+        const cudaError_t e = launch_pdl(kern, dim3((unsigned)g), dim3(32), smem, st, (const uint8_t*)table, ids, (uint8_t*)out, tokens,
+                                         vocab, (uint32_t)row_bytes, status, device_status_ptr());
+        return cuda_status(e, "embedding fwd (bulk) launch");
+    }
     int64_t grid = (tokens + EMB_TOK - 1) / EMB_TOK;
     const int64_t cap = (int64_t)sm_count() * 16;
     if (grid > cap) grid = cap;
