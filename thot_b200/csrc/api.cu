@@ -317,6 +317,22 @@ int nb2_bert_embedding_ln_fwd(const void* word, const void* pos, const void* typ
     NB2_REQUIRE(word && ids && gamma && beta && y, NB2_ERR_NULL, "bert embedding fwd: word, ids, gamma, beta and y must be non-NULL");
     int rc = require_device();
     if (rc != 0) return rc;
+    // Preferred: the ring kernel of the residual-add norm with a row lookup (word rows by id as x,
+    // position rows repeating with S as the residual, the type row as a constant).  It needs a second
+    // streamed source, so without position embeddings the type row plays that part (period 1).
+    if (pos != nullptr || type != nullptr) {
+        NormArgs a{};
+        a.x = word; a.gamma = gamma; a.beta = beta; a.y = y; a.sum_out = sum_out;
+        a.mean_out = mean; a.rstd_out = rstd; a.rows = B * S; a.D = D; a.eps = (float)eps;
+        a.act = NB2_ACT_NONE; a.rms = false; a.stream = (cudaStream_t)stream;
+        a.res = pos != nullptr ? pos : type;
+        a.gather.ids = ids; a.gather.vocab = vocab; a.gather.ids_are_i32 = index_type == NB2_I32;
+        a.gather.res_period = pos != nullptr ? S : 1;
+        a.gather.extra = pos != nullptr ? type : nullptr;
+        a.gather.status = status;
+        rc = dtype == NB2_F32 ? launch_norm_fwd<float, false>(a) : launch_norm_fwd<__nv_bfloat16, false>(a);
+        if (rc != kNotFused) return rc;
+    }
     return launch_bert_embed_ln_fwd(word, pos, type, ids, gamma, beta, sum_out, y, mean, rstd, B, S, vocab, D, (float)eps,
                                     dtype, index_type, status, (cudaStream_t)stream);
 }

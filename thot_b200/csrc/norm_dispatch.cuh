@@ -16,6 +16,7 @@ struct NormArgs {
     void* y; void* dx; float* partials;
     const void* res = nullptr; void* sum_out = nullptr;   // forward: normalise x + res, also write the sum
     const void* dres = nullptr;                           // backward: dx += dres
+    RowGather gather = {nullptr, 0, 0, nullptr, nullptr, 0};   // forward with res: optional row lookup (BERT front end)
     int64_t rows; int64_t D; float eps; int act; bool rms;
     cudaStream_t stream;
 };

@@ -140,17 +140,38 @@ __device__ __forceinline__ void tma_setup(const TmaSmem& sm, int groups, int sta
     __syncthreads();
 }
 
-// group leader: request one row of each source (up to three) into a slot, one after the other
-__device__ __forceinline__ void request_row(uint64_t* bar, uint8_t* slot, const uint8_t* src0, const uint8_t* src1,
-                                            const uint8_t* src2, int64_t row, uint32_t row_bytes, uint64_t policy) {
+// group leader: request one row of each source (up to three) into a slot, one after the other;
+// each source has its own row index (the same row for plain tensors, a looked-up row for a gather)
+__device__ __forceinline__ void request_rows(uint64_t* bar, uint8_t* slot, const uint8_t* src0, int64_t r0,
+                                             const uint8_t* src1, int64_t r1, const uint8_t* src2, int64_t r2,
+                                             uint32_t row_bytes, uint64_t policy) {
     const uint32_t nsrc = 1u + (src1 != nullptr) + (src2 != nullptr);
     mbar_arrive_expect_tx(bar, nsrc * row_bytes);
     for (uint32_t off = 0; off < row_bytes; off += kBulkChunk) {
         const uint32_t n = row_bytes - off < kBulkChunk ? row_bytes - off : kBulkChunk;
-        bulk_g2s(slot + off, src0 + row * (int64_t)row_bytes + off, n, bar, policy);
-        if (src1 != nullptr) bulk_g2s(slot + row_bytes + off, src1 + row * (int64_t)row_bytes + off, n, bar, policy);
-        if (src2 != nullptr) bulk_g2s(slot + 2 * row_bytes + off, src2 + row * (int64_t)row_bytes + off, n, bar, policy);
+        bulk_g2s(slot + off, src0 + r0 * (int64_t)row_bytes + off, n, bar, policy);
+        if (src1 != nullptr) bulk_g2s(slot + row_bytes + off, src1 + r1 * (int64_t)row_bytes + off, n, bar, policy);
+        if (src2 != nullptr) bulk_g2s(slot + 2 * row_bytes + off, src2 + r2 * (int64_t)row_bytes + off, n, bar, policy);
     }
+}
+__device__ __forceinline__ void request_row(uint64_t* bar, uint8_t* slot, const uint8_t* src0, const uint8_t* src1,
+                                            const uint8_t* src2, int64_t row, uint32_t row_bytes, uint64_t policy) {
+    request_rows(bar, slot, src0, row, src1, row, src2, row, row_bytes, policy);
+}
+
+// Optional row lookup of the residual forward kernel (BERT's embedding front end,
+// src/block/details/transformers/bert.hpp:162-189): x rows are table rows picked by token id,
+// res rows repeat with the sequence length, and one more constant row is added.
+struct RowGather {
+    const void* ids;       // NULL: x is a plain [rows, D] tensor
+    int64_t vocab;         // rows of the x table
+    int64_t res_period;    // 0: res row == row; else res row == row % res_period
+    const void* extra;     // NULL or one [D] row added to every sum
+    int64_t* status;       // NULL or int64[2]: {1, first bad position} when an id is outside the table
+    int ids_are_i32;
+};
+__device__ __forceinline__ int64_t gather_id(const RowGather& g, int64_t row) {
+    return g.ids_are_i32 ? (int64_t)reinterpret_cast<const int32_t*>(g.ids)[row] : reinterpret_cast<const int64_t*>(g.ids)[row];
 }
 
 // ------------------------------------------------------------------ forward
@@ -165,7 +186,8 @@ __global__ void __launch_bounds__(NT, 1)
 norm_fwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __restrict__ gamma,
                     const T* __restrict__ beta, T* __restrict__ sum_out,
                     T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
-                    int64_t rows, int D, float eps, int stages, unsigned int* __restrict__ status) {
+                    int64_t rows, int D, float eps, int stages, unsigned int* __restrict__ status,
+                    const RowGather gather) {
     constexpr int EPV = VecTraits<T>::EPV;
     constexpr int RPC = NT / TPR;                 // row groups
     constexpr int WPR = (TPR + 31) / 32;
@@ -191,11 +213,32 @@ norm_fwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ res, const T*
     const int64_t first = (int64_t)blockIdx.x * RPC + grp;
     const int64_t stride = (int64_t)gridDim.x * RPC;
     uint64_t policy = 0;
+    // leader: which source rows a logical row maps to (identity unless a gather is configured)
+    auto request = [&](int s, int64_t row) {
+        int64_t xr = row, rr = row;
+        if constexpr (RES) {
+            if (gather.ids != nullptr) {
+                xr = gather_id(gather, row);
+                if (xr < 0 || xr >= gather.vocab) xr = 0;           // the consumers zero this row's x part
+            }
+            if (gather.res_period > 0) rr = row % gather.res_period;
+        }
+        request_rows(&full[s], ring + (size_t)s * slot_bytes, src, xr, src_res, rr, nullptr, 0, row_bytes, policy);
+    };
     if (tr == 0) {
         policy = policy_evict_first();
         for (int s = 0; s < stages; ++s) {
             const int64_t row = first + s * stride;
-            if (row < rows) request_row(&full[s], ring + (size_t)s * slot_bytes, src, src_res, nullptr, row, row_bytes, policy);
+            if (row < rows) request(s, row);
+        }
+    }
+    uint4 epk[RES ? VPT : 1];                                  // the constant extra row of a gather, if any
+    bool has_extra = false;
+    if constexpr (RES) {
+        has_extra = gather.extra != nullptr;
+        if (has_extra) {
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) epk[j] = ld_param(reinterpret_cast<const T*>(gather.extra) + (size_t)(tr + j * TPR) * EPV);
         }
     }
 
@@ -221,16 +264,33 @@ norm_fwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ res, const T*
         const uint4* srow = reinterpret_cast<const uint4*>(ring + (size_t)s * slot_bytes);
         float v[VPT][EPV];
         float sum = 0.f;
+        bool x_ok = true;
+        if constexpr (RES) {
+            if (gather.ids != nullptr) {
+                const int64_t id = gather_id(gather, row);
+                x_ok = id >= 0 && id < gather.vocab;
+                if (!x_ok && tr == 0 && gather.status != nullptr) { gather.status[0] = 1; gather.status[1] = row; }
+            }
+        }
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
             unpack<T>(srow[tr + j * TPR], v[j]);
             if constexpr (RES) {
+                if (!x_ok) {
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e) v[j][e] = 0.f;
+                }
                 float r[EPV];
                 unpack<T>(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(srow) + row_bytes)[tr + j * TPR], r);
 #pragma unroll
                 for (int e = 0; e < EPV; ++e) v[j][e] += r[e];
+                if (has_extra) {
+                    unpack<T>(epk[j], r);
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e) v[j][e] += r[e];
+                }
                 const uint4 packed = pack<T>(v[j]);
-                st_stream(sum_out + row * (int64_t)D + (size_t)(tr + j * TPR) * EPV, packed);
+                if (sum_out != nullptr) st_stream(sum_out + row * (int64_t)D + (size_t)(tr + j * TPR) * EPV, packed);
                 unpack<T>(packed, v[j]);                        // normalise what was stored (matters for bf16)
             }
 #pragma unroll
@@ -243,7 +303,7 @@ norm_fwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ res, const T*
         if (group_gave_up<TPR>(gave_up)) break;
         if (tr == 0) {
             const int64_t ahead = row + (int64_t)stages * stride;
-            if (ahead < rows) request_row(&full[s], ring + (size_t)s * slot_bytes, src, src_res, nullptr, ahead, row_bytes, policy);
+            if (ahead < rows) request(s, ahead);
         }
         if constexpr (RMS) {
             rs = rsqrtf(red0 + eps);
