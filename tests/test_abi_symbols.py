@@ -85,3 +85,22 @@ def test_python_host_refuses_cpu_tensors():
         abi.layernorm_fwd(x, None, None, 1e-5)
     with pytest.raises(TypeError):
         abi.dtype_code(torch.float16)
+
+
+def test_ctypes_signatures_match_the_header_prototypes():
+    """Every binding in thot_b200/abi.py passes exactly as many arguments as the C prototype takes,
+    and a pointer where the prototype has a pointer."""
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    protos = re.findall(r"\b(?:int|size_t|const char\*)\s+(nb2_[a-z0-9_]+)\s*\(([^;]*?)\)\s*;", text, flags=re.S)
+    assert len(protos) == len(declared_functions())
+    for name, args in protos:
+        params = [a.strip() for a in args.replace("\n", " ").split(",")] if args.strip() != "void" else []
+        res, argtypes = abi._SIGNATURES[name]
+        assert len(argtypes) == len(params), f"{name}: header has {len(params)} parameters, binding {len(argtypes)}"
+        for p, t in zip(params, argtypes):
+            is_ptr = "*" in p
+            bound_ptr = t in (ctypes.c_void_p, ctypes.c_char_p) or hasattr(t, "contents") or getattr(t, "_type_", None) not in ("i", "l", "q", "d", "L", "Q", "I")
+            if is_ptr:
+                assert bound_ptr, f"{name}: '{p}' is a pointer but is bound as {t}"
+            else:
+                assert t in (ctypes.c_int, ctypes.c_int64, ctypes.c_double, ctypes.c_size_t), f"{name}: '{p}' bound as {t}"
