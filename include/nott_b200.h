@@ -89,6 +89,15 @@ int nb2_sm_count(void);
 int nb2_device_status(unsigned int* status_host, int clear);
 
 /*
+ * Self-test of the bounded device-side wait (no counterpart in the reference).  Launches one
+ * small kernel that waits on a barrier nothing will ever complete, with the same wait routine
+ * the bulk-async kernels use but a limit of `cycle_limit` SM cycles (<= 2e9).  The wait must run
+ * out: afterwards nb2_device_status() returns NB2_ERR_DEVICE with code 3, *waited_cycles (device
+ * int64, may be NULL) holds how long the kernel waited, and the context stays usable.
+ */
+int nb2_selftest_bounded_wait(int64_t cycle_limit, int64_t* waited_cycles, void* stream);
+
+/*
  * Workspace sizes, in bytes, for the calls that need scratch memory.
  *   NB2_WS_NORM_BWD      : a = rows, b = D            -> partials buffer
  *   NB2_WS_EMBEDDING_BWD : a = tokens, b = vocab rows -> sort scratch

@@ -25,6 +25,7 @@ _SIGNATURES = {
     "nb2_last_error_string": (c_char_p, []),
     "nb2_sm_count": (c_int, []),
     "nb2_device_status": (c_int, [POINTER(ctypes.c_uint), c_int]),
+    "nb2_selftest_bounded_wait": (c_int, [c_int64, c_void_p, c_void_p]),
     "nb2_workspace_bytes": (c_size_t, [c_int, c_int64, c_int64, c_int]),
     "nb2_layernorm_fwd": (c_int, [c_void_p] * 6 + [c_int64, c_int64, c_double, c_int, c_int, c_void_p]),
     "nb2_layernorm_bwd": (c_int, [c_void_p] * 8 + [POINTER(c_int64), c_int64, c_int64, c_int, c_int, c_void_p]),

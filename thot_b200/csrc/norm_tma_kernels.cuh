@@ -22,6 +22,7 @@ namespace nb2 {
 // `status` kernel argument: a device word, 0 = ok, else (code << 16 | blockIdx) of the
 // first CTA that gave up waiting.
 constexpr unsigned int kStatusFullTimeout = 1;    // a requested row never arrived
+constexpr unsigned int kStatusSelfTest = 3;       // the self-test's wait ran out, as it must
 constexpr long long kWaitCycleLimit = 4000000000LL;   // ~2 s at 1.9 GHz
 
 constexpr int kTmaWarps = 16;
@@ -53,13 +54,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait.  Returns false (and records `code`) when the phase did not
 // complete in time or another thread of the CTA already gave up.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                                  unsigned int code, unsigned int* status) {
+                                                  unsigned int code, unsigned int* status,
+                                                  long long cycle_limit = kWaitCycleLimit) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (unsigned int it = 0; it < 0x40000000u; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if ((it & 63u) == 63u && clock64() - t0 > kWaitCycleLimit) break;
+        if ((it & 63u) == 63u && clock64() - t0 > cycle_limit) break;
     }
     *abort_flag = 1;
     atomicCAS(status, 0u, (code << 16) | (blockIdx.x & 0xffffu));
