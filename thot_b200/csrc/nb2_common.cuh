@@ -174,6 +174,97 @@ template <int ACT> __device__ __forceinline__ float act_grad(float z) {
     }
 }
 
+// ------------------------------------------------- packed fp32 pairs (sm_100)
+// Blackwell issues one instruction for two fp32 fused multiply-adds on a 64-bit register pair.
+// The norm kernels are bound by instruction issue once an activation is fused in (bf16 most of
+// all: half the bytes per element, the same arithmetic), so their per-element maths is written
+// on float2 pairs.  Each half is rounded exactly as the scalar instruction would round it, so
+// act_fwd2 gives the same bits as act_fwd above; act_grad2 forms Phi(z) without a branch and
+// differs from act_grad by at most 1.2e-7.
+// PK selects the packed instruction; with PK false the same expression runs as two scalar
+// instructions (identical results), which is what the fp32 forward kernels use: they are bound
+// by memory, not by issue, and measured 5% slower with the packed forms.
+template <bool PK = true> __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    if constexpr (PK) return __ffma2_rn(a, b, c);
+    else return make_float2(fmaf(a.x, b.x, c.x), fmaf(a.y, b.y, c.y));
+}
+template <bool PK = true> __device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    if constexpr (PK) return __fmul2_rn(a, b);
+    else return make_float2(__fmul_rn(a.x, b.x), __fmul_rn(a.y, b.y));
+}
+template <bool PK = true> __device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    if constexpr (PK) return __fadd2_rn(a, b);
+    else return make_float2(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y));
+}
+__device__ __forceinline__ float2 splat2(float s) { return make_float2(s, s); }
+
+// 16 bytes -> EPV/2 pairs of adjacent elements, and back
+template <typename T> __device__ __forceinline__ void unpack2(const uint4& v, float2* f);
+template <> __device__ __forceinline__ void unpack2<float>(const uint4& v, float2* f) {
+    f[0] = make_float2(__uint_as_float(v.x), __uint_as_float(v.y));
+    f[1] = make_float2(__uint_as_float(v.z), __uint_as_float(v.w));
+}
+template <> __device__ __forceinline__ void unpack2<__nv_bfloat16>(const uint4& v, float2* f) {
+    f[0] = make_float2(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u));
+    f[1] = make_float2(__uint_as_float(v.y << 16), __uint_as_float(v.y & 0xffff0000u));
+    f[2] = make_float2(__uint_as_float(v.z << 16), __uint_as_float(v.z & 0xffff0000u));
+    f[3] = make_float2(__uint_as_float(v.w << 16), __uint_as_float(v.w & 0xffff0000u));
+}
+template <typename T> __device__ __forceinline__ uint4 pack2(const float2* f);
+template <> __device__ __forceinline__ uint4 pack2<float>(const float2* f) {
+    return make_uint4(__float_as_uint(f[0].x), __float_as_uint(f[0].y), __float_as_uint(f[1].x), __float_as_uint(f[1].y));
+}
+template <> __device__ __forceinline__ uint4 pack2<__nv_bfloat16>(const float2* f) {
+    return make_uint4(pack_bf16x2(f[0].x, f[0].y), pack_bf16x2(f[1].x, f[1].y),
+                      pack_bf16x2(f[2].x, f[2].y), pack_bf16x2(f[3].x, f[3].y));
+}
+
+// q = Phi(-|z|), e = exp(-z^2/2), naz = -|z| for both halves
+template <bool PK>
+__device__ __forceinline__ void gelu_half_erfc2(float2 z, float2& q, float2& e, float2& naz) {
+    naz = make_float2(-fabsf(z.x), -fabsf(z.y));
+    const float2 d = fma2<PK>(splat2(-kErfcP), naz, splat2(1.0f));       // 1 + p |z|
+    const float2 t = make_float2(fast_rcp(d.x), fast_rcp(d.y));
+    const float2 w = mul2<PK>(mul2<PK>(z, z), splat2(-0.72134752044448170368f));
+    e = make_float2(fast_ex2(w.x), fast_ex2(w.y));
+    float2 p = fma2<PK>(splat2(kErfcA5), t, splat2(kErfcA4));
+    p = fma2<PK>(p, t, splat2(kErfcA3));
+    p = fma2<PK>(p, t, splat2(kErfcA2));
+    p = fma2<PK>(p, t, splat2(kErfcA1));
+    q = mul2<PK>(mul2<PK>(p, t), e);
+}
+template <int ACT, bool PK = true> __device__ __forceinline__ float2 act_fwd2(float2 z) {
+    if constexpr (ACT == NB2_ACT_GELU) {
+        float2 q, e, naz;
+        gelu_half_erfc2<PK>(z, q, e, naz);
+        return fma2<PK>(naz, q, make_float2(fmaxf(z.x, 0.0f), fmaxf(z.y, 0.0f)));
+    } else if constexpr (ACT == NB2_ACT_SILU) {
+        const float2 w = mul2<PK>(z, splat2(-1.44269504088896340736f));
+        const float2 d = add2<PK>(splat2(1.0f), make_float2(fast_ex2(w.x), fast_ex2(w.y)));
+        return mul2<PK>(z, make_float2(fast_rcp(d.x), fast_rcp(d.y)));
+    } else {
+        return z;
+    }
+}
+template <int ACT, bool PK = true> __device__ __forceinline__ float2 act_grad2(float2 z) {
+    if constexpr (ACT == NB2_ACT_GELU) {
+        float2 q, e, naz;
+        gelu_half_erfc2<PK>(z, q, e, naz);
+        // Phi(z) = 1/2 + sign(z) (1/2 - q): two sign copies instead of two compares and two selects
+        const float2 hq = fma2<PK>(q, splat2(-1.0f), splat2(0.5f));
+        const float2 sg = make_float2(copysignf(1.0f, z.x), copysignf(1.0f, z.y));
+        const float2 cdf = fma2<PK>(sg, hq, splat2(0.5f));
+        return fma2<PK>(mul2<PK>(z, splat2(kInvSqrt2Pi)), e, cdf);
+    } else if constexpr (ACT == NB2_ACT_SILU) {
+        const float2 w = mul2<PK>(z, splat2(-1.44269504088896340736f));
+        const float2 d = add2<PK>(splat2(1.0f), make_float2(fast_ex2(w.x), fast_ex2(w.y)));
+        const float2 s = make_float2(fast_rcp(d.x), fast_rcp(d.y));
+        return mul2<PK>(s, fma2<PK>(z, fma2<PK>(s, splat2(-1.0f), splat2(1.0f)), splat2(1.0f)));
+    } else {
+        return splat2(1.0f);
+    }
+}
+
 // ---------------------------------------------------------------- reductions
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

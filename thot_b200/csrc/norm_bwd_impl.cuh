@@ -6,10 +6,10 @@
 
 namespace nb2 {
 
-template <typename T, int TPR, int VPT, int ACT, bool RMS, bool RES>
+template <typename T, int TPR, int VPT, int ACT, bool RMS, bool RES, int NT>
 static int launch_bwd_tma_res(const NormArgs& a, int64_t* n_partials) {
-    auto kern = norm_bwd_tma_kernel<T, TPR, VPT, ACT, RMS, RES>;
-    const TmaTiling t = tma_tiling(a.D, (int)sizeof(T), TPR, RES ? 3 : 2);
+    auto kern = norm_bwd_tma_kernel<T, TPR, VPT, ACT, RMS, RES, NT>;
+    const TmaTiling t = tma_tiling(a.D, (int)sizeof(T), TPR, RES ? 3 : 2, NT);
     NB2_REQUIRE(t.smem <= kTmaMaxSmem, NB2_ERR_SHAPE, "norm ring kernel: %zu bytes of shared memory exceed the SM", t.smem);
     static thread_local size_t configured_all[kMaxDevices] = {};
     size_t& configured = configured_all[current_device_slot()];
@@ -19,8 +19,8 @@ static int launch_bwd_tma_res(const NormArgs& a, int64_t* n_partials) {
         if (rc != 0) return rc;
         configured = t.smem;
     }
-    const int grid = (int)tma_grid(a.rows, TPR, sm_count());
-    const cudaError_t e = launch_pdl(kern, dim3(grid), dim3(kTmaThreads), t.smem, a.stream, (const T*)a.x, (const T*)a.dy,
+    const int grid = (int)tma_grid(a.rows, TPR, sm_count(), NT);
+    const cudaError_t e = launch_pdl(kern, dim3(grid), dim3(NT), t.smem, a.stream, (const T*)a.x, (const T*)a.dy,
                                      (const T*)a.dres, (const T*)a.gamma, (const T*)a.beta, a.mean, a.rstd, (T*)a.dx,
                                      a.partials, a.rows, (int)a.D, t.stages, device_status_ptr());
     if (e != cudaSuccess) return cuda_status(e, "norm_bwd_tma_kernel launch");
@@ -28,14 +28,14 @@ static int launch_bwd_tma_res(const NormArgs& a, int64_t* n_partials) {
     return 0;
 }
 
-template <typename T, int TPR, int VPT, int ACT, bool RMS>
+template <typename T, int TPR, int VPT, int ACT, bool RMS, int NT = kTmaThreads>
 static int launch_bwd_tma(const NormArgs& a, int64_t* n_partials) {
     if (a.dres != nullptr) {
-        if constexpr (ACT == NB2_ACT_NONE) return launch_bwd_tma_res<T, TPR, VPT, ACT, RMS, true>(a, n_partials);
+        if constexpr (ACT == NB2_ACT_NONE) return launch_bwd_tma_res<T, TPR, VPT, ACT, RMS, true, NT>(a, n_partials);
         set_error("residual + norm is not fused with an activation");
         return NB2_ERR_DTYPE;
     }
-    return launch_bwd_tma_res<T, TPR, VPT, ACT, RMS, false>(a, n_partials);
+    return launch_bwd_tma_res<T, TPR, VPT, ACT, RMS, false, NT>(a, n_partials);
 }
 
 template <typename T, int ACT, bool RMS>
