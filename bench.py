@@ -301,6 +301,19 @@ def run_suite(args):
     for nm, code in (("gelu", abi.ACT_GELU), ("silu", abi.ACT_SILU)):
         timed(f"{nm}_fwd fp32 32Mi", lambda: abi.act_fwd(xf, code), 2 * n * 4)
         timed(f"{nm}_bwd fp32 32Mi", lambda: abi.act_bwd(xf, df, code), 3 * n * 4)
+    del xf, df
+    # attention probabilities (kernel.hpp:33-93): scores [16, 16, 1024, 1024], causal, then with an additive [B,T,S] mask
+    for dt, nm in ((torch.float32, "fp32"), (bf, "bf16")):
+        sc = torch.randn(16, 16, 1024, 1024, device=dev, generator=g).to(dt)
+        da_ = torch.randn(16, 16, 1024, 1024, device=dev, generator=g).to(dt)
+        at = abi.attention_softmax_fwd(sc, 0.125, causal=True)
+        e = sc.element_size()
+        timed(f"attention_softmax_fwd {nm} [16,16,1024,1024] causal", lambda: abi.attention_softmax_fwd(sc, 0.125, causal=True), 2 * sc.numel() * e)
+        mk = torch.randn(16, 1024, 1024, device=dev, generator=g).to(dt)
+        timed(f"attention_softmax_fwd {nm} [16,16,1024,1024] + mask [16,1024,1024]",
+              lambda: abi.attention_softmax_fwd(sc, 0.125, attn_mask=mk), 2 * sc.numel() * e + mk.numel() * e)
+        timed(f"attention_softmax_bwd {nm} [16,16,1024,1024]", lambda: abi.attention_softmax_bwd(at, da_, 0.125), 3 * sc.numel() * e)
+        del sc, da_, at, mk
     abi.device_status()
     _emit({"suite": results, "peak_gbs": peak, "unit": "GB/s", "data": "synthetic",
            "note": "timings include torch's output allocation from its caching allocator"})

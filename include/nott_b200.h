@@ -327,6 +327,31 @@ int nb2_rope_apply(const void* x, const float* cos_sin, void* out,
                    int dtype, int inverse, void* stream);
 
 /* ------------------------------------------------------------------ *
+ * Attention probabilities: the steps between the two matmuls of
+ * ScaledDotProductKernelImpl::forward (src/attention/details/kernel.hpp:33-92),
+ *   attn = softmax(scores * scale [key padding -> -inf] [+ attn_mask] [causal -> -inf], last dim)
+ * in one read of scores and one write of attn, where the reference makes five
+ * passes (division, masked_fill, add, masked_fill, softmax).
+ *   scores, attn : [B, H, T, S] contiguous, `dtype`; scale = 1/sqrt(head_dim) there.
+ *   key_padding  : [B, S] bytes, non-zero = that key is padding (kernel.hpp:36-39), or NULL.
+ *   attn_mask    : additive mask of `dtype` (kernel.hpp:41-84), or NULL; element
+ *                  (b, h, t, s) is read at b*mask_batch_stride + h*mask_head_stride + t*S + s,
+ *                  so [T,S] is strides (0, 0), [B,T,S] is (T*S, 0), [B,H,T,S] and
+ *                  [B*H,T,S] are (H*T*S, T*S).
+ *   causal != 0  : columns s > t are masked (Variant::Causal, kernel.hpp:86-91).
+ * A row with every column masked comes out as NaN, as torch::softmax gives it.
+ * bwd: dscores = scale * attn * (dattn - sum_s attn * dattn), rows = B*H*T; masked
+ * columns receive 0, as through masked_fill.  Dropout on attn (kernel.hpp:94) is
+ * not part of this call.
+ * ------------------------------------------------------------------ */
+int nb2_attention_softmax_fwd(const void* scores, const uint8_t* key_padding, const void* attn_mask,
+                              int64_t mask_batch_stride, int64_t mask_head_stride, void* attn,
+                              int64_t B, int64_t H, int64_t T, int64_t S, double scale, int causal,
+                              int dtype, void* stream);
+int nb2_attention_softmax_bwd(const void* attn, const void* dattn, void* dscores,
+                              int64_t rows, int64_t S, double scale, int dtype, void* stream);
+
+/* ------------------------------------------------------------------ *
  * Host-buffer training step of the fused LayerNorm->activation path: the call
  * a host-resident caller makes (the reference stages batches from pinned host
  * memory itself, src/core.hpp:4197-4227).  x_host, dy_host, y_host, dx_host

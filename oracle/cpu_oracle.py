@@ -157,6 +157,30 @@ def bert_embedding(word, pos, type_table, gamma, beta, ids, dy=None, eps=1e-12, 
     return out
 
 
+def _mask_strides(attn_mask, B, H, T, S):
+    if attn_mask is None:
+        return 0, 0
+    if attn_mask.ndim == 2:
+        return 0, 0
+    if attn_mask.ndim == 3 and attn_mask.shape[0] == B:
+        return T * S, 0
+    return H * T * S, T * S
+
+
+def attention_softmax(scores, scale, key_padding=None, attn_mask=None, causal=False, dattn=None):
+    """scores [B,H,T,S] fp32 -> dict(attn, dscores) in fp64 (kernel.hpp:33-93)."""
+    scores, attn_mask, dattn = _f32(scores), _f32(attn_mask), _f32(dattn)
+    B, H, T, S = scores.shape
+    kp = None if key_padding is None else np.ascontiguousarray(key_padding, dtype=np.uint8)
+    sb, sh = _mask_strides(attn_mask, B, H, T, S)
+    attn = np.empty(scores.shape)
+    ds = np.empty(scores.shape) if dattn is not None else None
+    with np.errstate(invalid="ignore"):
+        lib().orc_attention_softmax(_p(scores), _p(kp), _p(attn_mask), c_int64(sb), c_int64(sh), _p(dattn), c_int64(B), c_int64(H),
+                                    c_int64(T), c_int64(S), c_double(scale), c_int(int(causal)), _p(attn), _p(ds))
+    return dict(attn=attn, dscores=ds)
+
+
 def _round_bf16(a):
     u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
     return (((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16).astype(np.uint32).view(np.float32)

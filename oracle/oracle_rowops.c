@@ -239,3 +239,43 @@ void orc_rope_apply(const float* x, const float* cos_sin, int64_t B, int64_t S, 
                 }
             }
 }
+
+/*
+ * Attention probabilities: ScaledDotProductKernelImpl::forward between its two matmuls
+ * (src/attention/details/kernel.hpp:33-92).  scores / sqrt(head_dim) (:32-34, here scores * scale),
+ * key padding -> -inf (:36-39), + additive mask (:41-84), causal columns s > t -> -inf (:86-91),
+ * softmax over the last dim (:93).  mask element (b,h,t,s) sits at b*mask_sb + h*mask_sh + t*S + s.
+ * A row with every column masked is NaN, as torch::softmax makes it.
+ * Backward of softmax and of the scaling: dscores = scale * attn * (dattn - sum_s attn * dattn).
+ */
+void orc_attention_softmax(const float* scores, const uint8_t* key_padding, const float* mask, int64_t mask_sb,
+                           int64_t mask_sh, const float* dattn, int64_t B, int64_t H, int64_t T, int64_t S,
+                           double scale, int causal, double* attn, double* dscores) {
+    double* row = (double*)malloc(sizeof(double) * (size_t)(S > 0 ? S : 1));
+    for (int64_t b = 0; b < B; ++b)
+        for (int64_t h = 0; h < H; ++h)
+            for (int64_t t = 0; t < T; ++t) {
+                const int64_t r = (b * H + h) * T + t;
+                const float* src = scores + r * S;
+                double mx = -INFINITY;
+                for (int64_t s = 0; s < S; ++s) {
+                    double v = (double)src[s] * scale;
+                    if (key_padding && key_padding[b * S + s]) v = -INFINITY;
+                    if (mask) v += (double)mask[b * mask_sb + h * mask_sh + t * S + s];
+                    if (causal && s > t) v = -INFINITY;
+                    row[s] = v;
+                    if (v > mx) mx = v;
+                }
+                double sum = 0.0;
+                for (int64_t s = 0; s < S; ++s) { row[s] = exp(row[s] - mx); sum += row[s]; }
+                double dot = 0.0;
+                for (int64_t s = 0; s < S; ++s) {
+                    row[s] /= sum;
+                    if (attn) attn[r * S + s] = row[s];
+                    if (dattn) dot += row[s] * (double)dattn[r * S + s];
+                }
+                if (dattn && dscores)
+                    for (int64_t s = 0; s < S; ++s) dscores[r * S + s] = scale * row[s] * ((double)dattn[r * S + s] - dot);
+            }
+    free(row);
+}

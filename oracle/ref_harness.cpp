@@ -30,6 +30,7 @@
 #include "src/activation/apply.hpp"
 #include "src/block/details/transformers/mamba.hpp"
 #include "src/block/details/transformers/ebt.hpp"
+#include "src/attention/details/kernel.hpp"
 
 // bert.hpp pulls in src/layer/details/recurrent.hpp, which calls an overload of
 // at::Context::setFloat32Precision that libtorch 2.11 no longer has (four lines that set
@@ -349,6 +350,39 @@ double ref_time_norm_act(int rms, int64_t rows, int64_t D, double eps, int act, 
         result = std::chrono::duration<double>(t1 - t0).count() / (iters > 0 ? iters : 1);
     });
     return result;
+}
+
+// ScaledDotProductKernelImpl::forward (src/attention/details/kernel.hpp:20-94) run with key = value =
+// identity ([S, S], so head_dim == S): then scores == query exactly, and the module's output is its
+// attention matrix itself,
+//   attn = softmax(query / sqrt(S) [key padding -> -inf] [+ attn_mask] [causal -> -inf], dim -1).
+// key_padding: [B, S] bytes (non-zero = padded) or NULL.  attn_mask: additive, mask_dims in {2, 3, 4}
+// with shapes [T,S], [B,T,S], [B,H,T,S], or NULL.  With dattn, dquery (the gradient of
+// sum(attn * dattn) with respect to query) comes back in dscores.
+int ref_attention_softmax(const float* query, const uint8_t* key_padding, const float* attn_mask, int mask_dims,
+                          const float* dattn, int64_t B, int64_t H, int64_t T, int64_t S, int causal, int compute,
+                          float* attn, float* dscores) {
+    return guarded([&] {
+        namespace A = Nott::Attention;
+        A::Details::ScaledDotProductKernel kernel(0.0, causal ? A::Variant::Causal : A::Variant::Full);
+        const auto dt = compute_type(compute);
+        auto q = wrap(query, {B, H, T, S}, compute).clone().requires_grad_(dattn != nullptr);
+        auto eye = torch::eye(S, torch::TensorOptions().dtype(dt)).expand({B, H, S, S});
+        torch::Tensor mask, padding;
+        if (attn_mask != nullptr) {
+            std::vector<int64_t> shape = mask_dims == 2 ? std::vector<int64_t>{T, S}
+                                         : mask_dims == 3 ? std::vector<int64_t>{B, T, S} : std::vector<int64_t>{B, H, T, S};
+            mask = wrap(attn_mask, shape, compute);
+        }
+        if (key_padding != nullptr)
+            padding = torch::from_blob(const_cast<uint8_t*>(key_padding), {B, S}, torch::kUInt8).to(torch::kBool);
+        auto out = kernel->forward(q, eye, eye, mask, padding);
+        store(out, attn);
+        if (dattn != nullptr) {
+            (out * wrap(dattn, {B, H, T, S}, compute)).sum().backward();
+            store(q.grad(), dscores);
+        }
+    });
 }
 
 }  // extern "C"

@@ -154,6 +154,19 @@ def token_embedding(table, ids, dout=None, compute=0):
     return dict(out=out, dtable=dtable)
 
 
+def attention_softmax(scores, key_padding=None, attn_mask=None, causal=False, dattn=None, compute=0):
+    """The reference's ScaledDotProductKernel with key = value = identity: scale is 1/sqrt(S)."""
+    scores, attn_mask, dattn = _f32(scores), _f32(attn_mask), _f32(dattn)
+    B, H, T, S = scores.shape
+    kp = None if key_padding is None else np.ascontiguousarray(key_padding, dtype=np.uint8)
+    attn = np.empty(scores.shape, dtype=np.float32)
+    ds = np.empty(scores.shape, dtype=np.float32) if dattn is not None else None
+    dims = 0 if attn_mask is None else attn_mask.ndim
+    _chk(lib().ref_attention_softmax(_p(scores), _p(kp), _p(attn_mask), c_int(dims), _p(dattn), c_int64(B), c_int64(H),
+                                     c_int64(T), c_int64(S), c_int(int(causal)), c_int(compute), _p(attn), _p(ds)))
+    return dict(attn=attn, dscores=ds)
+
+
 def time_norm_act(kind, rows, D, eps, act, compute=0, iters=10, warmup=2) -> float:
     """Seconds per forward+backward of the reference modules, timed inside the harness."""
     t = lib().ref_time_norm_act(c_int(1 if kind == "rms" else 0), c_int64(rows), c_int64(D), c_double(eps),

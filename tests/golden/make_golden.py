@@ -137,6 +137,25 @@ def main():
     r64 = R.token_embedding(table, ids, dout, 1)
     np.savez(OUT / "embedding.npz", table=table, ids=ids, dout=dout, out=r["out"], dtable_f32=r["dtable"],
              dtable_f64=r64["dtable"])
+    # Attention probabilities through the reference's ScaledDotProductKernel with key = value = identity
+    # (kernel.hpp:20-94): key padding, additive masks of each accepted rank, causal; scale = 1/sqrt(S).
+    gen = torch.Generator().manual_seed(40)
+    B, H, T, S = 2, 3, 10, 24
+    scores = randn(gen, B, H, T, S, scale=3.0)
+    dattn = randn(gen, B, H, T, S)
+    padding = np.zeros((B, S), np.uint8)
+    padding[1, -7:] = 1
+    rec = dict(scores=scores, dattn=dattn, padding=padding, mask2=randn(gen, T, S), mask3=randn(gen, B, T, S),
+               mask4=randn(gen, B, H, T, S))
+    rec["mask2"][2, :5] = -np.inf                     # a float mask may carry -inf itself
+    cases = {"plain": (None, None, False), "causal": (None, None, True), "padding": ("padding", None, False),
+             "mask2": (None, "mask2", False), "mask3_padding": ("padding", "mask3", False), "mask4_causal": (None, "mask4", True)}
+    for name, (pk, mk, causal) in cases.items():
+        for tag, compute in (("f32", 0), ("f64", 1)):
+            r = R.attention_softmax(scores, rec[pk] if pk else None, rec[mk] if mk else None, causal, dattn, compute)
+            rec[f"{name}_attn_{tag}"] = r["attn"]
+            rec[f"{name}_dscores_{tag}"] = r["dscores"]
+    np.savez(OUT / "attention_softmax.npz", **rec)
     print("wrote", sorted(p.name for p in OUT.glob("*.npz")))
 
 

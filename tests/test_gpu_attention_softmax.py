@@ -1,0 +1,103 @@
+"""Attention probabilities (scale, key padding, additive mask, causal, softmax) in one kernel:
+C ABI against the reference's ScaledDotProductKernel goldens and the CPU oracle, and the C++
+drop-in module against the same arithmetic written with torch ops."""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import cpu_oracle as O
+from tests.gpu_util import check, make, to_dev
+from tests.test_oracle_golden import ATTN_CASES
+from thot_b200 import abi
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("name", sorted(ATTN_CASES))
+def test_golden_reference_kernel(golden_dir, name):
+    z = np.load(golden_dir / "attention_softmax.npz")
+    pk, mk, causal = ATTN_CASES[name]
+    scores = to_dev(z["scores"], torch.float32)
+    S = scores.shape[-1]
+    padding = torch.from_numpy(z[pk]).cuda() if pk else None
+    mask = torch.from_numpy(z[mk]).cuda() if mk else None
+    attn = abi.attention_softmax_fwd(scores, 1.0 / math.sqrt(S), padding, mask, causal)
+    check(attn, z[f"{name}_attn_f64"], "attn")
+    ds = abi.attention_softmax_bwd(attn, to_dev(z["dattn"], torch.float32), 1.0 / math.sqrt(S))
+    check(ds, z[f"{name}_dscores_f64"], "dscores")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("B,H,T,S,mask_rank,use_padding,causal", [
+    (2, 4, 128, 128, 0, False, True),        # one warp per row
+    (1, 2, 64, 512, 2, True, False),
+    (2, 2, 16, 2048, 3, False, False),       # several warps per row
+    (1, 1, 8, 8192, 4, True, False),         # the widest register-row shape for fp32
+    (2, 3, 9, 77, 4, True, True),            # ragged length: the three-sweep kernel
+    (1, 1, 3, 16400, 0, False, False),       # beyond the register-row shapes
+])
+def test_against_oracle(dtype, B, H, T, S, mask_rank, use_padding, causal):
+    scores, sn = make((B, H, T, S), 1, dtype, 2.0)
+    dattn, dn = make((B, H, T, S), 2, dtype)
+    mask_shape = {0: None, 2: (T, S), 3: (B, T, S), 4: (B, H, T, S)}[mask_rank]
+    mask, mn = make(mask_shape, 3, dtype) if mask_shape else (None, None)
+    padding = None
+    if use_padding:
+        padding = torch.zeros(B, S, dtype=torch.bool)
+        padding[-1, S - S // 3:] = True
+    scale = 1.0 / math.sqrt(64)
+    attn = abi.attention_softmax_fwd(scores, scale, None if padding is None else padding.cuda(), mask, causal)
+    ref = O.attention_softmax(sn, scale, None if padding is None else padding.numpy(), mn, causal, None)
+    check(attn.reshape(-1, S), ref["attn"].reshape(-1, S), "attn")
+    assert torch.allclose(attn.float().sum(-1), torch.ones(B, H, T, device="cuda"), atol=2e-2 if dtype == torch.bfloat16 else 1e-5)
+    # backward from the probabilities the kernel itself stored (bf16: rounded), as autograd would run it
+    an = attn.float().cpu().numpy().astype(np.float64)
+    dot = (an * dn).sum(-1, keepdims=True)
+    ds = abi.attention_softmax_bwd(attn, dattn, scale)
+    check(ds.reshape(-1, S), (scale * an * (dn - dot)).reshape(-1, S), "dscores")
+
+
+def test_a_fully_masked_row_is_nan_like_the_reference():
+    scores, _ = make((1, 1, 2, 64), 1, torch.float32)
+    padding = torch.ones(1, 64, dtype=torch.bool, device="cuda")
+    attn = abi.attention_softmax_fwd(scores, 0.125, padding)
+    assert torch.isnan(attn).all()
+    assert abi.lib().nb2_attention_softmax_fwd(None, None, None, 0, 0, None, 1, 1, 1, 8, 1.0, 0, 0, None) == -1   # NULL
+    assert abi.lib().nb2_attention_softmax_fwd(None, None, None, 0, 0, None, 1, 1, 0, 8, 1.0, 0, 0, None) == 0    # empty
+    assert abi.lib().nb2_attention_softmax_fwd(None, None, None, 0, 0, None, 1, 1, 1, 8, 1.0, 0, 7, None) == -3   # dtype
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_scaled_dot_product_module_matches_torch_ops(causal):
+    """The C++ drop-in for the reference's ScaledDotProductKernel against the reference's own sequence
+    of torch ops (kernel.hpp:26-95) run on the same GPU in fp32, values and gradients."""
+    from thot_b200 import _nott_b200_host as host
+    B, H, T, S, hd = 2, 3, 40, 56, 32
+    q, _ = make((B, H, T, hd), 1, torch.float32); k, _ = make((B, H, S, hd), 2, torch.float32); v, _ = make((B, H, S, hd), 3, torch.float32)
+    mask, _ = make((B, T, S), 4, torch.float32)
+    padding = torch.zeros(B, S, dtype=torch.bool, device="cuda"); padding[0, -9:] = True
+    dout, _ = make((B, H, T, hd), 5, torch.float32)
+
+    def reference(q, k, v):
+        scores = torch.matmul(q, k.transpose(-2, -1)) / math.sqrt(hd)
+        scores = scores.masked_fill(padding[:, None, None, :], float("-inf")) + mask[:, None]
+        if causal:
+            scores = scores.masked_fill(torch.ones(T, S, dtype=torch.bool, device="cuda").triu(1), float("-inf"))
+        return torch.matmul(torch.softmax(scores, -1), v)
+
+    grads = []
+    outs = []
+    for fn in (reference, lambda q, k, v: host.scaled_dot_product(q, k, v, mask, padding, causal)):
+        qi, ki, vi = (t.clone().requires_grad_(True) for t in (q, k, v))
+        out = fn(qi, ki, vi)
+        out.backward(dout)
+        outs.append(out.detach()); grads.append((qi.grad, ki.grad, vi.grad))
+    torch.testing.assert_close(outs[1], outs[0], rtol=1e-5, atol=1e-5)
+    for got, want in zip(grads[1], grads[0]):
+        torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-5)
+    with pytest.raises(ValueError):                     # std::invalid_argument, as the reference throws
+        host.attention_softmax(torch.zeros(B, H, T, S, device="cuda"), torch.zeros(T + 1, S, device="cuda"), None, 1.0, False)

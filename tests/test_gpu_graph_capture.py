@@ -45,3 +45,27 @@ def test_forward_backward_reduce_replay_matches_eager(dtype, D):
     torch.cuda.synchronize()
     assert torch.equal(y, y0) and torch.equal(dx, dx0) and torch.equal(grads, gr0)
     assert abi.device_status() == 0
+
+
+def test_bert_backward_with_its_side_stream_is_capturable():
+    """The BERT front-end backward sorts the ids on a side stream beside the LayerNorm backward;
+    a capture must follow that fork and join, and the replay must reproduce the eager gradients."""
+    B, S, D, vocab = 8, 64, 768, 1000
+    dtype = torch.bfloat16
+    ssum, _ = make((B * S, D), 1, dtype); dy, _ = make((B, S, D), 2, dtype)
+    g, _ = make((D,), 3, dtype, 0.02, 1.0)
+    ids = torch.randint(0, vocab, (B, S), generator=torch.Generator().manual_seed(4)).cuda()
+    mean = ssum.float().mean(-1); rstd = torch.rsqrt(ssum.float().var(-1, unbiased=False) + 1e-5)
+    dword0, dpos0, dtype00, grads0, dsum0 = abi.bert_embedding_ln_bwd(ssum, dy, ids, g, mean, rstd, vocab, pos_rows=S)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = abi.bert_embedding_ln_bwd(ssum, dy, ids, g, mean, rstd, vocab, pos_rows=S)
+    for t in out:
+        t.fill_(float("nan"))
+    for _ in range(2):
+        graph.replay()
+    torch.cuda.synchronize()
+    for got, want in zip(out, (dword0, dpos0, dtype00, grads0, dsum0)):
+        assert torch.equal(got, want)
+    assert abi.device_status() == 0

@@ -129,3 +129,32 @@ def test_bert_embedding_oracle_matches_reference_module(golden_dir):
     assert not g["dtype_f64"][1].any()                       # token types are always 0 (bert.hpp:184)
     tol.long_sum_close(o["dgamma"], g["dgamma_f64"], 21, ref32=g["dgamma_f32"])
     tol.long_sum_close(o["dbeta"], g["dbeta_f64"], 21, ref32=g["dbeta_f32"])
+
+
+ATTN_CASES = {"plain": (None, None, False), "causal": (None, None, True), "padding": ("padding", None, False),
+              "mask2": (None, "mask2", False), "mask3_padding": ("padding", "mask3", False), "mask4_causal": (None, "mask4", True)}
+
+
+@pytest.mark.parametrize("name", sorted(ATTN_CASES))
+def test_attention_softmax_oracle_matches_reference_kernel(golden_dir, name):
+    """Golden = the reference's ScaledDotProductKernel run with key = value = identity, so that its
+    output is the attention matrix of the given scores (scale 1/sqrt(S))."""
+    g = load(golden_dir, "attention_softmax")
+    pk, mk, causal = ATTN_CASES[name]
+    S = g["scores"].shape[-1]
+    o = O.attention_softmax(g["scores"], 1.0 / np.sqrt(S), g[pk] if pk else None, g[mk] if mk else None, causal, g["dattn"])
+    # the module ran in fp64 and its outputs were stored as fp32: agreement to fp32 rounding
+    np.testing.assert_allclose(o["attn"], g[f"{name}_attn_f64"], rtol=1.2e-7, atol=1e-12)
+    np.testing.assert_allclose(o["dscores"], g[f"{name}_dscores_f64"], rtol=1.2e-7, atol=1e-10)
+    tol.fp32_close(o["attn"], g[f"{name}_attn_f32"])
+    tol.fp32_close(o["dscores"], g[f"{name}_dscores_f32"])
+    assert np.allclose(o["attn"].sum(-1), 1.0)
+    if causal:
+        assert not np.triu(o["attn"], 1).any()          # nothing attends to a later column
+
+
+def test_attention_softmax_oracle_fully_masked_row_is_nan():
+    scores = np.zeros((1, 1, 2, 4), np.float32)
+    padding = np.ones((1, 4), np.uint8)
+    o = O.attention_softmax(scores, 0.5, padding)
+    assert np.isnan(o["attn"]).all()                     # torch::softmax of a row of -inf

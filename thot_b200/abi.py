@@ -25,6 +25,9 @@ _SIGNATURES = {
     "nb2_last_error_string": (c_char_p, []),
     "nb2_sm_count": (c_int, []),
     "nb2_device_status": (c_int, [POINTER(ctypes.c_uint), c_int]),
+    "nb2_attention_softmax_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int64,
+                                          c_double, c_int, c_int, c_void_p]),
+    "nb2_attention_softmax_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_double, c_int, c_void_p]),
     "nb2_selftest_bounded_wait": (c_int, [c_int64, c_void_p, c_void_p]),
     "nb2_workspace_bytes": (c_size_t, [c_int, c_int64, c_int64, c_int]),
     "nb2_layernorm_fwd": (c_int, [c_void_p] * 6 + [c_int64, c_int64, c_double, c_int, c_int, c_void_p]),
@@ -329,6 +332,38 @@ def bert_embedding_ln_bwd(ssum, dy, ids, gamma, mean, rstd, vocab: int, pos_rows
                                           _p(dsum), _p(dword), _p(dpos), pos_rows, _p(dtype0), _p(grads), B, S, vocab, D, code,
                                           _index_code(ids), _p(ws), ws_bytes, _stream()))
     return dword, dpos, dtype0, grads, dsum
+
+
+# ------------------------------------------------------------------ attention
+def attention_softmax_fwd(scores, scale: float, key_padding=None, attn_mask=None, causal: bool = False):
+    """scores [B, H, T, S] -> attn.  key_padding [B, S] bool/uint8; attn_mask additive, [T,S], [B,T,S],
+    [B*H,T,S] or [B,H,T,S] of the scores' dtype."""
+    _dev(scores)
+    B, H, T, S = scores.shape
+    out = torch.empty_like(scores)
+    sb = sh = 0
+    if attn_mask is not None:
+        attn_mask = attn_mask.to(scores.dtype).contiguous()
+        if attn_mask.dim() == 3 and attn_mask.shape[0] == B:
+            sb = T * S
+        elif attn_mask.dim() == 4 or (attn_mask.dim() == 3 and attn_mask.shape[0] == B * H):
+            sb, sh = H * T * S, T * S
+        elif attn_mask.dim() != 2:
+            raise ValueError("attention mask must be [T,S], [B,T,S], [B*H,T,S] or [B,H,T,S]")
+    if key_padding is not None:
+        key_padding = key_padding.to(torch.uint8).contiguous()
+    check(lib().nb2_attention_softmax_fwd(_p(scores), _p(key_padding), _p(attn_mask), sb, sh, _p(out), B, H, T, S, scale,
+                                          int(causal), dtype_code(scores.dtype), _stream()))
+    return out
+
+
+def attention_softmax_bwd(attn, dattn, scale: float):
+    _dev(attn)
+    S = attn.shape[-1]
+    out = torch.empty_like(attn)
+    check(lib().nb2_attention_softmax_bwd(_p(attn), _p(dattn), _p(out), attn.numel() // max(S, 1), S, scale,
+                                          dtype_code(attn.dtype), _stream()))
+    return out
 
 
 # --------------------------------------------------------------------- rope

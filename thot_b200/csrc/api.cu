@@ -54,6 +54,31 @@ unsigned int* device_status_ptr() {
     return p;
 }
 
+// A side stream and two events per host thread and device, for work that may run beside the
+// caller's stream (forked and joined with events, which a stream capture follows as well).
+// Never created while the caller's stream is capturing: the caller then gets nullptr and runs
+// the work in line.
+struct SideStream { cudaStream_t stream; cudaEvent_t fork, join; };
+static SideStream* side_stream(cudaStream_t user) {
+    static thread_local SideStream streams[kMaxDevices] = {};
+    static thread_local bool ready[kMaxDevices] = {};
+    const int slot = current_device_slot();
+    if (!ready[slot]) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(user, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return nullptr;
+        SideStream s = {};
+        if (cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+        if (cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        streams[slot] = s;
+        ready[slot] = true;
+    }
+    return &streams[slot];
+}
+
 static bool dtype_ok(int d) { return d == NB2_F32 || d == NB2_BF16; }
 static bool act_ok(int a) { return a == NB2_ACT_NONE || a == NB2_ACT_GELU || a == NB2_ACT_SILU; }
 static bool idx_ok(int i) { return i == NB2_I32 || i == NB2_I64; }
@@ -373,14 +398,53 @@ int nb2_bert_embedding_ln_bwd(const void* sum, const void* dy, const void* ids, 
         if (rc == 0 && dtype0) rc = cuda_status(cudaMemsetAsync(dtype0, 0, (size_t)D * elt, st), "bert embedding bwd memset");
         return rc;
     }
+    // The sort of the ids does not depend on the gradient: it runs on a side stream while the
+    // LayerNorm backward streams the activations, and joins before the row sums need it.
+    SideStream* side = side_stream(st);
+    if (side != nullptr) {
+        rc = cuda_status(cudaEventRecord(side->fork, st), "bert embedding bwd: fork");
+        if (rc == 0) rc = cuda_status(cudaStreamWaitEvent(side->stream, side->fork, 0), "bert embedding bwd: fork");
+        if (rc == 0) rc = launch_embedding_bwd_index(ids, tokens, vocab, index_type, sort_ws, sort_bytes, side->stream);
+        if (rc == 0) rc = cuda_status(cudaEventRecord(side->join, side->stream), "bert embedding bwd: join");
+        if (rc != 0) return rc;
+    }
     int64_t n = 0;
     rc = nb2_layernorm_bwd(sum, dy, gamma, nullptr, mean, rstd, dsum, partials, &n, tokens, D, dtype, NB2_ACT_NONE, stream);
     if (rc != 0) return rc;
     rc = nb2_colreduce_partials(partials, n, 2 * D, dgamma_dbeta, stream);
     if (rc != 0) return rc;
-    rc = launch_embedding_bwd(dsum, ids, dword, tokens, vocab, D, dtype, index_type, sort_ws, sort_bytes, st);
+    if (side != nullptr) rc = cuda_status(cudaStreamWaitEvent(st, side->join, 0), "bert embedding bwd: join");
+    else rc = launch_embedding_bwd_index(ids, tokens, vocab, index_type, sort_ws, sort_bytes, st);
+    if (rc != 0) return rc;
+    rc = launch_embedding_bwd_sum(dsum, dword, tokens, vocab, D, dtype, sort_ws, st);
     if (rc != 0) return rc;
     return launch_bert_embed_table_grads(dsum, dpos, dtype0, type_scratch, B, S, D, dtype, st);
+}
+
+int nb2_attention_softmax_fwd(const void* scores, const uint8_t* key_padding, const void* attn_mask,
+                              int64_t mask_batch_stride, int64_t mask_head_stride, void* attn, int64_t B, int64_t H,
+                              int64_t T, int64_t S, double scale, int causal, int dtype, void* stream) {
+    NB2_REQUIRE(dtype_ok(dtype), NB2_ERR_DTYPE, "attention softmax: dtype=%d", dtype);
+    NB2_REQUIRE(B >= 0 && H >= 0 && T >= 0 && S >= 0 && S < ((int64_t)1 << 31) && mask_batch_stride >= 0 && mask_head_stride >= 0,
+                NB2_ERR_SHAPE, "attention softmax: B=%lld H=%lld T=%lld S=%lld mask strides %lld, %lld", (long long)B,
+                (long long)H, (long long)T, (long long)S, (long long)mask_batch_stride, (long long)mask_head_stride);
+    if (B * H * T * S == 0) return 0;
+    NB2_REQUIRE(scores != nullptr && attn != nullptr, NB2_ERR_NULL, "attention softmax: NULL scores or output");
+    int rc = require_device();
+    if (rc != 0) return rc;
+    return launch_attention_softmax_fwd(scores, key_padding, attn_mask, mask_batch_stride, mask_head_stride, attn, B, H, T, S,
+                                        (float)scale, causal != 0, dtype, (cudaStream_t)stream);
+}
+int nb2_attention_softmax_bwd(const void* attn, const void* dattn, void* dscores, int64_t rows, int64_t S, double scale,
+                              int dtype, void* stream) {
+    NB2_REQUIRE(dtype_ok(dtype), NB2_ERR_DTYPE, "attention softmax bwd: dtype=%d", dtype);
+    NB2_REQUIRE(rows >= 0 && S >= 0 && S < ((int64_t)1 << 31), NB2_ERR_SHAPE, "attention softmax bwd: rows=%lld S=%lld",
+                (long long)rows, (long long)S);
+    if (rows * S == 0) return 0;
+    NB2_REQUIRE(attn != nullptr && dattn != nullptr && dscores != nullptr, NB2_ERR_NULL, "attention softmax bwd: NULL tensor");
+    int rc = require_device();
+    if (rc != 0) return rc;
+    return launch_attention_softmax_bwd(attn, dattn, dscores, rows, S, (float)scale, dtype, (cudaStream_t)stream);
 }
 
 int nb2_rope_table(float* cos_sin, const int32_t* positions, int64_t S, int64_t hd, double theta, void* stream) {

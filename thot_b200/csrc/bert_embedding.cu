@@ -185,6 +185,40 @@ batch_sum_kernel(const T* __restrict__ dsum, T* __restrict__ dpos, float* __rest
         if (acc_out != nullptr) acc_out[i] = acc;
     }
 }
+// the same sum, one 16-byte vector of the [S, D] plane per thread and 16 batch rows in flight
+template <typename T>
+__global__ void __launch_bounds__(128)
+batch_sum_vec_kernel(const T* __restrict__ dsum, T* __restrict__ dpos, float* __restrict__ acc_out, int64_t B, int64_t nvec_plane) {
+    constexpr int EPV = VecTraits<T>::EPV;
+    constexpr int U = 16;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec_plane; i += (int64_t)gridDim.x * blockDim.x) {
+        float acc[EPV];
+#pragma unroll
+        for (int e = 0; e < EPV; ++e) acc[e] = 0.f;
+        const T* src = dsum + i * EPV;
+        for (int64_t b0 = 0; b0 < B; b0 += U) {
+            uint4 r[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (b0 + u < B) r[u] = ld_stream(src + (b0 + u) * nvec_plane * EPV);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (b0 + u < B) {
+                    float f[EPV];
+                    unpack<T>(r[u], f);
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e) acc[e] += f[e];
+                }
+            }
+        }
+        if (dpos != nullptr) st_stream(dpos + i * EPV, pack<T>(acc));
+        if (acc_out != nullptr) {
+#pragma unroll
+            for (int e = 0; e < EPV; e += 4)
+                *reinterpret_cast<float4*>(acc_out + i * EPV + e) = make_float4(acc[e], acc[e + 1], acc[e + 2], acc[e + 3]);
+        }
+    }
+}
 __global__ void __launch_bounds__(256)
 cast_row_kernel(const float* __restrict__ src, void* __restrict__ dst, int64_t n, int bf16) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -255,7 +289,14 @@ int launch_bert_embed_table_grads(const void* dsum, void* dpos, void* dtype0, fl
     const int64_t cap = (int64_t)sm_count() * 16;
     if (grid > cap) grid = cap;
     float* acc = dtype0 != nullptr ? scratch : nullptr;
-    if (dtype == NB2_F32) batch_sum_kernel<float><<<(unsigned)grid, 256, 0, st>>>((const float*)dsum, (float*)dpos, acc, B, S, D);
+    const int elt = dtype == NB2_F32 ? 4 : 2;
+    const bool vec = (D * elt) % 16 == 0 && aligned16(dsum) && (dpos == nullptr || aligned16(dpos)) && (acc == nullptr || aligned16(acc));
+    if (vec) {
+        const int64_t nvec_plane = total * elt / 16;
+        const unsigned vgrid = (unsigned)((nvec_plane + 127) / 128 < 2 * cap ? (nvec_plane + 127) / 128 : 2 * cap);
+        if (dtype == NB2_F32) batch_sum_vec_kernel<float><<<vgrid, 128, 0, st>>>((const float*)dsum, (float*)dpos, acc, B, nvec_plane);
+        else batch_sum_vec_kernel<__nv_bfloat16><<<vgrid, 128, 0, st>>>((const __nv_bfloat16*)dsum, (__nv_bfloat16*)dpos, acc, B, nvec_plane);
+    } else if (dtype == NB2_F32) batch_sum_kernel<float><<<(unsigned)grid, 256, 0, st>>>((const float*)dsum, (float*)dpos, acc, B, S, D);
     else batch_sum_kernel<__nv_bfloat16><<<(unsigned)grid, 256, 0, st>>>((const __nv_bfloat16*)dsum, (__nv_bfloat16*)dpos, acc, B, S, D);
     int rc = cuda_status(cudaGetLastError(), "bert position gradient launch");
     if (rc != 0 || dtype0 == nullptr) return rc;

@@ -220,74 +220,98 @@ embedding_keys_kernel(const void* __restrict__ ids, uint64_t* __restrict__ keys,
     keys[t] = ((uint64_t)id << 32) | (uint64_t)(uint32_t)t;
 }
 
-// row_start[v] = first sorted position whose id is v, or -1 (the array is preset to -1)
+// row_range[v] = {first, one past last} sorted position whose id is v; both stay -1 (the preset)
+// for a table row no token used
 __global__ void __launch_bounds__(256)
-embedding_row_start_kernel(const uint64_t* __restrict__ keys, int32_t* __restrict__ row_start, int64_t tokens, int64_t vocab) {
+embedding_row_range_kernel(const uint64_t* __restrict__ keys, int2* __restrict__ row_range, int64_t tokens, int64_t vocab) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= tokens) return;
     const int64_t id = (int64_t)(keys[i] >> 32);
-    if (id < vocab && (i == 0 || (int64_t)(keys[i - 1] >> 32) != id)) row_start[id] = (int32_t)i;
+    const int64_t prev = i == 0 ? -1 : (int64_t)(keys[i - 1] >> 32);
+    if (id != prev) {
+        if (id < vocab) row_range[id].x = (int32_t)i;
+        if (prev >= 0 && prev < vocab) row_range[prev].y = (int32_t)i;
+    }
+    if (i == tokens - 1 && id < vocab) row_range[id].y = (int32_t)tokens;
 }
 
-// One CTA per table row v: sum the dout rows of v's run of sorted keys in fp32 in ascending t, or
-// write zeros when no token used the row.  Every row of dtable is written exactly once, so no
-// separate clearing pass is needed.
-template <typename T>
+// TR threads per table row v (CTA = 128 threads = 128 / TR table rows at a time): sum the dout rows
+// of v's run of sorted keys in fp32 in ascending t, or write zeros when no token used the row.
+// Every row of dtable is written exactly once, so no separate clearing pass is needed.  The run's
+// bounds are known up front, so U tokens' keys and then U x VU row vectors are all in flight before
+// the first addition; the additions keep the ascending order.
+template <typename T, int TR, int VU, int U>
 __global__ void __launch_bounds__(128)
 embedding_bwd_kernel(const T* __restrict__ dout, const uint64_t* __restrict__ keys,
-                     const int32_t* __restrict__ row_start, T* __restrict__ dtable,
-                     int64_t tokens, int64_t vocab, int64_t D, bool vec) {
+                     const int2* __restrict__ row_range, T* __restrict__ dtable,
+                     int64_t tokens, int64_t vocab, int64_t D) {
     constexpr int EPV = VecTraits<T>::EPV;
-    for (int64_t v = blockIdx.x; v < vocab; v += gridDim.x) {
-        const int32_t rs = __ldg(row_start + v);
-        const int64_t i = rs < 0 ? tokens : (int64_t)rs;        // no run: the loops below add nothing
+    constexpr int RPC = 128 / TR;
+    const int tr = threadIdx.x % TR;
+    const int64_t nvec = D / EPV;
+    for (int64_t v = (int64_t)blockIdx.x * RPC + threadIdx.x / TR; v < vocab; v += (int64_t)gridDim.x * RPC) {
+        const int2 range = __ldg(row_range + v);
+        const int64_t lo = range.x < 0 ? 0 : range.x, hi = range.x < 0 ? 0 : range.y;
         T* dst = dtable + v * D;
-        if (vec) {
-            // up to 4 column vectors per thread are in flight for every token of the run
-            const int64_t nvec = D / EPV;
-            for (int64_t c0 = threadIdx.x; c0 < nvec; c0 += 4 * (int64_t)blockDim.x) {
-                float acc[4][EPV];
+        for (int64_t c0 = tr; c0 < nvec; c0 += (int64_t)VU * TR) {
+            float acc[VU][EPV];
 #pragma unroll
-                for (int u = 0; u < 4; ++u)
+            for (int u = 0; u < VU; ++u)
 #pragma unroll
-                    for (int e = 0; e < EPV; ++e) acc[u][e] = 0.f;
-                for (int64_t j = i; j < tokens; ++j) {
-                    const uint64_t kj = keys[j];
-                    if ((int64_t)(kj >> 32) != v) break;
-                    const T* src = dout + (int64_t)(kj & 0xffffffffu) * D;
-                    uint4 r[4];
+                for (int e = 0; e < EPV; ++e) acc[u][e] = 0.f;
+            for (int64_t j = lo; j < hi; j += U) {
+                const T* src[U];
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const int64_t c = c0 + u * (int64_t)blockDim.x;
-                        if (c < nvec) r[u] = ld_stream(src + c * EPV);
+                for (int k = 0; k < U; ++k) {
+                    const int64_t jj = j + k < hi ? j + k : hi - 1;             // clamp: the extra loads are discarded
+                    src[k] = dout + (int64_t)(__ldg(keys + jj) & 0xffffffffu) * D;
+                }
+                uint4 r[U][VU];
+#pragma unroll
+                for (int k = 0; k < U; ++k)
+#pragma unroll
+                    for (int u = 0; u < VU; ++u) {
+                        const int64_t c = c0 + (int64_t)u * TR;
+                        if (c < nvec && j + k < hi) r[k][u] = ld_stream(src[k] + c * EPV);
                     }
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const int64_t c = c0 + u * (int64_t)blockDim.x;
-                        if (c < nvec) {
-                            float f[EPV];
-                            unpack<T>(r[u], f);
+                for (int k = 0; k < U; ++k) {
+                    if (j + k < hi) {
 #pragma unroll
-                            for (int e = 0; e < EPV; ++e) acc[u][e] += f[e];
+                        for (int u = 0; u < VU; ++u) {
+                            const int64_t c = c0 + (int64_t)u * TR;
+                            if (c < nvec) {
+                                float f[EPV];
+                                unpack<T>(r[k][u], f);
+#pragma unroll
+                                for (int e = 0; e < EPV; ++e) acc[u][e] += f[e];
+                            }
                         }
                     }
                 }
+            }
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int64_t c = c0 + u * (int64_t)blockDim.x;
-                    if (c < nvec) st_stream(dst + c * EPV, pack<T>(acc[u]));
-                }
+            for (int u = 0; u < VU; ++u) {
+                const int64_t c = c0 + (int64_t)u * TR;
+                if (c < nvec) st_stream(dst + c * EPV, pack<T>(acc[u]));
             }
-        } else {
-            for (int64_t c = threadIdx.x; c < D; c += blockDim.x) {
-                float acc = 0.f;
-                for (int64_t j = i; j < tokens; ++j) {
-                    const uint64_t kj = keys[j];
-                    if ((int64_t)(kj >> 32) != v) break;
-                    acc += to_f32(dout[(int64_t)(kj & 0xffffffffu) * D + c]);
-                }
-                dst[c] = from_f32<T>(acc);
-            }
+        }
+    }
+}
+
+// any width / alignment: one CTA per table row, scalar columns
+template <typename T>
+__global__ void __launch_bounds__(128)
+embedding_bwd_generic_kernel(const T* __restrict__ dout, const uint64_t* __restrict__ keys,
+                             const int2* __restrict__ row_range, T* __restrict__ dtable,
+                             int64_t tokens, int64_t vocab, int64_t D) {
+    for (int64_t v = blockIdx.x; v < vocab; v += gridDim.x) {
+        const int2 range = __ldg(row_range + v);
+        const int64_t lo = range.x < 0 ? 0 : range.x, hi = range.x < 0 ? 0 : range.y;
+        for (int64_t c = threadIdx.x; c < D; c += blockDim.x) {
+            float acc = 0.f;
+            for (int64_t j = lo; j < hi; ++j) acc += to_f32(dout[(int64_t)(keys[j] & 0xffffffffu) * D + c]);
+            dtable[v * D + c] = from_f32<T>(acc);
         }
     }
 }
@@ -313,48 +337,84 @@ static size_t round256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 size_t embedding_bwd_workspace(int64_t tokens, int64_t vocab) {
     if (tokens <= 0) return 256;
-    return 2 * round256((size_t)tokens * 8) + round256(cub_temp_bytes(tokens, vocab)) + round256((size_t)vocab * 4) + 256;
+    return 2 * round256((size_t)tokens * 8) + round256(cub_temp_bytes(tokens, vocab)) + round256((size_t)vocab * 8) + 256;
 }
 
-int launch_embedding_bwd(const void* dout, const void* ids, void* dtable, int64_t tokens, int64_t vocab,
-                         int64_t D, int dtype, int index_type, void* ws, size_t ws_bytes, cudaStream_t st) {
-    const int elt = dtype == NB2_F32 ? 4 : 2;
-    if (tokens == 0 || D == 0)       // nothing to sum: the gradient is all zeros
-        return cuda_status(cudaMemsetAsync(dtable, 0, (size_t)vocab * D * elt, st), "embedding bwd memset");
-    int rc = 0;
+// Workspace carve-up shared by the two phases below.
+struct EmbBwdWs { uint64_t* keys_in; uint64_t* keys_out; void* temp; size_t temp_bytes; int2* row_range; };
+static EmbBwdWs carve_bwd_ws(void* ws, int64_t tokens, int64_t vocab) {
+    uint8_t* base = (uint8_t*)(((uintptr_t)ws + 255) & ~(uintptr_t)255);
+    EmbBwdWs w;
+    w.keys_in = (uint64_t*)base;
+    w.keys_out = (uint64_t*)(base + round256((size_t)tokens * 8));
+    w.temp = base + 2 * round256((size_t)tokens * 8);
+    w.temp_bytes = cub_temp_bytes(tokens, vocab);
+    w.row_range = (int2*)((uint8_t*)w.temp + round256(w.temp_bytes));
+    return w;
+}
+
+// Phase 1 (needs only the ids): sorted (id, t) keys and each table row's run of them.
+int launch_embedding_bwd_index(const void* ids, int64_t tokens, int64_t vocab, int index_type, void* ws,
+                               size_t ws_bytes, cudaStream_t st) {
+    if (tokens == 0) return 0;
     NB2_REQUIRE(tokens < ((int64_t)1 << 31), NB2_ERR_SHAPE, "embedding bwd: %lld tokens exceed 2^31-1", (long long)tokens);
     NB2_REQUIRE(ws != nullptr, NB2_ERR_NULL, "embedding bwd: workspace is NULL");
     NB2_REQUIRE(ws_bytes >= embedding_bwd_workspace(tokens, vocab), NB2_ERR_WORKSPACE,
                 "embedding bwd: workspace %zu < required %zu", ws_bytes, embedding_bwd_workspace(tokens, vocab));
-    uint8_t* base = (uint8_t*)(((uintptr_t)ws + 255) & ~(uintptr_t)255);
-    uint64_t* keys_in = (uint64_t*)base;
-    uint64_t* keys_out = (uint64_t*)(base + round256((size_t)tokens * 8));
-    void* temp = base + 2 * round256((size_t)tokens * 8);
-    size_t temp_bytes = cub_temp_bytes(tokens, vocab);
-    int32_t* row_start = (int32_t*)((uint8_t*)temp + round256(temp_bytes));
-
+    const EmbBwdWs w = carve_bwd_ws(ws, tokens, vocab);
     const unsigned kgrid = (unsigned)((tokens + 255) / 256);
-    if (index_type == NB2_I32) embedding_keys_kernel<int32_t><<<kgrid, 256, 0, st>>>(ids, keys_in, tokens, vocab);
-    else                       embedding_keys_kernel<int64_t><<<kgrid, 256, 0, st>>>(ids, keys_in, tokens, vocab);
-    rc = cuda_status(cudaGetLastError(), "embedding keys launch");
+    if (index_type == NB2_I32) embedding_keys_kernel<int32_t><<<kgrid, 256, 0, st>>>(ids, w.keys_in, tokens, vocab);
+    else                       embedding_keys_kernel<int64_t><<<kgrid, 256, 0, st>>>(ids, w.keys_in, tokens, vocab);
+    int rc = cuda_status(cudaGetLastError(), "embedding keys launch");
     if (rc != 0) return rc;
-    rc = cuda_status(cub::DeviceRadixSort::SortKeys(temp, temp_bytes, keys_in, keys_out, (int)tokens, kKeyBeginBit,
-                                                    key_bits(vocab), st), "embedding key sort");
+    size_t temp_bytes = w.temp_bytes;
+    rc = cuda_status(cub::DeviceRadixSort::SortKeys(w.temp, temp_bytes, w.keys_in, w.keys_out, (int)tokens,
+                                                    kKeyBeginBit, key_bits(vocab), st), "embedding key sort");
     if (rc != 0) return rc;
-    rc = cuda_status(cudaMemsetAsync(row_start, 0xff, (size_t)vocab * 4, st), "embedding row-start preset");
+    rc = cuda_status(cudaMemsetAsync(w.row_range, 0xff, (size_t)vocab * 8, st), "embedding row-range preset");
     if (rc != 0) return rc;
-    embedding_row_start_kernel<<<kgrid, 256, 0, st>>>(keys_out, row_start, tokens, vocab);
-    rc = cuda_status(cudaGetLastError(), "embedding row-start launch");
-    if (rc != 0) return rc;
+    embedding_row_range_kernel<<<kgrid, 256, 0, st>>>(w.keys_out, w.row_range, tokens, vocab);
+    return cuda_status(cudaGetLastError(), "embedding row-range launch");
+}
+
+// Phase 2: the row sums, from the index phase 1 left in the same workspace.
+int launch_embedding_bwd_sum(const void* dout, void* dtable, int64_t tokens, int64_t vocab, int64_t D, int dtype,
+                             void* ws, cudaStream_t st) {
+    const int elt = dtype == NB2_F32 ? 4 : 2;
+    if (tokens == 0 || D == 0)       // nothing to sum: the gradient is all zeros
+        return cuda_status(cudaMemsetAsync(dtable, 0, (size_t)vocab * D * elt, st), "embedding bwd memset");
+    const EmbBwdWs w = carve_bwd_ws(ws, tokens, vocab);
+    const uint64_t* keys_out = w.keys_out;
+    const int2* row_range = w.row_range;
     const bool vec = (D * elt) % 16 == 0 && aligned16(dout) && aligned16(dtable);
-    int64_t grid = vocab;
     const int64_t cap = (int64_t)sm_count() * 64;
-    if (grid > cap) grid = cap;
-    if (dtype == NB2_F32)
-        embedding_bwd_kernel<float><<<(unsigned)grid, 128, 0, st>>>((const float*)dout, keys_out, row_start, (float*)dtable, tokens, vocab, D, vec);
-    else
-        embedding_bwd_kernel<__nv_bfloat16><<<(unsigned)grid, 128, 0, st>>>((const __nv_bfloat16*)dout, keys_out, row_start, (__nv_bfloat16*)dtable, tokens, vocab, D, vec);
+    const int64_t nvec = D * elt / 16;
+    auto grid_for = [&](int rows_per_cta) {
+        const int64_t need = (vocab + rows_per_cta - 1) / rows_per_cta;
+        return (unsigned)(need < cap ? need : cap);
+    };
+#define NB2_EMB_BWD(T_)                                                                                                   \
+    do {                                                                                                                   \
+        if (!vec)                                                                                                          \
+            embedding_bwd_generic_kernel<T_><<<grid_for(1), 128, 0, st>>>((const T_*)dout, keys_out, row_range, (T_*)dtable, tokens, vocab, D); \
+        else if (nvec <= 128)   /* rows up to 2 KiB: a warp per table row, four tokens in flight */                         \
+            embedding_bwd_kernel<T_, 32, 4, 4><<<grid_for(4), 128, 0, st>>>((const T_*)dout, keys_out, row_range, (T_*)dtable, tokens, vocab, D); \
+        else                    /* wider rows: the CTA per table row, two tokens in flight */                               \
+            embedding_bwd_kernel<T_, 128, 4, 2><<<grid_for(1), 128, 0, st>>>((const T_*)dout, keys_out, row_range, (T_*)dtable, tokens, vocab, D); \
+    } while (0)
+    if (dtype == NB2_F32) NB2_EMB_BWD(float);
+    else                  NB2_EMB_BWD(__nv_bfloat16);
+#undef NB2_EMB_BWD
     return cuda_status(cudaGetLastError(), "embedding bwd launch");
+}
+
+int launch_embedding_bwd(const void* dout, const void* ids, void* dtable, int64_t tokens, int64_t vocab,
+                         int64_t D, int dtype, int index_type, void* ws, size_t ws_bytes, cudaStream_t st) {
+    if (tokens > 0 && D > 0) {
+        const int rc = launch_embedding_bwd_index(ids, tokens, vocab, index_type, ws, ws_bytes, st);
+        if (rc != 0) return rc;
+    }
+    return launch_embedding_bwd_sum(dout, dtable, tokens, vocab, D, dtype, ws, st);
 }
 
 }  // namespace nb2

@@ -14,6 +14,11 @@ int launch_colreduce(const float* partials, int64_t n_partials, int64_t ncols, f
 int launch_embedding_fwd(const void* table, const void* ids, void* out, int64_t tokens, int64_t vocab,
                          int64_t D, int dtype, int index_type, int64_t* status, cudaStream_t st);
 size_t embedding_bwd_workspace(int64_t tokens, int64_t vocab);
+// the two phases of launch_embedding_bwd: the index needs only the ids, the sums need the index
+int launch_embedding_bwd_index(const void* ids, int64_t tokens, int64_t vocab, int index_type, void* ws,
+                               size_t ws_bytes, cudaStream_t st);
+int launch_embedding_bwd_sum(const void* dout, void* dtable, int64_t tokens, int64_t vocab, int64_t D, int dtype,
+                             void* ws, cudaStream_t st);
 int launch_embedding_bwd(const void* dout, const void* ids, void* dtable, int64_t tokens, int64_t vocab,
                          int64_t D, int dtype, int index_type, void* ws, size_t ws_bytes, cudaStream_t st);
 int launch_bert_embed_ln_fwd(const void* word, const void* pos, const void* type, const void* ids, const void* gamma,
@@ -25,5 +30,11 @@ int launch_bert_embed_table_grads(const void* dsum, void* dpos, void* dtype0, fl
 int launch_rope_table(float* cos_sin, const int32_t* positions, int64_t S, int64_t hd, double theta, cudaStream_t st);
 int launch_rope_apply(const void* x, const float* cos_sin, void* out, int64_t B, int64_t S, int64_t H,
                       int64_t hd, int dtype, bool inverse, cudaStream_t st);
+
+int launch_attention_softmax_fwd(const void* scores, const uint8_t* key_padding, const void* add_mask, int64_t mask_sb,
+                                 int64_t mask_sh, void* out, int64_t B, int64_t H, int64_t Tq, int64_t S, float scale,
+                                 int causal, int dtype, cudaStream_t st);
+int launch_attention_softmax_bwd(const void* attn, const void* dattn, void* dscores, int64_t rows, int64_t S, float scale,
+                                 int dtype, cudaStream_t st);
 
 }  // namespace nb2

@@ -1,0 +1,312 @@
+// Attention probabilities in one pass over the score matrix:
+//   attn = softmax(scores * scale [key padding -> -inf] [+ additive mask] [causal -> -inf], last dim)
+// which the reference's ScaledDotProductKernelImpl::forward (src/attention/details/kernel.hpp:33-92)
+// forms as a division, two masked_fill, an add and a softmax, each a full read and write of
+// [B, H, T, S].  Backward: dscores = scale * attn * (dattn - sum_j attn * dattn).
+//
+// One row (b, h, t) per group of TPR threads, the whole row in registers (up to 4 x 16 bytes per
+// thread), rows of a CTA independent of one another; persistent grid-stride over rows.  Rows whose
+// length or alignment does not fit 16-byte vectors take a three-sweep kernel, one CTA per row.
+#include <math.h>
+
+#include "launchers.h"
+
+namespace nb2 {
+
+namespace {
+
+constexpr float kLog2e = 1.44269504088896340736f;
+
+struct SoftmaxMask {
+    const uint8_t* key_padding;   // [B, S], non-zero = masked, or NULL
+    const void* add_mask;         // additive, element type of the scores, or NULL
+    int64_t mask_sb, mask_sh;     // element strides of add_mask over batch and head (0 = broadcast); row stride S
+    int causal;                   // column > row index t -> masked
+};
+
+template <int TPR, bool MAX>
+__device__ __forceinline__ float group_reduce(float v, float* red, int barrier_id) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float w = __shfl_xor_sync(0xffffffffu, v, o);
+        v = MAX ? fmaxf(v, w) : v + w;
+    }
+    if constexpr (TPR > 32) {
+        constexpr int WPR = TPR / 32;
+        const int w = (threadIdx.x % TPR) >> 5;
+        if ((threadIdx.x & 31) == 0) red[w] = v;
+        named_barrier(barrier_id, TPR);
+        float t = red[0];
+#pragma unroll
+        for (int i = 1; i < WPR; ++i) t = MAX ? fmaxf(t, red[i]) : t + red[i];
+        v = t;
+    }
+    return v;
+}
+
+template <typename T, int TPR, int VPT>
+__global__ void __launch_bounds__((TPR > 256 ? TPR : 256), (TPR > 256 ? 1 : 2))
+softmax_fwd_kernel(const T* __restrict__ scores, const SoftmaxMask m, T* __restrict__ out,
+                   int64_t rows, int64_t H, int64_t Tq, int S, float scale) {
+    constexpr int EPV = VecTraits<T>::EPV;
+    constexpr int THREADS = TPR > 256 ? TPR : 256;
+    constexpr int RPC = THREADS / TPR;
+    constexpr int WPR = (TPR + 31) / 32;
+    __shared__ float red_a[RPC][WPR], red_b[RPC][WPR];
+    const int grp = threadIdx.x / TPR, tr = threadIdx.x % TPR;
+    const int nvec = S / EPV;
+    pdl_wait();
+    for (int64_t row = (int64_t)blockIdx.x * RPC + grp; row < rows; row += (int64_t)gridDim.x * RPC) {
+        const int64_t t = row % Tq;
+        const int64_t bh = row / Tq;
+        const int64_t h = bh % H, b = bh / H;
+        const T* src = scores + row * (int64_t)S;
+        const T* mrow = m.add_mask ? reinterpret_cast<const T*>(m.add_mask) + b * m.mask_sb + h * m.mask_sh + t * (int64_t)S : nullptr;
+        const uint8_t* prow = m.key_padding ? m.key_padding + b * (int64_t)S : nullptr;
+        float v[VPT][EPV];
+        float mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int c = tr + j * TPR;
+            if (c < nvec) {
+                unpack<T>(ld_stream(src + (size_t)c * EPV), v[j]);
+                float mk[EPV];
+                if (mrow != nullptr) unpack<T>(ld_param(mrow + (size_t)c * EPV), mk);
+                uint8_t pad[EPV];
+                if (prow != nullptr) {
+                    if constexpr (EPV == 4) *reinterpret_cast<uint32_t*>(pad) = __ldg(reinterpret_cast<const uint32_t*>(prow + (size_t)c * EPV));
+                    else *reinterpret_cast<uint2*>(pad) = __ldg(reinterpret_cast<const uint2*>(prow + (size_t)c * EPV));
+                }
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) {
+                    float s = v[j][e] * scale;
+                    if (prow != nullptr && pad[e]) s = -INFINITY;
+                    if (mrow != nullptr) s += mk[e];
+                    if (m.causal && (int64_t)c * EPV + e > t) s = -INFINITY;
+                    v[j][e] = s;
+                    mx = fmaxf(mx, s);
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) v[j][e] = -INFINITY;
+            }
+        }
+        mx = group_reduce<TPR, true>(mx, red_a[grp], grp + 1);
+        // a row with every column masked has max = -inf: (-inf) - (-inf) is NaN, as in the reference
+        const float off = -mx * kLog2e;
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j)
+#pragma unroll
+            for (int e = 0; e < EPV; ++e) {
+                const float p = (tr + j * TPR < nvec) ? fast_ex2(fmaf(v[j][e], kLog2e, off)) : 0.f;
+                v[j][e] = p;
+                sum += p;
+            }
+        sum = group_reduce<TPR, false>(sum, red_b[grp], grp + 1);
+        const float inv = 1.0f / sum;
+        T* dst = out + row * (int64_t)S;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int c = tr + j * TPR;
+            if (c < nvec) {
+                float o[EPV];
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) o[e] = v[j][e] * inv;
+                st_stream(dst + (size_t)c * EPV, pack<T>(o));
+            }
+        }
+    }
+}
+
+template <typename T, int TPR, int VPT>
+__global__ void __launch_bounds__((TPR > 256 ? TPR : 256), (TPR > 256 ? 1 : 2))
+softmax_bwd_kernel(const T* __restrict__ attn, const T* __restrict__ dattn, T* __restrict__ dscores,
+                   int64_t rows, int S, float scale) {
+    constexpr int EPV = VecTraits<T>::EPV;
+    constexpr int THREADS = TPR > 256 ? TPR : 256;
+    constexpr int RPC = THREADS / TPR;
+    constexpr int WPR = (TPR + 31) / 32;
+    __shared__ float red_a[2][RPC][WPR];
+    const int grp = threadIdx.x / TPR, tr = threadIdx.x % TPR;
+    const int nvec = S / EPV;
+    pdl_wait();
+    int parity = 0;
+    for (int64_t row = (int64_t)blockIdx.x * RPC + grp; row < rows; row += (int64_t)gridDim.x * RPC, parity ^= 1) {
+        const T* ya = attn + row * (int64_t)S;
+        const T* da = dattn + row * (int64_t)S;
+        float y[VPT][EPV], d[VPT][EPV];
+        float dot = 0.f;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int c = tr + j * TPR;
+            if (c < nvec) {
+                unpack<T>(ld_stream(ya + (size_t)c * EPV), y[j]);
+                unpack<T>(ld_stream(da + (size_t)c * EPV), d[j]);
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) dot = fmaf(y[j][e], d[j][e], dot);
+            }
+        }
+        dot = group_reduce<TPR, false>(dot, red_a[parity][grp], grp + 1);
+        T* dst = dscores + row * (int64_t)S;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int c = tr + j * TPR;
+            if (c < nvec) {
+                float o[EPV];
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) o[e] = scale * (y[j][e] * (d[j][e] - dot));
+                st_stream(dst + (size_t)c * EPV, pack<T>(o));
+            }
+        }
+    }
+}
+
+// ---- any row length and alignment: one CTA per row, three sweeps over the row
+__device__ __forceinline__ float cta_reduce(float v, float* red, bool is_max) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float w = __shfl_xor_sync(0xffffffffu, v, o);
+        v = is_max ? fmaxf(v, w) : v + w;
+    }
+    __syncthreads();                               // red may still be read from the previous use
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = red[0];
+    for (int i = 1; i < (int)(blockDim.x >> 5); ++i) t = is_max ? fmaxf(t, red[i]) : t + red[i];
+    return t;
+}
+
+template <typename T>
+__device__ __forceinline__ float masked_score(const T* src, const T* mrow, const uint8_t* prow, int causal, int64_t t, int64_t c, float scale) {
+    float s = to_f32(src[c]) * scale;
+    if (prow != nullptr && prow[c]) s = -INFINITY;
+    if (mrow != nullptr) s += to_f32(mrow[c]);
+    if (causal && c > t) s = -INFINITY;
+    return s;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+softmax_fwd_generic(const T* __restrict__ scores, const SoftmaxMask m, T* __restrict__ out,
+                    int64_t rows, int64_t H, int64_t Tq, int64_t S, float scale) {
+    __shared__ float red[8];
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const int64_t t = row % Tq, bh = row / Tq, h = bh % H, b = bh / H;
+        const T* src = scores + row * S;
+        const T* mrow = m.add_mask ? reinterpret_cast<const T*>(m.add_mask) + b * m.mask_sb + h * m.mask_sh + t * S : nullptr;
+        const uint8_t* prow = m.key_padding ? m.key_padding + b * S : nullptr;
+        float mx = -INFINITY;
+        for (int64_t c = threadIdx.x; c < S; c += blockDim.x) mx = fmaxf(mx, masked_score(src, mrow, prow, m.causal, t, c, scale));
+        mx = cta_reduce(mx, red, true);
+        const float off = -mx * kLog2e;
+        float sum = 0.f;
+        for (int64_t c = threadIdx.x; c < S; c += blockDim.x) sum += fast_ex2(fmaf(masked_score(src, mrow, prow, m.causal, t, c, scale), kLog2e, off));
+        sum = cta_reduce(sum, red, false);
+        const float inv = 1.0f / sum;
+        for (int64_t c = threadIdx.x; c < S; c += blockDim.x)
+            out[row * S + c] = from_f32<T>(fast_ex2(fmaf(masked_score(src, mrow, prow, m.causal, t, c, scale), kLog2e, off)) * inv);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+softmax_bwd_generic(const T* __restrict__ attn, const T* __restrict__ dattn, T* __restrict__ dscores,
+                    int64_t rows, int64_t S, float scale) {
+    __shared__ float red[8];
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const T* ya = attn + row * S;
+        const T* da = dattn + row * S;
+        float dot = 0.f;
+        for (int64_t c = threadIdx.x; c < S; c += blockDim.x) dot = fmaf(to_f32(ya[c]), to_f32(da[c]), dot);
+        dot = cta_reduce(dot, red, false);
+        for (int64_t c = threadIdx.x; c < S; c += blockDim.x)
+            dscores[row * S + c] = from_f32<T>(scale * (to_f32(ya[c]) * (to_f32(da[c]) - dot)));
+    }
+}
+
+int pick_softmax_tpr(int64_t nvec) {
+    for (int tpr = 32; tpr <= 512; tpr *= 2)
+        if (nvec <= (int64_t)tpr * 4) return tpr;
+    return 0;
+}
+
+int64_t row_grid(int64_t rows, int tpr) {
+    const int threads = tpr > 256 ? tpr : 256;
+    const int rpc = threads / tpr;
+    const int64_t need = (rows + rpc - 1) / rpc;
+    const int64_t cap = (int64_t)sm_count() * (tpr > 256 ? 1 : 2) * 4;      // a few CTAs per slot: rows are short-lived
+    return need < cap ? (need < 1 ? 1 : need) : cap;
+}
+
+template <typename T, int TPR>
+int launch_fwd_tpr(const void* scores, const SoftmaxMask& m, void* out, int64_t rows, int64_t H, int64_t Tq, int64_t S,
+                   float scale, cudaStream_t st) {
+    constexpr int THREADS = TPR > 256 ? TPR : 256;
+    return cuda_status(launch_pdl(softmax_fwd_kernel<T, TPR, 4>, dim3((unsigned)row_grid(rows, TPR)), dim3(THREADS), 0, st,
+                                  (const T*)scores, m, (T*)out, rows, H, Tq, (int)S, scale),
+                       "softmax_fwd_kernel launch");
+}
+template <typename T, int TPR>
+int launch_bwd_tpr(const void* attn, const void* dattn, void* dscores, int64_t rows, int64_t S, float scale, cudaStream_t st) {
+    constexpr int THREADS = TPR > 256 ? TPR : 256;
+    return cuda_status(launch_pdl(softmax_bwd_kernel<T, TPR, 4>, dim3((unsigned)row_grid(rows, TPR)), dim3(THREADS), 0, st,
+                                  (const T*)attn, (const T*)dattn, (T*)dscores, rows, (int)S, scale),
+                       "softmax_bwd_kernel launch");
+}
+
+template <typename T>
+int launch_fwd_t(const void* scores, const SoftmaxMask& m, void* out, int64_t B, int64_t H, int64_t Tq, int64_t S, float scale,
+                 cudaStream_t st) {
+    constexpr int EPV = VecTraits<T>::EPV;
+    const int64_t rows = B * H * Tq;
+    const bool mask_ok = m.add_mask == nullptr || (aligned16(m.add_mask) && m.mask_sb % EPV == 0 && m.mask_sh % EPV == 0);
+    const bool pad_ok = m.key_padding == nullptr || (reinterpret_cast<uintptr_t>(m.key_padding) % EPV == 0);
+    const int tpr = (S % EPV == 0 && aligned16(scores) && aligned16(out) && mask_ok && pad_ok) ? pick_softmax_tpr(S / EPV) : 0;
+    switch (tpr) {
+        case 32:  return launch_fwd_tpr<T, 32>(scores, m, out, rows, H, Tq, S, scale, st);
+        case 64:  return launch_fwd_tpr<T, 64>(scores, m, out, rows, H, Tq, S, scale, st);
+        case 128: return launch_fwd_tpr<T, 128>(scores, m, out, rows, H, Tq, S, scale, st);
+        case 256: return launch_fwd_tpr<T, 256>(scores, m, out, rows, H, Tq, S, scale, st);
+        case 512: return launch_fwd_tpr<T, 512>(scores, m, out, rows, H, Tq, S, scale, st);
+        default: break;
+    }
+    const int64_t cap = (int64_t)sm_count() * 8;
+    softmax_fwd_generic<T><<<(unsigned)(rows < cap ? rows : cap), 256, 0, st>>>((const T*)scores, m, (T*)out, rows, H, Tq, S, scale);
+    return cuda_status(cudaGetLastError(), "softmax_fwd_generic launch");
+}
+
+template <typename T>
+int launch_bwd_t(const void* attn, const void* dattn, void* dscores, int64_t rows, int64_t S, float scale, cudaStream_t st) {
+    constexpr int EPV = VecTraits<T>::EPV;
+    const int tpr = (S % EPV == 0 && aligned16(attn) && aligned16(dattn) && aligned16(dscores)) ? pick_softmax_tpr(S / EPV) : 0;
+    switch (tpr) {
+        case 32:  return launch_bwd_tpr<T, 32>(attn, dattn, dscores, rows, S, scale, st);
+        case 64:  return launch_bwd_tpr<T, 64>(attn, dattn, dscores, rows, S, scale, st);
+        case 128: return launch_bwd_tpr<T, 128>(attn, dattn, dscores, rows, S, scale, st);
+        case 256: return launch_bwd_tpr<T, 256>(attn, dattn, dscores, rows, S, scale, st);
+        case 512: return launch_bwd_tpr<T, 512>(attn, dattn, dscores, rows, S, scale, st);
+        default: break;
+    }
+    const int64_t cap = (int64_t)sm_count() * 8;
+    softmax_bwd_generic<T><<<(unsigned)(rows < cap ? rows : cap), 256, 0, st>>>((const T*)attn, (const T*)dattn, (T*)dscores, rows, S, scale);
+    return cuda_status(cudaGetLastError(), "softmax_bwd_generic launch");
+}
+
+}  // namespace
+
+int launch_attention_softmax_fwd(const void* scores, const uint8_t* key_padding, const void* add_mask, int64_t mask_sb,
+                                 int64_t mask_sh, void* out, int64_t B, int64_t H, int64_t Tq, int64_t S, float scale,
+                                 int causal, int dtype, cudaStream_t st) {
+    const SoftmaxMask m = {key_padding, add_mask, mask_sb, mask_sh, causal};
+    return dtype == NB2_F32 ? launch_fwd_t<float>(scores, m, out, B, H, Tq, S, scale, st)
+                            : launch_fwd_t<__nv_bfloat16>(scores, m, out, B, H, Tq, S, scale, st);
+}
+
+int launch_attention_softmax_bwd(const void* attn, const void* dattn, void* dscores, int64_t rows, int64_t S, float scale,
+                                 int dtype, cudaStream_t st) {
+    return dtype == NB2_F32 ? launch_bwd_t<float>(attn, dattn, dscores, rows, S, scale, st)
+                            : launch_bwd_t<__nv_bfloat16>(attn, dattn, dscores, rows, S, scale, st);
+}
+
+}  // namespace nb2

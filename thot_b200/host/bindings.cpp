@@ -22,6 +22,17 @@ PYBIND11_MODULE(_nott_b200_host, m) {
     m.def("apply", [](int64_t type, torch::Tensor x) { return nb::apply(static_cast<nb::ActivationType>(type), std::move(x)); });
     m.def("silu_gate", [](torch::Tensor gate, torch::Tensor up) { return nb::silu_gate(gate, up); });
     m.def("embedding", [](torch::Tensor weight, torch::Tensor ids) { return nb::EmbeddingFunction::apply(std::move(weight), std::move(ids)); });
+    m.def("attention_softmax", [](torch::Tensor scores, c10::optional<torch::Tensor> mask, c10::optional<torch::Tensor> padding,
+                                  double scale, bool causal) {
+        pybind11::gil_scoped_release nogil;
+        return nb::AttentionSoftmaxFunction::apply(std::move(scores), std::move(mask), std::move(padding), scale, causal);
+    });
+    m.def("scaled_dot_product", [](torch::Tensor q, torch::Tensor k, torch::Tensor v, c10::optional<torch::Tensor> mask,
+                                   c10::optional<torch::Tensor> padding, bool causal) {
+        pybind11::gil_scoped_release nogil;
+        nb::ScaledDotProductKernel kernel(0.0, causal ? nb::AttentionVariant::Causal : nb::AttentionVariant::Full);
+        return kernel->forward(q, k, v, mask.value_or(torch::Tensor()), padding.value_or(torch::Tensor()));
+    });
     m.def("rotary_table", [](int64_t S, int64_t hd, double theta, torch::Device device) {
         return nb::RotaryTable(S, hd, theta, device).table();
     });

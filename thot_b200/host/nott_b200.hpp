@@ -30,6 +30,7 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <torch/torch.h>
 
+#include <cmath>
 #include <cstdint>
 #include <stdexcept>
 #include <string>
@@ -635,6 +636,90 @@ private:
     std::int64_t seq_len_, head_dim_;
     torch::Tensor table_;
 };
+
+// ------------------------------------------------------- attention probabilities, one pass
+// attn = softmax(scores * scale [key padding -> -inf] [+ mask] [causal -> -inf]) for scores
+// [B, H, T, S]: the steps between the two matmuls of ScaledDotProductKernelImpl::forward
+// (src/attention/details/kernel.hpp:33-93).  `mask` is additive and already of rank 2, 3 or 4.
+struct AttentionSoftmaxFunction : public torch::autograd::Function<AttentionSoftmaxFunction> {
+    static torch::Tensor forward(torch::autograd::AutogradContext* ctx, torch::Tensor scores, c10::optional<torch::Tensor> mask,
+                                 c10::optional<torch::Tensor> key_padding, double scale, bool causal) {
+        detail::require_cuda(scores, "Attention softmax");
+        if (scores.dim() != 4) throw std::invalid_argument("Attention softmax expects scores of shape (batch, heads, target, source).");
+        auto x = scores.contiguous();
+        const auto B = x.size(0), H = x.size(1), T = x.size(2), S = x.size(3);
+        torch::Tensor m, kp;
+        int64_t sb = 0, sh = 0;
+        if (mask.has_value() && mask->defined() && mask->numel() > 0) {
+            m = mask->to(x.scalar_type()).contiguous();
+            if (m.dim() == 2) {
+                if (m.size(0) != T || m.size(1) != S) throw std::invalid_argument("Attention mask dimensions mismatch: a 2D mask must be (target, source).");
+            } else if (m.dim() == 3) {
+                if (m.size(1) != T || m.size(2) != S || (m.size(0) != B && m.size(0) != B * H))
+                    throw std::invalid_argument("Attention mask dimensions mismatch: a 3D mask must be (batch or batch*heads, target, source).");
+                if (m.size(0) == B && H != 1) sb = T * S; else { sb = H * T * S; sh = T * S; }
+            } else if (m.dim() == 4) {
+                if (m.size(0) != B || m.size(1) != H || m.size(2) != T || m.size(3) != S)
+                    throw std::invalid_argument("Attention mask dimensions mismatch: a 4D mask must be (batch, heads, target, source).");
+                sb = H * T * S; sh = T * S;
+            } else {
+                throw std::invalid_argument("Unsupported attention mask dimensionality: " + std::to_string(m.dim()));
+            }
+        }
+        if (key_padding.has_value() && key_padding->defined() && key_padding->numel() > 0) {
+            kp = key_padding->to(torch::kBool).to(torch::kUInt8).contiguous();
+            if (kp.dim() != 2 || kp.size(0) != B || kp.size(1) != S)
+                throw std::invalid_argument("Key padding mask must be (batch, source).");
+        }
+        auto attn = torch::empty_like(x);
+        detail::check(nb2_attention_softmax_fwd(x.data_ptr(), kp.defined() ? kp.data_ptr<uint8_t>() : nullptr, detail::ptr_or_null(m),
+                                                sb, sh, attn.data_ptr(), B, H, T, S, scale, causal ? 1 : 0,
+                                                detail::dtype_code(x, "Attention softmax"), detail::stream()),
+                      "nb2_attention_softmax_fwd");
+        ctx->save_for_backward({attn});
+        ctx->saved_data["scale"] = scale;
+        return attn;
+    }
+    static torch::autograd::tensor_list backward(torch::autograd::AutogradContext* ctx, torch::autograd::tensor_list grads) {
+        auto attn = ctx->get_saved_variables()[0];
+        auto dattn = grads[0].contiguous();
+        auto ds = torch::empty_like(attn);
+        const auto S = attn.size(-1);
+        detail::check(nb2_attention_softmax_bwd(attn.data_ptr(), dattn.data_ptr(), ds.data_ptr(), S > 0 ? attn.numel() / S : 0, S,
+                                                ctx->saved_data["scale"].toDouble(), detail::dtype_code(attn, "Attention softmax backward"),
+                                                detail::stream()),
+                      "nb2_attention_softmax_bwd");
+        return {ds, torch::Tensor(), torch::Tensor(), torch::Tensor(), torch::Tensor()};
+    }
+};
+
+enum class AttentionVariant { Full, Causal };   // ::Nott::Attention::Variant (src/attention/attention.hpp:9-12)
+
+// Drop-in for Nott::Attention::Details::ScaledDotProductKernel (kernel.hpp:13-103): same constructor
+// arguments and forward signature; the two matmuls and the dropout stay libtorch calls, everything
+// between them is the single kernel above.
+class ScaledDotProductKernelImpl : public torch::nn::Module {
+public:
+    explicit ScaledDotProductKernelImpl(double dropout = 0.0, AttentionVariant variant = AttentionVariant::Full)
+        : variant_(variant), dropout_(register_module("dropout", torch::nn::Dropout(torch::nn::DropoutOptions(dropout)))) {}
+
+    torch::Tensor forward(const torch::Tensor& query, const torch::Tensor& key, const torch::Tensor& value,
+                          const torch::Tensor& attn_mask = {}, const torch::Tensor& key_padding_mask = {}) {
+        auto scores = torch::matmul(query, key.transpose(-2, -1));
+        const auto head_dim = query.size(-1);
+        const double scale = head_dim > 0 ? 1.0 / std::sqrt(static_cast<double>(head_dim)) : 1.0;
+        auto attn = AttentionSoftmaxFunction::apply(scores, detail::opt(attn_mask), detail::opt(key_padding_mask), scale,
+                                                    variant_ == AttentionVariant::Causal);
+        attn = dropout_->forward(attn);
+        return torch::matmul(attn, value);
+    }
+
+private:
+    AttentionVariant variant_{AttentionVariant::Full};
+    torch::nn::Dropout dropout_{nullptr};
+};
+TORCH_MODULE(ScaledDotProductKernel);
+
 
 struct RotaryFunction : public torch::autograd::Function<RotaryFunction> {
     static torch::Tensor forward(torch::autograd::AutogradContext* ctx, torch::Tensor x, torch::Tensor table) {
