@@ -2,7 +2,7 @@
 """Benchmark of the fused norm+activation path (forward + backward) on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload cfg2|cfg5:<ln|rms>:<fp32|bf16>:<D>]
+                    [--workload cfg2|cfg5:<ln|rms>:<fp32|bf16>:<D>[:<rows>]]
 
 One step = LayerNorm->GELU (or RMSNorm->SiLU) forward, backward (dX + per-CTA
 dgamma/dbeta partials), the partial reduce, and for N > 1 the NCCL allreduce of
@@ -46,14 +46,18 @@ class Workload:
             self.rows_per_rank, self.scaling = 32 * 1024, "weak"
             self.name = "LayerNorm->GELU(erf) fwd+bwd fp32 x[32,1024,1024] per GPU (the headline configuration)"
         elif spec.startswith("cfg5:"):
-            _, kind, dt, D = spec.split(":")
+            # an optional fifth field shrinks the row count: the same kernels on a case small enough to profile
+            parts = spec.split(":")
+            kind, dt, D = parts[1:4]
             self.kind, self.D = kind, int(D)
             self.dtype = {"fp32": torch.float32, "bf16": torch.bfloat16}[dt]
-            total = 1 << 20
+            total = int(parts[4]) if len(parts) > 4 else 1 << 20
             if total % world:
-                raise SystemExit("cfg5 needs a world size that divides 2^20")
+                raise SystemExit(f"cfg5 needs a world size that divides {total}")
             self.rows_per_rank, self.scaling = total // world, "strong"
-            self.name = f"{'LayerNorm->GELU' if kind == 'ln' else 'RMSNorm->SiLU'} fwd+bwd {dt} 2^20 rows x D={D} (whole-box sweep configuration)"
+            rows_txt = "2^20" if total == 1 << 20 else str(total)
+            self.name = (f"{'LayerNorm->GELU' if kind == 'ln' else 'RMSNorm->SiLU'} fwd+bwd {dt} {rows_txt} rows x D={D} "
+                         + ("(whole-box sweep configuration)" if total == 1 << 20 else "(sweep kernels on a reduced row count)"))
         else:
             raise SystemExit(f"unknown workload {spec}")
         self.act = 1 if self.kind == "ln" else 2          # GELU behind LayerNorm, SiLU behind RMSNorm

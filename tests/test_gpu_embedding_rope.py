@@ -124,3 +124,26 @@ def test_config4_rope_full_size_sampled():
         n_in = x.float().pow(2).sum(dtype=torch.float64)
         n_out = y.float().pow(2).sum(dtype=torch.float64)
         assert abs(float(n_out / n_in) - 1.0) < 1e-4
+
+
+@pytest.mark.parametrize("dtype,D", [(torch.float32, 256), (torch.bfloat16, 4096)])
+def test_embedding_bwd_with_one_id_used_by_most_tokens(dtype, D):
+    """A padding-like id that most tokens share goes through the long-run kernel (columns spread over
+    many warps); the sums keep the ascending-token order, so the result equals the oracle's."""
+    vocab, tokens = 300, 6000
+    gen = torch.Generator().manual_seed(5)
+    ids = torch.randint(0, vocab, (tokens,), generator=gen)
+    ids[torch.rand(tokens, generator=gen) < 0.7] = 17          # ~4200 tokens share id 17
+    ids[::5][:1200] = 250                                       # and a second run just above the threshold
+    dout, dn = make((tokens, D), 6, dtype)
+    got = abi.embedding_bwd(dout, ids.cuda(), vocab)
+    ref = O.embedding_bwd(dn, ids.numpy(), vocab)
+    n17 = int((ids == 17).sum())
+    assert n17 > 1024 and int((ids == 250).sum()) > 1024
+    if dtype == torch.float32:
+        tol.long_sum_close(got.cpu().numpy(), ref, n17)
+    else:
+        # bf16 output of an fp32 sum of n terms: 2 bf16 ulp, and the fp32 sum's own error where it cancels
+        np.testing.assert_allclose(got.float().cpu().numpy(), ref, rtol=2.0 ** -7, atol=1e-5 * np.sqrt(n17))
+    again = abi.embedding_bwd(dout, ids.cuda(), vocab)
+    assert torch.equal(got, again)                              # no atomics on the data: bit-identical reruns

@@ -220,6 +220,8 @@ embedding_keys_kernel(const void* __restrict__ ids, uint64_t* __restrict__ keys,
     keys[t] = ((uint64_t)id << 32) | (uint64_t)(uint32_t)t;
 }
 
+constexpr int64_t kLongRun = 1024;      // tokens of one id beyond which the row goes to the long-run kernel
+
 // row_range[v] = {first, one past last} sorted position whose id is v; both stay -1 (the preset)
 // for a table row no token used
 __global__ void __launch_bounds__(256)
@@ -244,7 +246,7 @@ template <typename T, int TR, int VU, int U>
 __global__ void __launch_bounds__(128)
 embedding_bwd_kernel(const T* __restrict__ dout, const uint64_t* __restrict__ keys,
                      const int2* __restrict__ row_range, T* __restrict__ dtable,
-                     int64_t tokens, int64_t vocab, int64_t D) {
+                     int64_t tokens, int64_t vocab, int64_t D, unsigned int* __restrict__ long_rows) {
     constexpr int EPV = VecTraits<T>::EPV;
     constexpr int RPC = 128 / TR;
     const int tr = threadIdx.x % TR;
@@ -252,6 +254,12 @@ embedding_bwd_kernel(const T* __restrict__ dout, const uint64_t* __restrict__ ke
     for (int64_t v = (int64_t)blockIdx.x * RPC + threadIdx.x / TR; v < vocab; v += (int64_t)gridDim.x * RPC) {
         const int2 range = __ldg(row_range + v);
         const int64_t lo = range.x < 0 ? 0 : range.x, hi = range.x < 0 ? 0 : range.y;
+        if (hi - lo > kLongRun) {
+            // one id used by very many tokens (padding, say): left to embedding_bwd_long_kernel, which
+            // spreads the row's columns over many warps.  The counter starts at -1 (the 0xff preset).
+            if (tr == 0) long_rows[2 + atomicAdd(long_rows, 1u)] = (unsigned int)v;
+            continue;
+        }
         T* dst = dtable + v * D;
         for (int64_t c0 = tr; c0 < nvec; c0 += (int64_t)VU * TR) {
             float acc[VU][EPV];
@@ -299,6 +307,46 @@ embedding_bwd_kernel(const T* __restrict__ dout, const uint64_t* __restrict__ ke
     }
 }
 
+// Table rows with a run of more than kLongRun tokens.  One warp per (row, 32 consecutive 16-byte
+// columns): it walks the whole run with U tokens in flight, so the additions of every column keep
+// the ascending-t order of the short-run kernel (same bits), while the row is spread over
+// D * elt / 512 warps instead of one.  long_rows[0] + 1 = number of rows listed from long_rows[1].
+template <typename T>
+__global__ void __launch_bounds__(128)
+embedding_bwd_long_kernel(const T* __restrict__ dout, const uint64_t* __restrict__ keys,
+                          const int2* __restrict__ row_range, T* __restrict__ dtable, int64_t D,
+                          const unsigned int* __restrict__ long_rows) {
+    constexpr int EPV = VecTraits<T>::EPV;
+    constexpr int U = 8;
+    const unsigned int count = long_rows[0] + 1u;
+    const int64_t nvec = D / EPV;
+    const int64_t c = ((int64_t)blockIdx.x * 4 + (threadIdx.x >> 5)) * 32 + (threadIdx.x & 31);
+    if (c >= nvec) return;
+    for (unsigned int r = blockIdx.y; r < count; r += gridDim.y) {
+        const int64_t v = long_rows[1 + r];
+        const int2 range = __ldg(row_range + v);
+        float acc[EPV];
+#pragma unroll
+        for (int e = 0; e < EPV; ++e) acc[e] = 0.f;
+        for (int64_t j = range.x; j < range.y; j += U) {
+            uint4 rv[U];
+#pragma unroll
+            for (int k = 0; k < U; ++k)
+                if (j + k < range.y) rv[k] = ld_stream(dout + (int64_t)(__ldg(keys + j + k) & 0xffffffffu) * D + c * EPV);
+#pragma unroll
+            for (int k = 0; k < U; ++k) {
+                if (j + k < range.y) {
+                    float f[EPV];
+                    unpack<T>(rv[k], f);
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e) acc[e] += f[e];
+                }
+            }
+        }
+        st_stream(dtable + v * D + c * EPV, pack<T>(acc));
+    }
+}
+
 // any width / alignment: one CTA per table row, scalar columns
 template <typename T>
 __global__ void __launch_bounds__(128)
@@ -334,14 +382,18 @@ static size_t cub_temp_bytes(int64_t tokens, int64_t vocab) {
 }
 
 static size_t round256(size_t v) { return (v + 255) & ~(size_t)255; }
+// list of long-run table rows: a counter and at most tokens / kLongRun entries
+static size_t max_long_rows(int64_t tokens) { return (size_t)(tokens / kLongRun) + 1; }
+static size_t long_list_bytes(int64_t tokens) { return (max_long_rows(tokens) + 2) * 4; }
 
 size_t embedding_bwd_workspace(int64_t tokens, int64_t vocab) {
     if (tokens <= 0) return 256;
-    return 2 * round256((size_t)tokens * 8) + round256(cub_temp_bytes(tokens, vocab)) + round256((size_t)vocab * 8) + 256;
+    return 2 * round256((size_t)tokens * 8) + round256(cub_temp_bytes(tokens, vocab)) + round256((size_t)vocab * 8) +
+           round256(long_list_bytes(tokens)) + 256;
 }
 
 // Workspace carve-up shared by the two phases below.
-struct EmbBwdWs { uint64_t* keys_in; uint64_t* keys_out; void* temp; size_t temp_bytes; int2* row_range; };
+struct EmbBwdWs { uint64_t* keys_in; uint64_t* keys_out; void* temp; size_t temp_bytes; int2* row_range; unsigned int* long_rows; };
 static EmbBwdWs carve_bwd_ws(void* ws, int64_t tokens, int64_t vocab) {
     uint8_t* base = (uint8_t*)(((uintptr_t)ws + 255) & ~(uintptr_t)255);
     EmbBwdWs w;
@@ -350,6 +402,7 @@ static EmbBwdWs carve_bwd_ws(void* ws, int64_t tokens, int64_t vocab) {
     w.temp = base + 2 * round256((size_t)tokens * 8);
     w.temp_bytes = cub_temp_bytes(tokens, vocab);
     w.row_range = (int2*)((uint8_t*)w.temp + round256(w.temp_bytes));
+    w.long_rows = (unsigned int*)((uint8_t*)w.row_range + round256((size_t)vocab * 8));     // directly behind: one preset covers both
     return w;
 }
 
@@ -371,7 +424,8 @@ int launch_embedding_bwd_index(const void* ids, int64_t tokens, int64_t vocab, i
     rc = cuda_status(cub::DeviceRadixSort::SortKeys(w.temp, temp_bytes, w.keys_in, w.keys_out, (int)tokens,
                                                     kKeyBeginBit, key_bits(vocab), st), "embedding key sort");
     if (rc != 0) return rc;
-    rc = cuda_status(cudaMemsetAsync(w.row_range, 0xff, (size_t)vocab * 8, st), "embedding row-range preset");
+    rc = cuda_status(cudaMemsetAsync(w.row_range, 0xff, round256((size_t)vocab * 8) + long_list_bytes(tokens), st),
+                     "embedding row-range preset");
     if (rc != 0) return rc;
     embedding_row_range_kernel<<<kgrid, 256, 0, st>>>(w.keys_out, w.row_range, tokens, vocab);
     return cuda_status(cudaGetLastError(), "embedding row-range launch");
@@ -386,6 +440,7 @@ int launch_embedding_bwd_sum(const void* dout, void* dtable, int64_t tokens, int
     const EmbBwdWs w = carve_bwd_ws(ws, tokens, vocab);
     const uint64_t* keys_out = w.keys_out;
     const int2* row_range = w.row_range;
+    unsigned int* long_rows = w.long_rows;
     const bool vec = (D * elt) % 16 == 0 && aligned16(dout) && aligned16(dtable);
     const int64_t cap = (int64_t)sm_count() * 64;
     const int64_t nvec = D * elt / 16;
@@ -398,9 +453,12 @@ int launch_embedding_bwd_sum(const void* dout, void* dtable, int64_t tokens, int
         if (!vec)                                                                                                          \
             embedding_bwd_generic_kernel<T_><<<grid_for(1), 128, 0, st>>>((const T_*)dout, keys_out, row_range, (T_*)dtable, tokens, vocab, D); \
         else if (nvec <= 128)   /* rows up to 2 KiB: a warp per table row, four tokens in flight */                         \
-            embedding_bwd_kernel<T_, 32, 4, 4><<<grid_for(4), 128, 0, st>>>((const T_*)dout, keys_out, row_range, (T_*)dtable, tokens, vocab, D); \
+            embedding_bwd_kernel<T_, 32, 4, 4><<<grid_for(4), 128, 0, st>>>((const T_*)dout, keys_out, row_range, (T_*)dtable, tokens, vocab, D, long_rows); \
         else                    /* wider rows: the CTA per table row, two tokens in flight */                               \
-            embedding_bwd_kernel<T_, 128, 4, 2><<<grid_for(1), 128, 0, st>>>((const T_*)dout, keys_out, row_range, (T_*)dtable, tokens, vocab, D); \
+            embedding_bwd_kernel<T_, 128, 4, 2><<<grid_for(1), 128, 0, st>>>((const T_*)dout, keys_out, row_range, (T_*)dtable, tokens, vocab, D, long_rows); \
+        if (vec && tokens > kLongRun)                                                                                       \
+            embedding_bwd_long_kernel<T_><<<dim3((unsigned)((nvec + 127) / 128), (unsigned)(max_long_rows(tokens) < 1024 ? max_long_rows(tokens) : 1024)), 128, 0, st>>>(        \
+                (const T_*)dout, keys_out, row_range, (T_*)dtable, D, long_rows);                                           \
     } while (0)
     if (dtype == NB2_F32) NB2_EMB_BWD(float);
     else                  NB2_EMB_BWD(__nv_bfloat16);
