@@ -425,7 +425,8 @@ int nb2_attention_softmax_fwd(const void* scores, const uint8_t* key_padding, co
                               int64_t mask_batch_stride, int64_t mask_head_stride, void* attn, int64_t B, int64_t H,
                               int64_t T, int64_t S, double scale, int causal, int dtype, void* stream) {
     NB2_REQUIRE(dtype_ok(dtype), NB2_ERR_DTYPE, "attention softmax: dtype=%d", dtype);
-    NB2_REQUIRE(B >= 0 && H >= 0 && T >= 0 && S >= 0 && S < ((int64_t)1 << 31) && mask_batch_stride >= 0 && mask_head_stride >= 0,
+    NB2_REQUIRE(B >= 0 && H >= 0 && T >= 0 && S >= 0 && S < ((int64_t)1 << 31) && H < ((int64_t)1 << 30) && T < ((int64_t)1 << 30) &&
+                    mask_batch_stride >= 0 && mask_head_stride >= 0,
                 NB2_ERR_SHAPE, "attention softmax: B=%lld H=%lld T=%lld S=%lld mask strides %lld, %lld", (long long)B,
                 (long long)H, (long long)T, (long long)S, (long long)mask_batch_stride, (long long)mask_head_stride);
     if (B * H * T * S == 0) return 0;

@@ -44,23 +44,88 @@ __device__ __forceinline__ float group_reduce(float v, float* red, int barrier_i
     return v;
 }
 
+// Merge of (max, sum-of-exponentials) pairs in log2 units: x = max, y = sum relative to that max.
+__device__ __forceinline__ float2 merge_pair(float2 a, float2 b) {
+    const float m = fmaxf(a.x, b.x);
+    // two empty sides (max -inf, sum 0) must merge to an empty pair, not to 2^(-inf + inf) = NaN
+    const float ms = m == -INFINITY ? 0.f : m;
+    return make_float2(m, a.y * fast_ex2(a.x - ms) + b.y * fast_ex2(b.x - ms));
+}
+template <int TPR>
+__device__ __forceinline__ float2 merge_max_sum(float2 v, float2* red, int barrier_id) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float2 w;
+        w.x = __shfl_xor_sync(0xffffffffu, v.x, o);
+        w.y = __shfl_xor_sync(0xffffffffu, v.y, o);
+        v = merge_pair(v, w);
+    }
+    if constexpr (TPR > 32) {
+        constexpr int WPR = TPR / 32;
+        const int w = (threadIdx.x % TPR) >> 5;
+        if ((threadIdx.x & 31) == 0) red[w] = v;
+        named_barrier(barrier_id, TPR);
+        float2 t = red[0];
+#pragma unroll
+        for (int i = 1; i < WPR; ++i) t = merge_pair(t, red[i]);
+        v = t;
+    }
+    return v;
+}
+
+// (batch, head, target position) of a row index, advanced by a fixed row stride without dividing:
+// a 64-bit division per row and thread cost more than the row's arithmetic.
+struct RowPos {
+    int64_t b; int h, t;
+    int64_t sb; int sh, st;       // the stride, decomposed the same way
+    int H, Tq;
+    __device__ __forceinline__ RowPos(int64_t row, int64_t stride, int64_t H_, int64_t Tq_) : H((int)H_), Tq((int)Tq_) {
+        t = (int)(row % Tq_); const int64_t bh = row / Tq_; h = (int)(bh % H_); b = bh / H_;
+        st = (int)(stride % Tq_); const int64_t sbh = stride / Tq_; sh = (int)(sbh % H_); sb = sbh / H_;
+    }
+    __device__ __forceinline__ void advance() {
+        t += st; if (t >= Tq) { t -= Tq; ++h; }
+        h += sh; if (h >= H) { h -= H; ++b; }
+        if (h >= H) { h -= H; ++b; }
+        b += sb;
+    }
+};
+
 template <typename T, int TPR, int VPT>
-__global__ void __launch_bounds__((TPR > 256 ? TPR : 256), (TPR > 256 ? 1 : 2))
+__global__ void __launch_bounds__((TPR > 256 ? TPR : 256), (TPR > 256 ? 1 : 3))
 softmax_fwd_kernel(const T* __restrict__ scores, const SoftmaxMask m, T* __restrict__ out,
                    int64_t rows, int64_t H, int64_t Tq, int S, float scale) {
     constexpr int EPV = VecTraits<T>::EPV;
     constexpr int THREADS = TPR > 256 ? TPR : 256;
     constexpr int RPC = THREADS / TPR;
     constexpr int WPR = (TPR + 31) / 32;
-    __shared__ float red_a[RPC][WPR], red_b[RPC][WPR];
+    __shared__ float red[2][RPC][2 * WPR];               // (max, sum) pairs, alternating by row parity
     const int grp = threadIdx.x / TPR, tr = threadIdx.x % TPR;
     const int nvec = S / EPV;
+    int parity = 0;
     pdl_wait();
-    for (int64_t row = (int64_t)blockIdx.x * RPC + grp; row < rows; row += (int64_t)gridDim.x * RPC) {
-        const int64_t t = row % Tq;
-        const int64_t bh = row / Tq;
-        const int64_t h = bh % H, b = bh / H;
+    const int64_t stride = (int64_t)gridDim.x * RPC;
+    // The next row's scores are requested before the current row's arithmetic, so two rows per
+    // group are in flight whatever the occupancy.  Under a causal mask the vectors that lie wholly
+    // beyond the diagonal are not read at all.
+    uint4 cur[VPT], nxt[VPT];
+    auto load_row = [&](int64_t row, int t, uint4* raw) {
         const T* src = scores + row * (int64_t)S;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int c = tr + j * TPR;
+            raw[j] = make_uint4(0u, 0u, 0u, 0u);
+            if (c < nvec && !(m.causal && c * EPV > t)) raw[j] = ld_stream(src + (size_t)c * EPV);
+        }
+    };
+    int64_t row = (int64_t)blockIdx.x * RPC + grp;
+    RowPos ahead(row, stride, H, Tq);                    // position of the row whose loads are issued next
+    if (row < rows) load_row(row, ahead.t, cur);
+    for (; row < rows; row += stride) {
+        const int t = ahead.t, h = ahead.h;
+        const int64_t b = ahead.b;
+        ahead.advance();
+        if (row + stride < rows) load_row(row + stride, ahead.t, nxt);
         const T* mrow = m.add_mask ? reinterpret_cast<const T*>(m.add_mask) + b * m.mask_sb + h * m.mask_sh + t * (int64_t)S : nullptr;
         const uint8_t* prow = m.key_padding ? m.key_padding + b * (int64_t)S : nullptr;
         float v[VPT][EPV];
@@ -69,7 +134,7 @@ softmax_fwd_kernel(const T* __restrict__ scores, const SoftmaxMask m, T* __restr
         for (int j = 0; j < VPT; ++j) {
             const int c = tr + j * TPR;
             if (c < nvec) {
-                unpack<T>(ld_stream(src + (size_t)c * EPV), v[j]);
+                unpack<T>(cur[j], v[j]);
                 float mk[EPV];
                 if (mrow != nullptr) unpack<T>(ld_param(mrow + (size_t)c * EPV), mk);
                 uint8_t pad[EPV];
@@ -82,7 +147,7 @@ softmax_fwd_kernel(const T* __restrict__ scores, const SoftmaxMask m, T* __restr
                     float s = v[j][e] * scale;
                     if (prow != nullptr && pad[e]) s = -INFINITY;
                     if (mrow != nullptr) s += mk[e];
-                    if (m.causal && (int64_t)c * EPV + e > t) s = -INFINITY;
+                    if (m.causal && c * EPV + e > t) s = -INFINITY;
                     v[j][e] = s;
                     mx = fmaxf(mx, s);
                 }
@@ -91,20 +156,24 @@ softmax_fwd_kernel(const T* __restrict__ scores, const SoftmaxMask m, T* __restr
                 for (int e = 0; e < EPV; ++e) v[j][e] = -INFINITY;
             }
         }
-        mx = group_reduce<TPR, true>(mx, red_a[grp], grp + 1);
-        // a row with every column masked has max = -inf: (-inf) - (-inf) is NaN, as in the reference
-        const float off = -mx * kLog2e;
+        // One reduction round: every thread exponentiates against its OWN maximum, and (max, sum)
+        // pairs are merged (m = max(ma, mb), s = sa 2^(ma-m) + sb 2^(mb-m), in log2 units); the
+        // thread's factor 2^(m_own - m) / s then rescales its exponentials.  A thread whose columns are
+        // all masked uses 0 in place of its -inf maximum; a row with every column masked ends with
+        // m = -inf and s = 0, the factor is inf and 0 * inf makes the whole row NaN, as in the reference.
+        const float m_own = mx == -INFINITY ? 0.f : mx * kLog2e;
         float sum = 0.f;
 #pragma unroll
         for (int j = 0; j < VPT; ++j)
 #pragma unroll
             for (int e = 0; e < EPV; ++e) {
-                const float p = (tr + j * TPR < nvec) ? fast_ex2(fmaf(v[j][e], kLog2e, off)) : 0.f;
+                const float p = fast_ex2(fmaf(v[j][e], kLog2e, -m_own));     // masked and out-of-range columns: 2^-inf = 0
                 v[j][e] = p;
                 sum += p;
             }
-        sum = group_reduce<TPR, false>(sum, red_b[grp], grp + 1);
-        const float inv = 1.0f / sum;
+        float2 ms = make_float2(mx * kLog2e, sum);
+        ms = merge_max_sum<TPR>(ms, reinterpret_cast<float2*>(red[parity][grp]), grp + 1);
+        const float inv = fast_ex2(m_own - ms.x) / ms.y;
         T* dst = out + row * (int64_t)S;
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
@@ -116,6 +185,9 @@ softmax_fwd_kernel(const T* __restrict__ scores, const SoftmaxMask m, T* __restr
                 st_stream(dst + (size_t)c * EPV, pack<T>(o));
             }
         }
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) cur[j] = nxt[j];
+        parity ^= 1;
     }
 }
 
@@ -132,17 +204,30 @@ softmax_bwd_kernel(const T* __restrict__ attn, const T* __restrict__ dattn, T* _
     const int nvec = S / EPV;
     pdl_wait();
     int parity = 0;
-    for (int64_t row = (int64_t)blockIdx.x * RPC + grp; row < rows; row += (int64_t)gridDim.x * RPC, parity ^= 1) {
-        const T* ya = attn + row * (int64_t)S;
-        const T* da = dattn + row * (int64_t)S;
+    const int64_t stride = (int64_t)gridDim.x * RPC;
+    uint4 cy[VPT], cd[VPT], ny[VPT], nd[VPT];           // this row and the next, requested one row ahead
+    auto load_row = [&](int64_t row, uint4* ry, uint4* rd) {
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int c = tr + j * TPR;
+            if (c < nvec) {
+                ry[j] = ld_stream(attn + row * (int64_t)S + (size_t)c * EPV);
+                rd[j] = ld_stream(dattn + row * (int64_t)S + (size_t)c * EPV);
+            }
+        }
+    };
+    int64_t row = (int64_t)blockIdx.x * RPC + grp;
+    if (row < rows) load_row(row, cy, cd);
+    for (; row < rows; row += stride, parity ^= 1) {
+        if (row + stride < rows) load_row(row + stride, ny, nd);
         float y[VPT][EPV], d[VPT][EPV];
         float dot = 0.f;
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
             const int c = tr + j * TPR;
             if (c < nvec) {
-                unpack<T>(ld_stream(ya + (size_t)c * EPV), y[j]);
-                unpack<T>(ld_stream(da + (size_t)c * EPV), d[j]);
+                unpack<T>(cy[j], y[j]);
+                unpack<T>(cd[j], d[j]);
 #pragma unroll
                 for (int e = 0; e < EPV; ++e) dot = fmaf(y[j][e], d[j][e], dot);
             }
@@ -159,6 +244,8 @@ softmax_bwd_kernel(const T* __restrict__ attn, const T* __restrict__ dattn, T* _
                 st_stream(dst + (size_t)c * EPV, pack<T>(o));
             }
         }
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) { cy[j] = ny[j]; cd[j] = nd[j]; }
     }
 }
 
@@ -225,9 +312,13 @@ softmax_bwd_generic(const T* __restrict__ attn, const T* __restrict__ dattn, T* 
     }
 }
 
-int pick_softmax_tpr(int64_t nvec) {
+// 4 vectors per thread in both directions and types.  Measured for the bf16 forward: 2 vectors per
+// thread (no spills at the three-CTA register budget, but half the bytes in flight per thread and
+// twice the threads per row) ran at 0.56 of the copy rate against 0.69 with 4.
+template <typename T> constexpr int fwd_vpt() { return 4; }
+int pick_softmax_tpr(int64_t nvec, int vpt = 4) {
     for (int tpr = 32; tpr <= 512; tpr *= 2)
-        if (nvec <= (int64_t)tpr * 4) return tpr;
+        if (nvec <= (int64_t)tpr * vpt) return tpr;
     return 0;
 }
 
@@ -235,7 +326,7 @@ int64_t row_grid(int64_t rows, int tpr) {
     const int threads = tpr > 256 ? tpr : 256;
     const int rpc = threads / tpr;
     const int64_t need = (rows + rpc - 1) / rpc;
-    const int64_t cap = (int64_t)sm_count() * (tpr > 256 ? 1 : 2) * 4;      // a few CTAs per slot: rows are short-lived
+    const int64_t cap = (int64_t)sm_count() * (tpr > 256 ? 1 : 3) * 4;      // a few CTAs per slot: rows are short-lived
     return need < cap ? (need < 1 ? 1 : need) : cap;
 }
 
@@ -243,7 +334,7 @@ template <typename T, int TPR>
 int launch_fwd_tpr(const void* scores, const SoftmaxMask& m, void* out, int64_t rows, int64_t H, int64_t Tq, int64_t S,
                    float scale, cudaStream_t st) {
     constexpr int THREADS = TPR > 256 ? TPR : 256;
-    return cuda_status(launch_pdl(softmax_fwd_kernel<T, TPR, 4>, dim3((unsigned)row_grid(rows, TPR)), dim3(THREADS), 0, st,
+    return cuda_status(launch_pdl(softmax_fwd_kernel<T, TPR, fwd_vpt<T>()>, dim3((unsigned)row_grid(rows, TPR)), dim3(THREADS), 0, st,
                                   (const T*)scores, m, (T*)out, rows, H, Tq, (int)S, scale),
                        "softmax_fwd_kernel launch");
 }
@@ -262,7 +353,7 @@ int launch_fwd_t(const void* scores, const SoftmaxMask& m, void* out, int64_t B,
     const int64_t rows = B * H * Tq;
     const bool mask_ok = m.add_mask == nullptr || (aligned16(m.add_mask) && m.mask_sb % EPV == 0 && m.mask_sh % EPV == 0);
     const bool pad_ok = m.key_padding == nullptr || (reinterpret_cast<uintptr_t>(m.key_padding) % EPV == 0);
-    const int tpr = (S % EPV == 0 && aligned16(scores) && aligned16(out) && mask_ok && pad_ok) ? pick_softmax_tpr(S / EPV) : 0;
+    const int tpr = (S % EPV == 0 && aligned16(scores) && aligned16(out) && mask_ok && pad_ok) ? pick_softmax_tpr(S / EPV, fwd_vpt<T>()) : 0;
     switch (tpr) {
         case 32:  return launch_fwd_tpr<T, 32>(scores, m, out, rows, H, Tq, S, scale, st);
         case 64:  return launch_fwd_tpr<T, 64>(scores, m, out, rows, H, Tq, S, scale, st);
