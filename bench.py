@@ -241,10 +241,36 @@ def run_suite(args):
         results.append({"op": name, "us": sec * 1e6, "algorithmic_bytes": nbytes, "achieved_gbs": nbytes / sec / 1e9,
                         "frac_of_measured_peak": nbytes / sec / 1e9 / peak, "frac_of_nominal_8000": nbytes / sec / 8e12})
 
+    only = {t for t in args.only.split(",") if t}
+
+    def want(group):
+        return not only or group in only
+
     g = torch.Generator(device=dev).manual_seed(7)
     bf = torch.bfloat16
     # configs[2]: RMSNorm bf16 x[16,4096,4096], then out = silu(a) * b for a, b [65536, 11008]
     rows, D = 65536, 4096
+    if want("rmsnorm") or want("addnorm"):
+        _suite_norms(abi, timed, dev, g, rows, D, want)
+    if want("gate"):
+        _suite_gate(abi, timed, dev, g, rows)
+    if want("embedding"):
+        _suite_embedding(abi, timed, dev, g)
+    if want("bert"):
+        _suite_bert(abi, timed, dev, g)
+    if want("rope"):
+        _suite_rope(abi, timed, dev, g)
+    if want("act"):
+        _suite_act(abi, timed, dev, g)
+    if want("attention"):
+        _suite_attention(abi, timed, dev, g)
+    abi.device_status()
+    _emit({"suite": results, "peak_gbs": peak, "unit": "GB/s", "data": "synthetic",
+           "note": "timings include torch's output allocation from its caching allocator"})
+
+
+def _suite_norms(abi, timed, dev, g, rows, D, want):
+    bf = torch.bfloat16
     x = torch.randn(rows, D, device=dev, generator=g).to(bf); dy = torch.randn(rows, D, device=dev, generator=g).to(bf)
     w = (1 + 0.02 * torch.randn(D, device=dev, generator=g)).to(bf)
     y, rstd = abi.rmsnorm_fwd(x, w, 1e-6)
@@ -264,6 +290,10 @@ def run_suite(args):
     timed("add+layernorm_fwd fp32 [32768,1024]", lambda: abi.add_norm_fwd("ln", xf32, rf32, gf, bf_, 1e-5), 4 * 32768 * 1024 * 4)
     timed("add+layernorm_bwd+reduce fp32 [32768,1024]", lambda: abi.add_norm_bwd("ln", s32, xf32, rf32, gf, m32, r32), 4 * 32768 * 1024 * 4)
     del xf32, rf32, s32, y32
+
+
+def _suite_gate(abi, timed, dev, g, rows):
+    bf = torch.bfloat16
     H = 11008
     a = torch.randn(rows, H, device=dev, generator=g).to(bf); b = torch.randn(rows, H, device=dev, generator=g).to(bf)
     d = torch.randn(rows, H, device=dev, generator=g).to(bf)
@@ -273,6 +303,10 @@ def run_suite(args):
     ab = torch.cat([a[:16384], b[:16384]], dim=1)              # SwiGLU form: halves of one [rows, 2H] tensor
     timed("silu_gate_fwd bf16 swiglu-strided [16384,2x11008]", lambda: abi.silu_gate_fwd(ab[:, :H], ab[:, H:]), 3 * 16384 * H * 2)
     del a, b, d, da, db, ab
+
+
+def _suite_embedding(abi, timed, dev, g):
+    bf = torch.bfloat16
     # configs[3]: gather table[32000,4096] bf16, ids int32 [32,2048]; rotary q,k [32,2048,32,128] bf16
     table = (0.02 * torch.randn(32000, 4096, device=dev, generator=g)).to(bf)
     ids = torch.randint(0, 32000, (32, 2048), device=dev, generator=g, dtype=torch.int32)
@@ -281,6 +315,10 @@ def run_suite(args):
     timed("embedding_bwd bf16 (zero table + sort + segmented sum)", lambda: abi.embedding_bwd(dout, ids, 32000),
           65536 * 4096 * 2 + 32000 * 4096 * 2 + 65536 * 4, iters=10)
     del table, dout
+
+
+def _suite_bert(abi, timed, dev, g):
+    bf = torch.bfloat16
     # BERT front end (bert.hpp:155-194): vocab 30522, D 768, ids [256, 512]
     Bb, Sb, Db = 256, 512, 768
     wordt = (0.02 * torch.randn(30522, Db, device=dev, generator=g)).to(bf)
@@ -295,17 +333,28 @@ def run_suite(args):
     timed("bert_embedding+layernorm_bwd bf16 (LN bwd + 3 table gradients)",
           lambda: abi.bert_embedding_ln_bwd(sb, yb, idb, gb, mb, rb, 30522, pos_rows=512), 4 * Bb * Sb * Db * 2 + 30522 * Db * 2, iters=10)
     del wordt, yb, sb
+
+
+def _suite_rope(abi, timed, dev, g):
+    bf = torch.bfloat16
     q = torch.randn(32, 2048, 32, 128, device=dev, generator=g).to(bf)
     cs = abi.rope_table(2048, 128)
     timed("rope_apply bf16 [32,2048,32,128] (one of q, k)", lambda: abi.rope_apply(q, cs), 2 * q.numel() * 2)
     timed("rope_apply inverse (backward)", lambda: abi.rope_apply(q, cs, inverse=True), 2 * q.numel() * 2)
     del q
+
+
+def _suite_act(abi, timed, dev, g):
     n = 32 * 1024 * 1024
     xf = torch.randn(n, device=dev, generator=g); df = torch.randn(n, device=dev, generator=g)
     for nm, code in (("gelu", abi.ACT_GELU), ("silu", abi.ACT_SILU)):
         timed(f"{nm}_fwd fp32 32Mi", lambda: abi.act_fwd(xf, code), 2 * n * 4)
         timed(f"{nm}_bwd fp32 32Mi", lambda: abi.act_bwd(xf, df, code), 3 * n * 4)
     del xf, df
+
+
+def _suite_attention(abi, timed, dev, g):
+    bf = torch.bfloat16
     # attention probabilities (kernel.hpp:33-93): scores [16, 16, 1024, 1024], causal, then with an additive [B,T,S] mask
     for dt, nm in ((torch.float32, "fp32"), (bf, "bf16")):
         sc = torch.randn(16, 16, 1024, 1024, device=dev, generator=g).to(dt)
@@ -318,9 +367,6 @@ def run_suite(args):
               lambda: abi.attention_softmax_fwd(sc, 0.125, attn_mask=mk), 2 * sc.numel() * e + mk.numel() * e)
         timed(f"attention_softmax_bwd {nm} [16,16,1024,1024]", lambda: abi.attention_softmax_bwd(at, da_, 0.125), 3 * sc.numel() * e)
         del sc, da_, at, mk
-    abi.device_status()
-    _emit({"suite": results, "peak_gbs": peak, "unit": "GB/s", "data": "synthetic",
-           "note": "timings include torch's output allocation from its caching allocator"})
 
 
 # ------------------------------------------------------------ cfg5 sweep
@@ -417,6 +463,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--sweep", action="store_true", help="whole-box sweep: 2^20 rows x D in {768..8192}, both norms, both dtypes")
     ap.add_argument("--suite", action="store_true", help="time the other kernels of the path (1 GPU) instead of the step")
+    ap.add_argument("--only", default="", help="with --suite: run only the groups named here, comma separated "
+                    "(rmsnorm, addnorm, gate, embedding, bert, rope, act, attention)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 

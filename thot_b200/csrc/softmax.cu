@@ -91,11 +91,17 @@ struct RowPos {
     }
 };
 
-template <typename T, int TPR, int VPT>
+// FLAGS: bit 0 key padding present, bit 1 additive mask present, bit 2 causal.  Compile-time, so
+// that a call without masks spends nothing on them: with run-time tests the kernel executed 33
+// instructions per score and was bound by issue (ncu: 71% issue slots busy, ALU pipe 60%).
+constexpr int kSmPad = 1, kSmMask = 2, kSmCausal = 4;
+
+template <typename T, int TPR, int VPT, int FLAGS>
 __global__ void __launch_bounds__((TPR > 256 ? TPR : 256), (TPR > 256 ? 1 : 3))
 softmax_fwd_kernel(const T* __restrict__ scores, const SoftmaxMask m, T* __restrict__ out,
                    int64_t rows, int64_t H, int64_t Tq, int S, float scale) {
     constexpr int EPV = VecTraits<T>::EPV;
+    constexpr bool PAD = (FLAGS & kSmPad) != 0, MASK = (FLAGS & kSmMask) != 0, CAUSAL = (FLAGS & kSmCausal) != 0;
     constexpr int THREADS = TPR > 256 ? TPR : 256;
     constexpr int RPC = THREADS / TPR;
     constexpr int WPR = (TPR + 31) / 32;
@@ -115,7 +121,7 @@ softmax_fwd_kernel(const T* __restrict__ scores, const SoftmaxMask m, T* __restr
         for (int j = 0; j < VPT; ++j) {
             const int c = tr + j * TPR;
             raw[j] = make_uint4(0u, 0u, 0u, 0u);
-            if (c < nvec && !(m.causal && c * EPV > t)) raw[j] = ld_stream(src + (size_t)c * EPV);
+            if (c < nvec && !(CAUSAL && c * EPV > t)) raw[j] = ld_stream(src + (size_t)c * EPV);
         }
     };
     int64_t row = (int64_t)blockIdx.x * RPC + grp;
@@ -126,31 +132,37 @@ softmax_fwd_kernel(const T* __restrict__ scores, const SoftmaxMask m, T* __restr
         const int64_t b = ahead.b;
         ahead.advance();
         if (row + stride < rows) load_row(row + stride, ahead.t, nxt);
-        const T* mrow = m.add_mask ? reinterpret_cast<const T*>(m.add_mask) + b * m.mask_sb + h * m.mask_sh + t * (int64_t)S : nullptr;
-        const uint8_t* prow = m.key_padding ? m.key_padding + b * (int64_t)S : nullptr;
+        const T* mrow = MASK ? reinterpret_cast<const T*>(m.add_mask) + b * m.mask_sb + h * m.mask_sh + t * (int64_t)S : nullptr;
+        const uint8_t* prow = PAD ? m.key_padding + b * (int64_t)S : nullptr;
         float v[VPT][EPV];
         float mx = -INFINITY;
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
             const int c = tr + j * TPR;
-            if (c < nvec) {
+            // a vector past the row's end, or wholly beyond the diagonal, is all -inf and costs nothing more
+            if (c < nvec && !(CAUSAL && c * EPV > t)) {
                 unpack<T>(cur[j], v[j]);
                 float mk[EPV];
-                if (mrow != nullptr) unpack<T>(ld_param(mrow + (size_t)c * EPV), mk);
+                if constexpr (MASK) unpack<T>(ld_param(mrow + (size_t)c * EPV), mk);
                 uint8_t pad[EPV];
-                if (prow != nullptr) {
+                if constexpr (PAD) {
                     if constexpr (EPV == 4) *reinterpret_cast<uint32_t*>(pad) = __ldg(reinterpret_cast<const uint32_t*>(prow + (size_t)c * EPV));
                     else *reinterpret_cast<uint2*>(pad) = __ldg(reinterpret_cast<const uint2*>(prow + (size_t)c * EPV));
                 }
 #pragma unroll
                 for (int e = 0; e < EPV; ++e) {
-                    float s = v[j][e] * scale;
-                    if (prow != nullptr && pad[e]) s = -INFINITY;
-                    if (mrow != nullptr) s += mk[e];
-                    if (m.causal && c * EPV + e > t) s = -INFINITY;
-                    v[j][e] = s;
-                    mx = fmaxf(mx, s);
+                    float sc = v[j][e] * scale;
+                    if constexpr (PAD) sc = pad[e] ? -INFINITY : sc;
+                    if constexpr (MASK) sc += mk[e];
+                    v[j][e] = sc;
                 }
+                if (CAUSAL && c * EPV + EPV - 1 > t) {        // the one vector that straddles the diagonal
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e)
+                        if (c * EPV + e > t) v[j][e] = -INFINITY;
+                }
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) mx = fmaxf(mx, v[j][e]);
             } else {
 #pragma unroll
                 for (int e = 0; e < EPV; ++e) v[j][e] = -INFINITY;
@@ -330,13 +342,28 @@ int64_t row_grid(int64_t rows, int tpr) {
     return need < cap ? (need < 1 ? 1 : need) : cap;
 }
 
+template <typename T, int TPR, int FLAGS>
+int launch_fwd_flags(const void* scores, const SoftmaxMask& m, void* out, int64_t rows, int64_t H, int64_t Tq, int64_t S,
+                     float scale, cudaStream_t st) {
+    constexpr int THREADS = TPR > 256 ? TPR : 256;
+    return cuda_status(launch_pdl(softmax_fwd_kernel<T, TPR, fwd_vpt<T>(), FLAGS>, dim3((unsigned)row_grid(rows, TPR)), dim3(THREADS), 0, st,
+                                  (const T*)scores, m, (T*)out, rows, H, Tq, (int)S, scale),
+                       "softmax_fwd_kernel launch");
+}
 template <typename T, int TPR>
 int launch_fwd_tpr(const void* scores, const SoftmaxMask& m, void* out, int64_t rows, int64_t H, int64_t Tq, int64_t S,
                    float scale, cudaStream_t st) {
-    constexpr int THREADS = TPR > 256 ? TPR : 256;
-    return cuda_status(launch_pdl(softmax_fwd_kernel<T, TPR, fwd_vpt<T>()>, dim3((unsigned)row_grid(rows, TPR)), dim3(THREADS), 0, st,
-                                  (const T*)scores, m, (T*)out, rows, H, Tq, (int)S, scale),
-                       "softmax_fwd_kernel launch");
+    const int flags = (m.key_padding ? kSmPad : 0) | (m.add_mask ? kSmMask : 0) | (m.causal ? kSmCausal : 0);
+    switch (flags) {
+        case 0: return launch_fwd_flags<T, TPR, 0>(scores, m, out, rows, H, Tq, S, scale, st);
+        case 1: return launch_fwd_flags<T, TPR, 1>(scores, m, out, rows, H, Tq, S, scale, st);
+        case 2: return launch_fwd_flags<T, TPR, 2>(scores, m, out, rows, H, Tq, S, scale, st);
+        case 3: return launch_fwd_flags<T, TPR, 3>(scores, m, out, rows, H, Tq, S, scale, st);
+        case 4: return launch_fwd_flags<T, TPR, 4>(scores, m, out, rows, H, Tq, S, scale, st);
+        case 5: return launch_fwd_flags<T, TPR, 5>(scores, m, out, rows, H, Tq, S, scale, st);
+        case 6: return launch_fwd_flags<T, TPR, 6>(scores, m, out, rows, H, Tq, S, scale, st);
+        default: return launch_fwd_flags<T, TPR, 7>(scores, m, out, rows, H, Tq, S, scale, st);
+    }
 }
 template <typename T, int TPR>
 int launch_bwd_tpr(const void* attn, const void* dattn, void* dscores, int64_t rows, int64_t S, float scale, cudaStream_t st) {
