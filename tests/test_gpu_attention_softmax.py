@@ -101,3 +101,28 @@ def test_scaled_dot_product_module_matches_torch_ops(causal):
         torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-5)
     with pytest.raises(ValueError):                     # std::invalid_argument, as the reference throws
         host.attention_softmax(torch.zeros(B, H, T, S, device="cuda"), torch.zeros(T + 1, S, device="cuda"), None, 1.0, False)
+
+
+def test_full_size_properties_bf16():
+    """[16, 16, 1024, 1024] bf16, causal (the measured case): every row sums to 1, nothing attends to a
+    later column, reruns are bit-identical, and sampled rows match the oracle."""
+    B, H, T, S = 16, 16, 1024, 1024
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    scores = torch.randn(B, H, T, S, device="cuda", generator=gen).to(torch.bfloat16)
+    attn = abi.attention_softmax_fwd(scores, 0.125, causal=True)
+    sums = attn.float().sum(-1)
+    assert torch.allclose(sums, torch.ones_like(sums), atol=2e-2)
+    assert not torch.triu(attn[3, 5], 1).any() and not torch.triu(attn[-1, -1], 1).any()
+    assert torch.equal(attn, abi.attention_softmax_fwd(scores, 0.125, causal=True))
+    for (b, h) in ((0, 0), (7, 9), (15, 15)):
+        # sampled rows t = 0, 97, ...: the definition, with the causal cut, in fp64 on the host
+        rows = np.arange(0, T, 97)
+        x = scores[b, h, ::97].float().cpu().numpy().astype(np.float64) * 0.125
+        x[np.arange(S)[None, :] > rows[:, None]] = -np.inf
+        e = np.exp(x - x.max(-1, keepdims=True)); ref = e / e.sum(-1, keepdims=True)
+        check(attn[b, h, ::97], ref, f"rows of ({b},{h})")
+    d = torch.randn(B, H, T, S, device="cuda", generator=gen).to(torch.bfloat16)
+    ds = abi.attention_softmax_bwd(attn, d, 0.125)
+    # softmax backward is orthogonal to the all-ones direction: every row of dscores sums to ~0
+    assert ds.float().sum(-1).abs().max() < 2e-2
+    assert not torch.triu(ds[2, 2], 1).any()
