@@ -461,6 +461,8 @@ def main():
     ap.add_argument("--workload", default="cfg2")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--reserve-sms", type=int, default=-1,
+                    help="SMs the persistent norm kernels leave to the overlapped allreduce (default: 4 for N > 1, 0 for N = 1)")
     ap.add_argument("--sweep", action="store_true", help="whole-box sweep: 2^20 rows x D in {768..8192}, both norms, both dtypes")
     ap.add_argument("--suite", action="store_true", help="time the other kernels of the path (1 GPU) instead of the step")
     ap.add_argument("--only", default="", help="with --suite: run only the groups named here, comma separated "
@@ -492,10 +494,16 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU fallback")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    # The allreduce of step k runs beside the kernels of step k+1.  Those are persistent, one CTA per SM
+    # with a fixed share of the rows each, so the collective gets SMs of its own: NCCL is held to 4 CTAs
+    # and the norm kernels leave 4 SMs unused (measured: a one-CTA kernel spinning for 50 us beside the
+    # backward stretched it from 93 to 106 us; with one SM set aside it did not).
+    reserve = args.reserve_sms if args.reserve_sms >= 0 else (4 if world > 1 else 0)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("NCCL_MAX_CTAS", str(max(reserve, 1)))
         dist.init_process_group("nccl", device_id=dev)
-    abi.lib()
+    abi.lib().nb2_reserve_sms(reserve)
 
     rows, D = w.rows_per_rank, w.D
     x, dy, gamma, beta = synth_inputs(w, rows, dev, seed=1234 + rank)
@@ -670,7 +678,7 @@ def main():
             "dtype": "f32" if w.dtype == torch.float32 else "bf16", "data": "synthetic",
             "config": {"workload": w.name, "rows_per_gpu": rows, "D": D, "global_rows": rows * world,
                        "l2": "inputs larger than L2 (each step streams %.0f MB per GPU)" % (w.step_bytes() / 1e6),
-                       "collective": "NCCL allreduce of [%d] fp32 per step on a side stream, overlapping the next forward" % ncols if world > 1 else "none"},
+                       "collective": ("NCCL allreduce of [%d] fp32 per step on a side stream, overlapping the next forward; %d SMs left to it" % (ncols, reserve)) if world > 1 else "none"},
             "rows_per_s": rows * world / sec_per_step,
             "frac_of_nominal_8000_per_gpu": value / world / 8000.0,
             "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu, "e2e": e2e,

@@ -77,6 +77,14 @@ const char* nb2_last_error_string(void);
 /* Number of SMs the library sized its persistent grids for on the current
  * device (148 on B200); <= 0 when no device is usable. */
 int nb2_sm_count(void);
+/*
+ * Set aside `n` SMs (0 = none, the default) that the persistent norm kernels leave unused; returns
+ * the previous value.  Process-wide.  No counterpart in the reference.  For callers that run a
+ * kernel of their own beside these (the allreduce of the previous step on another stream): the
+ * norm kernels give each CTA a fixed share of the rows, one CTA per SM, and a CTA that finds its
+ * SM taken runs after all the others.
+ */
+int nb2_reserve_sms(int n);
 
 /*
  * Reads (synchronously) the device status word of the current device into

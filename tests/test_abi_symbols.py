@@ -104,3 +104,15 @@ def test_ctypes_signatures_match_the_header_prototypes():
                 assert bound_ptr, f"{name}: '{p}' is a pointer but is bound as {t}"
             else:
                 assert t in (ctypes.c_int, ctypes.c_int64, ctypes.c_double, ctypes.c_size_t), f"{name}: '{p}' bound as {t}"
+
+
+def test_reserve_sms_is_a_host_side_setting_that_returns_the_previous_value():
+    from thot_b200 import abi
+    L = abi.lib()
+    before = L.nb2_reserve_sms(3)
+    try:
+        assert L.nb2_reserve_sms(5) == 3
+        assert L.nb2_reserve_sms(-7) == 5          # negative means none
+        assert L.nb2_reserve_sms(0) == 0
+    finally:
+        L.nb2_reserve_sms(before)

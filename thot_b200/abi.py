@@ -24,6 +24,7 @@ _SIGNATURES = {
     "nb2_abi_version": (c_int, []),
     "nb2_last_error_string": (c_char_p, []),
     "nb2_sm_count": (c_int, []),
+    "nb2_reserve_sms": (c_int, [c_int]),
     "nb2_device_status": (c_int, [POINTER(ctypes.c_uint), c_int]),
     "nb2_attention_softmax_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                           c_double, c_int, c_int, c_void_p]),

@@ -1,6 +1,7 @@
 // extern "C" entry points of libnott_b200.so: argument validation, then the
 // launchers.  Declarations and the reference interfaces they replace are in
 // include/nott_b200.h.
+#include <atomic>
 #include <stdarg.h>
 #include <string.h>
 #include "launchers.h"
@@ -34,6 +35,17 @@ int sm_count() {
     }
     return cached_sms;
 }
+
+// SMs the persistent norm kernels size their grids for: all of them, less the number a caller set
+// aside for a kernel of its own that runs beside them (a collective on another stream).  Those
+// kernels give every CTA a fixed share of the rows, so a CTA that finds no free SM at launch would
+// run after the others and nearly double the kernel's time.
+static std::atomic<int> g_reserved_sms{0};
+int launch_sms() {
+    const int sms = sm_count() - g_reserved_sms.load(std::memory_order_relaxed);
+    return sms < 1 ? 1 : sms;
+}
+int exchange_reserved_sms(int n) { return g_reserved_sms.exchange(n < 0 ? 0 : n, std::memory_order_relaxed); }
 
 int current_device_slot() {
     int dev = 0;
@@ -162,6 +174,7 @@ extern "C" {
 
 int nb2_abi_version(void) { return NB2_ABI_VERSION; }
 const char* nb2_last_error_string(void) { return g_err; }
+int nb2_reserve_sms(int n) { return exchange_reserved_sms(n); }
 int nb2_sm_count(void) { return sm_count(); }
 
 int nb2_device_status(unsigned int* status_host, int clear) {

@@ -14,6 +14,7 @@ namespace nb2 {
 void set_error(const char* fmt, ...);
 int  cuda_status(cudaError_t e, const char* what);
 int  sm_count();           // SMs of the current device (cached per device)
+int  launch_sms();         // sm_count() less the SMs set aside by nb2_reserve_sms()
 
 #define NB2_REQUIRE(cond, code, ...)            \
     do {                                        \

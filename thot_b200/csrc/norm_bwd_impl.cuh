@@ -20,7 +20,7 @@ static int launch_bwd_tma_res(const NormArgs& a, int64_t* n_partials) {
         if (rc != 0) return rc;
         configured = t.smem;
     }
-    const int grid = (int)tma_grid(a.rows, TPR, sm_count(), NT);
+    const int grid = (int)tma_grid(a.rows, TPR, launch_sms(), NT);
     const cudaError_t e = launch_pdl(kern, dim3(grid), dim3(NT), t.smem, a.stream, (const T*)a.x, (const T*)a.dy,
                                      (const T*)a.dres, (const T*)a.gamma, (const T*)a.beta, a.mean, a.rstd, (T*)a.dx,
                                      a.partials, a.rows, (int)a.D, t.stages, device_status_ptr());
@@ -48,7 +48,7 @@ static int launch_bwd_wide_bf16(const NormArgs& a, int64_t* n_partials) {
         if (rc != 0) return rc;
         configured = t.smem;
     }
-    const int grid = (int)tma_grid(a.rows, TPR, sm_count());
+    const int grid = (int)tma_grid(a.rows, TPR, launch_sms());
     const cudaError_t e = launch_pdl(kern, dim3(grid), dim3(kTmaThreads), t.smem, a.stream, (const T*)a.x, (const T*)a.dy,
                                      (const T*)a.gamma, (const T*)a.beta, a.mean, a.rstd, (T*)a.dx, a.partials, a.rows,
                                      (int)a.D, t.stages, device_status_ptr());

@@ -18,7 +18,7 @@ static int launch_fwd_tma_nt(const NormArgs& a) {
         if (rc != 0) return rc;
         configured = t.smem;
     }
-    const int grid = (int)tma_grid(a.rows, TPR, sm_count(), NT);
+    const int grid = (int)tma_grid(a.rows, TPR, launch_sms(), NT);
     const cudaError_t e = launch_pdl(kern, dim3(grid), dim3(NT), t.smem, a.stream, (const T*)a.x, (const T*)a.res,
                                      (const T*)a.gamma, (const T*)a.beta, (T*)a.sum_out, (T*)a.y, a.mean_out, a.rstd_out,
                                      a.rows, (int)a.D, a.eps, t.stages, device_status_ptr(), a.gather);
