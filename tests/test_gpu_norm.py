@@ -200,3 +200,27 @@ def test_no_kernel_gave_up_waiting():
     abi.layernorm_bwd(x, x, g, b, mean, rstd, abi.ACT_GELU)
     torch.cuda.synchronize()
     assert abi.device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_layernorm_statistics_with_an_outlying_first_column_and_a_large_offset(dtype):
+    """Rows whose first column is far from the rest, and rows with a mean far above their spread, are where
+    a statistics shortcut (one-pass sums, a shift by a sampled column) would lose digits; the two-pass
+    statistics must match the oracle there."""
+    rows, D = 96, 1024
+    gen = torch.Generator().manual_seed(77)
+    x = torch.randn(rows, D, generator=gen)
+    x[:32] = x[:32] * 0.1 + 10.0              # mean = 100 x spread (fp32 input rounding alone costs 6e-6 on xhat)
+    x[32:64, 0] = 5000.0                      # first column 5000 sigma away
+    x[64:, 0] = -7.5
+    x = x.to(dtype)
+    g, gn = make((D,), 2, dtype, 0.02, 1.0); b, bn = make((D,), 3, dtype, 0.02)
+    y, mean, rstd = abi.layernorm_fwd(x.cuda(), g, b, 1e-5, abi.ACT_NONE)
+    ref = O.layernorm_act(x.float().numpy(), gn, bn, None, 1e-5, abi.ACT_NONE)
+    np.testing.assert_allclose(mean.cpu().numpy(), ref["mean"], rtol=1e-6, atol=1e-6)
+    np.testing.assert_allclose(rstd.cpu().numpy(), ref["rstd"], rtol=2e-5)
+    if dtype == torch.float32:
+        # y = xhat*gamma+beta with |xhat| up to 32 (the outlier itself): relative tolerance on that scale
+        np.testing.assert_allclose(y.cpu().numpy(), ref["y"], rtol=2e-5, atol=2e-5)
+    else:
+        check(y, ref["y"], "y")
