@@ -314,6 +314,11 @@ def _suite_embedding(abi, timed, dev, g):
     dout = torch.randn(65536, 4096, device=dev, generator=g).to(bf)
     timed("embedding_bwd bf16 (zero table + sort + segmented sum)", lambda: abi.embedding_bwd(dout, ids, 32000),
           65536 * 4096 * 2 + 32000 * 4096 * 2 + 65536 * 4, iters=10)
+    index = abi.embedding_index(ids, 32000)
+    timed("embedding_index int32 65536 ids (sort + row ranges; once per ids tensor, beside the forward gather)",
+          lambda: abi.embedding_index(ids, 32000), 65536 * 4, iters=10)
+    timed("embedding_bwd_indexed bf16 (segmented sum from a prebuilt index)", lambda: abi.embedding_bwd_indexed(dout, index, 32000),
+          65536 * 4096 * 2 + 32000 * 4096 * 2, iters=10)
     del table, dout
 
 

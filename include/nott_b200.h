@@ -281,6 +281,18 @@ int nb2_embedding_bwd(const void* dout, const void* ids, void* dtable,
                       int64_t tokens, int64_t vocab, int64_t D,
                       int dtype, int index_type,
                       void* workspace, size_t workspace_bytes, void* stream);
+/*
+ * The same backward in two calls.  nb2_embedding_index needs only the ids (it sorts them and
+ * records each table row's run of tokens in `workspace`, same size as above), so a host can issue
+ * it when the ids arrive -- beside the forward gather, on another stream -- and keep the workspace;
+ * nb2_embedding_bwd_indexed then forms dtable from dout and that workspace alone.  Called back to
+ * back on one stream they are nb2_embedding_bwd.  One index serves any number of backward calls
+ * over the same ids, one at a time (the index also holds the call's list of long token runs).
+ */
+int nb2_embedding_index(const void* ids, int64_t tokens, int64_t vocab, int index_type,
+                        void* workspace, size_t workspace_bytes, void* stream);
+int nb2_embedding_bwd_indexed(const void* dout, void* dtable, int64_t tokens, int64_t vocab, int64_t D,
+                              int dtype, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------ *
  * BERT's embedding front end in one pass:

@@ -147,3 +147,25 @@ def test_embedding_bwd_with_one_id_used_by_most_tokens(dtype, D):
         np.testing.assert_allclose(got.float().cpu().numpy(), ref, rtol=2.0 ** -7, atol=1e-5 * np.sqrt(n17))
     again = abi.embedding_bwd(dout, ids.cuda(), vocab)
     assert torch.equal(got, again)                              # no atomics on the data: bit-identical reruns
+
+
+def test_embedding_backward_from_a_prebuilt_index_equals_the_one_call_form():
+    """nb2_embedding_index + nb2_embedding_bwd_indexed: same bits as nb2_embedding_bwd, and one index serves
+    several backward calls (skewed ids included, so the long-run list is rebuilt per call)."""
+    vocab, tokens, D = 500, 9000, 512
+    gen = torch.Generator().manual_seed(21)
+    ids = torch.randint(0, vocab, (tokens,), generator=gen, dtype=torch.int32)
+    ids[::3] = 7                                               # 3000 tokens on one row: the long-run kernel
+    idc = ids.cuda()
+    index = abi.embedding_index(idc, vocab)
+    for seed in (1, 2):
+        dout, _ = make((tokens, D), seed, torch.bfloat16)
+        assert torch.equal(abi.embedding_bwd_indexed(dout, index, vocab), abi.embedding_bwd(dout, idc, vocab))
+    L = abi.lib()
+    assert L.nb2_embedding_bwd_indexed(None, None, 4, 8, 16, 0, None, 0, None) == -1            # NULL
+    small = torch.empty(64, dtype=torch.uint8, device="cuda")
+    dt = torch.empty(vocab, D, device="cuda")
+    do = torch.empty(tokens, D, device="cuda")
+    import ctypes
+    P = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    assert L.nb2_embedding_bwd_indexed(P(do), P(dt), tokens, vocab, D, 0, P(small), 64, None) == -5   # workspace too small

@@ -26,6 +26,8 @@ _SIGNATURES = {
     "nb2_sm_count": (c_int, []),
     "nb2_reserve_sms": (c_int, [c_int]),
     "nb2_device_status": (c_int, [POINTER(ctypes.c_uint), c_int]),
+    "nb2_embedding_index": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_size_t, c_void_p]),
+    "nb2_embedding_bwd_indexed": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_size_t, c_void_p]),
     "nb2_attention_softmax_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                           c_double, c_int, c_int, c_void_p]),
     "nb2_attention_softmax_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_double, c_int, c_void_p]),
@@ -297,6 +299,25 @@ def embedding_bwd(dout, ids, vocab: int):
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dout.device)
     check(lib().nb2_embedding_bwd(_p(d2), _p(flat), _p(dtable), flat.numel(), vocab, D, dtype_code(dout.dtype),
                                   _index_code(ids), _p(ws), ws_bytes, _stream()))
+    return dtable
+
+
+def embedding_index(ids, vocab: int, dtype=torch.float32):
+    """Sorted token runs of `ids` for embedding_bwd_indexed: build once per ids tensor."""
+    flat = ids.reshape(-1).contiguous()
+    ws_bytes = workspace_bytes(WS_EMBEDDING_BWD, flat.numel(), vocab, dtype_code(dtype))
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=ids.device)
+    check(lib().nb2_embedding_index(_p(flat), flat.numel(), vocab, _index_code(ids), _p(ws), ws_bytes, _stream()))
+    return ws
+
+
+def embedding_bwd_indexed(dout, index_ws, vocab: int):
+    _dev(dout)
+    D = dout.shape[-1]
+    d2 = dout.reshape(-1, D)
+    dtable = torch.empty(vocab, D, dtype=dout.dtype, device=dout.device)
+    check(lib().nb2_embedding_bwd_indexed(_p(d2), _p(dtable), d2.shape[0], vocab, D, dtype_code(dout.dtype), _p(index_ws),
+                                          index_ws.numel(), _stream()))
     return dtable
 
 

@@ -344,6 +344,30 @@ int nb2_embedding_bwd(const void* dout, const void* ids, void* dtable, int64_t t
     return launch_embedding_bwd(dout, ids, dtable, tokens, vocab, D, dtype, index_type, workspace, workspace_bytes, (cudaStream_t)stream);
 }
 
+int nb2_embedding_index(const void* ids, int64_t tokens, int64_t vocab, int index_type, void* workspace,
+                        size_t workspace_bytes, void* stream) {
+    NB2_REQUIRE(idx_ok(index_type), NB2_ERR_DTYPE, "embedding index: index_type=%d", index_type);
+    NB2_REQUIRE(tokens >= 0 && vocab > 0 && vocab < ((int64_t)1 << 31), NB2_ERR_SHAPE, "embedding index: tokens=%lld vocab=%lld",
+                (long long)tokens, (long long)vocab);
+    if (tokens == 0) return 0;
+    NB2_REQUIRE(ids != nullptr, NB2_ERR_NULL, "embedding index: NULL ids");
+    int rc = require_device();
+    if (rc != 0) return rc;
+    return launch_embedding_bwd_index(ids, tokens, vocab, index_type, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+int nb2_embedding_bwd_indexed(const void* dout, void* dtable, int64_t tokens, int64_t vocab, int64_t D, int dtype,
+                              void* workspace, size_t workspace_bytes, void* stream) {
+    NB2_REQUIRE(dtype_ok(dtype), NB2_ERR_DTYPE, "embedding bwd: dtype=%d", dtype);
+    NB2_REQUIRE(tokens >= 0 && vocab > 0 && vocab < ((int64_t)1 << 31) && D > 0, NB2_ERR_SHAPE,
+                "embedding bwd: tokens=%lld vocab=%lld D=%lld", (long long)tokens, (long long)vocab, (long long)D);
+    NB2_REQUIRE(dtable && (tokens == 0 || (dout && workspace)), NB2_ERR_NULL, "embedding bwd: NULL pointer");
+    NB2_REQUIRE(tokens == 0 || workspace_bytes >= embedding_bwd_workspace(tokens, vocab), NB2_ERR_WORKSPACE,
+                "embedding bwd: workspace %zu < required %zu", workspace_bytes, embedding_bwd_workspace(tokens, vocab));
+    int rc = require_device();
+    if (rc != 0) return rc;
+    return launch_embedding_bwd_sum(dout, dtable, tokens, vocab, D, dtype, workspace, (cudaStream_t)stream);
+}
+
 int nb2_bert_embedding_ln_fwd(const void* word, const void* pos, const void* type, const void* ids, const void* gamma,
                               const void* beta, void* sum_out, void* y, float* mean, float* rstd, int64_t B, int64_t S,
                               int64_t vocab, int64_t D, double eps, int dtype, int index_type, int64_t* status,

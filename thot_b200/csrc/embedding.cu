@@ -402,7 +402,7 @@ static EmbBwdWs carve_bwd_ws(void* ws, int64_t tokens, int64_t vocab) {
     w.temp = base + 2 * round256((size_t)tokens * 8);
     w.temp_bytes = cub_temp_bytes(tokens, vocab);
     w.row_range = (int2*)((uint8_t*)w.temp + round256(w.temp_bytes));
-    w.long_rows = (unsigned int*)((uint8_t*)w.row_range + round256((size_t)vocab * 8));     // directly behind: one preset covers both
+    w.long_rows = (unsigned int*)((uint8_t*)w.row_range + round256((size_t)vocab * 8));
     return w;
 }
 
@@ -424,8 +424,7 @@ int launch_embedding_bwd_index(const void* ids, int64_t tokens, int64_t vocab, i
     rc = cuda_status(cub::DeviceRadixSort::SortKeys(w.temp, temp_bytes, w.keys_in, w.keys_out, (int)tokens,
                                                     kKeyBeginBit, key_bits(vocab), st), "embedding key sort");
     if (rc != 0) return rc;
-    rc = cuda_status(cudaMemsetAsync(w.row_range, 0xff, round256((size_t)vocab * 8) + long_list_bytes(tokens), st),
-                     "embedding row-range preset");
+    rc = cuda_status(cudaMemsetAsync(w.row_range, 0xff, (size_t)vocab * 8, st), "embedding row-range preset");
     if (rc != 0) return rc;
     embedding_row_range_kernel<<<kgrid, 256, 0, st>>>(w.keys_out, w.row_range, tokens, vocab);
     return cuda_status(cudaGetLastError(), "embedding row-range launch");
@@ -441,6 +440,9 @@ int launch_embedding_bwd_sum(const void* dout, void* dtable, int64_t tokens, int
     const uint64_t* keys_out = w.keys_out;
     const int2* row_range = w.row_range;
     unsigned int* long_rows = w.long_rows;
+    // the list of long runs belongs to this call (an index may serve several): its counter restarts at -1
+    int rc0 = cuda_status(cudaMemsetAsync(long_rows, 0xff, 4, st), "embedding long-run list preset");
+    if (rc0 != 0) return rc0;
     const bool vec = (D * elt) % 16 == 0 && aligned16(dout) && aligned16(dtable);
     const int64_t cap = (int64_t)sm_count() * 64;
     const int64_t nvec = D * elt / 16;

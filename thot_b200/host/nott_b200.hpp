@@ -28,6 +28,7 @@
 
 #include <ATen/autocast_mode.h>
 #include <ATen/cuda/CUDAContext.h>
+#include <ATen/cuda/CUDAEvent.h>
 #include <torch/torch.h>
 
 #include <cmath>
@@ -467,12 +468,32 @@ struct EmbeddingFunction : public torch::autograd::Function<EmbeddingFunction> {
         auto flat = ids.contiguous().view({-1});
         const auto vocab = w.size(0), D = w.size(1);
         auto out = torch::empty({flat.size(0), D}, w.options());
-        detail::check(nb2_embedding_fwd(w.data_ptr(), flat.data_ptr(), out.data_ptr(), flat.size(0), vocab, D,
-                                        detail::dtype_code(w, "Embedding"),
-                                        flat.scalar_type() == torch::kInt32 ? NB2_I32 : NB2_I64, nullptr,
-                                        detail::stream()),
-                      "nb2_embedding_fwd");
-        ctx->save_for_backward({flat});
+        const int code = detail::dtype_code(w, "Embedding");
+        const int icode = flat.scalar_type() == torch::kInt32 ? NB2_I32 : NB2_I64;
+        // The backward's index (token runs per table row) depends on the ids alone: it is built here, on a
+        // pool stream beside the gather, and joined before returning, so the backward is one kernel.
+        torch::Tensor index;
+        if (weight.requires_grad() && torch::GradMode::is_enabled() && flat.size(0) > 0) {
+            const auto ws = nb2_workspace_bytes(NB2_WS_EMBEDDING_BWD, flat.size(0), vocab, code);
+            index = torch::empty({(int64_t)ws}, w.options().dtype(torch::kUInt8));
+            auto cur = at::cuda::getCurrentCUDAStream();
+            auto side = at::cuda::getStreamFromPool(false, cur.device_index());
+            at::cuda::CUDAEvent fork, join;
+            fork.record(cur);
+            fork.block(side);
+            detail::check(nb2_embedding_index(flat.data_ptr(), flat.size(0), vocab, icode, index.data_ptr(), ws, side.stream()),
+                          "nb2_embedding_index");
+            join.record(side);
+            detail::check(nb2_embedding_fwd(w.data_ptr(), flat.data_ptr(), out.data_ptr(), flat.size(0), vocab, D, code, icode,
+                                            nullptr, cur.stream()),
+                          "nb2_embedding_fwd");
+            join.block(cur);
+        } else {
+            detail::check(nb2_embedding_fwd(w.data_ptr(), flat.data_ptr(), out.data_ptr(), flat.size(0), vocab, D, code, icode,
+                                            nullptr, detail::stream()),
+                          "nb2_embedding_fwd");
+        }
+        ctx->save_for_backward({flat, index});
         ctx->saved_data["vocab"] = vocab;
         auto shape = ids.sizes().vec();
         shape.push_back(D);
@@ -480,18 +501,25 @@ struct EmbeddingFunction : public torch::autograd::Function<EmbeddingFunction> {
     }
     static torch::autograd::tensor_list backward(torch::autograd::AutogradContext* ctx,
                                                  torch::autograd::tensor_list grads) {
-        auto flat = ctx->get_saved_variables()[0];
+        auto saved = ctx->get_saved_variables();
+        auto flat = saved[0], index = saved[1];
         const auto vocab = ctx->saved_data["vocab"].toInt();
         const auto D = grads[0].size(-1);
         auto dout = grads[0].contiguous().view({-1, D});
         const int code = detail::dtype_code(dout, "Embedding backward");
         auto dtable = torch::empty({vocab, D}, dout.options());
-        const auto ws = nb2_workspace_bytes(NB2_WS_EMBEDDING_BWD, flat.size(0), vocab, code);
-        auto scratch = torch::empty({(int64_t)ws}, dout.options().dtype(torch::kUInt8));
-        detail::check(nb2_embedding_bwd(dout.data_ptr(), flat.data_ptr(), dtable.data_ptr(), flat.size(0), vocab, D, code,
-                                        flat.scalar_type() == torch::kInt32 ? NB2_I32 : NB2_I64, scratch.data_ptr(), ws,
-                                        detail::stream()),
-                      "nb2_embedding_bwd");
+        if (index.defined()) {
+            detail::check(nb2_embedding_bwd_indexed(dout.data_ptr(), dtable.data_ptr(), flat.size(0), vocab, D, code, index.data_ptr(),
+                                                    (size_t)index.numel(), detail::stream()),
+                          "nb2_embedding_bwd_indexed");
+        } else {
+            const auto ws = nb2_workspace_bytes(NB2_WS_EMBEDDING_BWD, flat.size(0), vocab, code);
+            auto scratch = torch::empty({(int64_t)ws}, dout.options().dtype(torch::kUInt8));
+            detail::check(nb2_embedding_bwd(dout.data_ptr(), flat.data_ptr(), dtable.data_ptr(), flat.size(0), vocab, D, code,
+                                            flat.scalar_type() == torch::kInt32 ? NB2_I32 : NB2_I64, scratch.data_ptr(), ws,
+                                            detail::stream()),
+                          "nb2_embedding_bwd");
+        }
         return {dtable, torch::Tensor()};
     }
 };
