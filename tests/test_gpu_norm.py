@@ -224,3 +224,23 @@ def test_layernorm_statistics_with_an_outlying_first_column_and_a_large_offset(d
         np.testing.assert_allclose(y.cpu().numpy(), ref["y"], rtol=2e-5, atol=2e-5)
     else:
         check(y, ref["y"], "y")
+
+
+def test_reserved_sms_change_the_grid_not_the_results():
+    """nb2_reserve_sms(n): the persistent kernels run on fewer CTAs; rows are independent, so y and dX keep
+    their bits, and the parameter gradients (summed over a different number of partials) stay in tolerance."""
+    rows, D = 20000, 1024
+    x, xn = make((rows, D), 1, torch.float32); dy, dyn = make((rows, D), 2, torch.float32)
+    g, gn = make((D,), 3, torch.float32, 0.02, 1.0); b, bn = make((D,), 4, torch.float32, 0.02)
+    base = run_gpu("ln", x, g, b, dy, 1e-5, abi.ACT_GELU)
+    L = abi.lib()
+    before = L.nb2_reserve_sms(16)
+    try:
+        held = run_gpu("ln", x, g, b, dy, 1e-5, abi.ACT_GELU)
+    finally:
+        L.nb2_reserve_sms(before)
+    assert torch.equal(base["y"], held["y"]) and torch.equal(base["dx"], held["dx"])
+    ref = O.layernorm_act(xn, gn, bn, dyn, 1e-5, abi.ACT_GELU)
+    tol.long_sum_close(held["dgamma"].cpu().numpy(), ref["dgamma"], rows)
+    tol.long_sum_close(held["dbeta"].cpu().numpy(), ref["dbeta"], rows)
+    assert abi.device_status() == 0
