@@ -2,13 +2,16 @@
 """Benchmark of the fused norm+activation path (forward + backward) on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload cfg2|cfg5:<ln|rms>:<fp32|bf16>:<D>[:<rows>]]
+                    [--workload cfg5:<ln|rms>:<fp32|bf16>:<D>[:<rows>]|cfg2] [--exchange nccl|peer]
 
 One step = LayerNorm->GELU (or RMSNorm->SiLU) forward, backward (dX + per-CTA
-dgamma/dbeta partials), the partial reduce, and for N > 1 the NCCL allreduce of
-the [2, D] gradients.  Default workload: x[32,1024,1024] fp32, LayerNorm -> exact
-GELU, eps 1e-5, per GPU (weak scaling).  `cfg5:*` is the whole-box sweep: 2^20
-rows split evenly over the ranks (strong scaling).
+dgamma/dbeta partials), the partial reduce, and for N > 1 the sum over ranks of
+the [2, D] gradients (NCCL allreduce, or the library's own peer-store exchange).
+Default workload: one point of the whole-box sweep in the range the metric's
+targets are stated for: 2^20 rows x D=2048 fp32, LayerNorm -> exact GELU, eps 1e-5,
+rows split evenly over the ranks (strong scaling).  `cfg2` is x[32,1024,1024] fp32
+per GPU (weak scaling); the default run also reports it as a sub-record so the
+behaviour of a 0.12 ms step stays visible.
 
 Prints ONE JSON line on rank 0.  `value` is algorithmic HBM GB/s of the whole job
 (inputs resident in HBM), `e2e` the same metric through the host-buffer C-ABI call
@@ -34,7 +37,8 @@ import torch  # noqa: E402
 
 METRIC = "fused_norm_act_fwd_bwd_hbm_gbs"
 UNIT = "GB/s"
-FALLBACK_HBM_GBS = 6650.0          # earlier measurement on this pool, used only without MEASURED_PEAKS.json
+FALLBACK_HBM_GBS = 6650.0          # used only when MEASURED_PEAKS.json is absent
+DEFAULT_WORKLOAD = "cfg5:ln:fp32:2048"
 
 
 # ----------------------------------------------------------------- workloads
@@ -44,7 +48,7 @@ class Workload:
         if spec == "cfg2":
             self.kind, self.dtype, self.D = "ln", torch.float32, 1024
             self.rows_per_rank, self.scaling = 32 * 1024, "weak"
-            self.name = "LayerNorm->GELU(erf) fwd+bwd fp32 x[32,1024,1024] per GPU (the headline configuration)"
+            self.name = "LayerNorm->GELU(erf) fwd+bwd fp32 x[32,1024,1024] per GPU"
         elif spec.startswith("cfg5:"):
             # an optional fifth field shrinks the row count: the same kernels on a case small enough to profile
             parts = spec.split(":")
@@ -93,10 +97,14 @@ def synth_inputs(w: Workload, rows: int, device, seed: int):
 
 # -------------------------------------------------------------------- clocks
 class ClockSampler:
-    """Polls NVML for SM clock and throttle reasons while the timed region runs."""
+    """Polls NVML for SM clock and throttle reasons.  The thread is started before the warm-up
+    and polls every 20 ms; samples count only while `armed` (the timed region), so nothing is
+    created or torn down inside that region."""
 
-    def __init__(self, index: int):
+    def __init__(self, index: int, period_s: float = 0.02):
         self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.period_s = period_s
+        self.armed = False
         self._stop = threading.Event()
         self._thread = None
         try:
@@ -122,18 +130,20 @@ class ClockSampler:
         except Exception:
             pass
 
-    def __enter__(self):
+    def start(self):
         def loop():
             while not self._stop.is_set():
-                self.sample()
-                time.sleep(0.002)
+                if self.armed:
+                    self.sample()
+                time.sleep(self.period_s)
         self._thread = threading.Thread(target=loop, daemon=True)
         self._thread.start()
         return self
 
-    def __exit__(self, *a):
+    def stop(self):
         self._stop.set()
-        self._thread.join()
+        if self._thread is not None:
+            self._thread.join()
 
     def summary(self):
         if not self.samples:
@@ -143,12 +153,20 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------- reference arm
-def reference_cpu_run(w: Workload, steps: int, warmup: int, budget_s: float = 20.0):
+def config_of(w: Workload, world: int) -> dict:
+    """The `config` object of the JSON line; both arms print the same one."""
+    return {"workload": w.name, "workload_spec": w.spec, "rows_per_gpu": w.rows_per_rank, "D": w.D,
+            "global_rows": w.rows_per_rank * world,
+            "l2": "inputs larger than L2 (each step streams %.0f MB per GPU)" % (w.step_bytes() / 1e6)}
+
+
+def reference_cpu_run(w: Workload, steps: int, warmup: int, budget_s: float = 20.0, exact_steps: bool = False):
     """The reference's own modules (oracle/_ref: Nott headers + libtorch CPU, all host threads),
-    forward + autograd backward, on a bounded row sample of the workload (at most 32 Mi elements,
-    which is the whole of the default workload); timed inside the harness so only the module calls
-    are on the clock.  Falls back to the single-core C port when the reference library was not
-    built.  Returns (GB/s, seconds per step, sample rows, passes, description)."""
+    forward + autograd backward, on a bounded row sample of the workload (at most 32 Mi elements);
+    timed inside the harness so only the module calls are on the clock.  With `exact_steps` the
+    requested number of timed passes is kept and the row sample shrinks to fit the time budget;
+    otherwise the number of passes shrinks.  Falls back to the single-core C port when the
+    reference library was not built.  Returns (GB/s, seconds per step, sample rows, passes, description)."""
     from oracle import reference as R
     from oracle import cpu_oracle as O
 
@@ -158,9 +176,16 @@ def reference_cpu_run(w: Workload, steps: int, warmup: int, budget_s: float = 20
         R.set_num_threads(os.cpu_count() or 1)      # torchrun exports OMP_NUM_THREADS=1; the baseline gets every host core
         sample_rows = max(1, min(w.rows_per_rank, (32 << 20) // w.D))
         compute = 2 if bf16 else 0       # the reference runs in the tensor's own dtype
-        per = R.time_norm_act(w.kind, sample_rows, w.D, w.eps, w.act, compute, iters=1, warmup=max(1, min(warmup, 2)))
-        n = max(1, min(steps, int(budget_s / max(per, 1e-6))))
-        sec = R.time_norm_act(w.kind, sample_rows, w.D, w.eps, w.act, compute, iters=n, warmup=0)
+        per = R.time_norm_act(w.kind, sample_rows, w.D, w.eps, w.act, compute, iters=1, warmup=1)
+        if exact_steps:
+            n = max(1, steps)
+            total = per * (n + warmup)
+            if total > budget_s:
+                sample_rows = max(64, int(sample_rows * budget_s / total))
+            sec = R.time_norm_act(w.kind, sample_rows, w.D, w.eps, w.act, compute, iters=n, warmup=max(0, warmup))
+        else:
+            n = max(1, min(steps, int(budget_s / max(per, 1e-6))))
+            sec = R.time_norm_act(w.kind, sample_rows, w.D, w.eps, w.act, compute, iters=n, warmup=0)
         cores = R.num_threads()
     else:
         sample_rows = min(w.rows_per_rank, 512)
@@ -180,7 +205,7 @@ def reference_cpu_run(w: Workload, steps: int, warmup: int, budget_s: float = 20
         t0 = time.perf_counter()
         one()
         per = time.perf_counter() - t0
-        n = max(1, min(steps, int(budget_s / max(per, 1e-6))))
+        n = max(1, steps) if exact_steps and per * steps <= budget_s else max(1, min(steps, int(budget_s / max(per, 1e-6))))
         t0 = time.perf_counter()
         for _ in range(n):
             one()
@@ -199,15 +224,18 @@ def reference_cpu_run(w: Workload, steps: int, warmup: int, budget_s: float = 20
 
 
 def run_reference_arm(args, w: Workload, rank: int, world: int):
+    """`--impl reference`: the reference's CPU implementation of the same step on this box's host
+    cores; rank 0 alone runs it.  Same metric, unit, config, steps and warmup as the GPU arm; each
+    step is a bounded row sample of the workload."""
     if rank != 0:
         return
-    gbs, sec, sample_rows, n, desc = reference_cpu_run(w, args.steps, args.warmup, budget_s=60.0)
+    gbs, sec, sample_rows, n, desc = reference_cpu_run(w, args.steps, args.warmup, budget_s=240.0, exact_steps=True)
     line = {
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": world, "steps": n,
-        "warmup": min(args.warmup, 3), "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": w.scaling,
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": w.scaling,
         "vs_baseline": None, "dtype": "f32" if w.dtype == torch.float32 else "bf16", "data": "synthetic",
-        "config": {"workload": w.name, "rows_per_step": sample_rows, "D": w.D,
-                   "note": "reference CPU implementation on the host cores; each step is a bounded row sample"},
+        "config": config_of(w, world),
+        "note": "reference CPU implementation on the host cores; each step is a bounded row sample (see cpu_baseline.sample)",
         "cpu_baseline": desc,
         "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "rows_per_s": sample_rows / sec, "gpu_launches": 0,
@@ -378,43 +406,52 @@ def _suite_attention(abi, timed, dev, g):
 def run_sweep(args, rank, world, local):
     """`--sweep`: the whole-box sweep configuration in one go: LayerNorm->GELU and RMSNorm->SiLU, fp32 and bf16,
     D in {768, 1024, 2048, 4096, 8192}, 2^20 rows split evenly over the ranks (strong scaling),
-    forward / backward(+partial reduce, + NCCL allreduce for N > 1) timed separately with CUDA
-    events, max over ranks.  One JSON line."""
+    forward / backward (+ partial reduce and, for N > 1, the sum over ranks) timed separately with CUDA
+    events, max over ranks, with libtorch's CUDA ops on the same tensors beside them.  One JSON line."""
+    import ctypes
     import torch.distributed as dist
     from thot_b200 import abi
-    from thot_b200.sharding import allreduce_param_grads, row_shard
 
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    comm = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
-    peaks_file = ROOT / "MEASURED_PEAKS.json"
-    peak = float(json.loads(peaks_file.read_text())["hbm_gbs"]) if peaks_file.exists() else FALLBACK_HBM_GBS
+        box = [abi.comm_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        comm = abi.Comm(box[0], rank, world, abi.EXCHANGE_PEER if args.exchange == "peer" else abi.EXCHANGE_NCCL, max_cols=2 * 8192)
+    peak, _ = _peak()
     total_rows = 1 << 20
-    _, rows = row_shard(total_rows, world, rank)
     iters = max(3, min(args.steps, 10))
+    stream = torch.cuda.current_stream()
+    st = ctypes.c_void_p(stream.cuda_stream)
+    only = {t for t in args.only.split(",") if t}
     out = []
-    for kind, act, eps in (("ln", abi.ACT_GELU, 1e-5), ("rms", abi.ACT_SILU, 1e-6)):
-        for dt, name in ((torch.float32, "fp32"), (torch.bfloat16, "bf16")):
+    for kind in ("ln", "rms"):
+        for name in ("fp32", "bf16"):
             for D in (768, 1024, 2048, 4096, 8192):
-                gen = torch.Generator(device=dev).manual_seed(rank)
-                x = torch.randn(rows, D, device=dev, generator=gen).to(dt)
-                dy = torch.randn(rows, D, device=dev, generator=gen).to(dt)
-                g = (1 + 0.02 * torch.randn(D, device=dev, generator=gen)).to(dt)
-                b = (0.02 * torch.randn(D, device=dev, generator=gen)).to(dt)
-                elt = x.element_size()
-                if kind == "ln":
-                    y, mean, rstd = abi.layernorm_fwd(x, g, b, eps, act)
-                    f = lambda: abi.layernorm_fwd(x, g, b, eps, act)
-                    bw = lambda: allreduce_param_grads(abi.layernorm_bwd(x, dy, g, b, mean, rstd, act)[1].view(-1))
-                else:
-                    y, rstd = abi.rmsnorm_fwd(x, g, eps, act)
-                    f = lambda: abi.rmsnorm_fwd(x, g, eps, act)
-                    bw = lambda: allreduce_param_grads(abi.rmsnorm_bwd(x, dy, g, rstd, act)[1])
+                spec = f"cfg5:{kind}:{name}:{D}"
+                if only and spec not in only and f"{kind}:{name}" not in only:
+                    continue
+                w = Workload(spec, world)
+                r = StepRunner(w, comm, dev, seed=rank)
+                rows = r.rows
+
+                def f():
+                    r.fwd(st)
+
+                def bw():
+                    r.bwd(st)
+                    if comm is None:
+                        r.reduce(st)
+                    else:
+                        comm.exchange_begin(r.partials, r.nparts.value, r.grads[0])
+                        comm.exchange_end()
+
                 res = {}
-                for tag, fn, nbytes in (("fwd", f, 2 * rows * D * elt), ("bwd", bw, 3 * rows * D * elt)):
-                    for _ in range(2):
+                for tag, fn, nbytes in (("fwd", f, 2 * rows * D * w.elt), ("bwd", bw, 3 * rows * D * w.elt)):
+                    for _ in range(3):
                         fn()
                     if world > 1:
                         dist.barrier()
@@ -430,15 +467,31 @@ def run_sweep(args, rank, world, local):
                         t = torch.tensor([ms], device=dev)
                         dist.all_reduce(t, op=dist.ReduceOp.MAX)
                         ms = float(t.item())
-                    res[tag] = {"ms": ms, "gbs": nbytes * world / ms / 1e6, "frac_of_measured_per_gpu": nbytes / ms / 1e6 / peak}
-                out.append({"op": "LayerNorm->GELU" if kind == "ln" else "RMSNorm->SiLU", "dtype": name, "D": D,
-                            "rows_total": total_rows, "rows_per_s_fwd_bwd": total_rows / ((res["fwd"]["ms"] + res["bwd"]["ms"]) / 1e3),
-                            **{f"{k}_{m}": v[m] for k, v in res.items() for m in v}})
-                del x, dy, y
+                    res[tag] = {"ms": ms, "gbs": nbytes * world / ms / 1e6, "frac_of_measured_per_gpu": nbytes / ms / 1e6 / peak,
+                                "frac_of_nominal_8000_per_gpu": nbytes / ms / 1e6 / 8000.0}
+                row = {"op": "LayerNorm->GELU" if kind == "ln" else "RMSNorm->SiLU", "dtype": name, "D": D,
+                       "rows_total": total_rows, "rows_per_s_fwd_bwd": total_rows / ((res["fwd"]["ms"] + res["bwd"]["ms"]) / 1e3),
+                       **{f"{k}_{m}": v[m] for k, v in res.items() for m in v}}
+                if not args.no_comparator:
+                    try:
+                        cmpr = gpu_comparator(w, r, iters)
+                        ours_same_rows = (res["fwd"]["ms"] + res["bwd"]["ms"]) * cmpr["rows"] / rows
+                        row["gpu_comparator"] = {"rows": cmpr["rows"], "ms_per_step": cmpr["ms_per_step"],
+                                                 "speedup": cmpr["ms_per_step"] / ours_same_rows}
+                    except Exception as exc:
+                        row["gpu_comparator"] = {"error": str(exc)}
+                out.append(row)
+                r.close()
+                del r
+                torch.cuda.empty_cache()
     abi.device_status()
     if rank == 0:
         _emit({"sweep": out, "n_gpus": world, "peak_gbs": peak, "scaling": "strong", "data": "synthetic",
-               "note": "backward includes the partial reduce, torch's output allocation and, for N > 1, the NCCL allreduce"})
+               "exchange": "none" if world == 1 else args.exchange,
+               "note": "backward includes the partial reduce and, for N > 1, the sum over ranks; gpu_comparator = libtorch CUDA ops "
+                       "(forward + autograd backward) on a bounded row sample of the same tensors"})
+    if comm is not None:
+        comm.close()
     if world > 1:
         dist.destroy_process_group()
 
@@ -453,6 +506,229 @@ def _emit(line: dict) -> None:
 _REAL_STDOUT = 1
 
 
+def _peak():
+    peaks_file = ROOT / "MEASURED_PEAKS.json"
+    if peaks_file.exists():
+        return float(json.loads(peaks_file.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class StepRunner:
+    """One workload on this rank: device-resident synthetic inputs, the C step driver
+    (nb2_step_run: forward, end of the previous exchange, backward, partial reduce + exchange),
+    and the same kernels one by one for the per-kernel timings."""
+
+    def __init__(self, w: Workload, comm, dev, seed: int):
+        import ctypes
+        from thot_b200 import abi
+
+        self.abi, self.w, self.comm, self.dev = abi, w, comm, dev
+        rows, D = w.rows_per_rank, w.D
+        self.rows, self.D = rows, D
+        self.x, self.dy, self.gamma, self.beta = synth_inputs(w, rows, dev, seed)
+        self.code = abi.dtype_code(w.dtype)
+        self.y, self.dx = torch.empty_like(self.x), torch.empty_like(self.x)
+        self.ncols = (2 if w.kind == "ln" else 1) * D
+        self.grads = [torch.zeros(self.ncols, dtype=torch.float32, device=dev) for _ in range(2)]
+        self.step = abi.NormStep(comm, w.kind, rows, D, w.dtype, w.act, w.eps)
+        self.k = 0
+        # buffers of the one-by-one launches
+        self.mean = torch.empty(max(rows, 1), dtype=torch.float32, device=dev)
+        self.rstd = torch.empty(max(rows, 1), dtype=torch.float32, device=dev)
+        self.partials = torch.empty(abi.workspace_bytes(abi.WS_NORM_BWD, rows, D, self.code) // 4, dtype=torch.float32, device=dev)
+        self.nparts = ctypes.c_int64(0)
+        self._ct = ctypes
+
+    def run(self):
+        self.step.run(self.x, self.dy, self.gamma, self.beta, self.y, self.dx, self.grads[self.k & 1])
+        self.k += 1
+
+    def finish(self):
+        self.step.finish()
+
+    # ---- the same kernels, one launch each
+    def _ptrs(self):
+        P = lambda t: None if t is None else self._ct.c_void_p(t.data_ptr())  # noqa: E731
+        return P
+
+    def fwd(self, st):
+        abi, w, P, L = self.abi, self.w, self._ptrs(), self.abi.lib()
+        if w.kind == "ln":
+            abi.check(L.nb2_layernorm_fwd(P(self.x), P(self.gamma), P(self.beta), P(self.y), P(self.mean), P(self.rstd),
+                                          self.rows, self.D, w.eps, self.code, w.act, st))
+        else:
+            abi.check(L.nb2_rmsnorm_fwd(P(self.x), P(self.gamma), P(self.y), P(self.rstd), self.rows, self.D, w.eps, self.code, w.act, st))
+
+    def bwd(self, st):
+        abi, w, P, L = self.abi, self.w, self._ptrs(), self.abi.lib()
+        if w.kind == "ln":
+            abi.check(L.nb2_layernorm_bwd(P(self.x), P(self.dy), P(self.gamma), P(self.beta), P(self.mean), P(self.rstd), P(self.dx),
+                                          P(self.partials), self._ct.byref(self.nparts), self.rows, self.D, self.code, w.act, st))
+        else:
+            abi.check(L.nb2_rmsnorm_bwd(P(self.x), P(self.dy), P(self.gamma), P(self.rstd), P(self.dx), P(self.partials),
+                                        self._ct.byref(self.nparts), self.rows, self.D, self.code, w.act, st))
+
+    def reduce(self, st):
+        abi, P, L = self.abi, self._ptrs(), self.abi.lib()
+        abi.check(L.nb2_colreduce_partials(P(self.partials), self.nparts.value, self.ncols, P(self.grads[0]), st))
+
+    def close(self):
+        self.step.close()
+
+
+def timed_steps(runner: StepRunner, steps: int, warmup: int, world: int, dev, clocks=None):
+    """W untimed steps, then exactly K steps between barrier + synchronize on both sides, CUDA events
+    on the launching stream, max over ranks.  Returns seconds per step."""
+    import torch.distributed as dist
+
+    stream = torch.cuda.current_stream()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        runner.run()
+    runner.finish()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if clocks is not None:
+        clocks.armed = True
+    e0.record(stream)
+    for _ in range(steps):
+        runner.run()
+    runner.finish()                              # the last exchange is inside the timed region
+    e1.record(stream)
+    if clocks is not None:
+        clocks.sample()                          # the queue is still draining here
+    torch.cuda.synchronize()
+    if clocks is not None:
+        clocks.armed = False
+    ms = e0.elapsed_time(e1)
+    barrier()
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms / 1e3 / steps
+
+
+def kernel_times(runner: StepRunner, n_prof: int):
+    """Per-kernel durations inside a step sequence: CUDA events around each launch."""
+    import ctypes
+    stream = torch.cuda.current_stream()
+    st = ctypes.c_void_p(stream.cuda_stream)
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(n_prof)]
+    for i in range(3):
+        runner.fwd(st); runner.bwd(st); runner.reduce(st)
+    torch.cuda.synchronize()
+    for i in range(n_prof):
+        ev[i][0].record(stream); runner.fwd(st)
+        ev[i][1].record(stream); runner.bwd(st)
+        ev[i][2].record(stream); runner.reduce(st)
+        ev[i][3].record(stream)
+    torch.cuda.synchronize()
+    t_fwd = float(np.mean([ev[i][0].elapsed_time(ev[i][1]) for i in range(n_prof)])) / 1e3
+    t_bwd = float(np.mean([ev[i][1].elapsed_time(ev[i][2]) for i in range(n_prof)])) / 1e3
+    t_red = float(np.mean([ev[i][2].elapsed_time(ev[i][3]) for i in range(n_prof)])) / 1e3
+    return t_fwd, t_bwd, t_red
+
+
+def gpu_comparator(w: Workload, runner: StepRunner, steps: int):
+    """What the reference executes when its tensors live on a GPU: libtorch's CUDA ops, unfused.
+    LayerNorm: layer_norm -> gelu(erf) (classic.hpp:436,451); RMSNorm: the op chain of
+    mamba.hpp:134-140 (pow, mean, +eps, rsqrt, mul, mul) -> silu; forward + autograd backward with the
+    same dY on the same device tensors, CUDA-event timed.  Rows are bounded so that autograd's saved
+    tensors fit beside the benchmark's own buffers."""
+    import torch.nn.functional as F
+
+    rows = min(runner.rows, (1 << 30) // max(w.D * w.elt // 2, 1))      # at most ~2 GiB per tensor
+    if rows <= 0:
+        return None
+    x = runner.x[:rows].detach().requires_grad_(True)
+    dy = runner.dy[:rows]
+    g = runner.gamma.detach().requires_grad_(True)
+    b = runner.beta.detach().requires_grad_(True) if runner.beta is not None else None
+
+    def one():
+        if w.kind == "ln":
+            y = F.gelu(F.layer_norm(x, (w.D,), g, b, w.eps))
+        else:
+            variance = x.pow(2).mean(-1, True)
+            y = F.silu(x * torch.rsqrt(variance + w.eps) * g)
+        y.backward(dy)
+        x.grad = None
+        g.grad = None
+        if b is not None:
+            b.grad = None
+
+    n = max(3, min(steps, 10))
+    for _ in range(3):
+        one()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n):
+        one()
+    e1.record()
+    torch.cuda.synchronize()
+    sec = e0.elapsed_time(e1) / 1e3 / n
+    del x, g, b
+    torch.cuda.empty_cache()
+    return {"what": "libtorch CUDA " + ("layer_norm -> gelu(erf)" if w.kind == "ln" else "pow/mean/rsqrt/mul/mul -> silu") + ", forward + autograd backward",
+            "rows": rows, "steps": n, "ms_per_step": sec * 1e3, "value": w.step_bytes(rows) / sec / 1e9, "unit": UNIT,
+            "rows_per_s": rows / sec}
+
+
+def e2e_run(w: Workload, runner: StepRunner, steps: int, world: int, dev):
+    """The same metric through the host-buffer C-ABI call: pinned host tensors in and out, the
+    host<->device copies inside the timed region.  PCIe-bound by construction."""
+    import torch.distributed as dist
+    abi = runner.abi
+    D = w.D
+    e2e_rows = min(runner.rows, (512 << 20) // (D * w.elt))       # pinned host buffers of at most 512 MiB each
+    if e2e_rows <= 0:
+        return None
+    hs = abi.HostStep(e2e_rows, D, w.dtype)
+    hx = runner.x[:e2e_rows].cpu().pin_memory(); hdy = runner.dy[:e2e_rows].cpu().pin_memory()
+    hg = runner.gamma.cpu()
+    hb = runner.beta.cpu() if runner.beta is not None else None
+    hy = torch.empty_like(hx).pin_memory(); hdx = torch.empty_like(hx).pin_memory()
+    hgr = torch.empty(runner.ncols, dtype=torch.float32).pin_memory()
+
+    def one():
+        if w.kind == "ln":
+            hs.step(hx, hdy, hg, hb, hy, hdx, hgr, w.eps, w.act)
+        else:
+            hs.step_rms(hx, hdy, hg, hy, hdx, hgr, w.eps, w.act)
+
+    n_e2e = max(3, min(steps, 30))
+    for _ in range(3):
+        one()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(n_e2e):
+        one()
+    torch.cuda.synchronize()
+    dt = (time.perf_counter() - t0) / n_e2e
+    if world > 1:
+        t = torch.tensor([dt], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = float(t.item())
+    hs.close()
+    act_bytes = e2e_rows * D * w.elt
+    nparam = (2 if w.kind == "ln" else 1) * D
+    return {"value": w.step_bytes(e2e_rows) * world / dt / 1e9, "unit": UNIT,
+            "h2d_bytes_per_step": 2 * act_bytes + nparam * w.elt, "d2h_bytes_per_step": 2 * act_bytes + nparam * 4,
+            "ms_per_step": dt * 1e3, "rows_per_step": e2e_rows, "steps": n_e2e,
+            "call": ("nb2_layernorm_act_step_host" if w.kind == "ln" else "nb2_rmsnorm_act_step_host")
+                    + " (x, dY in pinned host memory; y, dX, parameter gradients out)",
+            "note": "bound by the host link: every step moves 4 activation tensors over PCIe, the kernels are idle most of the time"}
+
+
 def main():
     global _REAL_STDOUT
     sys.stdout.flush()
@@ -460,20 +736,27 @@ def main():
     os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=2000)
-    ap.add_argument("--warmup", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="cfg2")
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
+    ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer"],
+                    help="how the parameter gradients are summed over ranks: NCCL allreduce on a side stream, "
+                         "or the library's own peer-store exchange fused into the partial reduce")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--reserve-sms", type=int, default=-1,
-                    help="SMs the persistent norm kernels leave to the overlapped allreduce (default: 4 for N > 1, 0 for N = 1)")
+    ap.add_argument("--no-comparator", action="store_true")
+    ap.add_argument("--no-cfg2", action="store_true", help="skip the x[32,1024,1024] sub-record")
+    ap.add_argument("--reserve-sms", type=int, default=0,
+                    help="SMs the persistent norm kernels leave to a kernel that runs beside them (default 0)")
     ap.add_argument("--sweep", action="store_true", help="whole-box sweep: 2^20 rows x D in {768..8192}, both norms, both dtypes")
     ap.add_argument("--suite", action="store_true", help="time the other kernels of the path (1 GPU) instead of the step")
     ap.add_argument("--only", default="", help="with --suite: run only the groups named here, comma separated "
-                    "(rmsnorm, addnorm, gate, embedding, bert, rope, act, attention)")
+                    "(rmsnorm, addnorm, gate, embedding, bert, rope, act, attention); with --sweep: only these points "
+                    "(cfg5:ln:bf16:2048 or ln:bf16)")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3)
+    if args.warmup < 3:
+        print(f"bench: --warmup {args.warmup} is below the 3 warm-up steps the timing rules ask for", file=sys.stderr)
 
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
@@ -493,180 +776,80 @@ def main():
 
     import torch.distributed as dist
     from thot_b200 import abi
-    from thot_b200.sharding import allreduce_param_grads
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU fallback")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    # The allreduce of step k runs beside the kernels of step k+1.  Those are persistent, one CTA per SM
-    # with a fixed share of the rows each, so the collective gets SMs of its own: NCCL is held to 4 CTAs
-    # and the norm kernels leave 4 SMs unused (measured: a one-CTA kernel spinning for 50 us beside the
-    # backward stretched it from 93 to 106 us; with one SM set aside it did not).
-    reserve = args.reserve_sms if args.reserve_sms >= 0 else (4 if world > 1 else 0)
+    clocks = ClockSampler(local).start()          # before the warm-up; it samples only inside the timed region
+    comm = None
+    mode = abi.EXCHANGE_PEER if args.exchange == "peer" else abi.EXCHANGE_NCCL
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ.setdefault("NCCL_MAX_CTAS", str(max(reserve, 1)))
-        dist.init_process_group("nccl", device_id=dev)
-    abi.lib().nb2_reserve_sms(reserve)
+        dist.init_process_group("nccl", device_id=dev)     # plumbing: barrier, max over ranks, passing the id
+        box = [abi.comm_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        comm = abi.Comm(box[0], rank, world, mode, max_cols=2 * 8192)
+    abi.lib().nb2_reserve_sms(max(args.reserve_sms, 0))
 
-    rows, D = w.rows_per_rank, w.D
-    x, dy, gamma, beta = synth_inputs(w, rows, dev, seed=1234 + rank)
-    code = abi.dtype_code(w.dtype)
-    y, dx = torch.empty_like(x), torch.empty_like(x)
-    mean = torch.empty(rows, dtype=torch.float32, device=dev)
-    rstd = torch.empty(rows, dtype=torch.float32, device=dev)
-    ncols = (2 if w.kind == "ln" else 1) * D
-    partials = torch.empty(abi.workspace_bytes(abi.WS_NORM_BWD, rows, D, code) // 4, dtype=torch.float32, device=dev)
-    grads2 = [torch.empty(ncols, dtype=torch.float32, device=dev) for _ in range(2)]
-    grads = grads2[0]
-    L = abi.lib()
-    import ctypes
-    nparts = ctypes.c_int64(0)
-    P = lambda t: None if t is None else ctypes.c_void_p(t.data_ptr())  # noqa: E731
-    px, pdy, pg, pb, py, pdx, pm, pr, pp = map(P, (x, dy, gamma, beta, y, dx, mean, rstd, partials))
-    pgr2 = [P(t) for t in grads2]
-    stream = torch.cuda.current_stream()
-    st = ctypes.c_void_p(stream.cuda_stream)
-
-    def fwd():
-        if w.kind == "ln":
-            abi.check(L.nb2_layernorm_fwd(px, pg, pb, py, pm, pr, rows, D, w.eps, code, w.act, st))
-        else:
-            abi.check(L.nb2_rmsnorm_fwd(px, pg, py, pr, rows, D, w.eps, code, w.act, st))
-
-    def bwd():
-        if w.kind == "ln":
-            abi.check(L.nb2_layernorm_bwd(px, pdy, pg, pb, pm, pr, pdx, pp, ctypes.byref(nparts), rows, D, code, w.act, st))
-        else:
-            abi.check(L.nb2_rmsnorm_bwd(px, pdy, pg, pr, pdx, pp, ctypes.byref(nparts), rows, D, code, w.act, st))
-
-    # For N > 1 the [2, D] allreduce of step k runs on its own stream and overlaps the forward of
-    # step k+1 (nothing reads the reduced gradients before the optimizer would); the gradient
-    # buffer is double-buffered and a buffer is rewritten only after its previous allreduce ended.
-    comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
-    ready = [torch.cuda.Event() for _ in range(2)]
-    done = [None, None]
-    counter = [0]
-
-    def reduce_grads():
-        i = counter[0] % 2
-        if done[i] is not None:
-            stream.wait_event(done[i])
-        abi.check(L.nb2_colreduce_partials(pp, nparts.value, ncols, pgr2[i], st))
-
-    def exchange():
-        i = counter[0] % 2
-        counter[0] += 1
-        if world == 1:
-            return
-        ready[i].record(stream)
-        comm_stream.wait_event(ready[i])
-        with torch.cuda.stream(comm_stream):
-            allreduce_param_grads(grads2[i])
-            ev = torch.cuda.Event()
-            ev.record(comm_stream)
-        done[i] = ev
-
-    def step():
-        fwd()
-        bwd()
-        reduce_grads()
-        exchange()
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(args.warmup):
-        step()
-    barrier()
-
-    # ---- timed region: exactly K steps, device time, max over ranks
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    clocks = ClockSampler(local)
-    with clocks:
-        e0.record(stream)
-        for _ in range(args.steps):
-            step()
-        if comm_stream is not None:
-            stream.wait_stream(comm_stream)  # the last allreduces are inside the timed region
-        e1.record(stream)
-        clocks.sample()                      # the queue is still draining here
-        torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
-    barrier()
-    if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    sec_per_step = ms / 1e3 / args.steps
+    runner = StepRunner(w, comm, dev, seed=1234 + rank)
+    sec_per_step = timed_steps(runner, args.steps, args.warmup, world, dev, clocks)
+    clocks.stop()
     value = w.step_bytes() * world / sec_per_step / 1e9
 
     # ---- per-kernel durations inside the same step sequence (CUDA events around each launch)
-    n_prof = min(args.steps, 200)
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(n_prof)]
-    for i in range(n_prof):
-        ev[i][0].record(stream); fwd()
-        ev[i][1].record(stream); bwd()
-        ev[i][2].record(stream); reduce_grads()
-        ev[i][3].record(stream)
-        exchange()
-    torch.cuda.synchronize()
-    t_fwd = float(np.mean([ev[i][0].elapsed_time(ev[i][1]) for i in range(n_prof)])) / 1e3
-    t_bwd = float(np.mean([ev[i][1].elapsed_time(ev[i][2]) for i in range(n_prof)])) / 1e3
-    t_red = float(np.mean([ev[i][2].elapsed_time(ev[i][3]) for i in range(n_prof)])) / 1e3
-
-    peaks_file = ROOT / "MEASURED_PEAKS.json"
-    if peaks_file.exists():
-        peak, peak_src = float(json.loads(peaks_file.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
-    else:
-        peak, peak_src = FALLBACK_HBM_GBS, "fallback"
+    t_fwd, t_bwd, t_red = kernel_times(runner, min(args.steps, 50))
+    peak, peak_src = _peak()
     traffic = None
     tf = ROOT / "profiles" / "traffic.json"
     if tf.exists():
-        traffic = json.loads(tf.read_text()).get(f"{w.kind}_bwd:{args.workload}")
+        traffic = json.loads(tf.read_text()).get(f"{w.kind}_bwd:{w.spec}")
     bwd_gbs = w.bwd_bytes() / t_bwd / 1e9
     fwd_gbs = w.fwd_bytes() / t_fwd / 1e9
-    roofline = {"bound": "hbm", "kernel": "norm_bwd_kernel (dX + dgamma/dbeta partials)", "achieved": bwd_gbs,
+    roofline = {"bound": "hbm", "kernel": "norm_bwd_tma_kernel (dX + dgamma/dbeta partials)", "achieved": bwd_gbs,
                 "peak": peak, "unit": "GB/s", "frac": bwd_gbs / peak, "traffic": traffic, "peak_source": peak_src,
-                "frac_of_nominal_8000": bwd_gbs / 8000.0}
+                "frac_of_nominal_8000": bwd_gbs / 8000.0,
+                "algorithmic_bytes_per_launch": w.bwd_bytes(), "launch_us": t_bwd * 1e6}
     kernels = {
         "norm_fwd_kernel": {"ms": t_fwd * 1e3, "achieved_gbs": fwd_gbs, "frac": fwd_gbs / peak, "frac_of_nominal_8000": fwd_gbs / 8000.0},
         "norm_bwd_kernel": {"ms": t_bwd * 1e3, "achieved_gbs": bwd_gbs, "frac": bwd_gbs / peak, "frac_of_nominal_8000": bwd_gbs / 8000.0},
         "colreduce_kernel": {"ms": t_red * 1e3},
     }
 
-    # ---- end to end through the host-buffer C-ABI call (pinned host memory, copies timed)
+    comparator = None
+    if not args.no_comparator:
+        try:
+            comparator = gpu_comparator(w, runner, args.steps)
+            if comparator is not None:
+                comparator["ours_ms_per_step_same_rows"] = sec_per_step * 1e3 * comparator["rows"] / max(runner.rows, 1)
+                comparator["speedup"] = (value / world) / comparator["value"]
+        except Exception as exc:
+            comparator = {"error": str(exc)}
+
     e2e = None
     if not args.no_e2e:
-        e2e_rows = min(rows, 1 << 16)       # bounded so pinned host buffers stay modest on wide rows
-        hs = abi.HostStep(e2e_rows, D, w.dtype) if w.kind == "ln" else None
-        if hs is not None:
-            hx = x[:e2e_rows].cpu().pin_memory(); hdy = dy[:e2e_rows].cpu().pin_memory()
-            hg, hb = gamma.cpu(), beta.cpu()
-            hy = torch.empty_like(hx).pin_memory(); hdx = torch.empty_like(hx).pin_memory()
-            hgr = torch.empty(2, D, dtype=torch.float32).pin_memory()
-            n_e2e = max(3, min(args.steps, 30))
-            for _ in range(3):
-                hs.step(hx, hdy, hg, hb, hy, hdx, hgr, w.eps, w.act)
-            barrier()
-            t0 = time.perf_counter()
-            for _ in range(n_e2e):
-                hs.step(hx, hdy, hg, hb, hy, hdx, hgr, w.eps, w.act)
-            torch.cuda.synchronize()
-            dt = (time.perf_counter() - t0) / n_e2e
-            if world > 1:
-                t = torch.tensor([dt], device=dev, dtype=torch.float64)
-                dist.all_reduce(t, op=dist.ReduceOp.MAX)
-                dt = float(t.item())
-            hs.close()
-            act_bytes = e2e_rows * D * w.elt
-            e2e = {"value": w.step_bytes(e2e_rows) * world / dt / 1e9, "unit": UNIT,
-                   "h2d_bytes_per_step": 2 * act_bytes + 2 * D * w.elt, "d2h_bytes_per_step": 2 * act_bytes + 2 * D * 4,
-                   "ms_per_step": dt * 1e3, "rows_per_step": e2e_rows, "steps": n_e2e,
-                   "call": "nb2_layernorm_act_step_host (x, dY in; y, dX, dgamma|dbeta out)"}
+        e2e = e2e_run(w, runner, args.steps, world, dev)
+
+    # ---- x[32,1024,1024] per GPU as a sub-record: a 0.12 ms step, where fixed per-step costs show
+    cfg2 = None
+    if not args.no_cfg2 and w.spec != "cfg2":
+        w2 = Workload("cfg2", world)
+        r2 = StepRunner(w2, comm, dev, seed=4321 + rank)
+        s2 = timed_steps(r2, max(args.steps, 200), max(args.warmup, 10), world, dev)
+        f2, b2, c2 = kernel_times(r2, 50)
+        cfg2 = {"workload": w2.name, "scaling": "weak", "ms_per_step": s2 * 1e3, "value": w2.step_bytes() * world / s2 / 1e9, "unit": UNIT,
+                "rows_per_s": w2.rows_per_rank * world / s2, "steps": max(args.steps, 200),
+                "fwd": {"ms": f2 * 1e3, "frac": w2.fwd_bytes() / f2 / 1e9 / peak, "frac_of_nominal_8000": w2.fwd_bytes() / f2 / 8e12},
+                "bwd": {"ms": b2 * 1e3, "frac": w2.bwd_bytes() / b2 / 1e9 / peak, "frac_of_nominal_8000": w2.bwd_bytes() / b2 / 8e12},
+                "colreduce_ms": c2 * 1e3}
+        if not args.no_comparator:
+            try:
+                cmp2 = gpu_comparator(w2, r2, 10)
+                cfg2["gpu_comparator"] = {"ms_per_step": cmp2["ms_per_step"], "speedup": (cfg2["value"] / world) / cmp2["value"]}
+            except Exception as exc:
+                cfg2["gpu_comparator"] = {"error": str(exc)}
+        r2.close()
+        del r2
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -675,21 +858,35 @@ def main():
         except Exception as exc:      # a missing oracle must not hide the GPU numbers
             cpu = {"error": str(exc)}
 
+    status = abi.device_status()
+    launches_per_step = 3 + (1 if (world > 1 and mode == abi.EXCHANGE_PEER) else 0)
     if rank == 0:
+        if world == 1:
+            exchange = "none"
+        elif mode == abi.EXCHANGE_NCCL:
+            exchange = ("ncclAllReduce of [%d] fp32 per step, issued by the C step driver on the communicator's side stream; "
+                        "it overlaps the next step's forward" % runner.ncols)
+        else:
+            exchange = ("peer-store exchange of [%d] fp32 per step: the partial-reduce kernel stores this rank's sums into every "
+                        "peer's buffer over NVLink; a collect kernel after the next forward adds them in rank order" % runner.ncols)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": sec_per_step * 1e3, "higher_is_better": True,
             "scaling": w.scaling, "vs_baseline": None,
             "dtype": "f32" if w.dtype == torch.float32 else "bf16", "data": "synthetic",
-            "config": {"workload": w.name, "rows_per_gpu": rows, "D": D, "global_rows": rows * world,
-                       "l2": "inputs larger than L2 (each step streams %.0f MB per GPU)" % (w.step_bytes() / 1e6),
-                       "collective": ("NCCL allreduce of [%d] fp32 per step on a side stream, overlapping the next forward; %d SMs left to it" % (ncols, reserve)) if world > 1 else "none"},
-            "rows_per_s": rows * world / sec_per_step,
+            "config": config_of(w, world),
+            "exchange": exchange, "reserved_sms": max(args.reserve_sms, 0),
+            "rows_per_s": w.rows_per_rank * world / sec_per_step,
+            "frac_of_measured_per_gpu": value / world / peak,
             "frac_of_nominal_8000_per_gpu": value / world / 8000.0,
-            "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu, "e2e": e2e,
-            "clocks": clocks.summary(), "gpu_launches": 3 * args.steps,
+            "roofline": roofline, "kernels": kernels, "gpu_comparator": comparator, "cpu_baseline": cpu, "e2e": e2e,
+            "cfg2": cfg2, "device_status": status,
+            "clocks": clocks.summary(), "gpu_launches": launches_per_step * args.steps,
         }
         _emit(line)
+    runner.close()
+    if comm is not None:
+        comm.close()
     if world > 1:
         dist.destroy_process_group()
 

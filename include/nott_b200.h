@@ -60,7 +60,9 @@ enum {
     NB2_ERR_DTYPE = -3,       /* unknown dtype / act / index type         */
     NB2_ERR_ALIGN = -4,       /* pointer or stride alignment              */
     NB2_ERR_WORKSPACE = -5,   /* workspace too small                      */
-    NB2_ERR_DEVICE = -6       /* device-side status word reported a fault */
+    NB2_ERR_DEVICE = -6,      /* device-side status word reported a fault */
+    NB2_ERR_COMM = -7,        /* the gradient exchange failed or its communicator was aborted */
+    NB2_ERR_COMM_TIMEOUT = -8 /* the gradient exchange did not finish before the deadline */
 };
 
 /* which operation a workspace query is for */
@@ -390,6 +392,109 @@ int nb2_layernorm_act_step_host(nb2_host_ctx* ctx,
                                 const void* gamma_host, const void* beta_host,
                                 void* y_host, void* dx_host, float* dgamma_dbeta_host,
                                 int64_t rows, int64_t D, double eps, int dtype, int act);
+/* The same step for RMSNorm (src/block/details/transformers/mamba.hpp:124-142) with its
+ * activation: weight_host [D] in, dweight_host [D] fp32 out; same context type. */
+int nb2_rmsnorm_act_step_host(nb2_host_ctx* ctx,
+                              const void* x_host, const void* dy_host, const void* weight_host,
+                              void* y_host, void* dx_host, float* dweight_host,
+                              int64_t rows, int64_t D, double eps, int dtype, int act);
+
+/* ------------------------------------------------------------------ *
+ * Row-sharded step across the GPUs of one box, one process per GPU.
+ * The reference runs on one device (src/core.hpp:1706-1708 pins cuda:0); with
+ * rows (batch x sequence) split over ranks the forward and dX need no
+ * communication and the only exchange is the sum over ranks of the fp32
+ * parameter gradients ([2, D] LayerNorm, [D] RMSNorm), which nothing reads
+ * before the optimizer step (src/core.hpp:3811-3820).
+ *
+ * nb2_comm: one communicator per process.  Rank 0 makes an id
+ * (nb2_comm_unique_id, NB2_COMM_ID_BYTES bytes) and hands it to the other
+ * ranks by any host-side channel; every rank then calls nb2_comm_create with
+ * its device current.  `exchange` selects how gradients travel:
+ *   NB2_EXCHANGE_NCCL : ncclAllReduce (fp32 sum, in place) on a side stream the
+ *                       communicator owns, after the partial reduce.
+ *   NB2_EXCHANGE_PEER : the partial-reduce kernel stores the rank's sums
+ *                       straight into every peer's receive buffer over NVLink
+ *                       (memory mapped with CUDA IPC) and a small second kernel
+ *                       adds the ranks' slots in rank order; NCCL is used at
+ *                       creation only (to pass the IPC handles around).
+ * max_cols bounds the gradient vector length (2 * D for LayerNorm).
+ * Creating and destroying a communicator or a step allocate and free device
+ * memory and synchronise; nothing else here does.  With world == 1 no NCCL is
+ * needed and `id_host` may be NULL.
+ * ------------------------------------------------------------------ */
+#define NB2_COMM_ID_BYTES 128
+enum { NB2_EXCHANGE_NCCL = 0, NB2_EXCHANGE_PEER = 1 };
+enum { NB2_NORM_LAYER = 0, NB2_NORM_RMS = 1 };
+typedef struct nb2_comm nb2_comm;
+int nb2_comm_unique_id(void* id_host);
+int nb2_comm_create(nb2_comm** comm, const void* id_host, int rank, int world, int exchange, int64_t max_cols);
+int nb2_comm_destroy(nb2_comm* comm);
+int nb2_comm_info(const nb2_comm* comm, int* rank, int* world, int* exchange);
+
+/*
+ * Partial reduce + exchange as one stream-ordered unit, in two halves so that
+ * the exchange can run beside other work of the stream:
+ *   begin : sums the per-CTA partials (as nb2_colreduce_partials does: fp64,
+ *           fixed order) and starts the sum over ranks.  `grads` ([ncols] fp32)
+ *           must not be read or written by the caller until `end`.
+ *   end   : makes `stream` wait for the exchange; afterwards (in stream order)
+ *           `grads` holds the sum over all ranks, bit-identical on every rank
+ *           in the PEER form.  A no-op when nothing is outstanding.
+ * One exchange may be outstanding per communicator.  comm == NULL, or a
+ * one-rank NCCL communicator, makes begin the plain partial reduce.
+ */
+int nb2_grad_exchange_begin(nb2_comm* comm, const float* partials, int64_t n_partials, int64_t ncols,
+                            float* grads, void* stream);
+int nb2_grad_exchange_end(nb2_comm* comm, void* stream);
+
+/*
+ * Host-side watchdog for the exchange started last (a rank that died or never
+ * joined leaves the collective waiting).  Polls the
+ * exchange's completion and the communicator's asynchronous error state for at
+ * most timeout_s seconds.  On an asynchronous error returns NB2_ERR_COMM, on
+ * expiry NB2_ERR_COMM_TIMEOUT; in both cases the communicator has been aborted
+ * (ncclCommAbort, which makes a collective kernel that is still waiting leave
+ * the GPU) and every later call on it returns NB2_ERR_COMM.  nb2_comm_abort does
+ * the same on request (a rank that learned of a peer's death on the host).
+ */
+int nb2_comm_wait(nb2_comm* comm, double timeout_s);
+int nb2_comm_abort(nb2_comm* comm);
+
+/*
+ * Self-tests without a counterpart in the reference.
+ * nb2_selftest_comm_watchdog runs the watchdog's policy against scripted
+ * callbacks (needs no GPU and no second rank): completion is reported after
+ * `polls_until_done` polls (< 0: never), an asynchronous error `error_code`
+ * after `polls_until_error` polls (< 0: never); returns what nb2_comm_wait would
+ * and stores the number of aborts in *aborts_host.
+ * nb2_selftest_peer_wait launches the PEER form's device-side wait on a flag no
+ * rank will publish, with a limit of cycle_limit SM cycles (<= 2e9): the kernel
+ * returns by itself and nb2_device_status() then reports code 4.
+ */
+int nb2_selftest_comm_watchdog(int polls_until_done, int polls_until_error, int error_code, double timeout_s,
+                               int* aborts_host);
+int nb2_selftest_peer_wait(nb2_comm* comm, int64_t cycle_limit, void* stream);
+
+/*
+ * One training step of the fused norm->activation path on this rank's row
+ * shard: forward, backward (dX + partials), partial reduce and the exchange.
+ * This is the loop body `layer.forward(x)` -> `apply(activation)` ->
+ * `loss.backward()` of src/core.hpp:1927-1934,3811-3820 for one norm layer.
+ *   run    : enqueues forward(k), end of exchange(k-1), backward(k),
+ *            begin of exchange(k) on `stream`; so exchange k-1 had the whole
+ *            forward of step k to finish in.  `grads` of step k is complete
+ *            after the next run (or finish) in stream order; alternate two
+ *            buffers to keep the previous step's gradients readable.
+ *   finish : ends the outstanding exchange.
+ * The step owns mean/rstd/partials scratch for `rows` x `D`.
+ */
+typedef struct nb2_step nb2_step;
+int nb2_step_create(nb2_step** step, nb2_comm* comm, int norm, int64_t rows, int64_t D, int dtype, int act, double eps);
+int nb2_step_destroy(nb2_step* step);
+int nb2_step_run(nb2_step* step, const void* x, const void* dy, const void* gamma, const void* beta,
+                 void* y, void* dx, float* grads, void* stream);
+int nb2_step_finish(nb2_step* step, void* stream);
 
 #if defined(__GNUC__)
 #pragma GCC visibility pop

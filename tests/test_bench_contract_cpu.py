@@ -21,7 +21,15 @@ def bench():
     return mod
 
 
-def test_headline_workload_is_the_fp32_layernorm_gelu_case(bench):
+def test_default_workload_is_the_sweep_point_in_the_target_range(bench):
+    w = bench.Workload(bench.DEFAULT_WORKLOAD, 8)
+    assert (w.kind, w.dtype, w.D, w.rows_per_rank, w.scaling) == ("ln", torch.float32, 2048, (1 << 20) // 8, "strong")
+    one = bench.Workload(bench.DEFAULT_WORKLOAD, 1)
+    assert bench.config_of(one, 1)["global_rows"] == bench.config_of(w, 8)["global_rows"] == 1 << 20
+    assert set(bench.config_of(one, 1)) == {"workload", "workload_spec", "rows_per_gpu", "D", "global_rows", "l2"}
+
+
+def test_cfg2_workload_is_the_fp32_layernorm_gelu_case(bench):
     w = bench.Workload("cfg2", 8)
     assert (w.kind, w.dtype, w.D, w.rows_per_rank, w.scaling) == ("ln", torch.float32, 1024, 32768, "weak")
     n, d = 32768, 1024

@@ -88,3 +88,28 @@ def test_fused_equals_composed_bitwise_in_fp32():
     s, y, mean, rstd = abi.add_norm_fwd("ln", a, b, gamma, beta, 1e-5)
     y2, mean2, rstd2 = abi.layernorm_fwd(a + b, gamma, beta, 1e-5)
     assert torch.equal(s, a + b) and torch.equal(y, y2) and torch.equal(rstd, rstd2)
+
+
+@pytest.mark.parametrize("kind", ["ln", "rms"])
+def test_residual_offset_by_one_element_takes_the_composed_path(kind):
+    """A residual (and a residual gradient) that is only 4-byte aligned cannot feed the 16-byte bulk copies of
+    the fused kernels: the call must run add + norm instead, with the same results, and must not fault."""
+    rows, D = 300, 1024
+    eps = 1e-5 if kind == "ln" else 1e-6
+    a, an = make((rows, D), 21, torch.float32)
+    base, basen = make((rows * D + 1,), 22, torch.float32)
+    b = base[1:].view(rows, D); bn = basen[1:].reshape(rows, D)
+    dbase, dbasen = make((rows * D + 1,), 23, torch.float32)
+    dsum = dbase[1:].view(rows, D); dsn = dbasen[1:].reshape(rows, D)
+    assert b.data_ptr() % 16 != 0 and dsum.data_ptr() % 16 != 0
+    dy, dyn = make((rows, D), 24, torch.float32)
+    gamma, gn = make((D,), 25, torch.float32, 0.02, 1.0)
+    beta, ben = make((D,), 26, torch.float32, 0.02) if kind == "ln" else (None, None)
+    s, y, dx, grads = run(kind, a, b, gamma, beta, dy, dsum, eps)
+    ref = O.add_norm(kind, an, bn, gn, ben, dyn, dsn, eps)
+    assert np.array_equal(s.cpu().numpy(), ref["sum"])
+    check(y, ref["y"], "y"); check(dx, ref["dx"], "dx")
+    # and the same bits as the aligned call
+    s2, y2, dx2, grads2 = run(kind, a, b.clone(), gamma, beta, dy, dsum.clone(), eps)
+    assert torch.equal(y, y2) and torch.equal(dx, dx2)
+    assert abi.device_status() == 0

@@ -244,3 +244,34 @@ def test_reserved_sms_change_the_grid_not_the_results():
     tol.long_sum_close(held["dgamma"].cpu().numpy(), ref["dgamma"], rows)
     tol.long_sum_close(held["dbeta"].cpu().numpy(), ref["dbeta"], rows)
     assert abi.device_status() == 0
+
+
+def test_reserved_sms_also_shrink_the_register_row_grids():
+    """RMSNorm fp32 with rows under 16 KiB takes the register-row kernels in both directions; they honour the
+    reservation as the ring kernels do (fewer CTAs, so fewer partials), with unchanged y and dX."""
+    rows, D = 20000, 1024
+    x, xn = make((rows, D), 1, torch.float32); dy, dyn = make((rows, D), 2, torch.float32)
+    w, wn = make((D,), 3, torch.float32, 0.02, 1.0)
+    L = abi.lib()
+    code = abi.dtype_code(torch.float32)
+
+    def bwd_partials():
+        y, rstd = abi.rmsnorm_fwd(x, w, 1e-6, abi.ACT_SILU)
+        dx = torch.empty_like(x)
+        parts = torch.empty(abi.workspace_bytes(abi.WS_NORM_BWD, rows, D, code) // 4, device="cuda")
+        import ctypes
+        n = ctypes.c_int64(0)
+        abi.check(L.nb2_rmsnorm_bwd(x.data_ptr(), dy.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx.data_ptr(), parts.data_ptr(),
+                                    ctypes.byref(n), rows, D, code, abi.ACT_SILU, None))
+        torch.cuda.synchronize()
+        return y, dx, n.value
+
+    y0, dx0, n0 = bwd_partials()
+    before = L.nb2_reserve_sms(16)
+    try:
+        y1, dx1, n1 = bwd_partials()
+    finally:
+        L.nb2_reserve_sms(before)
+    sms = L.nb2_sm_count()
+    assert n0 == 2 * sms and n1 == 2 * (sms - 16), (n0, n1, sms)
+    assert torch.equal(y0, y1) and torch.equal(dx0, dx1)

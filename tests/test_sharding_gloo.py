@@ -12,7 +12,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from thot_b200.sharding import allreduce_param_grads, row_shard
+from thot_b200.sharding import ExchangeError, allreduce_param_grads, check_layout, row_shard
 
 
 def test_row_shard_partitions_exactly():
@@ -77,3 +77,77 @@ def test_two_rank_gloo_allreduce_matches_unsharded(tmp_path, rows):
     world, port = 2, _free_port()
     mp.spawn(_worker, args=(world, port, rows, 48, str(tmp_path)), nprocs=world, join=True)
     assert all((tmp_path / f"ok{r}").exists() for r in range(world))
+
+
+# ---- failures made on the host: a rank with another D, a rank that never joins the exchange
+def _mismatch_worker(rank, world, port, result_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        D = 48 if rank == 0 else 64                      # rank 1 was configured with another width
+        try:
+            check_layout(2 * D, "ln", 0, timeout_s=20.0)
+        except ExchangeError as exc:
+            assert "disagree" in str(exc)
+            with open(os.path.join(result_dir, f"raised{rank}"), "w") as f:
+                f.write(str(exc))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_rank_with_another_width_is_an_error_not_a_hang(tmp_path):
+    world, port = 2, _free_port()
+    mp.spawn(_mismatch_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    assert all((tmp_path / f"raised{r}").exists() for r in range(world))
+
+
+def _skip_worker(rank, world, port, result_dir):
+    import time
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.ones(16, dtype=torch.float32)
+        allreduce_param_grads(g, timeout_s=20.0)          # step 0: everybody joins
+        assert torch.equal(g, torch.full((16,), float(world)))
+        if rank == 1:
+            time.sleep(3.0)                               # step 1: this rank leaves between steps and never joins
+        else:
+            t0 = time.perf_counter()
+            try:
+                allreduce_param_grads(torch.ones(16, dtype=torch.float32), timeout_s=1.0)
+            except ExchangeError as exc:
+                waited = time.perf_counter() - t0
+                with open(os.path.join(result_dir, "raised0"), "w") as f:
+                    f.write(f"{waited:.2f} {exc}")
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def test_rank_that_skips_the_exchange_times_the_others_out(tmp_path):
+    world, port = 2, _free_port()
+    mp.spawn(_skip_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    text = (tmp_path / "raised0").read_text()
+    assert float(text.split()[0]) < 2.5, text          # raised at the 1 s deadline, not when the peer left
+
+
+def test_watchdog_policy_without_a_gpu():
+    """nb2_comm_wait's policy against scripted callbacks: completion, an asynchronous error of the
+    communicator (abort + NB2_ERR_COMM) and a deadline that passes (abort + NB2_ERR_COMM_TIMEOUT)."""
+    import ctypes
+    import time
+    from thot_b200 import abi
+    L = abi.lib()
+    aborts = ctypes.c_int(-1)
+    assert L.nb2_selftest_comm_watchdog(5, -1, 0, 1.0, ctypes.byref(aborts)) == 0 and aborts.value == 0
+    assert L.nb2_selftest_comm_watchdog(-1, 3, 5, 1.0, ctypes.byref(aborts)) == abi.ERR_COMM and aborts.value == 1
+    assert b"asynchronous error 5" in L.nb2_last_error_string()
+    t0 = time.perf_counter()
+    assert L.nb2_selftest_comm_watchdog(-1, -1, 0, 0.2, ctypes.byref(aborts)) == abi.ERR_COMM_TIMEOUT and aborts.value == 1
+    assert 0.15 < time.perf_counter() - t0 < 1.0
+    # completion that arrives before a later error wins
+    assert L.nb2_selftest_comm_watchdog(2, 10, 5, 1.0, ctypes.byref(aborts)) == 0 and aborts.value == 0

@@ -34,6 +34,18 @@ def _nvcc() -> str:
     raise RuntimeError("nvcc not found: libnott_b200.so cannot be built (there is no CPU fallback)")
 
 
+def _nccl_include() -> list[str]:
+    """The NCCL header (types and enums only; the functions are resolved with dlopen at run time)."""
+    try:
+        import nvidia.nccl as pkg
+        inc = Path(list(pkg.__path__)[0]) / "include"
+        if (inc / "nccl.h").exists():
+            return ["-I", str(inc)]
+    except Exception:
+        pass
+    return []
+
+
 def _sources() -> list[Path]:
     return sorted(CSRC.glob("*.cu"))
 
@@ -59,7 +71,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
     def compile_one(src: Path) -> Path:
         obj = OBJ_DIR / (src.stem + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+        cmd = [nvcc, *NVCC_FLAGS, *_nccl_include(), "-c", str(src), "-o", str(obj)]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         res = subprocess.run(cmd, capture_output=True, text=True)
@@ -71,7 +83,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
         objs = list(pool.map(compile_one, _sources()))
-    link = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB_PATH), *map(str, objs)]
+    link = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB_PATH), *map(str, objs), "-ldl"]
     res = subprocess.run(link, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")

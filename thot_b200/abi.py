@@ -17,6 +17,10 @@ F32, BF16 = 0, 1
 ACT_NONE, ACT_GELU, ACT_SILU = 0, 1, 2
 I32, I64 = 0, 1
 WS_NORM_BWD, WS_EMBEDDING_BWD, WS_ROPE_TABLE, WS_BERT_EMBEDDING_BWD = 0, 1, 2, 3
+EXCHANGE_NCCL, EXCHANGE_PEER = 0, 1
+NORM_LAYER, NORM_RMS = 0, 1
+COMM_ID_BYTES = 128
+ERR_COMM, ERR_COMM_TIMEOUT = -7, -8
 
 LIB_PATH = Path(__file__).resolve().parent / "libnott_b200.so"
 
@@ -59,6 +63,21 @@ _SIGNATURES = {
     "nb2_host_ctx_create": (c_int, [POINTER(c_void_p), c_int64, c_int64, c_int, c_int64]),
     "nb2_host_ctx_destroy": (c_int, [c_void_p]),
     "nb2_layernorm_act_step_host": (c_int, [c_void_p] * 8 + [c_int64, c_int64, c_double, c_int, c_int]),
+    "nb2_rmsnorm_act_step_host": (c_int, [c_void_p] * 7 + [c_int64, c_int64, c_double, c_int, c_int]),
+    "nb2_comm_unique_id": (c_int, [c_void_p]),
+    "nb2_comm_create": (c_int, [POINTER(c_void_p), c_void_p, c_int, c_int, c_int, c_int64]),
+    "nb2_comm_destroy": (c_int, [c_void_p]),
+    "nb2_comm_info": (c_int, [c_void_p, POINTER(c_int), POINTER(c_int), POINTER(c_int)]),
+    "nb2_grad_exchange_begin": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
+    "nb2_grad_exchange_end": (c_int, [c_void_p, c_void_p]),
+    "nb2_comm_wait": (c_int, [c_void_p, c_double]),
+    "nb2_comm_abort": (c_int, [c_void_p]),
+    "nb2_selftest_comm_watchdog": (c_int, [c_int, c_int, c_int, c_double, POINTER(c_int)]),
+    "nb2_selftest_peer_wait": (c_int, [c_void_p, c_int64, c_void_p]),
+    "nb2_step_create": (c_int, [POINTER(c_void_p), c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_double]),
+    "nb2_step_destroy": (c_int, [c_void_p]),
+    "nb2_step_run": (c_int, [c_void_p] * 8 + [c_void_p]),
+    "nb2_step_finish": (c_int, [c_void_p, c_void_p]),
 }
 
 _lib = None
@@ -421,10 +440,98 @@ class HostStep:
         check(lib().nb2_layernorm_act_step_host(self._ctx, _p(x), _p(dy), _p(gamma), _p(beta), _p(y), _p(dx),
                                                 _p(dgamma_dbeta), rows, self.D, eps, dtype_code(self.dtype), act))
 
+    def step_rms(self, x, dy, weight, y, dx, dweight, eps: float, act: int):
+        for t in (x, dy, weight, y, dx, dweight):
+            if t.is_cuda:
+                raise ValueError("HostStep takes host tensors")
+        rows = x.shape[0]
+        check(lib().nb2_rmsnorm_act_step_host(self._ctx, _p(x), _p(dy), _p(weight), _p(y), _p(dx), _p(dweight), rows, self.D, eps,
+                                              dtype_code(self.dtype), act))
+
     def close(self):
         if self._ctx:
             lib().nb2_host_ctx_destroy(self._ctx)
             self._ctx = c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+# ------------------------------------------------------- row-sharded step
+def comm_unique_id() -> bytes:
+    """Rank 0 makes the id; the other ranks receive it over any host-side channel."""
+    buf = ctypes.create_string_buffer(COMM_ID_BYTES)
+    check(lib().nb2_comm_unique_id(buf))
+    return buf.raw
+
+
+class Comm:
+    """One communicator per process (device = torch's current device)."""
+
+    def __init__(self, unique_id, rank: int, world: int, exchange: int = EXCHANGE_NCCL, max_cols: int = 2 * 8192):
+        self._h = c_void_p()
+        self.rank, self.world, self.exchange = rank, world, exchange
+        idbuf = ctypes.create_string_buffer(bytes(unique_id), COMM_ID_BYTES) if unique_id is not None else None
+        check(lib().nb2_comm_create(ctypes.byref(self._h), idbuf, rank, world, exchange, max_cols))
+
+    @property
+    def handle(self):
+        return self._h
+
+    def exchange_begin(self, partials, n_partials: int, grads):
+        check(lib().nb2_grad_exchange_begin(self._h, _p(partials), n_partials, grads.numel(), _p(grads), _stream()))
+
+    def exchange_end(self):
+        check(lib().nb2_grad_exchange_end(self._h, _stream()))
+
+    def allreduce_(self, grads):
+        """In-place sum over ranks of one fp32 vector (a single "partial")."""
+        src = grads.clone()
+        self.exchange_begin(src, 1, grads)
+        self.exchange_end()
+        return grads
+
+    def wait(self, timeout_s: float):
+        check(lib().nb2_comm_wait(self._h, float(timeout_s)))
+
+    def abort(self):
+        check(lib().nb2_comm_abort(self._h))
+
+    def close(self):
+        if self._h:
+            lib().nb2_comm_destroy(self._h)
+            self._h = c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class NormStep:
+    """forward + backward + partial reduce + exchange of one norm layer on this rank's rows."""
+
+    def __init__(self, comm, kind: str, rows: int, D: int, dtype: torch.dtype, act: int, eps: float):
+        self._h = c_void_p()
+        self._comm = comm          # keeps the communicator alive
+        self.kind, self.rows, self.D = kind, rows, D
+        check(lib().nb2_step_create(ctypes.byref(self._h), comm.handle if comm is not None else None,
+                                    NORM_LAYER if kind == "ln" else NORM_RMS, rows, D, dtype_code(dtype), act, eps))
+
+    def run(self, x, dy, gamma, beta, y, dx, grads):
+        check(lib().nb2_step_run(self._h, _p(x), _p(dy), _p(gamma), _p(beta), _p(y), _p(dx), _p(grads), _stream()))
+
+    def finish(self):
+        check(lib().nb2_step_finish(self._h, _stream()))
+
+    def close(self):
+        if self._h:
+            lib().nb2_step_destroy(self._h)
+            self._h = c_void_p()
 
     def __del__(self):
         try:

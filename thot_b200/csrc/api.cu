@@ -186,7 +186,7 @@ int nb2_device_status(unsigned int* status_host, int clear) {
     if (clear && *status_host != 0) rc = cuda_status(cudaMemset(p, 0, sizeof(unsigned int)), "device status clear");
     if (rc != 0) return rc;
     if (*status_host != 0) {
-        set_error("a kernel gave up waiting: code %u in CTA %u (1 = a requested row never arrived in shared memory, 3 = the bounded-wait self-test)",
+        set_error("a kernel gave up waiting: code %u in CTA %u (1 = a requested row never arrived in shared memory, 3 = the bounded-wait self-test, 4 = a peer rank's gradient slot never arrived)",
                   *status_host >> 16, *status_host & 0xffffu);
         return NB2_ERR_DEVICE;
     }

@@ -130,9 +130,9 @@ embedding_fwd_bulk_kernel(const uint8_t* __restrict__ table, const void* __restr
                     bulk_s2g(out + t * (int64_t)row_bytes, ring + (size_t)s * row_bytes, row_bytes);
                     bulk_commit();
                     bulk_wait_read_all();                // the slot may be overwritten once the copy out has read it
+                    parity ^= 1u << s;                   // only a completed phase flips: the drain below waits on a timed-out slot's own phase
                 }
             }
-            parity ^= 1u << s;
         } else {
             if (lane == 0 && status != nullptr) { status[0] = 1; status[1] = t; }
             for (uint32_t off = lane * 16; off < row_bytes; off += 32 * 16)

@@ -112,20 +112,22 @@ extern "C" int nb2_host_ctx_destroy(nb2_host_ctx* ctx) {
         if (rc_ != 0) { cudaDeviceSynchronize(); return rc_; }        \
     } while (0)
 
-extern "C" int nb2_layernorm_act_step_host(nb2_host_ctx* c, const void* x_host, const void* dy_host,
-                                           const void* gamma_host, const void* beta_host, void* y_host,
-                                           void* dx_host, float* dgamma_dbeta_host, int64_t rows, int64_t D,
-                                           double eps, int dtype, int act) {
+// One host-buffer step for either norm.  LayerNorm: gamma, beta in, [2, D] gradients out; RMSNorm:
+// weight in (beta_host unused), [D] gradient out.
+static int norm_act_step_host(nb2_host_ctx* c, bool rms, const void* x_host, const void* dy_host,
+                              const void* gamma_host, const void* beta_host, void* y_host, void* dx_host,
+                              float* grads_host, int64_t rows, int64_t D, double eps, int dtype, int act) {
     NB2_REQUIRE(c != nullptr, NB2_ERR_NULL, "host step: NULL context");
     NB2_REQUIRE(D == c->D && dtype == c->dtype && rows >= 0 && rows <= c->max_rows, NB2_ERR_SHAPE,
                 "host step: rows=%lld D=%lld dtype=%d do not fit the context (max_rows=%lld D=%lld dtype=%d)",
                 (long long)rows, (long long)D, dtype, (long long)c->max_rows, (long long)c->D, c->dtype);
-    NB2_REQUIRE(x_host && dy_host && gamma_host && beta_host && y_host && dx_host && dgamma_dbeta_host,
+    NB2_REQUIRE(x_host && dy_host && gamma_host && (rms || beta_host) && y_host && dx_host && grads_host,
                 NB2_ERR_NULL, "host step: NULL pointer");
     ST_CUDA(cudaSetDevice(c->device));
     const size_t row_bytes = (size_t)D * c->elt;
+    const int64_t ncols = (rms ? 1 : 2) * D;
     ST_CUDA(cudaMemcpyAsync(c->gamma, gamma_host, row_bytes, cudaMemcpyHostToDevice, c->s_in));
-    ST_CUDA(cudaMemcpyAsync(c->beta, beta_host, row_bytes, cudaMemcpyHostToDevice, c->s_in));
+    if (!rms) ST_CUDA(cudaMemcpyAsync(c->beta, beta_host, row_bytes, cudaMemcpyHostToDevice, c->s_in));
     const int64_t nchunks = (rows + c->chunk_rows - 1) / c->chunk_rows;
     for (int64_t i = 0; i < nchunks; ++i) {
         auto& s = c->set[i % HP_SETS];
@@ -138,10 +140,15 @@ extern "C" int nb2_layernorm_act_step_host(nb2_host_ctx* c, const void* x_host, 
         ST_CUDA(cudaMemcpyAsync(s.dy, (const char*)dy_host + off, bytes, cudaMemcpyHostToDevice, c->s_in));
         ST_CUDA(cudaEventRecord(s.in_done, c->s_in));
         ST_CUDA(cudaStreamWaitEvent(c->s_run, s.in_done, 0));
-        ST_RC(nb2_layernorm_fwd(s.x, c->gamma, c->beta, s.y, s.mean, s.rstd, n, D, eps, dtype, act, c->s_run));
         int64_t parts = 0;
-        ST_RC(nb2_layernorm_bwd(s.x, s.dy, c->gamma, c->beta, s.mean, s.rstd, s.dx, s.partials, &parts, n, D, dtype, act, c->s_run));
-        ST_RC(nb2_colreduce_partials(s.partials, parts, 2 * D, c->chunk_sums + (size_t)i * 2 * D, c->s_run));
+        if (rms) {
+            ST_RC(nb2_rmsnorm_fwd(s.x, c->gamma, s.y, s.rstd, n, D, eps, dtype, act, c->s_run));
+            ST_RC(nb2_rmsnorm_bwd(s.x, s.dy, c->gamma, s.rstd, s.dx, s.partials, &parts, n, D, dtype, act, c->s_run));
+        } else {
+            ST_RC(nb2_layernorm_fwd(s.x, c->gamma, c->beta, s.y, s.mean, s.rstd, n, D, eps, dtype, act, c->s_run));
+            ST_RC(nb2_layernorm_bwd(s.x, s.dy, c->gamma, c->beta, s.mean, s.rstd, s.dx, s.partials, &parts, n, D, dtype, act, c->s_run));
+        }
+        ST_RC(nb2_colreduce_partials(s.partials, parts, ncols, c->chunk_sums + (size_t)i * ncols, c->s_run));
         ST_CUDA(cudaEventRecord(s.run_done, c->s_run));
         ST_CUDA(cudaStreamWaitEvent(c->s_out, s.run_done, 0));
         ST_CUDA(cudaMemcpyAsync((char*)y_host + off, s.y, bytes, cudaMemcpyDeviceToHost, c->s_out));
@@ -149,13 +156,28 @@ extern "C" int nb2_layernorm_act_step_host(nb2_host_ctx* c, const void* x_host, 
         ST_CUDA(cudaEventRecord(s.out_done, c->s_out));
     }
     if (nchunks > 0) {
-        ST_RC(nb2_colreduce_partials(c->chunk_sums, nchunks, 2 * D, c->total, c->s_run));
+        ST_RC(nb2_colreduce_partials(c->chunk_sums, nchunks, ncols, c->total, c->s_run));
     } else {
-        ST_CUDA(cudaMemsetAsync(c->total, 0, (size_t)2 * D * 4, c->s_run));
+        ST_CUDA(cudaMemsetAsync(c->total, 0, (size_t)ncols * 4, c->s_run));
     }
-    ST_CUDA(cudaMemcpyAsync(dgamma_dbeta_host, c->total, (size_t)2 * D * 4, cudaMemcpyDeviceToHost, c->s_run));
+    ST_CUDA(cudaMemcpyAsync(grads_host, c->total, (size_t)ncols * 4, cudaMemcpyDeviceToHost, c->s_run));
     ST_CUDA(cudaStreamSynchronize(c->s_in));
     ST_CUDA(cudaStreamSynchronize(c->s_run));
     ST_CUDA(cudaStreamSynchronize(c->s_out));
     return 0;
+}
+
+extern "C" int nb2_layernorm_act_step_host(nb2_host_ctx* c, const void* x_host, const void* dy_host,
+                                           const void* gamma_host, const void* beta_host, void* y_host,
+                                           void* dx_host, float* dgamma_dbeta_host, int64_t rows, int64_t D,
+                                           double eps, int dtype, int act) {
+    return norm_act_step_host(c, false, x_host, dy_host, gamma_host, beta_host, y_host, dx_host, dgamma_dbeta_host, rows, D,
+                              eps, dtype, act);
+}
+
+extern "C" int nb2_rmsnorm_act_step_host(nb2_host_ctx* c, const void* x_host, const void* dy_host,
+                                         const void* weight_host, void* y_host, void* dx_host, float* dweight_host,
+                                         int64_t rows, int64_t D, double eps, int dtype, int act) {
+    return norm_act_step_host(c, true, x_host, dy_host, weight_host, nullptr, y_host, dx_host, dweight_host, rows, D, eps,
+                              dtype, act);
 }

@@ -108,7 +108,7 @@ static int launch_bwd_cfg(const NormArgs& a, int64_t* n_partials) {
     constexpr int VPT = bwd_vpt<T>();
     constexpr int THREADS = TPR > 256 ? TPR : 256;
     constexpr int MINB = TPR > 256 ? 1 : 2;
-    const int grid = (int)norm_bwd_grid(a.rows, TPR, sm_count());
+    const int grid = (int)norm_bwd_grid(a.rows, TPR, launch_sms());
     norm_bwd_kernel<T, TPR, VPT, ACT, RMS, MINB><<<grid, THREADS, 0, a.stream>>>(
         (const T*)a.x, (const T*)a.dy, (const T*)a.gamma, (const T*)a.beta, a.mean, a.rstd,
         (T*)a.dx, a.partials, a.rows, (int)a.D);

@@ -9,6 +9,7 @@
 // memory).  For them this file keeps that scratch in a fixed array inside the
 // library image.  Nothing here calls cudaMalloc, cudaFree or any allocating
 // library routine.
+#include <atomic>
 #include "launchers.h"
 
 namespace nb2 {
@@ -25,13 +26,19 @@ static __device__ __align__(256) float g_static_partials[kStaticPartialFloats];
 // device address comes from cudaGetSymbolAddress, asked once per device with
 // that device current.
 static float* static_partials_ptr(int* rc_out) {
-    static thread_local float* ptrs[kMaxDevices] = {};
-    float*& p = ptrs[current_device_slot()];
+    // one slot per device for the whole process (not per host thread): once any thread has made the
+    // first call on a device, every later call on it, from any thread, only reads the cached address
+    static std::atomic<float*> ptrs[kMaxDevices];
+    std::atomic<float*>& slot = ptrs[current_device_slot()];
     *rc_out = 0;
+    float* p = slot.load(std::memory_order_acquire);
     if (p == nullptr) {
         void* addr = nullptr;
         *rc_out = cuda_status(cudaGetSymbolAddress(&addr, g_static_partials), "cudaGetSymbolAddress(static partials)");
-        if (*rc_out == 0) p = static_cast<float*>(addr);
+        if (*rc_out == 0) {
+            p = static_cast<float*>(addr);
+            slot.store(p, std::memory_order_release);      // two racing first calls store the same address
+        }
     }
     return p;
 }

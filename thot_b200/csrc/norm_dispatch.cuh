@@ -144,6 +144,10 @@ static inline bool norm_fast_path_ok(const NormArgs& a, int vpt) {
         (a.dx && !aligned16(a.dx)) || (a.gamma && !aligned16(a.gamma)) ||
         (a.beta && !aligned16(a.beta)) || (a.partials && !aligned16(a.partials)))
         return false;
+    // the fused residual kernels copy these with 16-byte bulk copies and vector accesses as well
+    if ((a.res && !aligned16(a.res)) || (a.sum_out && !aligned16(a.sum_out)) || (a.dres && !aligned16(a.dres)) ||
+        (a.gather.extra && !aligned16(a.gather.extra)))
+        return false;
     return true;
 }
 

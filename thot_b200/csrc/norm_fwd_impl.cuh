@@ -72,7 +72,7 @@ static int launch_fwd_cfg(const NormArgs& a) {
     constexpr int MINB = TPR > 256 ? 1 : 2;
     constexpr int RPC = THREADS / TPR;
     int64_t need = (a.rows + RPC - 1) / RPC;
-    int64_t cap = (int64_t)sm_count() * MINB;
+    int64_t cap = (int64_t)launch_sms() * MINB;
     const int grid = (int)(need < cap ? need : cap);
     norm_fwd_kernel<T, TPR, VPT, ACT, RMS, MINB><<<grid, THREADS, 0, a.stream>>>(
         (const T*)a.x, (const T*)a.gamma, (const T*)a.beta, (T*)a.y, a.mean_out, a.rstd_out,
