@@ -308,6 +308,10 @@ int nb2_embedding_bwd_indexed(const void* dout, void* dtable, int64_t tokens, in
  * pre-norm sum rounded to the tensor dtype) may be NULL for inference; the
  * backward needs it, with mean and rstd.  Bad ids behave as in
  * nb2_embedding_fwd (zero word row + status word).
+ * ids == NULL selects the module's other branch (bert.hpp:164-171: an input that
+ * is not a Long tensor is taken as ready-made embeddings): `word` is then the
+ * [B*S, D] embeddings themselves, `vocab` is ignored, and in the backward dsum is
+ * the gradient of that input (dword is not written and may be NULL).
  * Backward: dsum = LayerNorm backward of dy (written to the caller's
  * [B*S, D] buffer), dword = deterministic scatter-add of dsum by id, dpos[s] =
  * sum over the batch of dsum[:, s] (rows >= S of the pos_rows-row gradient are

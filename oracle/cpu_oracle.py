@@ -131,8 +131,15 @@ def add_norm(kind, a, b, gamma, beta, dy, dsum, eps, bf16=False):
 def bert_embedding(word, pos, type_table, gamma, beta, ids, dy=None, eps=1e-12, bf16=False):
     """BertEmbeddingImpl::forward (src/block/details/transformers/bert.hpp:155-194): word gather by
     id, position gather of arange(S), token-type gather of zeros (row 0), sum, LayerNorm(eps 1e-12).
-    With dy: gradients of the three tables (type: row 0 only) and of gamma/beta."""
+    With dy: gradients of the three tables (type: row 0 only) and of gamma/beta.
+    ids None: `word` is a ready-made [B, S, D] embeddings tensor (the module's other input branch,
+    bert.hpp:164-171); dword is then not produced and dsum is the gradient of that input."""
     word = _f32(word)
+    if ids is None:
+        B, S, D = word.shape
+        vocab = B * S
+        word = word.reshape(B * S, D)
+        ids = np.arange(B * S, dtype=np.int64).reshape(B, S)
     ids = np.ascontiguousarray(ids, dtype=np.int64)
     B, S = ids.shape
     vocab, D = word.shape

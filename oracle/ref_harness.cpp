@@ -317,6 +317,46 @@ int ref_bert_embedding(const float* word, const float* pos, const float* type, c
     });
 }
 
+// The other branch of BertEmbeddingImpl::forward (bert.hpp:164-171): an input that is not a Long tensor is taken
+// as ready-made [B, S, D] embeddings; position and type rows are added and the sum is LayerNorm'ed.  dinput is
+// the gradient of that input.
+int ref_bert_embedding_from_embeddings(const float* input, const float* pos, const float* type, const float* gamma,
+                                       const float* beta, const float* dy, int64_t B, int64_t S, int64_t max_pos,
+                                       int64_t type_vocab, int64_t D, int compute,
+                                       float* y, float* dinput, float* dpos, float* dtype, float* dgamma, float* dbeta) {
+    return guarded([&] {
+        namespace Bt = Nott::Block::Details::Transformer::Bert;
+        Bt::EmbeddingOptions opt{};
+        opt.vocab_size = 4;                               // a word table exists but is not used by this branch
+        opt.type_vocab_size = type_vocab;
+        opt.max_position_embeddings = max_pos;
+        opt.dropout = 0.0;
+        opt.use_token_type = type != nullptr;
+        opt.use_position_embeddings = pos != nullptr;
+        Bt::Detail::BertEmbedding emb(D, opt);
+        emb->to(compute_type(compute));
+        auto params = emb->named_parameters();
+        {
+            torch::NoGradGuard ng;
+            if (pos) params["position_embeddings.weight"].copy_(wrap(pos, {max_pos, D}, compute));
+            if (type) params["token_type_embeddings.weight"].copy_(wrap(type, {type_vocab, D}, compute));
+            params["layer_norm.weight"].copy_(wrap(gamma, {D}, compute));
+            params["layer_norm.bias"].copy_(wrap(beta, {D}, compute));
+        }
+        auto in = wrap(input, {B, S, D}, compute).clone().requires_grad_(dy != nullptr);
+        auto out = emb->forward(in);
+        store(out, y);
+        if (dy != nullptr) {
+            out.backward(wrap(dy, {B, S, D}, compute));
+            store(in.grad(), dinput);
+            if (pos) store(params["position_embeddings.weight"].grad(), dpos);
+            if (type) store(params["token_type_embeddings.weight"].grad(), dtype);
+            store(params["layer_norm.weight"].grad(), dgamma);
+            store(params["layer_norm.bias"].grad(), dbeta);
+        }
+    });
+}
+
 // Times forward + autograd backward of LayerNorm->act (rms == 0) or Nott's
 // RMSNorm->act (rms != 0) on seeded N(0,1) inputs that are built once; only the
 // module calls are inside the clock.  Returns seconds per iteration (mean of

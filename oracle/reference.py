@@ -115,6 +115,25 @@ def bert_embedding(word, pos, type_table, gamma, beta, ids, dy=None, compute=0):
     return dict(y=y, dword=dword, dpos=dpos, dtype=dtype, dgamma=dg, dbeta=db)
 
 
+def bert_embedding_from_embeddings(inp, pos, type_table, gamma, beta, dy=None, compute=0):
+    """BertEmbedding fed ready-made [B, S, D] embeddings (bert.hpp:164-171) instead of token ids."""
+    inp, pos, type_table, gamma, beta, dy = map(_f32, (inp, pos, type_table, gamma, beta, dy))
+    B, S, D = inp.shape
+    max_pos = pos.shape[0] if pos is not None else 0
+    tv = type_table.shape[0] if type_table is not None else 0
+    y = np.empty((B, S, D), np.float32)
+    bwd = dy is not None
+    dinp = np.empty((B, S, D), np.float32) if bwd else None
+    dpos = np.empty((max_pos, D), np.float32) if bwd and pos is not None else None
+    dtype = np.empty((tv, D), np.float32) if bwd and type_table is not None else None
+    dg = np.empty(D, np.float32) if bwd else None
+    db = np.empty(D, np.float32) if bwd else None
+    _chk(lib().ref_bert_embedding_from_embeddings(_p(inp), _p(pos), _p(type_table), _p(gamma), _p(beta), _p(dy), c_int64(B), c_int64(S),
+                                                  c_int64(max_pos), c_int64(tv), c_int64(D), c_int(compute),
+                                                  _p(y), _p(dinp), _p(dpos), _p(dtype), _p(dg), _p(db)))
+    return dict(y=y, dinput=dinp, dpos=dpos, dtype=dtype, dgamma=dg, dbeta=db)
+
+
 def act(x, dy, act_code, compute=0):
     x, dy = _f32(x), _f32(dy)
     y = np.empty(x.shape, np.float32)
@@ -174,3 +193,41 @@ def time_norm_act(kind, rows, D, eps, act, compute=0, iters=10, warmup=2) -> flo
     if t < 0:
         raise RuntimeError("reference harness: " + lib().ref_last_error().decode())
     return float(t)
+
+
+# ---- the reference's RegisteredLayer / ForwardBinding driving the drop-in modules (libnott_binding.so)
+_bind = None
+
+
+def binding_available() -> bool:
+    return build_ref.BINDING_LIB.exists()
+
+
+def binding_lib():
+    global _bind
+    if _bind is None:
+        import torch  # noqa: F401
+
+        if not build_ref.BINDING_LIB.exists():
+            raise RuntimeError("oracle/_ref/libnott_binding.so is not built (needs the reference checkout)")
+        _bind = ctypes.CDLL(str(build_ref.BINDING_LIB))
+        _bind.refbind_last_error.restype = ctypes.c_char_p
+    return _bind
+
+
+BIND_MODULE, BIND_COPY, BIND_INLINE_COPY_MOVE, BIND_REFERENCE_F32, BIND_REFERENCE_F64 = range(5)
+
+
+def binding_layernorm_gelu(which, x, dy, gamma, beta, eps=1e-5, bf16=False):
+    """`layer.forward(x)` then `apply(layer.activation, .)` through a RegisteredLayer, plus backward.
+    which: BIND_MODULE / BIND_COPY / BIND_INLINE_COPY_MOVE run Nott::B200::LayerNorm (GeLU fused) on CUDA,
+    BIND_REFERENCE_F32 / _F64 the reference pair torch::nn::LayerNorm + apply(GeLU) on CPU.  x, dy: [B, S, D]."""
+    x, dy, gamma, beta = _f32(x), _f32(dy), _f32(gamma), _f32(beta)
+    B, S, D = x.shape
+    y = np.empty((B, S, D), np.float32); dx = np.empty((B, S, D), np.float32)
+    dg = np.empty(D, np.float32); db = np.empty(D, np.float32)
+    rc = binding_lib().refbind_layernorm_gelu(c_int(which), _p(x), _p(dy), _p(gamma), _p(beta), c_int64(B), c_int64(S), c_int64(D),
+                                              c_double(eps), c_int(int(bf16)), _p(y), _p(dx), _p(dg), _p(db))
+    if rc != 0:
+        raise RuntimeError("binding harness: " + binding_lib().refbind_last_error().decode())
+    return dict(y=y, dx=dx, dgamma=dg, dbeta=db)

@@ -128,6 +128,14 @@ def main():
         for k, v in r.items():
             rec[f"{k}_{tag}"] = v
     np.savez(OUT / "bert_embedding.npz", **rec)
+    # the same module fed ready-made embeddings (bert.hpp:164-171)
+    inp = randn(gen, B, S, D, scale=0.5)
+    rec = dict(input=inp, pos=pos, type=typ, gamma=gamma, beta=beta, dy=dy)
+    for tag, compute in (("f32", 0), ("f64", 1)):
+        r = R.bert_embedding_from_embeddings(inp, pos, typ, gamma, beta, dy, compute)
+        for k, v in r.items():
+            rec[f"{k}_{tag}"] = v
+    np.savez(OUT / "bert_embedding_float_input.npz", **rec)
 
     gen = torch.Generator().manual_seed(12)
     table = randn(gen, 64, 40, scale=0.02)

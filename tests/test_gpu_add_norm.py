@@ -109,7 +109,12 @@ def test_residual_offset_by_one_element_takes_the_composed_path(kind):
     ref = O.add_norm(kind, an, bn, gn, ben, dyn, dsn, eps)
     assert np.array_equal(s.cpu().numpy(), ref["sum"])
     check(y, ref["y"], "y"); check(dx, ref["dx"], "dx")
-    # and the same bits as the aligned call
+    # the aligned call (fused kernel) agrees within the tolerance; its statistics are summed in another order
     s2, y2, dx2, grads2 = run(kind, a, b.clone(), gamma, beta, dy, dsum.clone(), eps)
-    assert torch.equal(y, y2) and torch.equal(dx, dx2)
+    assert torch.equal(s, s2)
+    check(y2, ref["y"], "aligned y"); check(dx2, ref["dx"], "aligned dx")
+    g1 = grads.reshape(-1, D).cpu().numpy(); g2 = grads2.reshape(-1, D).cpu().numpy()
+    for i, k in enumerate(("dgamma", "dbeta") if kind == "ln" else ("dgamma",)):
+        tol.long_sum_close(g1[i], ref[k], rows)
+        tol.long_sum_close(g2[i], ref[k], rows)
     assert abi.device_status() == 0

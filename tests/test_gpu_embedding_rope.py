@@ -81,6 +81,23 @@ def test_config4_embedding_full_size_bit_exact():
     assert out.view(torch.int16).numpy().reshape(-1, 4096).tobytes() == ref.tobytes()
 
 
+def test_config4_embedding_backward_full_size_against_the_oracle():
+    """dtable[32000,4096] from dout[65536,4096] bf16 and int32 ids [32,2048]: every table row against the C
+    oracle's scatter-add (fp64 sums in ascending token order, rounded once to bf16), one-call and indexed forms."""
+    vocab, D, tokens = 32000, 4096, 32 * 2048
+    gen = torch.Generator().manual_seed(44)
+    ids = torch.randint(0, vocab, (32, 2048), generator=gen, dtype=torch.int32)
+    dout = torch.randn(tokens, D, generator=gen).bfloat16()
+    got = abi.embedding_bwd(dout.cuda(), ids.cuda(), vocab)
+    ref = O.embedding_bwd(dout.float().numpy(), ids.numpy().reshape(-1), vocab)
+    check(got, ref, "config 4 dtable")
+    counts = np.bincount(ids.numpy().reshape(-1), minlength=vocab)
+    assert float(got[torch.from_numpy(counts == 0).cuda()].float().abs().sum()) == 0.0     # unused rows are zero
+    index = abi.embedding_index(ids.cuda(), vocab)
+    assert torch.equal(abi.embedding_bwd_indexed(dout.cuda(), index, vocab), got)
+    assert abi.device_status() == 0
+
+
 def test_rope_table_matches_oracle():
     for S, hd, theta in [(2048, 128, 10000.0), (17, 64, 500000.0), (5, 2, 10000.0), (3, 1024, 10000.0)]:
         cs = abi.rope_table(S, hd, theta).cpu().numpy()

@@ -3,7 +3,10 @@
 shares one device array between calls, and a failure here must not hide the other tests.
 
 Checked through the C ABI against the ordinary entry points (nb2_layernorm_bwd +
-nb2_colreduce_partials with a caller-allocated workspace), on two calls in a row."""
+nb2_colreduce_partials with a caller-allocated workspace) and against the CPU oracle, on two
+calls in a row.  "Allocates nothing" is checked with the driver's own count of free device
+memory (cudaMemGetInfo through torch.cuda.mem_get_info), which sees every allocation of the
+process whoever makes it, not only the ones that go through torch's caching allocator."""
 from __future__ import annotations
 
 import ctypes
@@ -11,6 +14,7 @@ import ctypes
 import pytest
 import torch
 
+from oracle import cpu_oracle as O
 from tests import tol
 from tests.gpu_util import check, make
 from thot_b200 import abi
@@ -30,23 +34,31 @@ def test_static_scratch_backward_matches_the_allocating_path_twice(dtype, D):
     rows = 3000
     act = abi.ACT_GELU
     for call in range(2):                               # the second call reuses the array with stale contents
-        x, _ = make((rows, D), 100 + call, dtype)
-        dy, _ = make((rows, D), 200 + call, dtype)
-        gamma, _ = make((D,), 300 + call, dtype, 0.02, 1.0)
-        beta, _ = make((D,), 400 + call, dtype, 0.02)
+        x, xn = make((rows, D), 100 + call, dtype)
+        dy, dyn = make((rows, D), 200 + call, dtype)
+        gamma, gn = make((D,), 300 + call, dtype, 0.02, 1.0)
+        beta, bn = make((D,), 400 + call, dtype, 0.02)
         y, mean, rstd = abi.layernorm_fwd(x, gamma, beta, 1e-5, act)
         dx_ref, grads_ref = abi.layernorm_bwd(x, dy, gamma, beta, mean, rstd, act)
         dx = torch.empty_like(x)
         grads = torch.full((2, D), float("nan"), device="cuda")
+        if call == 0:
+            # the first call on a device also looks up the array's address; make it before measuring
+            assert _static_bwd(x, dy, gamma, beta, mean, rstd, act, dx, grads) == 0
         torch.cuda.synchronize()
-        before = torch.cuda.memory_allocated()
+        free_before, _ = torch.cuda.mem_get_info()
+        torch_before = torch.cuda.memory_allocated()
         assert _static_bwd(x, dy, gamma, beta, mean, rstd, act, dx, grads) == 0
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
-        check(dx, dx_ref.float().cpu().numpy(), "dx")                       # same kernel, same grid: identical
-        assert torch.equal(dx, dx_ref)
-        tol.long_sum_close(grads.cpu().numpy(), grads_ref.double().cpu().numpy(), rows)
+        free_after, _ = torch.cuda.mem_get_info()
+        assert free_after >= free_before, (free_before, free_after)       # no cudaMalloc by anybody during the call
+        assert torch.cuda.memory_allocated() == torch_before
+        assert torch.equal(dx, dx_ref)                                      # same kernel, same grid: identical
         assert torch.equal(grads, grads_ref)
+        ref = O.layernorm_act(xn, gn, bn, dyn, 1e-5, act)                   # and against the oracle directly
+        check(dx, ref["dx"], "dx")
+        tol.long_sum_close(grads[0].cpu().numpy(), ref["dgamma"], rows)
+        tol.long_sum_close(grads[1].cpu().numpy(), ref["dbeta"], rows)
     assert abi.device_status() == 0
 
 

@@ -9,13 +9,22 @@ fp32 outputs against the LIVE fp32 reference (libtorch CPU) are adjudicated by t
     result where one exists: an element passes when inside the tolerance of the fp32
     reference OR at least as close to fp64 as the fp32 reference is.  (libtorch's fp32
     CPU GELU is itself 1.1e-6 off in the tail around z = -3.5.)
-long fp32 sums over n rows (dgamma, dbeta, dweight): a sum of n terms of unit scale has
-    natural magnitude sqrt(n) even where it cancels to ~0, and fp32 accumulation (ours and
-    the reference's alike) carries an error proportional to that magnitude.  The relative
-    tolerance is therefore applied to max(|ref|, sqrt(n)):
-        |got - ref64| <= 1e-6 + 1e-5 * max(|ref64|, sqrt(n)),
-    or inside the fp32 tolerance of the fp32 reference, or at least as close to fp64 as the
-    fp32 reference is.
+long fp32 sums over n rows (dgamma, dbeta, dweight), `long_sum_close`.  Each element is classified
+    by the first rule it meets, and the call returns how many elements met which:
+      tol64  : |got - ref64| <= 1e-6 + 1e-5 |ref64|, the stated tolerance against the exact (fp64) sum;
+      tol32  : the stated tolerance against the fp32 CPU reference (libtorch through the reference's
+               own modules), when one is given;
+      closer : at least as close to the fp64 sum as the fp32 CPU reference is;
+      vector : the element met none of the above (its fp32 CPU value happens to lie nearer the exact
+               sum than ours), but over the whole vector the GPU result is closer to fp64 than the
+               fp32 CPU reference in BOTH the largest and the root-mean-square distance;
+      sqrt_n : |got - ref64| <= 1e-6 + 1e-5 max(|ref64|, sqrt(n)): a sum of n unit-scale terms has
+               natural magnitude sqrt(n) even where it cancels to ~0, and any fp32 accumulation
+               carries an error proportional to that.  This rule is NOT part of the stated
+               tolerance.  It is accepted only where no fp32 CPU reference exists for the case
+               (`strict=False`: small shape sweeps against the C oracle, consistency properties
+               between two GPU results); with `strict=True` (every configuration-sized case) an
+               element that only this rule admits fails the test.
 integer / byte outputs: exact.
 """
 from __future__ import annotations
@@ -51,23 +60,45 @@ def fp32_close_adjudicated(got, ref32, ref64):
                              f"closer to fp64; first at {i}: got {got[i]!r} ref32 {ref32[i]!r} ref64 {ref64[i]!r}")
 
 
-def long_sum_close(got, ref64, n_terms, ref32=None):
-    """dgamma/dbeta/dweight over `n_terms` rows; see the module docstring for the rule."""
-    got = np.asarray(got, np.float64); ref64 = np.asarray(ref64, np.float64)
-    scale = np.maximum(np.abs(ref64), float(n_terms) ** 0.5)
-    ok = np.abs(got - ref64) <= FP32_ATOL + FP32_RTOL * scale
+PARITY_LOG = []          # one record per labelled long_sum_close call; written out by tests/conftest.py
+
+
+def long_sum_close(got, ref64, n_terms, ref32=None, strict=False, label=None):
+    """dgamma/dbeta/dweight over `n_terms` rows; see the module docstring for the rules.
+    Returns {"tol64": k, "tol32": k, "closer": k, "vector": k, "sqrt_n": k, ...distances}."""
+    got = np.asarray(got, np.float64).ravel(); ref64 = np.asarray(ref64, np.float64).ravel()
+    assert got.shape == ref64.shape, (got.shape, ref64.shape)
+    if strict and ref32 is None:
+        raise ValueError("strict long-sum check needs the fp32 CPU reference")
+    d_gpu = np.abs(got - ref64)
+    rule = np.full(got.shape, "", dtype=object)
+    rule[d_gpu <= FP32_ATOL + FP32_RTOL * np.abs(ref64)] = "tol64"
+    stats = {"n_terms": int(n_terms), "elements": int(got.size), "max_dist_gpu_to_f64": float(d_gpu.max(initial=0.0)),
+             "rms_dist_gpu_to_f64": float(np.sqrt(np.mean(d_gpu ** 2))) if got.size else 0.0}
     if ref32 is not None:
-        ref32 = np.asarray(ref32, np.float64)
+        ref32 = np.asarray(ref32, np.float64).ravel()
+        d_ref = np.abs(ref32 - ref64)
         slack = np.spacing(np.abs(ref64).astype(np.float32)).astype(np.float64)
-        ok |= np.abs(got - ref32) <= FP32_ATOL + FP32_RTOL * np.abs(ref32)
-        ok |= np.abs(got - ref64) <= np.abs(ref32 - ref64) + slack
-    else:
-        ref32 = ref64
-    bad = ~ok
+        rule[(rule == "") & (np.abs(got - ref32) <= FP32_ATOL + FP32_RTOL * np.abs(ref32))] = "tol32"
+        rule[(rule == "") & (d_gpu <= d_ref + slack)] = "closer"
+        stats.update(max_dist_f32cpu_to_f64=float(d_ref.max(initial=0.0)), rms_dist_f32cpu_to_f64=float(np.sqrt(np.mean(d_ref ** 2))))
+        if stats["max_dist_gpu_to_f64"] <= stats["max_dist_f32cpu_to_f64"] and stats["rms_dist_gpu_to_f64"] <= stats["rms_dist_f32cpu_to_f64"]:
+            rule[rule == ""] = "vector"
+    scale = np.maximum(np.abs(ref64), float(n_terms) ** 0.5)
+    rule[(rule == "") & (d_gpu <= FP32_ATOL + FP32_RTOL * scale)] = "sqrt_n"
+    counts = {k: int((rule == k).sum()) for k in ("tol64", "tol32", "closer", "vector", "sqrt_n")}
+    stats.update(counts)
+    if label is not None:
+        PARITY_LOG.append(dict(stats, label=label, strict=bool(strict)))
+    bad = rule == ""
+    if strict:
+        bad |= rule == "sqrt_n"
     if bad.any():
         i = int(np.argmax(bad))
-        raise AssertionError(f"{bad.sum()} of {bad.size} long sums fail; first at {i}: got {got.flat[i]!r} "
-                             f"ref32 {ref32.flat[i]!r} ref64 {ref64.flat[i]!r}")
+        r32 = ref32[i] if ref32 is not None else float("nan")
+        raise AssertionError(f"{int(bad.sum())} of {bad.size} long sums fail ({'strict' if strict else 'lenient'}; rules met: {counts}); "
+                             f"first at {i}: got {got[i]!r} ref32 {r32!r} ref64 {ref64[i]!r}")
+    return stats
 
 
 def to_bf16_bits(a) -> np.ndarray:

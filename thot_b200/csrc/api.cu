@@ -376,7 +376,8 @@ int nb2_bert_embedding_ln_fwd(const void* word, const void* pos, const void* typ
     NB2_REQUIRE(B >= 0 && S >= 0 && vocab > 0 && D > 0 && D < ((int64_t)1 << 31), NB2_ERR_SHAPE,
                 "bert embedding fwd: B=%lld S=%lld vocab=%lld D=%lld", (long long)B, (long long)S, (long long)vocab, (long long)D);
     if (B == 0 || S == 0) return 0;
-    NB2_REQUIRE(word && ids && gamma && beta && y, NB2_ERR_NULL, "bert embedding fwd: word, ids, gamma, beta and y must be non-NULL");
+    NB2_REQUIRE(word && gamma && beta && y, NB2_ERR_NULL, "bert embedding fwd: word, gamma, beta and y must be non-NULL");
+    if (ids == nullptr) vocab = B * S;          // ready-made embeddings: row t of `word` belongs to token t
     int rc = require_device();
     if (rc != 0) return rc;
     // Preferred: the ring kernel of the residual-add norm with a row lookup (word rows by id as x,
@@ -408,7 +409,7 @@ int nb2_bert_embedding_ln_bwd(const void* sum, const void* dy, const void* ids, 
                     D < ((int64_t)1 << 31) && pos_rows >= (dpos ? S : 0), NB2_ERR_SHAPE,
                 "bert embedding bwd: B=%lld S=%lld vocab=%lld D=%lld pos_rows=%lld", (long long)B, (long long)S,
                 (long long)vocab, (long long)D, (long long)pos_rows);
-    NB2_REQUIRE(sum && dy && ids && gamma && mean && rstd && dsum && dword && dgamma_dbeta && workspace, NB2_ERR_NULL,
+    NB2_REQUIRE(sum && dy && gamma && mean && rstd && dsum && (dword || !ids) && dgamma_dbeta && workspace, NB2_ERR_NULL,
                 "bert embedding bwd: a required pointer is NULL");
     const int64_t tokens = B * S;
     const size_t need = nb2_workspace_bytes(NB2_WS_BERT_EMBEDDING_BWD, B * ((int64_t)1 << 32) + S, vocab * ((int64_t)1 << 32) + D, dtype);
@@ -430,14 +431,15 @@ int nb2_bert_embedding_ln_bwd(const void* sum, const void* dy, const void* ids, 
         if (rc != 0) return rc;
     }
     if (tokens == 0) {
-        rc = cuda_status(cudaMemsetAsync(dword, 0, (size_t)vocab * D * elt, st), "bert embedding bwd memset");
+        if (ids != nullptr) rc = cuda_status(cudaMemsetAsync(dword, 0, (size_t)vocab * D * elt, st), "bert embedding bwd memset");
         if (rc == 0) rc = cuda_status(cudaMemsetAsync(dgamma_dbeta, 0, (size_t)2 * D * 4, st), "bert embedding bwd memset");
         if (rc == 0 && dtype0) rc = cuda_status(cudaMemsetAsync(dtype0, 0, (size_t)D * elt, st), "bert embedding bwd memset");
         return rc;
     }
     // The sort of the ids does not depend on the gradient: it runs on a side stream while the
     // LayerNorm backward streams the activations, and joins before the row sums need it.
-    SideStream* side = side_stream(st);
+    // ids == NULL: the input was ready-made embeddings, dsum is its gradient and there is no word table
+    SideStream* side = ids != nullptr ? side_stream(st) : nullptr;
     if (side != nullptr) {
         rc = cuda_status(cudaEventRecord(side->fork, st), "bert embedding bwd: fork");
         if (rc == 0) rc = cuda_status(cudaStreamWaitEvent(side->stream, side->fork, 0), "bert embedding bwd: fork");
@@ -450,11 +452,13 @@ int nb2_bert_embedding_ln_bwd(const void* sum, const void* dy, const void* ids, 
     if (rc != 0) return rc;
     rc = nb2_colreduce_partials(partials, n, 2 * D, dgamma_dbeta, stream);
     if (rc != 0) return rc;
-    if (side != nullptr) rc = cuda_status(cudaStreamWaitEvent(st, side->join, 0), "bert embedding bwd: join");
-    else rc = launch_embedding_bwd_index(ids, tokens, vocab, index_type, sort_ws, sort_bytes, st);
-    if (rc != 0) return rc;
-    rc = launch_embedding_bwd_sum(dsum, dword, tokens, vocab, D, dtype, sort_ws, st);
-    if (rc != 0) return rc;
+    if (ids != nullptr) {
+        if (side != nullptr) rc = cuda_status(cudaStreamWaitEvent(st, side->join, 0), "bert embedding bwd: join");
+        else rc = launch_embedding_bwd_index(ids, tokens, vocab, index_type, sort_ws, sort_bytes, st);
+        if (rc != 0) return rc;
+        rc = launch_embedding_bwd_sum(dsum, dword, tokens, vocab, D, dtype, sort_ws, st);
+        if (rc != 0) return rc;
+    }
     return launch_bert_embed_table_grads(dsum, dpos, dtype0, type_scratch, B, S, D, dtype, st);
 }
 

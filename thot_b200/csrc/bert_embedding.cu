@@ -15,8 +15,9 @@
 
 namespace nb2 {
 
+// ids == NULL: `word` already holds one row per token (ready-made embeddings, bert.hpp:164-171)
 template <typename I> __device__ __forceinline__ int64_t load_token(const void* ids, int64_t t) {
-    return (int64_t)reinterpret_cast<const I*>(ids)[t];
+    return ids == nullptr ? t : (int64_t)reinterpret_cast<const I*>(ids)[t];
 }
 
 template <typename T, typename I, int TPR, int VPT>

@@ -80,10 +80,14 @@ PYBIND11_MODULE(_nott_b200_host, m) {
             size_t i = 0;
             for (auto& kv : mod->named_parameters()) { names.push_back(kv.key()); if (i < values.size()) kv.value().copy_(values[i]); ++i; }
         }
+        // `ids` may also be ready-made [B, S, D] embeddings (bert.hpp:164-171); their gradient is appended last
+        const bool embeddings = ids.is_floating_point();
+        if (embeddings) ids = ids.clone().requires_grad_(true);
         auto y = mod->forward(ids);
         y.backward(dy);
         std::vector<torch::Tensor> out{y.detach()};
-        for (auto& kv : mod->named_parameters()) out.push_back(kv.value().grad());
+        for (auto& kv : mod->named_parameters()) out.push_back(kv.value().grad().defined() ? kv.value().grad() : torch::zeros_like(kv.value()));
+        if (embeddings) out.push_back(ids.grad());
         return std::make_pair(names, out);
     });
     m.def("module_errors", []() {

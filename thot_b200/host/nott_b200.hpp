@@ -540,29 +540,39 @@ TORCH_MODULE(Embedding);
 // BertEmbeddingImpl (src/block/details/transformers/bert.hpp:116-204) as one forward kernel and one
 // fused backward: word[ids] + position[arange(S)] + token_type[0], LayerNorm(eps 1e-12), dropout.
 struct BertEmbeddingFunction : public torch::autograd::Function<BertEmbeddingFunction> {
-    static torch::Tensor forward(torch::autograd::AutogradContext* ctx, torch::Tensor ids, torch::Tensor word,
+    // `input` is either [batch, sequence] token ids (int32 or int64; the reference takes int64 only) or, as in
+    // the reference's other branch (bert.hpp:164-171), ready-made [batch, sequence, D] embeddings.
+    static torch::Tensor forward(torch::autograd::AutogradContext* ctx, torch::Tensor input, torch::Tensor word,
                                  c10::optional<torch::Tensor> pos_opt, c10::optional<torch::Tensor> type_opt,
                                  torch::Tensor gamma, torch::Tensor beta, double eps) {
-        detail::require_cuda(word, "BERT embeddings");
-        if (ids.dim() != 2 || (ids.scalar_type() != torch::kInt64 && ids.scalar_type() != torch::kInt32))
-            throw std::invalid_argument("BERT embeddings expect [batch, sequence] int32 or int64 token ids.");
-        const int code = detail::dtype_code(word, "BERT embeddings");
-        auto w = word.contiguous();
+        detail::require_cuda(gamma, "BERT embeddings");
+        const bool from_ids = input.scalar_type() == torch::kInt64 || input.scalar_type() == torch::kInt32;
+        if (from_ids && input.dim() != 2) throw std::invalid_argument("BERT embeddings expect [batch, sequence] token ids.");
+        if (!from_ids && input.dim() != 3) throw std::invalid_argument("BERT embeddings expect [batch, sequence, embed_dim] embeddings.");
+        if (from_ids && !word.defined()) throw std::invalid_argument("BERT embeddings received token ids but have no word table.");
+        auto w = from_ids ? word.contiguous() : input.contiguous();
+        detail::require_cuda(w, "BERT embeddings");
+        const int code = detail::dtype_code(w, "BERT embeddings");
         auto pos = detail::param_like(pos_opt.value_or(torch::Tensor()), w);
         auto type = detail::param_like(type_opt.value_or(torch::Tensor()), w);
         auto g = detail::param_like(gamma, w), b = detail::param_like(beta, w);
-        const auto B = ids.size(0), S = ids.size(1), vocab = w.size(0), D = w.size(1);
+        const auto B = input.size(0), S = input.size(1), D = w.size(-1);
+        const auto vocab = from_ids ? w.size(0) : B * S;
         if (pos.defined() && pos.size(0) < S) throw std::invalid_argument("BERT embeddings: sequence longer than max_position_embeddings.");
-        auto idc = ids.contiguous();
+        auto idc = from_ids ? input.contiguous() : torch::Tensor();
         auto y = torch::empty({B, S, D}, w.options());
         auto sum = torch::empty({B * S, D}, w.options());
         auto stats = torch::empty({2, B * S}, w.options().dtype(torch::kFloat32));
-        detail::check(nb2_bert_embedding_ln_fwd(w.data_ptr(), detail::ptr_or_null(pos), detail::ptr_or_null(type), idc.data_ptr(),
-                                                g.data_ptr(), b.data_ptr(), sum.data_ptr(), y.data_ptr(),
+        detail::check(nb2_bert_embedding_ln_fwd(w.data_ptr(), detail::ptr_or_null(pos), detail::ptr_or_null(type),
+                                                detail::ptr_or_null(idc), g.data_ptr(), b.data_ptr(), sum.data_ptr(), y.data_ptr(),
                                                 stats[0].data_ptr<float>(), stats[1].data_ptr<float>(), B, S, vocab, D, eps, code,
-                                                idc.scalar_type() == torch::kInt32 ? NB2_I32 : NB2_I64, nullptr, detail::stream()),
+                                                from_ids && idc.scalar_type() == torch::kInt32 ? NB2_I32 : NB2_I64, nullptr,
+                                                detail::stream()),
                       "nb2_bert_embedding_ln_fwd");
-        ctx->save_for_backward({sum, idc, g, stats});
+        ctx->save_for_backward({sum, from_ids ? idc : torch::empty({0}, w.options().dtype(torch::kInt64)), g, stats});
+        ctx->saved_data["from_ids"] = from_ids;
+        ctx->saved_data["B"] = B;
+        ctx->saved_data["S"] = S;
         ctx->saved_data["vocab"] = vocab;
         ctx->saved_data["pos_rows"] = pos.defined() ? pos.size(0) : (int64_t)0;
         ctx->saved_data["type_rows"] = type.defined() ? type.size(0) : (int64_t)0;
@@ -571,27 +581,31 @@ struct BertEmbeddingFunction : public torch::autograd::Function<BertEmbeddingFun
     static torch::autograd::tensor_list backward(torch::autograd::AutogradContext* ctx, torch::autograd::tensor_list grads) {
         auto saved = ctx->get_saved_variables();
         auto sum = saved[0], ids = saved[1], g = saved[2], stats = saved[3];
-        const auto B = ids.size(0), S = ids.size(1), D = sum.size(1);
+        const bool from_ids = ctx->saved_data["from_ids"].toBool();
+        const auto B = ctx->saved_data["B"].toInt(), S = ctx->saved_data["S"].toInt(), D = sum.size(1);
         const auto vocab = ctx->saved_data["vocab"].toInt(), pos_rows = ctx->saved_data["pos_rows"].toInt(),
                    type_rows = ctx->saved_data["type_rows"].toInt();
         const int code = detail::dtype_code(sum, "BERT embeddings backward");
         auto dy = grads[0].contiguous().to(sum.scalar_type());
         auto dsum = torch::empty_like(sum);
-        auto dword = torch::empty({vocab, D}, sum.options());
-        torch::Tensor dpos, dtype;
+        torch::Tensor dword, dpos, dtype;
+        if (from_ids) dword = torch::empty({vocab, D}, sum.options());
         if (pos_rows > 0) dpos = torch::empty({pos_rows, D}, sum.options());
         if (type_rows > 0) dtype = torch::zeros({type_rows, D}, sum.options());       // rows other than 0 get no gradient
         auto sums = torch::empty({2, D}, sum.options().dtype(torch::kFloat32));
         const auto ws = nb2_workspace_bytes(NB2_WS_BERT_EMBEDDING_BWD, (B << 32) | S, (vocab << 32) | D, code);
         auto scratch = torch::empty({(int64_t)ws}, sum.options().dtype(torch::kUInt8));
-        detail::check(nb2_bert_embedding_ln_bwd(sum.data_ptr(), dy.data_ptr(), ids.data_ptr(), g.data_ptr(),
+        detail::check(nb2_bert_embedding_ln_bwd(sum.data_ptr(), dy.data_ptr(), from_ids ? ids.data_ptr() : nullptr, g.data_ptr(),
                                                 stats[0].data_ptr<float>(), stats[1].data_ptr<float>(), dsum.data_ptr(),
-                                                dword.data_ptr(), dpos.defined() ? dpos.data_ptr() : nullptr, pos_rows,
+                                                dword.defined() ? dword.data_ptr() : nullptr,
+                                                dpos.defined() ? dpos.data_ptr() : nullptr, pos_rows,
                                                 type_rows > 0 ? dtype.data_ptr() : nullptr, sums.data_ptr<float>(), B, S, vocab, D,
-                                                code, ids.scalar_type() == torch::kInt32 ? NB2_I32 : NB2_I64, scratch.data_ptr(),
-                                                ws, detail::stream()),
+                                                code, from_ids && ids.scalar_type() == torch::kInt32 ? NB2_I32 : NB2_I64,
+                                                scratch.data_ptr(), ws, detail::stream()),
                       "nb2_bert_embedding_ln_bwd");
-        return {torch::Tensor(), dword, dpos, dtype, sums[0].to(g.scalar_type()), sums[1].to(g.scalar_type()), torch::Tensor()};
+        // ids carry no gradient; ready-made embeddings receive dsum
+        return {from_ids ? torch::Tensor() : dsum.view({B, S, D}), dword, dpos, dtype, sums[0].to(g.scalar_type()),
+                sums[1].to(g.scalar_type()), torch::Tensor()};
     }
 };
 
@@ -623,6 +637,10 @@ public:
 
     torch::Tensor forward(torch::Tensor input) {
         if (!input.defined()) return input;
+        const bool ids = input.scalar_type() == torch::kInt64 || input.scalar_type() == torch::kInt32;
+        if (!ids && input.size(-1) != embed_dim_)          // the reference's own check and message (bert.hpp:166-170)
+            throw std::invalid_argument("BERT embeddings expected last dimension " + std::to_string(embed_dim_) +
+                                        " but received " + std::to_string(input.size(-1)) + ".");
         torch::Tensor out = BertEmbeddingFunction::apply(
             std::move(input), word_embeddings_->weight,
             position_embeddings_ ? detail::opt(position_embeddings_->weight) : c10::nullopt,
