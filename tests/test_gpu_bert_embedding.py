@@ -84,3 +84,75 @@ def test_bad_ids_and_module_names():
                      "layer_norm.weight", "layer_norm.bias"]
     assert out[0].shape == (2, 5, 32) and all(t is not None for t in out[1:])
     assert not out[2][1].any() and not out[3][5:].any()      # type row 1 and positions >= S get no gradient
+
+
+def test_ready_made_embeddings_golden_through_the_module(golden_dir):
+    """BertEmbedding fed [B, S, D] embeddings instead of ids (bert.hpp:164-171): position and type rows are
+    added and the sum is LayerNorm'ed; the C++ drop-in module against the reference module's own outputs."""
+    from thot_b200 import _nott_b200_host as host
+    z = np.load(golden_dir / "bert_embedding_float_input.npz")
+    g = {k: z[k] for k in z.files}
+    B, S, D = g["input"].shape
+    dev = lambda k: to_dev(g[k], torch.float32)  # noqa: E731
+    word = torch.zeros(4, D, device="cuda")
+    # parameter order of the module: word, token type, position, layer_norm.weight, layer_norm.bias
+    names, out = host.bert_embedding_module_step(D, 4, g["type"].shape[0], g["pos"].shape[0], dev("input"), dev("dy"),
+                                                 [word, dev("type"), dev("pos"), dev("gamma"), dev("beta")])
+    y, dword, dtype, dpos, dgamma, dbeta, dinput = out
+    tol.fp32_close(y.cpu().numpy(), g["y_f32"], rtol=2e-5, atol=2e-6)
+    np.testing.assert_allclose(dinput.cpu().numpy(), g["dinput_f64"], rtol=2e-5, atol=2e-4)
+    np.testing.assert_allclose(dpos.cpu().numpy(), g["dpos_f64"], rtol=2e-5, atol=2e-4)
+    np.testing.assert_allclose(dtype.cpu().numpy(), g["dtype_f64"], rtol=2e-5, atol=2e-4)
+    tol.long_sum_close(dgamma.cpu().numpy(), g["dgamma_f64"], B * S, ref32=g["dgamma_f32"])
+    tol.long_sum_close(dbeta.cpu().numpy(), g["dbeta_f64"], B * S, ref32=g["dbeta_f32"])
+    assert float(dword.abs().sum()) == 0.0                  # the word table is not part of this branch
+    with pytest.raises(Exception, match="expected last dimension"):
+        host.bert_embedding_module_step(D, 4, 2, 16, torch.zeros(2, 3, D + 1, device="cuda"), torch.zeros(2, 3, D + 1, device="cuda"), [])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("D,B,S,use_pos,use_type", [(768, 8, 128, True, True), (1024, 3, 77, True, False), (100, 2, 9, False, True),
+                                                    (96, 2, 5, False, False)])
+def test_ready_made_embeddings_against_oracle(dtype, D, B, S, use_pos, use_type):
+    eps = 1e-5
+    inp, inn = make((B, S, D), 1, dtype, 0.5)
+    pos, pn = make((max(S, 16), D), 2, dtype, 0.5) if use_pos else (None, None)
+    typ, tn = make((2, D), 3, dtype, 0.5) if use_type else (None, None)
+    gamma, gn = make((D,), 4, dtype, 0.02, 1.0); beta, bn = make((D,), 5, dtype, 0.02)
+    dy, dyn = make((B, S, D), 7, dtype)
+    L = abi.lib()
+    import ctypes
+    P = lambda t: None if t is None else ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    code = abi.dtype_code(dtype)
+    y = torch.empty_like(inp); ssum = torch.empty(B * S, D, dtype=dtype, device="cuda")
+    mean = torch.empty(B * S, device="cuda"); rstd = torch.empty(B * S, device="cuda")
+    abi.check(L.nb2_bert_embedding_ln_fwd(P(inp), P(pos), P(typ), None, P(gamma), P(beta), P(ssum), P(y), P(mean), P(rstd),
+                                          B, S, 1, D, eps, code, abi.I64, None, None))
+    ref = O.bert_embedding(inn, pn, tn, gn, bn, None, dyn, eps, bf16=dtype == torch.bfloat16)
+    if dtype == torch.float32:
+        assert np.array_equal(ssum.cpu().numpy(), ref["sum"])
+    else:
+        assert np.array_equal(bits(ssum), tol.to_bf16_bits(ref["sum"]))
+    check(y.reshape(B * S, D), ref["y"].reshape(B * S, D), "y")
+    dsum = torch.empty_like(ssum)
+    pos_rows = pos.shape[0] if use_pos else 0
+    dpos = torch.empty(pos_rows, D, dtype=dtype, device="cuda") if use_pos else None
+    dtype0 = torch.empty(D, dtype=dtype, device="cuda") if use_type else None
+    grads = torch.empty(2, D, device="cuda")
+    ws_bytes = abi.workspace_bytes(abi.WS_BERT_EMBEDDING_BWD, (B << 32) | S, ((B * S) << 32) | D, code)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+    abi.check(L.nb2_bert_embedding_ln_bwd(P(ssum), P(dy), None, P(gamma), P(mean), P(rstd), P(dsum), None, P(dpos), pos_rows,
+                                          P(dtype0), P(grads), B, S, B * S, D, code, abi.I64, P(ws), ws_bytes, None))
+    check(dsum, ref["dsum"] if dtype == torch.float32 else O.layernorm_act(ref["sum"], gn, bn, dyn.reshape(B * S, D), eps)["dx"], "dsum")
+    ds = dsum.float().cpu().numpy().astype(np.float64)
+    if use_pos:
+        full = np.zeros((pos_rows, D)); full[:S] = ds.reshape(B, S, D).sum(axis=0)
+        check(dpos, full, "dpos")
+    if use_type:
+        if dtype == torch.float32:
+            tol.long_sum_close(dtype0.cpu().numpy(), ds.sum(axis=0), B * S)
+        else:
+            tol.bf16_ulp_close(bits(dtype0), ds.sum(axis=0))
+    tol.long_sum_close(grads[0].cpu().numpy(), ref["dgamma"], B * S)
+    tol.long_sum_close(grads[1].cpu().numpy(), ref["dbeta"], B * S)
+    assert abi.device_status() == 0

@@ -131,6 +131,20 @@ def test_bert_embedding_oracle_matches_reference_module(golden_dir):
     tol.long_sum_close(o["dbeta"], g["dbeta_f64"], 21, ref32=g["dbeta_f32"])
 
 
+def test_bert_embedding_oracle_with_ready_made_embeddings(golden_dir):
+    """The module's other input branch (bert.hpp:164-171): a float [B, S, D] input is the embeddings themselves."""
+    g = load(golden_dir, "bert_embedding_float_input")
+    B, S, D = g["input"].shape
+    o = O.bert_embedding(g["input"], g["pos"], g["type"], g["gamma"], g["beta"], None, g["dy"])
+    tol.fp32_close(o["y"], g["y_f32"], rtol=2e-5, atol=2e-6)
+    np.testing.assert_allclose(o["y"], g["y_f64"], rtol=2e-6, atol=2e-6)
+    np.testing.assert_allclose(o["dsum"].reshape(B, S, D), g["dinput_f64"], rtol=1e-5, atol=1e-4)
+    np.testing.assert_allclose(o["dpos"], g["dpos_f64"][:S], rtol=1e-5, atol=1e-4)
+    np.testing.assert_allclose(o["dtype0"], g["dtype_f64"][0], rtol=1e-5, atol=1e-4)
+    tol.long_sum_close(o["dgamma"], g["dgamma_f64"], B * S, ref32=g["dgamma_f32"])
+    tol.long_sum_close(o["dbeta"], g["dbeta_f64"], B * S, ref32=g["dbeta_f32"])
+
+
 ATTN_CASES = {"plain": (None, None, False), "causal": (None, None, True), "padding": ("padding", None, False),
               "mask2": (None, "mask2", False), "mask3_padding": ("padding", "mask3", False), "mask4_causal": (None, "mask4", True)}
 
