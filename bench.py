@@ -399,7 +399,13 @@ def _suite_attention(abi, timed, dev, g):
         timed(f"attention_softmax_fwd {nm} [16,16,1024,1024] + mask [16,1024,1024]",
               lambda: abi.attention_softmax_fwd(sc, 0.125, attn_mask=mk), 2 * sc.numel() * e + mk.numel() * e)
         timed(f"attention_softmax_bwd {nm} [16,16,1024,1024]", lambda: abi.attention_softmax_bwd(at, da_, 0.125), 3 * sc.numel() * e)
-        del sc, da_, at, mk
+        # with the dropout that follows (kernel.hpp:94): noise read in the same pass; training also writes the probabilities
+        nz = ((torch.rand(16, 16, 1024, 1024, device=dev, generator=g) >= 0.1).float() / 0.9).to(dt)
+        timed(f"attention_softmax+dropout_fwd {nm} [16,16,1024,1024] causal (2 reads, 2 writes)",
+              lambda: abi.attention_softmax_fwd(sc, 0.125, causal=True, noise=nz), 4 * sc.numel() * e)
+        timed(f"attention_softmax+dropout_bwd {nm} [16,16,1024,1024] (3 reads, 1 write)",
+              lambda: abi.attention_softmax_bwd(at, da_, 0.125, noise=nz), 4 * sc.numel() * e)
+        del sc, da_, at, mk, nz
 
 
 # ------------------------------------------------------------ cfg5 sweep

@@ -377,6 +377,26 @@ int nb2_attention_softmax_fwd(const void* scores, const uint8_t* key_padding, co
 int nb2_attention_softmax_bwd(const void* attn, const void* dattn, void* dscores,
                               int64_t rows, int64_t S, double scale, int dtype, void* stream);
 
+/*
+ * The same pass with the dropout that follows it (kernel.hpp:94 `attn = dropout_->forward(attn)`;
+ * also the multiplicative-noise module of src/layer/details/dropout.hpp:32-51,
+ * `input * N(1, sqrt(p/(1-p)))`):   out = attn * noise,
+ * where `noise` ([B, H, T, S], `dtype`) is drawn by the caller with libtorch -- a Bernoulli keep
+ * mask divided by 1-p for torch::nn::Dropout, empty_like(attn).normal_(1, std) for the noise
+ * module -- so the random stream is the host framework's and results are reproducible against
+ * the reference given the same tensor.  attn (rounded to `dtype`, as the reference's tensor is) is
+ * also written to attn_pre when that is non-NULL: the backward needs it.
+ * bwd: dattn = dout * noise (rounded to `dtype`), then the softmax backward above; 3 reads and 1
+ * write where the reference's autograd makes 2 passes (4 reads, 2 writes).
+ */
+int nb2_attention_softmax_dropout_fwd(const void* scores, const uint8_t* key_padding, const void* attn_mask,
+                                      int64_t mask_batch_stride, int64_t mask_head_stride,
+                                      const void* noise, void* attn_pre, void* out,
+                                      int64_t B, int64_t H, int64_t T, int64_t S, double scale, int causal,
+                                      int dtype, void* stream);
+int nb2_attention_softmax_dropout_bwd(const void* attn_pre, const void* noise, const void* dout, void* dscores,
+                                      int64_t rows, int64_t S, double scale, int dtype, void* stream);
+
 /* ------------------------------------------------------------------ *
  * Host-buffer training step of the fused LayerNorm->activation path: the call
  * a host-resident caller makes (the reference stages batches from pinned host

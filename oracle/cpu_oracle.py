@@ -174,18 +174,22 @@ def _mask_strides(attn_mask, B, H, T, S):
     return H * T * S, T * S
 
 
-def attention_softmax(scores, scale, key_padding=None, attn_mask=None, causal=False, dattn=None):
-    """scores [B,H,T,S] fp32 -> dict(attn, dscores) in fp64 (kernel.hpp:33-93)."""
-    scores, attn_mask, dattn = _f32(scores), _f32(attn_mask), _f32(dattn)
+def attention_softmax(scores, scale, key_padding=None, attn_mask=None, causal=False, dattn=None, noise=None):
+    """scores [B,H,T,S] fp32 -> dict(attn, dscores) in fp64 (kernel.hpp:33-93).  With `noise` (the dropout's
+    multiplicative noise, kernel.hpp:94 / dropout.hpp:41-43) also `dropped` = attn * noise, and dattn is the
+    gradient of `dropped`."""
+    scores, attn_mask, dattn, noise = _f32(scores), _f32(attn_mask), _f32(dattn), _f32(noise)
     B, H, T, S = scores.shape
     kp = None if key_padding is None else np.ascontiguousarray(key_padding, dtype=np.uint8)
     sb, sh = _mask_strides(attn_mask, B, H, T, S)
     attn = np.empty(scores.shape)
     ds = np.empty(scores.shape) if dattn is not None else None
+    dropped = np.empty(scores.shape) if noise is not None else None
     with np.errstate(invalid="ignore"):
-        lib().orc_attention_softmax(_p(scores), _p(kp), _p(attn_mask), c_int64(sb), c_int64(sh), _p(dattn), c_int64(B), c_int64(H),
-                                    c_int64(T), c_int64(S), c_double(scale), c_int(int(causal)), _p(attn), _p(ds))
-    return dict(attn=attn, dscores=ds)
+        lib().orc_attention_softmax_noise(_p(scores), _p(kp), _p(attn_mask), c_int64(sb), c_int64(sh), _p(dattn), _p(noise), c_int64(B),
+                                          c_int64(H), c_int64(T), c_int64(S), c_double(scale), c_int(int(causal)), _p(attn), _p(dropped),
+                                          _p(ds))
+    return dict(attn=attn, dscores=ds, dropped=dropped)
 
 
 def _round_bf16(a):

@@ -248,9 +248,25 @@ void orc_rope_apply(const float* x, const float* cos_sin, int64_t B, int64_t S, 
  * A row with every column masked is NaN, as torch::softmax makes it.
  * Backward of softmax and of the scaling: dscores = scale * attn * (dattn - sum_s attn * dattn).
  */
+void orc_attention_softmax_noise(const float* scores, const uint8_t* key_padding, const float* mask, int64_t mask_sb,
+                                 int64_t mask_sh, const float* dattn, const float* noise, int64_t B, int64_t H, int64_t T,
+                                 int64_t S, double scale, int causal, double* attn, double* dropped, double* dscores);
+
 void orc_attention_softmax(const float* scores, const uint8_t* key_padding, const float* mask, int64_t mask_sb,
                            int64_t mask_sh, const float* dattn, int64_t B, int64_t H, int64_t T, int64_t S,
                            double scale, int causal, double* attn, double* dscores) {
+    orc_attention_softmax_noise(scores, key_padding, mask, mask_sb, mask_sh, dattn, NULL, B, H, T, S, scale, causal, attn, NULL,
+                                dscores);
+}
+
+/*
+ * The same with the dropout that follows the softmax in the reference (src/attention/details/kernel.hpp:94;
+ * multiplicative-noise form of src/layer/details/dropout.hpp:41-43): dropped = attn * noise for a given noise
+ * tensor.  dattn is then the gradient of `dropped`: the gradient reaching attn is dattn * noise.
+ */
+void orc_attention_softmax_noise(const float* scores, const uint8_t* key_padding, const float* mask, int64_t mask_sb,
+                                 int64_t mask_sh, const float* dattn, const float* noise, int64_t B, int64_t H, int64_t T,
+                                 int64_t S, double scale, int causal, double* attn, double* dropped, double* dscores) {
     double* row = (double*)malloc(sizeof(double) * (size_t)(S > 0 ? S : 1));
     for (int64_t b = 0; b < B; ++b)
         for (int64_t h = 0; h < H; ++h)
@@ -270,12 +286,17 @@ void orc_attention_softmax(const float* scores, const uint8_t* key_padding, cons
                 for (int64_t s = 0; s < S; ++s) { row[s] = exp(row[s] - mx); sum += row[s]; }
                 double dot = 0.0;
                 for (int64_t s = 0; s < S; ++s) {
+                    const double nz = noise ? (double)noise[r * S + s] : 1.0;
                     row[s] /= sum;
                     if (attn) attn[r * S + s] = row[s];
-                    if (dattn) dot += row[s] * (double)dattn[r * S + s];
+                    if (dropped) dropped[r * S + s] = row[s] * nz;
+                    if (dattn) dot += row[s] * (double)dattn[r * S + s] * nz;
                 }
                 if (dattn && dscores)
-                    for (int64_t s = 0; s < S; ++s) dscores[r * S + s] = scale * row[s] * ((double)dattn[r * S + s] - dot);
+                    for (int64_t s = 0; s < S; ++s) {
+                        const double nz = noise ? (double)noise[r * S + s] : 1.0;
+                        dscores[r * S + s] = scale * row[s] * ((double)dattn[r * S + s] * nz - dot);
+                    }
             }
     free(row);
 }

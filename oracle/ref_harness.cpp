@@ -14,6 +14,7 @@
 //   - torch::nn::LayerNorm built the way the blocks build it
 //     src/block/details/transformers/classic.hpp:399-404 (options :54-57)
 //   - EBT TokenEmbedding (nn::Embedding gather)   src/block/details/transformers/ebt.hpp:81-160
+//   - HardDropout: input * N(1, sqrt(p/(1-p)))   src/layer/details/dropout.hpp:23-58
 //   - BertEmbedding (word + position + type gathers, LayerNorm eps 1e-12)
 //                                                 src/block/details/transformers/bert.hpp:116-204
 //
@@ -31,6 +32,7 @@
 #include "src/block/details/transformers/mamba.hpp"
 #include "src/block/details/transformers/ebt.hpp"
 #include "src/attention/details/kernel.hpp"
+#include "src/layer/details/dropout.hpp"
 
 // bert.hpp pulls in src/layer/details/recurrent.hpp, which calls an overload of
 // at::Context::setFloat32Precision that libtorch 2.11 no longer has (four lines that set
@@ -420,6 +422,49 @@ int ref_attention_softmax(const float* query, const uint8_t* key_padding, const 
         store(out, attn);
         if (dattn != nullptr) {
             (out * wrap(dattn, {B, H, T, S}, compute)).sum().backward();
+            store(q.grad(), dscores);
+        }
+    });
+}
+
+// Attention probabilities followed by the reference's multiplicative-noise dropout
+// (src/layer/details/dropout.hpp:32-51: eps = empty_like(input).normal_(1, sqrt(p/(1-p))), output = input * eps).
+// The module draws eps from libtorch's default generator; seeding it with `seed` right before the module runs and
+// again before an identical normal_ call here yields the very tensor the module used, which is returned as `noise`
+// so that another implementation can be fed the same values.  dout is the gradient of the dropped probabilities.
+int ref_attention_softmax_dropout(const float* query, const uint8_t* key_padding, const float* attn_mask, int mask_dims,
+                                  const float* dout, int64_t B, int64_t H, int64_t T, int64_t S, int causal, double p,
+                                  int64_t seed, int compute, float* attn, float* noise, float* out, float* dscores) {
+    return guarded([&] {
+        namespace A = Nott::Attention;
+        namespace L = Nott::Layer::Details;
+        A::Details::ScaledDotProductKernel kernel(0.0, causal ? A::Variant::Causal : A::Variant::Full);
+        const auto dt = compute_type(compute);
+        auto q = wrap(query, {B, H, T, S}, compute).clone().requires_grad_(dout != nullptr);
+        auto eye = torch::eye(S, torch::TensorOptions().dtype(dt)).expand({B, H, S, S});
+        torch::Tensor mask, padding;
+        if (attn_mask != nullptr) {
+            std::vector<int64_t> shape = mask_dims == 2 ? std::vector<int64_t>{T, S}
+                                         : mask_dims == 3 ? std::vector<int64_t>{B, T, S} : std::vector<int64_t>{B, H, T, S};
+            mask = wrap(attn_mask, shape, compute);
+        }
+        if (key_padding != nullptr)
+            padding = torch::from_blob(const_cast<uint8_t*>(key_padding), {B, S}, torch::kUInt8).to(torch::kBool);
+        auto probs = kernel->forward(q, eye, eye, mask, padding);
+        store(probs, attn);
+        L::HardDropoutOptions options;
+        options.probability = p;
+        L::HardDropout drop(options);
+        drop->train();
+        torch::manual_seed(static_cast<uint64_t>(seed));
+        auto dropped = drop->forward(probs);
+        store(dropped, out);
+        torch::manual_seed(static_cast<uint64_t>(seed));
+        auto eps = torch::empty_like(probs).normal_(1.0, std::sqrt(p / (1.0 - p)));
+        store(eps, noise);
+        if (!torch::equal(dropped.detach(), (probs * eps).detach())) throw std::runtime_error("the re-drawn noise is not the module's");
+        if (dout != nullptr) {
+            (dropped * wrap(dout, {B, H, T, S}, compute)).sum().backward();
             store(q.grad(), dscores);
         }
     });

@@ -186,6 +186,22 @@ def attention_softmax(scores, key_padding=None, attn_mask=None, causal=False, da
     return dict(attn=attn, dscores=ds)
 
 
+def attention_softmax_dropout(scores, p, seed, key_padding=None, attn_mask=None, causal=False, dout=None, compute=0):
+    """ScaledDotProductKernel's probabilities (key = value = identity) followed by the reference's HardDropout
+    (input * N(1, sqrt(p/(1-p)))) seeded with `seed`; also returns the noise tensor the module drew."""
+    scores, attn_mask, dout = _f32(scores), _f32(attn_mask), _f32(dout)
+    B, H, T, S = scores.shape
+    kp = None if key_padding is None else np.ascontiguousarray(key_padding, dtype=np.uint8)
+    attn = np.empty(scores.shape, dtype=np.float32); noise = np.empty(scores.shape, dtype=np.float32)
+    out = np.empty(scores.shape, dtype=np.float32)
+    ds = np.empty(scores.shape, dtype=np.float32) if dout is not None else None
+    dims = 0 if attn_mask is None else attn_mask.ndim
+    _chk(lib().ref_attention_softmax_dropout(_p(scores), _p(kp), _p(attn_mask), c_int(dims), _p(dout), c_int64(B), c_int64(H),
+                                             c_int64(T), c_int64(S), c_int(int(causal)), c_double(p), c_int64(seed), c_int(compute),
+                                             _p(attn), _p(noise), _p(out), _p(ds)))
+    return dict(attn=attn, noise=noise, out=out, dscores=ds)
+
+
 def time_norm_act(kind, rows, D, eps, act, compute=0, iters=10, warmup=2) -> float:
     """Seconds per forward+backward of the reference modules, timed inside the harness."""
     t = lib().ref_time_norm_act(c_int(1 if kind == "rms" else 0), c_int64(rows), c_int64(D), c_double(eps),

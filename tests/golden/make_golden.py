@@ -164,6 +164,15 @@ def main():
             rec[f"{name}_attn_{tag}"] = r["attn"]
             rec[f"{name}_dscores_{tag}"] = r["dscores"]
     np.savez(OUT / "attention_softmax.npz", **rec)
+    # ... followed by the reference's multiplicative-noise dropout (dropout.hpp:32-51), p = 0.25, seeded; the stored
+    # noise is the tensor the module drew
+    drop = dict(scores=scores, dout=dattn, padding=padding, mask3=rec["mask3"], p=0.25, seed=1234)
+    for name, (pk, mk, causal) in {"plain": (None, None, False), "mask3_padding_causal": ("padding", "mask3", True)}.items():
+        for tag, compute in (("f32", 0), ("f64", 1)):
+            r = R.attention_softmax_dropout(scores, 0.25, 1234, rec[pk] if pk else None, rec[mk] if mk else None, causal, dattn, compute)
+            for k, v in r.items():
+                drop[f"{name}_{k}_{tag}"] = v
+    np.savez(OUT / "attention_softmax_dropout.npz", **drop)
     print("wrote", sorted(p.name for p in OUT.glob("*.npz")))
 
 

@@ -126,3 +126,97 @@ def test_full_size_properties_bf16():
     # softmax backward is orthogonal to the all-ones direction: every row of dscores sums to ~0
     assert ds.float().sum(-1).abs().max() < 2e-2
     assert not torch.triu(ds[2, 2], 1).any()
+
+
+# ---- the dropout that follows the softmax, in the same pass (kernel.hpp:94; dropout.hpp:32-51)
+@pytest.mark.parametrize("name", ["plain", "mask3_padding_causal"])
+def test_dropout_golden_reference_modules(golden_dir, name):
+    """Golden = the reference's ScaledDotProductKernel probabilities followed by its HardDropout module
+    (input * N(1, sqrt(p/(1-p)))), with the noise tensor that module drew."""
+    z = np.load(golden_dir / "attention_softmax_dropout.npz")
+    scores = to_dev(z["scores"], torch.float32)
+    S = scores.shape[-1]
+    use = name != "plain"
+    padding = torch.from_numpy(z["padding"]).cuda() if use else None
+    mask = torch.from_numpy(z["mask3"]).cuda() if use else None
+    noise = to_dev(z[f"{name}_noise_f32"], torch.float32)
+    out, pre = abi.attention_softmax_fwd(scores, 1.0 / math.sqrt(S), padding, mask, use, noise=noise)
+    check(pre, z[f"{name}_attn_f64"], "attn")
+    check(out, z[f"{name}_out_f32"], "dropped (reference fp32)")
+    check(out, z[f"{name}_attn_f64"].astype(np.float64) * z[f"{name}_noise_f32"], "dropped")
+    ds = abi.attention_softmax_bwd(pre, to_dev(z["dout"], torch.float32), 1.0 / math.sqrt(S), noise=noise)
+    check(ds, z[f"{name}_dscores_f32"], "dscores (reference fp32)")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("B,H,T,S,use_mask,causal,bernoulli", [
+    (2, 4, 128, 128, False, True, True),
+    (1, 2, 64, 512, True, False, False),
+    (2, 2, 16, 2048, True, False, True),
+    (2, 3, 9, 77, True, True, False),         # ragged length: the three-sweep kernel
+])
+def test_dropout_against_oracle(dtype, B, H, T, S, use_mask, causal, bernoulli):
+    p = 0.2
+    scores, sn = make((B, H, T, S), 1, dtype, 2.0)
+    dout, dn = make((B, H, T, S), 2, dtype)
+    mask, mn = make((B, T, S), 3, dtype) if use_mask else (None, None)
+    gen = torch.Generator().manual_seed(9)
+    if bernoulli:      # torch::nn::Dropout's form: keep mask over 1-p (1.25 is a bf16 number)
+        noise_t = (torch.rand(B, H, T, S, generator=gen) >= p).float() / (1 - p)
+    else:              # the multiplicative-noise module: N(1, sqrt(p/(1-p)))
+        noise_t = 1 + math.sqrt(p / (1 - p)) * torch.randn(B, H, T, S, generator=gen)
+    noise_t = noise_t.to(dtype)
+    nn_ = noise_t.float().numpy()
+    scale = 0.125
+    out, pre = abi.attention_softmax_fwd(scores, scale, None, mask, causal, noise=noise_t.cuda())
+    ref = O.attention_softmax(sn, scale, None, mn, causal, None)
+    check(pre.reshape(-1, S), ref["attn"].reshape(-1, S), "attn before the noise")
+    # the dropped probabilities are the STORED probabilities times the noise, rounded once
+    pn = pre.float().cpu().numpy().astype(np.float64)
+    check(out.reshape(-1, S), (pn * nn_).reshape(-1, S), "dropped")
+    assert torch.equal(pre, abi.attention_softmax_fwd(scores, scale, None, mask, causal))         # same bits as the plain call
+    out_only, none = abi.attention_softmax_fwd(scores, scale, None, mask, causal, noise=noise_t.cuda(), want_pre=False)
+    assert none is None and torch.equal(out_only, out)
+    # backward: the gradient of the probabilities is dout * noise as a tensor of the activation type
+    ds = abi.attention_softmax_bwd(pre, dout, scale, noise=noise_t.cuda())
+    if dtype == torch.float32:
+        dattn = (dn.astype(np.float32) * nn_).astype(np.float64)
+    else:
+        from tests import tol
+        dattn = tol.bf16_bits_to_f32(tol.to_bf16_bits(dn.astype(np.float64) * nn_)).astype(np.float64).reshape(dn.shape)
+    dot = (pn * dattn).sum(-1, keepdims=True)
+    check(ds.reshape(-1, S), (scale * pn * (dattn - dot)).reshape(-1, S), "dscores")
+    # and it equals the two-step form: a separate multiply, then the plain softmax backward
+    two_step = abi.attention_softmax_bwd(pre, (dout.float() * noise_t.cuda().float()).to(dtype), scale)
+    assert torch.equal(ds, two_step)
+
+
+def test_dropout_module_matches_torch_ops_given_the_same_noise():
+    from thot_b200 import _nott_b200_host as host
+    B, H, T, S, hd = 2, 3, 40, 56, 32
+    q, _ = make((B, H, T, hd), 1, torch.float32); k, _ = make((B, H, S, hd), 2, torch.float32); v, _ = make((B, H, S, hd), 3, torch.float32)
+    dout, _ = make((B, H, T, hd), 5, torch.float32)
+    p = 0.3
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    noise = (torch.rand(B, H, T, S, device="cuda", generator=gen) >= p).float() / (1 - p)
+
+    def reference(q, k, v):
+        attn = torch.softmax(torch.matmul(q, k.transpose(-2, -1)) / math.sqrt(hd), -1)
+        return torch.matmul(attn * noise, v)
+
+    res = []
+    for fn in (reference, lambda q, k, v: host.scaled_dot_product_dropout(q, k, v, noise, p, False)):
+        qi, ki, vi = (t.clone().requires_grad_(True) for t in (q, k, v))
+        out = fn(qi, ki, vi)
+        out.backward(dout)
+        res.append((out.detach(), qi.grad, ki.grad, vi.grad))
+    for got, want in zip(res[1], res[0]):
+        torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-5)
+    # the module's own draw: about a fraction p of the probabilities is dropped and the rest is scaled by 1/(1-p)
+    vi = torch.eye(S, device="cuda").expand(B, H, S, S).contiguous()
+    kept = host.scaled_dot_product_dropout(q, k, vi, None, p, False)       # value = identity: the output is attn * noise
+    plain = torch.softmax(torch.matmul(q, k.transpose(-2, -1)) / math.sqrt(hd), -1)
+    ratio = kept / plain
+    dropped = (kept == 0).float().mean().item()
+    assert abs(dropped - p) < 0.03
+    assert torch.allclose(ratio[kept != 0], torch.full_like(ratio[kept != 0], 1 / (1 - p)), rtol=1e-4)

@@ -172,3 +172,22 @@ def test_attention_softmax_oracle_fully_masked_row_is_nan():
     padding = np.ones((1, 4), np.uint8)
     o = O.attention_softmax(scores, 0.5, padding)
     assert np.isnan(o["attn"]).all()                     # torch::softmax of a row of -inf
+
+
+@pytest.mark.parametrize("name", ["plain", "mask3_padding_causal"])
+def test_attention_dropout_oracle_matches_reference_modules(golden_dir, name):
+    """Golden = ScaledDotProductKernel's probabilities followed by the reference's HardDropout module
+    (dropout.hpp:32-51), with the noise that module drew from the seeded generator."""
+    g = load(golden_dir, "attention_softmax_dropout")
+    use = name != "plain"
+    S = g["scores"].shape[-1]
+    for tag in ("f32", "f64"):
+        noise = g[f"{name}_noise_{tag}"]
+        o = O.attention_softmax(g["scores"], 1.0 / np.sqrt(S), g["padding"] if use else None, g["mask3"] if use else None, use,
+                                g["dout"], noise=noise)
+        tol.fp32_close(o["attn"], g[f"{name}_attn_{tag}"])
+        tol.fp32_close(o["dropped"], g[f"{name}_out_{tag}"], rtol=2e-5, atol=2e-6)
+        tol.fp32_close(o["dscores"], g[f"{name}_dscores_{tag}"], rtol=2e-5, atol=2e-6)
+    # the module's noise has the moments it should: mean 1, std sqrt(p/(1-p))
+    p = float(g["p"])
+    assert abs(g["plain_noise_f32"].mean() - 1.0) < 0.05 and abs(g["plain_noise_f32"].std() - np.sqrt(p / (1 - p))) < 0.05

@@ -35,6 +35,9 @@ _SIGNATURES = {
     "nb2_attention_softmax_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                           c_double, c_int, c_int, c_void_p]),
     "nb2_attention_softmax_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_double, c_int, c_void_p]),
+    "nb2_attention_softmax_dropout_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
+                                                  c_int64, c_int64, c_int64, c_int64, c_double, c_int, c_int, c_void_p]),
+    "nb2_attention_softmax_dropout_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_double, c_int, c_void_p]),
     "nb2_selftest_bounded_wait": (c_int, [c_int64, c_void_p, c_void_p]),
     "nb2_workspace_bytes": (c_size_t, [c_int, c_int64, c_int64, c_int]),
     "nb2_layernorm_fwd": (c_int, [c_void_p] * 6 + [c_int64, c_int64, c_double, c_int, c_int, c_void_p]),
@@ -376,9 +379,11 @@ def bert_embedding_ln_bwd(ssum, dy, ids, gamma, mean, rstd, vocab: int, pos_rows
 
 
 # ------------------------------------------------------------------ attention
-def attention_softmax_fwd(scores, scale: float, key_padding=None, attn_mask=None, causal: bool = False):
+def attention_softmax_fwd(scores, scale: float, key_padding=None, attn_mask=None, causal: bool = False, noise=None,
+                          want_pre: bool = True):
     """scores [B, H, T, S] -> attn.  key_padding [B, S] bool/uint8; attn_mask additive, [T,S], [B,T,S],
-    [B*H,T,S] or [B,H,T,S] of the scores' dtype."""
+    [B*H,T,S] or [B,H,T,S] of the scores' dtype.  With `noise` ([B,H,T,S], the dropout's multiplicative
+    noise) returns (attn * noise, attn before the noise or None)."""
     _dev(scores)
     B, H, T, S = scores.shape
     out = torch.empty_like(scores)
@@ -393,15 +398,25 @@ def attention_softmax_fwd(scores, scale: float, key_padding=None, attn_mask=None
             raise ValueError("attention mask must be [T,S], [B,T,S], [B*H,T,S] or [B,H,T,S]")
     if key_padding is not None:
         key_padding = key_padding.to(torch.uint8).contiguous()
+    if noise is not None:
+        pre = torch.empty_like(scores) if want_pre else None
+        check(lib().nb2_attention_softmax_dropout_fwd(_p(scores), _p(key_padding), _p(attn_mask), sb, sh, _p(noise.contiguous()), _p(pre),
+                                                      _p(out), B, H, T, S, scale, int(causal), dtype_code(scores.dtype), _stream()))
+        return out, pre
     check(lib().nb2_attention_softmax_fwd(_p(scores), _p(key_padding), _p(attn_mask), sb, sh, _p(out), B, H, T, S, scale,
                                           int(causal), dtype_code(scores.dtype), _stream()))
     return out
 
 
-def attention_softmax_bwd(attn, dattn, scale: float):
+def attention_softmax_bwd(attn, dattn, scale: float, noise=None):
+    """noise given: `attn` is the probabilities before the noise and `dattn` the gradient of attn * noise."""
     _dev(attn)
     S = attn.shape[-1]
     out = torch.empty_like(attn)
+    if noise is not None:
+        check(lib().nb2_attention_softmax_dropout_bwd(_p(attn), _p(noise.contiguous()), _p(dattn), _p(out), attn.numel() // max(S, 1), S,
+                                                      scale, dtype_code(attn.dtype), _stream()))
+        return out
     check(lib().nb2_attention_softmax_bwd(_p(attn), _p(dattn), _p(out), attn.numel() // max(S, 1), S, scale,
                                           dtype_code(attn.dtype), _stream()))
     return out

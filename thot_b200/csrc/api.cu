@@ -489,6 +489,35 @@ int nb2_attention_softmax_bwd(const void* attn, const void* dattn, void* dscores
     return launch_attention_softmax_bwd(attn, dattn, dscores, rows, S, (float)scale, dtype, (cudaStream_t)stream);
 }
 
+int nb2_attention_softmax_dropout_fwd(const void* scores, const uint8_t* key_padding, const void* attn_mask,
+                                      int64_t mask_batch_stride, int64_t mask_head_stride, const void* noise, void* attn_pre,
+                                      void* out, int64_t B, int64_t H, int64_t T, int64_t S, double scale, int causal, int dtype,
+                                      void* stream) {
+    NB2_REQUIRE(dtype_ok(dtype), NB2_ERR_DTYPE, "attention softmax + dropout: dtype=%d", dtype);
+    NB2_REQUIRE(B >= 0 && H >= 0 && T >= 0 && S >= 0 && S < ((int64_t)1 << 31) && H < ((int64_t)1 << 30) && T < ((int64_t)1 << 30) &&
+                    mask_batch_stride >= 0 && mask_head_stride >= 0,
+                NB2_ERR_SHAPE, "attention softmax + dropout: B=%lld H=%lld T=%lld S=%lld mask strides %lld, %lld", (long long)B,
+                (long long)H, (long long)T, (long long)S, (long long)mask_batch_stride, (long long)mask_head_stride);
+    if (B * H * T * S == 0) return 0;
+    NB2_REQUIRE(scores != nullptr && out != nullptr && noise != nullptr, NB2_ERR_NULL, "attention softmax + dropout: NULL scores, noise or output");
+    int rc = require_device();
+    if (rc != 0) return rc;
+    return launch_attention_softmax_fwd(scores, key_padding, attn_mask, mask_batch_stride, mask_head_stride, out, B, H, T, S,
+                                        (float)scale, causal != 0, dtype, (cudaStream_t)stream, noise, attn_pre);
+}
+int nb2_attention_softmax_dropout_bwd(const void* attn_pre, const void* noise, const void* dout, void* dscores, int64_t rows,
+                                      int64_t S, double scale, int dtype, void* stream) {
+    NB2_REQUIRE(dtype_ok(dtype), NB2_ERR_DTYPE, "attention softmax + dropout bwd: dtype=%d", dtype);
+    NB2_REQUIRE(rows >= 0 && S >= 0 && S < ((int64_t)1 << 31), NB2_ERR_SHAPE, "attention softmax + dropout bwd: rows=%lld S=%lld",
+                (long long)rows, (long long)S);
+    if (rows * S == 0) return 0;
+    NB2_REQUIRE(attn_pre != nullptr && noise != nullptr && dout != nullptr && dscores != nullptr, NB2_ERR_NULL,
+                "attention softmax + dropout bwd: NULL tensor");
+    int rc = require_device();
+    if (rc != 0) return rc;
+    return launch_attention_softmax_bwd(attn_pre, dout, dscores, rows, S, (float)scale, dtype, (cudaStream_t)stream, noise);
+}
+
 int nb2_rope_table(float* cos_sin, const int32_t* positions, int64_t S, int64_t hd, double theta, void* stream) {
     NB2_REQUIRE(S >= 0 && hd >= 2 && hd % 2 == 0, NB2_ERR_SHAPE, "rope table: S=%lld head_dim=%lld (need an even head_dim >= 2)", (long long)S, (long long)hd);
     NB2_REQUIRE(theta > 0.0, NB2_ERR_SHAPE, "rope table: theta=%g must be positive", theta);

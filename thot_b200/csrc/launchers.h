@@ -33,8 +33,8 @@ int launch_rope_apply(const void* x, const float* cos_sin, void* out, int64_t B,
 
 int launch_attention_softmax_fwd(const void* scores, const uint8_t* key_padding, const void* add_mask, int64_t mask_sb,
                                  int64_t mask_sh, void* out, int64_t B, int64_t H, int64_t Tq, int64_t S, float scale,
-                                 int causal, int dtype, cudaStream_t st);
+                                 int causal, int dtype, cudaStream_t st, const void* noise = nullptr, void* pre_out = nullptr);
 int launch_attention_softmax_bwd(const void* attn, const void* dattn, void* dscores, int64_t rows, int64_t S, float scale,
-                                 int dtype, cudaStream_t st);
+                                 int dtype, cudaStream_t st, const void* noise = nullptr);
 
 }  // namespace nb2

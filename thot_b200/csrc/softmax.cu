@@ -3,6 +3,10 @@
 // which the reference's ScaledDotProductKernelImpl::forward (src/attention/details/kernel.hpp:33-92)
 // forms as a division, two masked_fill, an add and a softmax, each a full read and write of
 // [B, H, T, S].  Backward: dscores = scale * attn * (dattn - sum_j attn * dattn).
+// Optionally the dropout that follows (kernel.hpp:94; the multiplicative-noise form of
+// src/layer/details/dropout.hpp:32-51) rides in the same pass: out = attn * noise with a noise
+// tensor the caller drew (a Bernoulli mask over 1-p, or N(1, sqrt(p/(1-p)))), so the random stream
+// stays libtorch's; the backward takes the same noise.
 //
 // One row (b, h, t) per group of TPR threads, the whole row in registers (up to 4 x 16 bytes per
 // thread), rows of a CTA independent of one another; persistent grid-stride over rows.  Rows whose
@@ -22,6 +26,8 @@ struct SoftmaxMask {
     const void* add_mask;         // additive, element type of the scores, or NULL
     int64_t mask_sb, mask_sh;     // element strides of add_mask over batch and head (0 = broadcast); row stride S
     int causal;                   // column > row index t -> masked
+    const void* noise = nullptr;  // [B, H, T, S] multiplicative dropout noise of the scores' type, or NULL
+    void* pre_out = nullptr;      // with noise: where the probabilities before the noise go (the backward's input), or NULL
 };
 
 template <int TPR, bool MAX>
@@ -94,7 +100,7 @@ struct RowPos {
 // FLAGS: bit 0 key padding present, bit 1 additive mask present, bit 2 causal.  Compile-time, so
 // that a call without masks spends nothing on them: with run-time tests the kernel executed 33
 // instructions per score and was bound by issue (ncu: 71% issue slots busy, ALU pipe 60%).
-constexpr int kSmPad = 1, kSmMask = 2, kSmCausal = 4;
+constexpr int kSmPad = 1, kSmMask = 2, kSmCausal = 4, kSmNoise = 8;
 
 template <typename T, int TPR, int VPT, int FLAGS>
 __global__ void __launch_bounds__((TPR > 256 ? TPR : 256), (TPR > 256 ? 1 : 3))
@@ -102,6 +108,7 @@ softmax_fwd_kernel(const T* __restrict__ scores, const SoftmaxMask m, T* __restr
                    int64_t rows, int64_t H, int64_t Tq, int S, float scale) {
     constexpr int EPV = VecTraits<T>::EPV;
     constexpr bool PAD = (FLAGS & kSmPad) != 0, MASK = (FLAGS & kSmMask) != 0, CAUSAL = (FLAGS & kSmCausal) != 0;
+    constexpr bool NOISE = (FLAGS & kSmNoise) != 0;
     constexpr int THREADS = TPR > 256 ? TPR : 256;
     constexpr int RPC = THREADS / TPR;
     constexpr int WPR = (TPR + 31) / 32;
@@ -187,6 +194,15 @@ softmax_fwd_kernel(const T* __restrict__ scores, const SoftmaxMask m, T* __restr
         ms = merge_max_sum<TPR>(ms, reinterpret_cast<float2*>(red[parity][grp]), grp + 1);
         const float inv = fast_ex2(m_own - ms.x) / ms.y;
         T* dst = out + row * (int64_t)S;
+        // the noise of this row is requested before the reduction's result is needed
+        uint4 nz[NOISE ? VPT : 1];
+        if constexpr (NOISE) {
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                const int c = tr + j * TPR;
+                if (c < nvec) nz[j] = ld_stream(reinterpret_cast<const T*>(m.noise) + row * (int64_t)S + (size_t)c * EPV);
+            }
+        }
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
             const int c = tr + j * TPR;
@@ -194,6 +210,16 @@ softmax_fwd_kernel(const T* __restrict__ scores, const SoftmaxMask m, T* __restr
                 float o[EPV];
 #pragma unroll
                 for (int e = 0; e < EPV; ++e) o[e] = v[j][e] * inv;
+                if constexpr (NOISE) {
+                    // the probabilities are a tensor of type T before the noise multiplies them (kernel.hpp:93-94)
+                    const uint4 pre = pack<T>(o);
+                    if (m.pre_out != nullptr) st_stream(reinterpret_cast<T*>(m.pre_out) + row * (int64_t)S + (size_t)c * EPV, pre);
+                    float nv[EPV];
+                    unpack<T>(pre, o);
+                    unpack<T>(nz[j], nv);
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e) o[e] *= nv[e];
+                }
                 st_stream(dst + (size_t)c * EPV, pack<T>(o));
             }
         }
@@ -203,10 +229,12 @@ softmax_fwd_kernel(const T* __restrict__ scores, const SoftmaxMask m, T* __restr
     }
 }
 
-template <typename T, int TPR, int VPT>
+// NOISE: dattn is the gradient of (attn * noise); the gradient reaching attn is dattn * noise, a tensor of
+// type T in the reference's autograd (rounded before the softmax backward uses it).
+template <typename T, int TPR, int VPT, bool NOISE>
 __global__ void __launch_bounds__((TPR > 256 ? TPR : 256), (TPR > 256 ? 1 : 2))
-softmax_bwd_kernel(const T* __restrict__ attn, const T* __restrict__ dattn, T* __restrict__ dscores,
-                   int64_t rows, int S, float scale) {
+softmax_bwd_kernel(const T* __restrict__ attn, const T* __restrict__ dattn, const T* __restrict__ noise,
+                   T* __restrict__ dscores, int64_t rows, int S, float scale) {
     constexpr int EPV = VecTraits<T>::EPV;
     constexpr int THREADS = TPR > 256 ? TPR : 256;
     constexpr int RPC = THREADS / TPR;
@@ -218,20 +246,22 @@ softmax_bwd_kernel(const T* __restrict__ attn, const T* __restrict__ dattn, T* _
     int parity = 0;
     const int64_t stride = (int64_t)gridDim.x * RPC;
     uint4 cy[VPT], cd[VPT], ny[VPT], nd[VPT];           // this row and the next, requested one row ahead
-    auto load_row = [&](int64_t row, uint4* ry, uint4* rd) {
+    uint4 cn[NOISE ? VPT : 1], nn[NOISE ? VPT : 1];
+    auto load_row = [&](int64_t row, uint4* ry, uint4* rd, uint4* rn) {
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
             const int c = tr + j * TPR;
             if (c < nvec) {
                 ry[j] = ld_stream(attn + row * (int64_t)S + (size_t)c * EPV);
                 rd[j] = ld_stream(dattn + row * (int64_t)S + (size_t)c * EPV);
+                if constexpr (NOISE) rn[j] = ld_stream(noise + row * (int64_t)S + (size_t)c * EPV);
             }
         }
     };
     int64_t row = (int64_t)blockIdx.x * RPC + grp;
-    if (row < rows) load_row(row, cy, cd);
+    if (row < rows) load_row(row, cy, cd, cn);
     for (; row < rows; row += stride, parity ^= 1) {
-        if (row + stride < rows) load_row(row + stride, ny, nd);
+        if (row + stride < rows) load_row(row + stride, ny, nd, nn);
         float y[VPT][EPV], d[VPT][EPV];
         float dot = 0.f;
 #pragma unroll
@@ -240,6 +270,13 @@ softmax_bwd_kernel(const T* __restrict__ attn, const T* __restrict__ dattn, T* _
             if (c < nvec) {
                 unpack<T>(cy[j], y[j]);
                 unpack<T>(cd[j], d[j]);
+                if constexpr (NOISE) {
+                    float nv[EPV];
+                    unpack<T>(cn[j], nv);
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e) d[j][e] *= nv[e];
+                    unpack<T>(pack<T>(d[j]), d[j]);              // the gradient of attn as a tensor of type T
+                }
 #pragma unroll
                 for (int e = 0; e < EPV; ++e) dot = fmaf(y[j][e], d[j][e], dot);
             }
@@ -257,7 +294,10 @@ softmax_bwd_kernel(const T* __restrict__ attn, const T* __restrict__ dattn, T* _
             }
         }
 #pragma unroll
-        for (int j = 0; j < VPT; ++j) { cy[j] = ny[j]; cd[j] = nd[j]; }
+        for (int j = 0; j < VPT; ++j) {
+            cy[j] = ny[j]; cd[j] = nd[j];
+            if constexpr (NOISE) cn[j] = nn[j];
+        }
     }
 }
 
@@ -303,24 +343,32 @@ softmax_fwd_generic(const T* __restrict__ scores, const SoftmaxMask m, T* __rest
         for (int64_t c = threadIdx.x; c < S; c += blockDim.x) sum += fast_ex2(fmaf(masked_score(src, mrow, prow, m.causal, t, c, scale), kLog2e, off));
         sum = cta_reduce(sum, red, false);
         const float inv = 1.0f / sum;
-        for (int64_t c = threadIdx.x; c < S; c += blockDim.x)
-            out[row * S + c] = from_f32<T>(fast_ex2(fmaf(masked_score(src, mrow, prow, m.causal, t, c, scale), kLog2e, off)) * inv);
+        for (int64_t c = threadIdx.x; c < S; c += blockDim.x) {
+            T p = from_f32<T>(fast_ex2(fmaf(masked_score(src, mrow, prow, m.causal, t, c, scale), kLog2e, off)) * inv);
+            if (m.noise != nullptr) {
+                if (m.pre_out != nullptr) reinterpret_cast<T*>(m.pre_out)[row * S + c] = p;
+                p = from_f32<T>(to_f32(p) * to_f32(reinterpret_cast<const T*>(m.noise)[row * S + c]));
+            }
+            out[row * S + c] = p;
+        }
     }
 }
 
 template <typename T>
 __global__ void __launch_bounds__(256)
-softmax_bwd_generic(const T* __restrict__ attn, const T* __restrict__ dattn, T* __restrict__ dscores,
-                    int64_t rows, int64_t S, float scale) {
+softmax_bwd_generic(const T* __restrict__ attn, const T* __restrict__ dattn, const T* __restrict__ noise,
+                    T* __restrict__ dscores, int64_t rows, int64_t S, float scale) {
     __shared__ float red[8];
     for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const T* ya = attn + row * S;
         const T* da = dattn + row * S;
+        const T* nz = noise ? noise + row * S : nullptr;
+        auto grad = [&](int64_t c) { return nz ? to_f32(from_f32<T>(to_f32(da[c]) * to_f32(nz[c]))) : to_f32(da[c]); };
         float dot = 0.f;
-        for (int64_t c = threadIdx.x; c < S; c += blockDim.x) dot = fmaf(to_f32(ya[c]), to_f32(da[c]), dot);
+        for (int64_t c = threadIdx.x; c < S; c += blockDim.x) dot = fmaf(to_f32(ya[c]), grad(c), dot);
         dot = cta_reduce(dot, red, false);
         for (int64_t c = threadIdx.x; c < S; c += blockDim.x)
-            dscores[row * S + c] = from_f32<T>(scale * (to_f32(ya[c]) * (to_f32(da[c]) - dot)));
+            dscores[row * S + c] = from_f32<T>(scale * (to_f32(ya[c]) * (grad(c) - dot)));
     }
 }
 
@@ -353,7 +401,7 @@ int launch_fwd_flags(const void* scores, const SoftmaxMask& m, void* out, int64_
 template <typename T, int TPR>
 int launch_fwd_tpr(const void* scores, const SoftmaxMask& m, void* out, int64_t rows, int64_t H, int64_t Tq, int64_t S,
                    float scale, cudaStream_t st) {
-    const int flags = (m.key_padding ? kSmPad : 0) | (m.add_mask ? kSmMask : 0) | (m.causal ? kSmCausal : 0);
+    const int flags = (m.key_padding ? kSmPad : 0) | (m.add_mask ? kSmMask : 0) | (m.causal ? kSmCausal : 0) | (m.noise ? kSmNoise : 0);
     switch (flags) {
         case 0: return launch_fwd_flags<T, TPR, 0>(scores, m, out, rows, H, Tq, S, scale, st);
         case 1: return launch_fwd_flags<T, TPR, 1>(scores, m, out, rows, H, Tq, S, scale, st);
@@ -362,14 +410,27 @@ int launch_fwd_tpr(const void* scores, const SoftmaxMask& m, void* out, int64_t 
         case 4: return launch_fwd_flags<T, TPR, 4>(scores, m, out, rows, H, Tq, S, scale, st);
         case 5: return launch_fwd_flags<T, TPR, 5>(scores, m, out, rows, H, Tq, S, scale, st);
         case 6: return launch_fwd_flags<T, TPR, 6>(scores, m, out, rows, H, Tq, S, scale, st);
-        default: return launch_fwd_flags<T, TPR, 7>(scores, m, out, rows, H, Tq, S, scale, st);
+        case 7: return launch_fwd_flags<T, TPR, 7>(scores, m, out, rows, H, Tq, S, scale, st);
+        case 8: return launch_fwd_flags<T, TPR, 8>(scores, m, out, rows, H, Tq, S, scale, st);
+        case 9: return launch_fwd_flags<T, TPR, 9>(scores, m, out, rows, H, Tq, S, scale, st);
+        case 10: return launch_fwd_flags<T, TPR, 10>(scores, m, out, rows, H, Tq, S, scale, st);
+        case 11: return launch_fwd_flags<T, TPR, 11>(scores, m, out, rows, H, Tq, S, scale, st);
+        case 12: return launch_fwd_flags<T, TPR, 12>(scores, m, out, rows, H, Tq, S, scale, st);
+        case 13: return launch_fwd_flags<T, TPR, 13>(scores, m, out, rows, H, Tq, S, scale, st);
+        case 14: return launch_fwd_flags<T, TPR, 14>(scores, m, out, rows, H, Tq, S, scale, st);
+        default: return launch_fwd_flags<T, TPR, 15>(scores, m, out, rows, H, Tq, S, scale, st);
     }
 }
 template <typename T, int TPR>
-int launch_bwd_tpr(const void* attn, const void* dattn, void* dscores, int64_t rows, int64_t S, float scale, cudaStream_t st) {
+int launch_bwd_tpr(const void* attn, const void* dattn, const void* noise, void* dscores, int64_t rows, int64_t S, float scale,
+                   cudaStream_t st) {
     constexpr int THREADS = TPR > 256 ? TPR : 256;
-    return cuda_status(launch_pdl(softmax_bwd_kernel<T, TPR, 4>, dim3((unsigned)row_grid(rows, TPR)), dim3(THREADS), 0, st,
-                                  (const T*)attn, (const T*)dattn, (T*)dscores, rows, (int)S, scale),
+    if (noise != nullptr)
+        return cuda_status(launch_pdl(softmax_bwd_kernel<T, TPR, 4, true>, dim3((unsigned)row_grid(rows, TPR)), dim3(THREADS), 0, st,
+                                      (const T*)attn, (const T*)dattn, (const T*)noise, (T*)dscores, rows, (int)S, scale),
+                           "softmax_bwd_kernel launch");
+    return cuda_status(launch_pdl(softmax_bwd_kernel<T, TPR, 4, false>, dim3((unsigned)row_grid(rows, TPR)), dim3(THREADS), 0, st,
+                                  (const T*)attn, (const T*)dattn, (const T*)nullptr, (T*)dscores, rows, (int)S, scale),
                        "softmax_bwd_kernel launch");
 }
 
@@ -380,7 +441,8 @@ int launch_fwd_t(const void* scores, const SoftmaxMask& m, void* out, int64_t B,
     const int64_t rows = B * H * Tq;
     const bool mask_ok = m.add_mask == nullptr || (aligned16(m.add_mask) && m.mask_sb % EPV == 0 && m.mask_sh % EPV == 0);
     const bool pad_ok = m.key_padding == nullptr || (reinterpret_cast<uintptr_t>(m.key_padding) % EPV == 0);
-    const int tpr = (S % EPV == 0 && aligned16(scores) && aligned16(out) && mask_ok && pad_ok) ? pick_softmax_tpr(S / EPV, fwd_vpt<T>()) : 0;
+    const bool noise_ok = m.noise == nullptr || (aligned16(m.noise) && (m.pre_out == nullptr || aligned16(m.pre_out)));
+    const int tpr = (S % EPV == 0 && aligned16(scores) && aligned16(out) && mask_ok && pad_ok && noise_ok) ? pick_softmax_tpr(S / EPV, fwd_vpt<T>()) : 0;
     switch (tpr) {
         case 32:  return launch_fwd_tpr<T, 32>(scores, m, out, rows, H, Tq, S, scale, st);
         case 64:  return launch_fwd_tpr<T, 64>(scores, m, out, rows, H, Tq, S, scale, st);
@@ -395,19 +457,21 @@ int launch_fwd_t(const void* scores, const SoftmaxMask& m, void* out, int64_t B,
 }
 
 template <typename T>
-int launch_bwd_t(const void* attn, const void* dattn, void* dscores, int64_t rows, int64_t S, float scale, cudaStream_t st) {
+int launch_bwd_t(const void* attn, const void* dattn, const void* noise, void* dscores, int64_t rows, int64_t S, float scale,
+                 cudaStream_t st) {
     constexpr int EPV = VecTraits<T>::EPV;
-    const int tpr = (S % EPV == 0 && aligned16(attn) && aligned16(dattn) && aligned16(dscores)) ? pick_softmax_tpr(S / EPV) : 0;
+    const int tpr = (S % EPV == 0 && aligned16(attn) && aligned16(dattn) && aligned16(dscores) && (noise == nullptr || aligned16(noise)))
+                        ? pick_softmax_tpr(S / EPV) : 0;
     switch (tpr) {
-        case 32:  return launch_bwd_tpr<T, 32>(attn, dattn, dscores, rows, S, scale, st);
-        case 64:  return launch_bwd_tpr<T, 64>(attn, dattn, dscores, rows, S, scale, st);
-        case 128: return launch_bwd_tpr<T, 128>(attn, dattn, dscores, rows, S, scale, st);
-        case 256: return launch_bwd_tpr<T, 256>(attn, dattn, dscores, rows, S, scale, st);
-        case 512: return launch_bwd_tpr<T, 512>(attn, dattn, dscores, rows, S, scale, st);
+        case 32:  return launch_bwd_tpr<T, 32>(attn, dattn, noise, dscores, rows, S, scale, st);
+        case 64:  return launch_bwd_tpr<T, 64>(attn, dattn, noise, dscores, rows, S, scale, st);
+        case 128: return launch_bwd_tpr<T, 128>(attn, dattn, noise, dscores, rows, S, scale, st);
+        case 256: return launch_bwd_tpr<T, 256>(attn, dattn, noise, dscores, rows, S, scale, st);
+        case 512: return launch_bwd_tpr<T, 512>(attn, dattn, noise, dscores, rows, S, scale, st);
         default: break;
     }
     const int64_t cap = (int64_t)sm_count() * 8;
-    softmax_bwd_generic<T><<<(unsigned)(rows < cap ? rows : cap), 256, 0, st>>>((const T*)attn, (const T*)dattn, (T*)dscores, rows, S, scale);
+    softmax_bwd_generic<T><<<(unsigned)(rows < cap ? rows : cap), 256, 0, st>>>((const T*)attn, (const T*)dattn, (const T*)noise, (T*)dscores, rows, S, scale);
     return cuda_status(cudaGetLastError(), "softmax_bwd_generic launch");
 }
 
@@ -415,16 +479,18 @@ int launch_bwd_t(const void* attn, const void* dattn, void* dscores, int64_t row
 
 int launch_attention_softmax_fwd(const void* scores, const uint8_t* key_padding, const void* add_mask, int64_t mask_sb,
                                  int64_t mask_sh, void* out, int64_t B, int64_t H, int64_t Tq, int64_t S, float scale,
-                                 int causal, int dtype, cudaStream_t st) {
-    const SoftmaxMask m = {key_padding, add_mask, mask_sb, mask_sh, causal};
+                                 int causal, int dtype, cudaStream_t st, const void* noise, void* pre_out) {
+    SoftmaxMask m = {key_padding, add_mask, mask_sb, mask_sh, causal};
+    m.noise = noise;
+    m.pre_out = pre_out;
     return dtype == NB2_F32 ? launch_fwd_t<float>(scores, m, out, B, H, Tq, S, scale, st)
                             : launch_fwd_t<__nv_bfloat16>(scores, m, out, B, H, Tq, S, scale, st);
 }
 
 int launch_attention_softmax_bwd(const void* attn, const void* dattn, void* dscores, int64_t rows, int64_t S, float scale,
-                                 int dtype, cudaStream_t st) {
-    return dtype == NB2_F32 ? launch_bwd_t<float>(attn, dattn, dscores, rows, S, scale, st)
-                            : launch_bwd_t<__nv_bfloat16>(attn, dattn, dscores, rows, S, scale, st);
+                                 int dtype, cudaStream_t st, const void* noise) {
+    return dtype == NB2_F32 ? launch_bwd_t<float>(attn, dattn, noise, dscores, rows, S, scale, st)
+                            : launch_bwd_t<__nv_bfloat16>(attn, dattn, noise, dscores, rows, S, scale, st);
 }
 
 }  // namespace nb2

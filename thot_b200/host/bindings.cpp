@@ -33,6 +33,16 @@ PYBIND11_MODULE(_nott_b200_host, m) {
         nb::ScaledDotProductKernel kernel(0.0, causal ? nb::AttentionVariant::Causal : nb::AttentionVariant::Full);
         return kernel->forward(q, k, v, mask.value_or(torch::Tensor()), padding.value_or(torch::Tensor()));
     });
+    // dropout on the probabilities, fused: with `noise` the caller's tensor is used; without it and p > 0 the
+    // module draws a keep mask itself (training mode)
+    m.def("scaled_dot_product_dropout", [](torch::Tensor q, torch::Tensor k, torch::Tensor v, c10::optional<torch::Tensor> noise,
+                                           double p, bool causal) {
+        pybind11::gil_scoped_release nogil;
+        nb::ScaledDotProductKernel kernel(p, causal ? nb::AttentionVariant::Causal : nb::AttentionVariant::Full);
+        kernel->train();
+        if (noise.has_value()) return kernel->forward_with_noise(q, k, v, *noise);
+        return kernel->forward(q, k, v);
+    });
     m.def("rotary_table", [](int64_t S, int64_t hd, double theta, torch::Device device) {
         return nb::RotaryTable(S, hd, theta, device).table();
     });

@@ -688,8 +688,12 @@ private:
 // [B, H, T, S]: the steps between the two matmuls of ScaledDotProductKernelImpl::forward
 // (src/attention/details/kernel.hpp:33-93).  `mask` is additive and already of rank 2, 3 or 4.
 struct AttentionSoftmaxFunction : public torch::autograd::Function<AttentionSoftmaxFunction> {
+    // `noise`: optional multiplicative dropout noise of the scores' shape (a keep mask over 1-p for
+    // torch::nn::Dropout, kernel.hpp:94; N(1, sqrt(p/(1-p))) for the noise module, dropout.hpp:41-43).  With it the
+    // result is attn * noise, formed in the same pass.
     static torch::Tensor forward(torch::autograd::AutogradContext* ctx, torch::Tensor scores, c10::optional<torch::Tensor> mask,
-                                 c10::optional<torch::Tensor> key_padding, double scale, bool causal) {
+                                 c10::optional<torch::Tensor> key_padding, double scale, bool causal,
+                                 c10::optional<torch::Tensor> noise_opt = c10::nullopt) {
         detail::require_cuda(scores, "Attention softmax");
         if (scores.dim() != 4) throw std::invalid_argument("Attention softmax expects scores of shape (batch, heads, target, source).");
         auto x = scores.contiguous();
@@ -717,51 +721,86 @@ struct AttentionSoftmaxFunction : public torch::autograd::Function<AttentionSoft
             if (kp.dim() != 2 || kp.size(0) != B || kp.size(1) != S)
                 throw std::invalid_argument("Key padding mask must be (batch, source).");
         }
+        const int code = detail::dtype_code(x, "Attention softmax");
         auto attn = torch::empty_like(x);
+        ctx->saved_data["scale"] = scale;
+        if (noise_opt.has_value() && noise_opt->defined()) {
+            auto noise = noise_opt->to(x.scalar_type()).contiguous();
+            if (noise.sizes() != x.sizes()) throw std::invalid_argument("Attention dropout noise must have the shape of the scores.");
+            auto out = torch::empty_like(x);
+            detail::check(nb2_attention_softmax_dropout_fwd(x.data_ptr(), kp.defined() ? kp.data_ptr<uint8_t>() : nullptr,
+                                                            detail::ptr_or_null(m), sb, sh, noise.data_ptr(), attn.data_ptr(),
+                                                            out.data_ptr(), B, H, T, S, scale, causal ? 1 : 0, code, detail::stream()),
+                          "nb2_attention_softmax_dropout_fwd");
+            ctx->save_for_backward({attn, noise});
+            return out;
+        }
         detail::check(nb2_attention_softmax_fwd(x.data_ptr(), kp.defined() ? kp.data_ptr<uint8_t>() : nullptr, detail::ptr_or_null(m),
-                                                sb, sh, attn.data_ptr(), B, H, T, S, scale, causal ? 1 : 0,
-                                                detail::dtype_code(x, "Attention softmax"), detail::stream()),
+                                                sb, sh, attn.data_ptr(), B, H, T, S, scale, causal ? 1 : 0, code, detail::stream()),
                       "nb2_attention_softmax_fwd");
         ctx->save_for_backward({attn});
-        ctx->saved_data["scale"] = scale;
         return attn;
     }
     static torch::autograd::tensor_list backward(torch::autograd::AutogradContext* ctx, torch::autograd::tensor_list grads) {
-        auto attn = ctx->get_saved_variables()[0];
+        auto saved = ctx->get_saved_variables();
+        auto attn = saved[0];
         auto dattn = grads[0].contiguous();
         auto ds = torch::empty_like(attn);
         const auto S = attn.size(-1);
-        detail::check(nb2_attention_softmax_bwd(attn.data_ptr(), dattn.data_ptr(), ds.data_ptr(), S > 0 ? attn.numel() / S : 0, S,
-                                                ctx->saved_data["scale"].toDouble(), detail::dtype_code(attn, "Attention softmax backward"),
-                                                detail::stream()),
-                      "nb2_attention_softmax_bwd");
-        return {ds, torch::Tensor(), torch::Tensor(), torch::Tensor(), torch::Tensor()};
+        const auto rows = S > 0 ? attn.numel() / S : 0;
+        const double scale = ctx->saved_data["scale"].toDouble();
+        const int code = detail::dtype_code(attn, "Attention softmax backward");
+        if (saved.size() > 1)
+            detail::check(nb2_attention_softmax_dropout_bwd(attn.data_ptr(), saved[1].data_ptr(), dattn.data_ptr(), ds.data_ptr(), rows, S,
+                                                            scale, code, detail::stream()),
+                          "nb2_attention_softmax_dropout_bwd");
+        else
+            detail::check(nb2_attention_softmax_bwd(attn.data_ptr(), dattn.data_ptr(), ds.data_ptr(), rows, S, scale, code, detail::stream()),
+                          "nb2_attention_softmax_bwd");
+        return {ds, torch::Tensor(), torch::Tensor(), torch::Tensor(), torch::Tensor(), torch::Tensor()};
     }
 };
 
 enum class AttentionVariant { Full, Causal };   // ::Nott::Attention::Variant (src/attention/attention.hpp:9-12)
 
 // Drop-in for Nott::Attention::Details::ScaledDotProductKernel (kernel.hpp:13-103): same constructor
-// arguments and forward signature; the two matmuls and the dropout stay libtorch calls, everything
-// between them is the single kernel above.
+// arguments and forward signature; the two matmuls stay libtorch calls, everything between them -- the
+// dropout on the probabilities included -- is the single kernel above.  In training with p > 0 the keep mask
+// is drawn with libtorch (bernoulli_(1-p) / (1-p): the distribution of torch::nn::Dropout, from libtorch's
+// generator, though not the same draws as its fused dropout kernel) and handed to the kernel as noise.
 class ScaledDotProductKernelImpl : public torch::nn::Module {
 public:
     explicit ScaledDotProductKernelImpl(double dropout = 0.0, AttentionVariant variant = AttentionVariant::Full)
-        : variant_(variant), dropout_(register_module("dropout", torch::nn::Dropout(torch::nn::DropoutOptions(dropout)))) {}
+        : variant_(variant), p_(dropout),
+          dropout_(register_module("dropout", torch::nn::Dropout(torch::nn::DropoutOptions(dropout)))) {}
 
     torch::Tensor forward(const torch::Tensor& query, const torch::Tensor& key, const torch::Tensor& value,
                           const torch::Tensor& attn_mask = {}, const torch::Tensor& key_padding_mask = {}) {
         auto scores = torch::matmul(query, key.transpose(-2, -1));
         const auto head_dim = query.size(-1);
         const double scale = head_dim > 0 ? 1.0 / std::sqrt(static_cast<double>(head_dim)) : 1.0;
+        c10::optional<torch::Tensor> noise;
+        if (is_training() && p_ > 0.0) noise = torch::empty_like(scores).bernoulli_(1.0 - p_).div_(1.0 - p_);
         auto attn = AttentionSoftmaxFunction::apply(scores, detail::opt(attn_mask), detail::opt(key_padding_mask), scale,
-                                                    variant_ == AttentionVariant::Causal);
-        attn = dropout_->forward(attn);
+                                                    variant_ == AttentionVariant::Causal, noise);
+        return torch::matmul(attn, value);
+    }
+
+    // the same with the noise supplied by the caller (reproducible dropout; the multiplicative-noise module)
+    torch::Tensor forward_with_noise(const torch::Tensor& query, const torch::Tensor& key, const torch::Tensor& value,
+                                     const torch::Tensor& noise, const torch::Tensor& attn_mask = {},
+                                     const torch::Tensor& key_padding_mask = {}) {
+        auto scores = torch::matmul(query, key.transpose(-2, -1));
+        const auto head_dim = query.size(-1);
+        const double scale = head_dim > 0 ? 1.0 / std::sqrt(static_cast<double>(head_dim)) : 1.0;
+        auto attn = AttentionSoftmaxFunction::apply(scores, detail::opt(attn_mask), detail::opt(key_padding_mask), scale,
+                                                    variant_ == AttentionVariant::Causal, detail::opt(noise));
         return torch::matmul(attn, value);
     }
 
 private:
     AttentionVariant variant_{AttentionVariant::Full};
+    double p_{0.0};
     torch::nn::Dropout dropout_{nullptr};
 };
 TORCH_MODULE(ScaledDotProductKernel);
