@@ -582,9 +582,10 @@ class StepRunner:
         self.step.close()
 
 
-def timed_steps(runner: StepRunner, steps: int, warmup: int, world: int, dev, clocks=None):
+def timed_steps(runner: StepRunner, steps: int, warmup: int, world: int, dev, clocks=None, trace=None):
     """W untimed steps, then exactly K steps between barrier + synchronize on both sides, CUDA events
-    on the launching stream, max over ranks.  Returns seconds per step."""
+    on the launching stream, max over ranks.  Returns seconds per step.  `trace` (a dict) receives this
+    rank's per-step series: device time between consecutive steps' events and host time per launch call."""
     import torch.distributed as dist
 
     stream = torch.cuda.current_stream()
@@ -601,9 +602,16 @@ def timed_steps(runner: StepRunner, steps: int, warmup: int, world: int, dev, cl
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if clocks is not None:
         clocks.armed = True
+    step_ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps)] if trace is not None else None
+    host_t = []
     e0.record(stream)
-    for _ in range(steps):
+    for i in range(steps):
+        if trace is not None:
+            t0 = time.perf_counter()
         runner.run()
+        if trace is not None:
+            step_ev[i].record(stream)
+            host_t.append((time.perf_counter() - t0) * 1e6)
     runner.finish()                              # the last exchange is inside the timed region
     e1.record(stream)
     if clocks is not None:
@@ -612,6 +620,11 @@ def timed_steps(runner: StepRunner, steps: int, warmup: int, world: int, dev, cl
     if clocks is not None:
         clocks.armed = False
     ms = e0.elapsed_time(e1)
+    if trace is not None:
+        marks = [e0] + step_ev
+        trace["device_us_per_step"] = [round(marks[i].elapsed_time(marks[i + 1]) * 1e3, 1) for i in range(steps)]
+        trace["host_us_per_launch"] = [round(v, 1) for v in host_t]
+        trace["rank_ms"] = ms
     barrier()
     if world > 1:
         t = torch.tensor([ms], device=dev)
@@ -755,6 +768,8 @@ def main():
     ap.add_argument("--no-cfg2", action="store_true", help="skip the x[32,1024,1024] sub-record")
     ap.add_argument("--reserve-sms", type=int, default=0,
                     help="SMs the persistent norm kernels leave to a kernel that runs beside them (default 0)")
+    ap.add_argument("--trace-steps", action="store_true",
+                    help="record one CUDA event and one host timestamp per step and print every rank's series to stderr")
     ap.add_argument("--sweep", action="store_true", help="whole-box sweep: 2^20 rows x D in {768..8192}, both norms, both dtypes")
     ap.add_argument("--suite", action="store_true", help="time the other kernels of the path (1 GPU) instead of the step")
     ap.add_argument("--only", default="", help="with --suite: run only the groups named here, comma separated "
@@ -799,8 +814,11 @@ def main():
     abi.lib().nb2_reserve_sms(max(args.reserve_sms, 0))
 
     runner = StepRunner(w, comm, dev, seed=1234 + rank)
-    sec_per_step = timed_steps(runner, args.steps, args.warmup, world, dev, clocks)
+    trace = {} if args.trace_steps else None
+    sec_per_step = timed_steps(runner, args.steps, args.warmup, world, dev, clocks, trace)
     clocks.stop()
+    if trace is not None:
+        print("STEP_TRACE " + json.dumps({"rank": rank, "workload": w.spec, **trace}), file=sys.stderr, flush=True)
     value = w.step_bytes() * world / sec_per_step / 1e9
 
     # ---- per-kernel durations inside the same step sequence (CUDA events around each launch)
@@ -841,7 +859,10 @@ def main():
     if not args.no_cfg2 and w.spec != "cfg2":
         w2 = Workload("cfg2", world)
         r2 = StepRunner(w2, comm, dev, seed=4321 + rank)
-        s2 = timed_steps(r2, max(args.steps, 200), max(args.warmup, 10), world, dev)
+        trace2 = {} if args.trace_steps else None
+        s2 = timed_steps(r2, max(args.steps, 200), max(args.warmup, 10), world, dev, None, trace2)
+        if trace2 is not None:
+            print("STEP_TRACE " + json.dumps({"rank": rank, "workload": "cfg2", **trace2}), file=sys.stderr, flush=True)
         f2, b2, c2 = kernel_times(r2, 50)
         cfg2 = {"workload": w2.name, "scaling": "weak", "ms_per_step": s2 * 1e3, "value": w2.step_bytes() * world / s2 / 1e9, "unit": UNIT,
                 "rows_per_s": w2.rows_per_rank * world / s2, "steps": max(args.steps, 200),

@@ -52,7 +52,7 @@ def test_static_scratch_backward_matches_the_allocating_path_twice(dtype, D):
         torch.cuda.synchronize()
         free_after, _ = torch.cuda.mem_get_info()
         assert free_after >= free_before, (free_before, free_after)       # no cudaMalloc by anybody during the call
-        assert torch.cuda.memory_allocated() == torch_before
+        assert torch.cuda.memory_allocated() <= torch_before
         assert torch.equal(dx, dx_ref)                                      # same kernel, same grid: identical
         assert torch.equal(grads, grads_ref)
         ref = O.layernorm_act(xn, gn, bn, dyn, 1e-5, act)                   # and against the oracle directly

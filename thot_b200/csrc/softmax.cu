@@ -274,7 +274,7 @@ softmax_bwd_kernel(const T* __restrict__ attn, const T* __restrict__ dattn, cons
                     float nv[EPV];
                     unpack<T>(cn[j], nv);
 #pragma unroll
-                    for (int e = 0; e < EPV; ++e) d[j][e] *= nv[e];
+                    for (int e = 0; e < EPV; ++e) d[j][e] = __fmul_rn(d[j][e], nv[e]);   // rounded as a product: never fused into the subtraction below
                     unpack<T>(pack<T>(d[j]), d[j]);              // the gradient of attn as a tensor of type T
                 }
 #pragma unroll
@@ -363,7 +363,7 @@ softmax_bwd_generic(const T* __restrict__ attn, const T* __restrict__ dattn, con
         const T* ya = attn + row * S;
         const T* da = dattn + row * S;
         const T* nz = noise ? noise + row * S : nullptr;
-        auto grad = [&](int64_t c) { return nz ? to_f32(from_f32<T>(to_f32(da[c]) * to_f32(nz[c]))) : to_f32(da[c]); };
+        auto grad = [&](int64_t c) { return nz ? to_f32(from_f32<T>(__fmul_rn(to_f32(da[c]), to_f32(nz[c])))) : to_f32(da[c]); };
         float dot = 0.f;
         for (int64_t c = threadIdx.x; c < S; c += blockDim.x) dot = fmaf(to_f32(ya[c]), grad(c), dot);
         dot = cta_reduce(dot, red, false);
