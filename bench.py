@@ -886,7 +886,7 @@ def main():
             cpu = {"error": str(exc)}
 
     status = abi.device_status()
-    launches_per_step = 3 + (1 if (world > 1 and mode == abi.EXCHANGE_PEER) else 0)
+    launches_per_step = 3          # forward, backward, partial reduce (+ exchange in the same kernel in the peer form)
     if rank == 0:
         if world == 1:
             exchange = "none"
@@ -895,7 +895,7 @@ def main():
                         "it overlaps the next step's forward" % runner.ncols)
         else:
             exchange = ("peer-store exchange of [%d] fp32 per step: the partial-reduce kernel stores this rank's sums into every "
-                        "peer's buffer over NVLink; a collect kernel after the next forward adds them in rank order" % runner.ncols)
+                        "peer's buffer over NVLink and, one step later, adds the ranks' sums in rank order" % runner.ncols)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": sec_per_step * 1e3, "higher_is_better": True,

@@ -461,12 +461,15 @@ int nb2_comm_info(const nb2_comm* comm, int* rank, int* world, int* exchange);
  * the exchange can run beside other work of the stream:
  *   begin : sums the per-CTA partials (as nb2_colreduce_partials does: fp64,
  *           fixed order) and starts the sum over ranks.  `grads` ([ncols] fp32)
- *           must not be read or written by the caller until `end`.
- *   end   : makes `stream` wait for the exchange; afterwards (in stream order)
- *           `grads` holds the sum over all ranks, bit-identical on every rank
- *           in the PEER form.  A no-op when nothing is outstanding.
- * One exchange may be outstanding per communicator.  comm == NULL, or a
- * one-rank NCCL communicator, makes begin the plain partial reduce.
+ *           must not be read or written by the caller until the exchange is
+ *           complete.  An exchange that is still outstanding is completed by
+ *           this call first (PEER form: by the same kernel launch, so a step
+ *           costs one launch), which is why two gradient buffers alternate.
+ *   end   : completes the outstanding exchange: afterwards (in stream order)
+ *           its `grads` holds the sum over all ranks, bit-identical on every
+ *           rank in the PEER form.  A no-op when nothing is outstanding.
+ * comm == NULL, or a one-rank NCCL communicator, makes begin the plain partial
+ * reduce.
  */
 int nb2_grad_exchange_begin(nb2_comm* comm, const float* partials, int64_t n_partials, int64_t ncols,
                             float* grads, void* stream);
@@ -505,11 +508,11 @@ int nb2_selftest_peer_wait(nb2_comm* comm, int64_t cycle_limit, void* stream);
  * shard: forward, backward (dX + partials), partial reduce and the exchange.
  * This is the loop body `layer.forward(x)` -> `apply(activation)` ->
  * `loss.backward()` of src/core.hpp:1927-1934,3811-3820 for one norm layer.
- *   run    : enqueues forward(k), end of exchange(k-1), backward(k),
- *            begin of exchange(k) on `stream`; so exchange k-1 had the whole
- *            forward of step k to finish in.  `grads` of step k is complete
- *            after the next run (or finish) in stream order; alternate two
- *            buffers to keep the previous step's gradients readable.
+ *   run    : enqueues forward(k), backward(k) and begin of exchange(k) on
+ *            `stream`; exchange k-1 is completed after forward(k), so it had
+ *            that whole kernel to finish in.  `grads` of step k is complete
+ *            after the next run (or finish) in stream order: pass two buffers
+ *            alternately.
  *   finish : ends the outstanding exchange.
  * The step owns mean/rstd/partials scratch for `rows` x `D`.
  */

@@ -75,9 +75,13 @@ def test_exchange_of_a_single_vector_and_argument_checks():
     with pytest.raises(abi.Nb2Error, match="max_cols"):
         comm.exchange_begin(big, 1, big)
     comm.exchange_begin(keep, 1, v)
-    with pytest.raises(abi.Nb2Error, match="not ended"):
-        comm.exchange_begin(keep, 1, v)                   # one exchange may be outstanding
+    with pytest.raises(abi.Nb2Error, match="still outstanding"):
+        comm.exchange_begin(keep, 1, v)                   # the same buffer twice in a row without ending the first
+    w = torch.zeros_like(v)
+    comm.exchange_begin(keep * 2, 1, w)                   # another buffer: the launch also completes the first exchange
     comm.exchange_end()
+    torch.cuda.synchronize()
+    assert torch.equal(v, keep) and torch.equal(w, keep * 2)
     comm.close()
     with pytest.raises(abi.Nb2Error):
         abi.Comm(None, 3, 2, abi.EXCHANGE_NCCL)            # rank outside the world

@@ -1,0 +1,147 @@
+// Fully connected layer with its bias and activation as the GEMM's epilogue, on the 5th-generation tensor
+// cores:  y[M, N] = act( x[M, K] . W[N, K]^T + bias[N] )   (bf16 in and out, fp32 accumulation in TMEM).
+//
+// Reference: Nott's FC layer is torch::nn::Linear bound into a RegisteredLayer with the activation that follows
+// it (src/layer/details/fc.hpp:31-49), run as `layer.forward` then `apply(layer.activation, .)` by the feed
+// forward loop of the transformer blocks (src/block/details/transformers/classic.hpp:446-452) -- a GEMM, a bias
+// pass and an activation pass over [M, N] in libtorch.  Here the bias and the activation ride in the epilogue:
+// the accumulator tile leaves TMEM once, gets the bias row and the activation in registers and is stored.
+//
+// The mainloop and the epilogue pipeline are CUTLASS's sm_100 collectives (tcgen05.mma issued by one thread,
+// operands staged by TMA -- this CTA only, cluster 1x1x1, so no multicast load is generated -- accumulators in
+// TMEM, tcgen05.ld for the epilogue); the activation functors are this library's own (the same fitted erfc
+// GELU and SiLU as the row kernels), plugged into the epilogue visitor tree.
+#pragma once
+
+#include "cutlass/cutlass.h"
+#include "cute/tensor.hpp"
+#include "cutlass/numeric_types.h"
+#include "cutlass/gemm/device/gemm_universal_adapter.h"
+#include "cutlass/gemm/kernel/gemm_universal.hpp"
+#include "cutlass/gemm/collective/collective_builder.hpp"
+#include "cutlass/epilogue/collective/collective_builder.hpp"
+#include "cutlass/epilogue/fusion/operations.hpp"
+#include "cutlass/util/packed_stride.hpp"
+
+#include "nb2_common.cuh"
+
+namespace nb2 {
+
+// activation functors for the epilogue visitor tree: scalar and fragment (Array) forms
+template <int ACT, class T>
+struct EpilogueAct {
+    static const bool kIsHeavy = ACT != NB2_ACT_NONE;
+    CUTLASS_HOST_DEVICE T operator()(T const& v) const {
+#if defined(__CUDA_ARCH__)
+        return T(act_fwd<ACT>(float(v)));
+#else
+        return v;
+#endif
+    }
+};
+template <int ACT, class T, int N>
+struct EpilogueAct<ACT, cutlass::Array<T, N>> {
+    static const bool kIsHeavy = ACT != NB2_ACT_NONE;
+    CUTLASS_HOST_DEVICE cutlass::Array<T, N> operator()(cutlass::Array<T, N> const& v) const {
+        cutlass::Array<T, N> y;
+        EpilogueAct<ACT, T> op;
+        CUTLASS_PRAGMA_UNROLL
+        for (int i = 0; i < N; ++i) y[i] = op(v[i]);
+        return y;
+    }
+};
+template <class T> using EpilogueNone = EpilogueAct<NB2_ACT_NONE, T>;
+template <class T> using EpilogueGelu = EpilogueAct<NB2_ACT_GELU, T>;
+template <class T> using EpilogueSilu = EpilogueAct<NB2_ACT_SILU, T>;
+
+using LinElem = cutlass::bfloat16_t;
+using LinTile = cute::Shape<cute::_128, cute::_128, cute::_64>;
+using LinCluster = cute::Shape<cute::_1, cute::_1, cute::_1>;
+
+template <class FusionOp>
+struct LinearGemm {
+    using CollectiveEpilogue = typename cutlass::epilogue::collective::CollectiveBuilder<
+        cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, LinTile, LinCluster,
+        cutlass::epilogue::collective::EpilogueTileAuto, float, float,
+        void, cutlass::layout::RowMajor, 8,
+        LinElem, cutlass::layout::RowMajor, 8,
+        cutlass::epilogue::collective::EpilogueScheduleAuto, FusionOp>::CollectiveOp;
+    using CollectiveMainloop = typename cutlass::gemm::collective::CollectiveBuilder<
+        cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp,
+        LinElem, cutlass::layout::RowMajor, 8,          // x [M, K], K contiguous
+        LinElem, cutlass::layout::ColumnMajor, 8,       // W [N, K] row-major == B [K, N] column-major
+        float, LinTile, LinCluster,
+        cutlass::gemm::collective::StageCountAutoCarveout<static_cast<int>(sizeof(typename CollectiveEpilogue::SharedStorage))>,
+        cutlass::gemm::collective::KernelScheduleAuto>::CollectiveOp;
+    using Kernel = cutlass::gemm::kernel::GemmUniversal<cute::Shape<int, int, int, int>, CollectiveMainloop, CollectiveEpilogue, void>;
+    using Gemm = cutlass::gemm::device::GemmUniversalAdapter<Kernel>;
+};
+
+constexpr size_t kLinearWorkspaceBytes = 1 << 20;
+
+// One launch.  z_out == nullptr: D = act(acc + bias).  z_out given (AUX): also stores acc + bias, the backward's input.
+template <template <class> class Act, bool AUX>
+int run_linear(const void* x, const void* w, const void* bias, void* z_out, void* y, int64_t M, int64_t N, int64_t K,
+               void* workspace, size_t workspace_bytes, cudaStream_t st) {
+    using FusionPlain = cutlass::epilogue::fusion::LinCombPerColBiasEltAct<Act, LinElem, float, LinElem>;
+    using FusionAux = cutlass::epilogue::fusion::LinCombPerColBiasEltActAux<cutlass::layout::RowMajor, Act, LinElem, float, LinElem, LinElem>;
+    using Fusion = std::conditional_t<AUX, FusionAux, FusionPlain>;
+    using G = LinearGemm<Fusion>;
+    using Gemm = typename G::Gemm;
+    using StrideA = typename Gemm::GemmKernel::StrideA;
+    using StrideB = typename Gemm::GemmKernel::StrideB;
+    using StrideD = typename Gemm::GemmKernel::StrideD;
+    const int m = (int)M, n = (int)N, k = (int)K;
+    typename Gemm::Arguments args{};
+    args.mode = cutlass::gemm::GemmUniversalMode::kGemm;
+    args.problem_shape = {m, n, k, 1};
+    args.mainloop.ptr_A = static_cast<const LinElem*>(x);
+    args.mainloop.dA = cutlass::make_cute_packed_stride(StrideA{}, cute::make_shape(m, k, 1));
+    args.mainloop.ptr_B = static_cast<const LinElem*>(w);
+    args.mainloop.dB = cutlass::make_cute_packed_stride(StrideB{}, cute::make_shape(n, k, 1));
+    args.epilogue.ptr_C = nullptr;
+    args.epilogue.ptr_D = static_cast<LinElem*>(y);
+    args.epilogue.dD = cutlass::make_cute_packed_stride(StrideD{}, cute::make_shape(m, n, 1));
+    args.epilogue.thread.alpha = 1.0f;
+    args.epilogue.thread.beta = 0.0f;
+    args.epilogue.thread.bias_ptr = static_cast<const LinElem*>(bias);      // NULL: no bias (the visitor broadcasts 0)
+    if constexpr (AUX) {
+        args.epilogue.thread.aux_ptr = static_cast<LinElem*>(z_out);
+        args.epilogue.thread.dAux = cutlass::make_cute_packed_stride(StrideD{}, cute::make_shape(m, n, 1));
+    }
+    Gemm gemm;
+    if (gemm.can_implement(args) != cutlass::Status::kSuccess) {
+        set_error("linear: shape M=%lld N=%lld K=%lld is not supported by the tensor-core kernel (N and K must be multiples of 8)",
+                  (long long)M, (long long)N, (long long)K);
+        return NB2_ERR_SHAPE;
+    }
+    const size_t need = Gemm::get_workspace_size(args);
+    if (need > workspace_bytes || (need > 0 && workspace == nullptr)) {
+        set_error("linear: workspace %zu < required %zu", workspace_bytes, need);
+        return NB2_ERR_WORKSPACE;
+    }
+    cutlass::Status s = gemm.initialize(args, workspace, st);
+    if (s != cutlass::Status::kSuccess) {
+        set_error("linear: kernel initialisation failed (%s)", cutlassGetStatusString(s));
+        return NB2_ERR_SHAPE;
+    }
+    s = gemm.run(st);
+    if (s != cutlass::Status::kSuccess) {
+        const cudaError_t e = cudaGetLastError();
+        return e != cudaSuccess ? cuda_status(e, "linear (tcgen05 GEMM) launch") : (set_error("linear: launch failed (%s)", cutlassGetStatusString(s)), NB2_ERR_SHAPE);
+    }
+    return 0;
+}
+
+template <bool AUX>
+int run_linear_act(const void* x, const void* w, const void* bias, void* z_out, void* y, int64_t M, int64_t N, int64_t K, int act,
+                   void* workspace, size_t workspace_bytes, cudaStream_t st) {
+    switch (act) {
+        case NB2_ACT_NONE: return run_linear<EpilogueNone, AUX>(x, w, bias, z_out, y, M, N, K, workspace, workspace_bytes, st);
+        case NB2_ACT_GELU: return run_linear<EpilogueGelu, AUX>(x, w, bias, z_out, y, M, N, K, workspace, workspace_bytes, st);
+        case NB2_ACT_SILU: return run_linear<EpilogueSilu, AUX>(x, w, bias, z_out, y, M, N, K, workspace, workspace_bytes, st);
+        default: set_error("linear: unknown activation %d", act); return NB2_ERR_DTYPE;
+    }
+}
+
+}  // namespace nb2

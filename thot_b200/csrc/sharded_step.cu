@@ -9,11 +9,14 @@
 //                      sum) runs on a side stream owned by the communicator; the caller's stream
 //                      waits for it only where the gradients are needed.
 //   NB2_EXCHANGE_PEER  the partial-reduce kernel itself stores the rank's sums into a slot of every
-//                      peer's receive buffer (plain stores over NVLink to memory mapped with CUDA
-//                      IPC) and raises a per-CTA flag there; a second small kernel, placed where the
-//                      gradients are needed, waits (bounded) for the flags of all ranks and adds the
-//                      slots in rank order, so every rank gets the same bits.  No multicast object,
-//                      no TMA on peer memory, no collective library on the step path.
+//                      peer's receive buffer (plain 8-byte stores over NVLink to memory mapped with
+//                      CUDA IPC; every stored word carries the exchange number beside its value, so
+//                      no flag and no fence are needed).  The same kernel, one step later, first
+//                      picks up what the peers stored for the previous step -- long since arrived --
+//                      and adds the ranks' slots in rank order, so every rank gets the same bits.
+//                      One launch per step, the same count as the single-GPU partial reduce.  No
+//                      multicast object, no TMA on peer memory, no collective library on the step
+//                      path.
 //
 // NCCL is reached through dlopen (the library has no link-time dependency on it); the functions used
 // are ncclGetUniqueId, ncclCommInitRank, ncclAllReduce, ncclAllGather, ncclCommGetAsyncError,
@@ -147,44 +150,85 @@ struct nb2_comm {
     int64_t ncols_pending = 0;
     // peer form
     int64_t max_cols = 0;
-    int ctas_max = 0;
-    uint32_t step = 0;                           // exchange counter; flags carry it
-    float* slots = nullptr;                      // [2][world][max_cols], this rank's receive buffer
-    uint32_t* flags = nullptr;                   // [2][world][ctas_max]
-    float* peer_slots[kMaxRanks] = {};           // the same buffers of every rank as mapped here (own entry = slots)
-    uint32_t* peer_flags[kMaxRanks] = {};
-    void* ipc_base[2 * kMaxRanks] = {};          // what cudaIpcOpenMemHandle returned, to close again
+    uint32_t step = 0;                           // exchange counter; every stored word carries it
+    uint2* slots = nullptr;                      // [2][world][max_cols] of {value bits, exchange number}: this rank's receive buffer
+    uint2* peer_slots[kMaxRanks] = {};           // the same buffer of every rank as mapped here (own entry = slots)
+    void* ipc_base[kMaxRanks] = {};              // what cudaIpcOpenMemHandle returned, to close again
 };
 
 namespace nb2 {
 
 struct PeerPtrs {
-    float* slots[kMaxRanks];
-    uint32_t* flags[kMaxRanks];
+    uint2* slots[kMaxRanks];
 };
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// One 8-byte word {value bits, exchange number}: stored and loaded as a unit, so a reader that sees the
+// number it waits for also sees the value that was stored with it.
+__device__ __forceinline__ void st_word(uint2* p, float v, uint32_t step) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(step) : "memory");
 }
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
+__device__ __forceinline__ uint2 ld_word(const uint2* p) {
+    uint2 w;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(w.x), "=r"(w.y) : "l"(p) : "memory");
+    return w;
 }
 
-// Partial reduce fused with the hand-off to the peers.  Column tiling and summation order are those
-// of the stand-alone partial reduce (fp64, fixed order); instead of writing the sums to `out`, the
-// CTA's first warp stores its 32 columns into slot [parity][rank] of every rank's receive buffer
-// (its own included) and then publishes (release, system scope) the exchange number in flag
-// [parity][rank][CTA] of each.
+// The exchange kernel, 32 columns per CTA, two phases:
+//  collect (prev_out != NULL): the previous exchange.  Thread (rank r, column c) waits (bounded) until word
+//           [parity of prev_step][r][c] of this rank's buffer carries prev_step, then the ranks' values are added in
+//           rank order (fp64, rounded once): every rank adds the same numbers in the same order, so all ranks
+//           hold identical gradients.  A wait that runs out records kStatusPeerTimeout in the device status word
+//           and the CTA writes nothing.
+//  post    (partials != NULL): this exchange.  The per-CTA partials are summed as in the stand-alone partial
+//           reduce (fp64, fixed order) and the CTA's first warp stores its 32 sums, each with the exchange number,
+//           into slot [parity of step][rank] of every rank's buffer (its own included).
+// A slot parity is rewritten two exchanges later; by then its owner has collected it, because a peer can only
+// store exchange k+2 after it collected k+1, which needed this rank's store of k+1, which this rank issues after
+// its own collect of k (the barrier between the two phases).
 template <bool VEC>
 __global__ void __launch_bounds__(XC_THREADS)
-colreduce_post_kernel(const float* __restrict__ partials, int n_partials, int64_t ncols, PeerPtrs peers,
-                      int rank, int world, int64_t max_cols, int ctas_max, int parity, uint32_t step) {
+exchange_kernel(const float* __restrict__ partials, int n_partials, int64_t ncols, PeerPtrs peers, int rank, int world,
+                int64_t max_cols, uint32_t step, float* __restrict__ prev_out, int64_t prev_ncols, uint32_t prev_step,
+                unsigned int* __restrict__ status, long long cycle_limit) {
     __shared__ double red[32][XC_COLS + 1];
+    __shared__ int gave_up;
     const int64_t cbase = (int64_t)blockIdx.x * XC_COLS;
     pdl_release();
     pdl_wait();
+    if (prev_out != nullptr) {
+        if (threadIdx.x == 0) gave_up = 0;
+        __syncthreads();
+        const int r = threadIdx.x >> 5, cl = threadIdx.x & 31;          // 8 ranks per pass x 32 columns
+        const int64_t c = cbase + cl;
+        for (int r0 = 0; r0 < world; r0 += XC_THREADS / 32) {
+            float v = 0.f;
+            if (r0 + r < world && c < prev_ncols) {
+                const uint2* src = peers.slots[rank] + ((size_t)(prev_step & 1u) * world + (r0 + r)) * (size_t)max_cols + (size_t)c;
+                uint2 w = ld_word(src);
+                if (w.y != prev_step) {
+                    const long long t0 = clock64();
+                    for (unsigned int it = 0; it < 0x40000000u && w.y != prev_step; ++it) {
+                        w = ld_word(src);
+                        if (w.y != prev_step && (it & 15u) == 15u && clock64() - t0 > cycle_limit) break;
+                    }
+                }
+                if (w.y != prev_step) {
+                    gave_up = 1;
+                    atomicCAS(status, 0u, (kStatusPeerTimeout << 16) | (blockIdx.x & 0xffffu));
+                }
+                v = __uint_as_float(w.x);
+            }
+            if (r0 + r < kMaxRanks) red[r0 + r][cl] = (double)v;
+        }
+        __syncthreads();
+        if (threadIdx.x < 32 && !gave_up && c < prev_ncols) {
+            double t = 0.0;
+            for (int q = 0; q < world; ++q) t += red[q][threadIdx.x];
+            prev_out[c] = (float)t;
+        }
+        __syncthreads();                 // the collected words are consumed before this CTA stores the next exchange
+    }
+    if (ncols == 0) return;              // collect only
     if constexpr (VEC) {
         const int cl = threadIdx.x % 8, pl = threadIdx.x / 8;          // 8 column lanes x 4 columns, 32 partial lanes
         const int64_t c0 = cbase + cl * 4;
@@ -216,53 +260,8 @@ colreduce_post_kernel(const float* __restrict__ partials, int n_partials, int64_
 #pragma unroll
             for (int p = 0; p < 32; ++p) t += red[p][threadIdx.x];
             const float v = (float)t;
-            const size_t at = ((size_t)parity * world + rank) * (size_t)max_cols + (size_t)c;
-            for (int r = 0; r < world; ++r) peers.slots[r][at] = v;
-        }
-        __threadfence_system();
-        __syncwarp();
-        if (threadIdx.x < world)
-            st_release_sys(peers.flags[threadIdx.x] + ((size_t)parity * world + rank) * ctas_max + blockIdx.x, step);
-    }
-}
-
-// Where the gradients are needed: wait until every rank's flag for this CTA's columns carries the
-// exchange number, then add the slots in rank order (fp64, rounded once).  Every rank adds the same
-// numbers in the same order, so all ranks hold identical gradients.  The wait is bounded; a CTA that
-// gives up records kStatusPeerTimeout in the device status word and writes nothing.
-__global__ void __launch_bounds__(64)
-exchange_collect_kernel(const float* __restrict__ slots, const uint32_t* __restrict__ flags, float* __restrict__ out,
-                        int64_t ncols, int world, int64_t max_cols, int ctas_max, int parity, uint32_t step,
-                        unsigned int* __restrict__ status, long long cycle_limit) {
-    __shared__ int gave_up;
-    pdl_release();
-    pdl_wait();
-    if (threadIdx.x == 0) gave_up = 0;
-    __syncthreads();
-    if (threadIdx.x < world) {
-        const uint32_t* f = flags + ((size_t)parity * world + threadIdx.x) * ctas_max + blockIdx.x;
-        bool ok = ld_acquire_sys(f) == step;
-        if (!ok) {
-            const long long t0 = clock64();
-            for (unsigned int it = 0; it < 0x40000000u && !ok; ++it) {
-                ok = ld_acquire_sys(f) == step;
-                if (!ok && (it & 15u) == 15u && clock64() - t0 > cycle_limit) break;
-            }
-        }
-        if (!ok) {
-            gave_up = 1;
-            atomicCAS(status, 0u, (kStatusPeerTimeout << 16) | (blockIdx.x & 0xffffu));
-        }
-    }
-    __syncthreads();
-    if (gave_up) return;
-    if (threadIdx.x < XC_COLS) {
-        const int64_t c = (int64_t)blockIdx.x * XC_COLS + threadIdx.x;
-        if (c < ncols) {
-            double t = 0.0;
-            for (int r = 0; r < world; ++r)
-                t += (double)__ldcg(slots + ((size_t)parity * world + r) * (size_t)max_cols + (size_t)c);
-            out[c] = (float)t;
+            const size_t at = ((size_t)(step & 1u) * world + rank) * (size_t)max_cols + (size_t)c;
+            for (int r = 0; r < world; ++r) st_word(peers.slots[r] + at, v, step);
         }
     }
 }
@@ -288,10 +287,9 @@ static void nccl_abort(void* p) {
 
 static void comm_free(nb2_comm* c) {
     if (c == nullptr) return;
-    for (int i = 0; i < 2 * kMaxRanks; ++i)
+    for (int i = 0; i < kMaxRanks; ++i)
         if (c->ipc_base[i] != nullptr) cudaIpcCloseMemHandle(c->ipc_base[i]);
     cudaFree(c->slots);
-    cudaFree(c->flags);
     if (c->ready) cudaEventDestroy(c->ready);
     if (c->done) cudaEventDestroy(c->done);
     if (c->side) cudaStreamDestroy(c->side);
@@ -339,7 +337,6 @@ int nb2_comm_create(nb2_comm** comm, const void* id_host, int rank, int world, i
     NB2_REQUIRE(c != nullptr, NB2_ERR_NULL, "comm create: out of host memory");
     c->rank = rank; c->world = world; c->mode = mode;
     c->max_cols = (max_cols + XC_COLS - 1) / XC_COLS * XC_COLS;
-    c->ctas_max = (int)(c->max_cols / XC_COLS);
     CM_CUDA(cudaGetDevice(&c->device));
     CM_CUDA(cudaStreamCreateWithFlags(&c->side, cudaStreamNonBlocking));
     CM_CUDA(cudaEventCreateWithFlags(&c->ready, cudaEventDisableTiming));
@@ -353,25 +350,20 @@ int nb2_comm_create(nb2_comm** comm, const void* id_host, int rank, int world, i
         CM_NCCL(api->CommInitRank(&c->nccl, world, id, rank));
     }
     if (mode == NB2_EXCHANGE_PEER) {
-        const size_t slot_bytes = (size_t)2 * world * c->max_cols * sizeof(float);
-        const size_t flag_bytes = (size_t)2 * world * c->ctas_max * sizeof(uint32_t);
+        const size_t slot_bytes = (size_t)2 * world * c->max_cols * sizeof(uint2);
         CM_CUDA(cudaMalloc((void**)&c->slots, slot_bytes));
-        CM_CUDA(cudaMalloc((void**)&c->flags, flag_bytes));
-        CM_CUDA(cudaMemset(c->slots, 0, slot_bytes));
-        CM_CUDA(cudaMemset(c->flags, 0, flag_bytes));      // exchange numbers start at 1, so 0 never matches
+        CM_CUDA(cudaMemset(c->slots, 0, slot_bytes));      // exchange numbers start at 1, so a cleared word never matches
         c->peer_slots[rank] = c->slots;
-        c->peer_flags[rank] = c->flags;
         if (world > 1) {
-            // every rank's two IPC handles, gathered with the communicator that was just made
-            cudaIpcMemHandle_t mine[2];
-            CM_CUDA(cudaIpcGetMemHandle(&mine[0], c->slots));
-            CM_CUDA(cudaIpcGetMemHandle(&mine[1], c->flags));
+            // every rank's IPC handle, gathered with the communicator that was just made
+            cudaIpcMemHandle_t mine;
+            CM_CUDA(cudaIpcGetMemHandle(&mine, c->slots));
             uint8_t *dsend = nullptr, *drecv = nullptr;
             const size_t hb = sizeof(mine);
             CM_CUDA(cudaMalloc((void**)&dsend, hb));
             if (cudaMalloc((void**)&drecv, hb * world) != cudaSuccess) { cudaFree(dsend); comm_free(c); set_error("comm create: out of device memory"); return (int)cudaErrorMemoryAllocation; }
-            cudaIpcMemHandle_t all[2 * kMaxRanks];
-            int rc = cuda_status(cudaMemcpy(dsend, mine, hb, cudaMemcpyHostToDevice), "comm create: staging the handles");
+            cudaIpcMemHandle_t all[kMaxRanks];
+            int rc = cuda_status(cudaMemcpy(dsend, &mine, hb, cudaMemcpyHostToDevice), "comm create: staging the handle");
             if (rc == 0) rc = nccl_status(api, api->AllGather(dsend, drecv, hb, ncclUint8, c->nccl, c->side), "ncclAllGather of the IPC handles");
             if (rc == 0) rc = cuda_status(cudaStreamSynchronize(c->side), "comm create: handle exchange");
             if (rc == 0) rc = cuda_status(cudaMemcpy(all, drecv, hb * world, cudaMemcpyDeviceToHost), "comm create: reading the handles");
@@ -380,13 +372,10 @@ int nb2_comm_create(nb2_comm** comm, const void* id_host, int rank, int world, i
             if (rc != 0) { comm_free(c); return rc; }
             for (int r = 0; r < world; ++r) {
                 if (r == rank) continue;
-                void *ps = nullptr, *pf = nullptr;
-                CM_CUDA(cudaIpcOpenMemHandle(&ps, all[2 * r], cudaIpcMemLazyEnablePeerAccess));
-                c->ipc_base[2 * r] = ps;
-                CM_CUDA(cudaIpcOpenMemHandle(&pf, all[2 * r + 1], cudaIpcMemLazyEnablePeerAccess));
-                c->ipc_base[2 * r + 1] = pf;
-                c->peer_slots[r] = static_cast<float*>(ps);
-                c->peer_flags[r] = static_cast<uint32_t*>(pf);
+                void* ps = nullptr;
+                CM_CUDA(cudaIpcOpenMemHandle(&ps, all[r], cudaIpcMemLazyEnablePeerAccess));
+                c->ipc_base[r] = ps;
+                c->peer_slots[r] = static_cast<uint2*>(ps);
             }
             // nobody may store into a buffer that its owner has not cleared yet
             float* token = nullptr;
@@ -419,22 +408,42 @@ int nb2_comm_info(const nb2_comm* comm, int* rank, int* world, int* mode) {
     return 0;
 }
 
+// launches the peer form's kernel: collect of the outstanding exchange (if any) and/or post of a new one
+static int launch_exchange(nb2_comm* c, const float* partials, int64_t n_partials, int64_t ncols, uint32_t step,
+                           float* prev_out, int64_t prev_ncols, uint32_t prev_step, cudaStream_t st, long long cycle_limit) {
+    PeerPtrs pp;
+    for (int r = 0; r < kMaxRanks; ++r) pp.slots[r] = c->peer_slots[r];
+    const int64_t cols = ncols > prev_ncols ? ncols : prev_ncols;
+    const int grid = (int)((cols + XC_COLS - 1) / XC_COLS);
+    if (grid == 0) return 0;
+    const bool vec = ncols % 4 == 0 && aligned16(partials);
+    const cudaError_t e = vec ? launch_pdl(exchange_kernel<true>, dim3(grid), dim3(XC_THREADS), 0, st, partials, (int)n_partials, ncols, pp,
+                                           c->rank, c->world, c->max_cols, step, prev_out, prev_ncols, prev_step,
+                                           device_status_ptr(), cycle_limit)
+                              : launch_pdl(exchange_kernel<false>, dim3(grid), dim3(XC_THREADS), 0, st, partials, (int)n_partials, ncols, pp,
+                                           c->rank, c->world, c->max_cols, step, prev_out, prev_ncols, prev_step,
+                                           device_status_ptr(), cycle_limit);
+    return cuda_status(e, "exchange_kernel launch");
+}
+
 int nb2_grad_exchange_begin(nb2_comm* c, const float* partials, int64_t n_partials, int64_t ncols, float* grads,
                             void* stream) {
     NB2_REQUIRE(n_partials >= 0 && n_partials < ((int64_t)1 << 31) && ncols >= 0, NB2_ERR_SHAPE,
                 "gradient exchange: n_partials=%lld ncols=%lld", (long long)n_partials, (long long)ncols);
     if (c == nullptr || (c->world == 1 && c->mode == NB2_EXCHANGE_NCCL))
         return nb2_colreduce_partials(partials, n_partials, ncols, grads, stream);
-    NB2_REQUIRE(!c->outstanding, NB2_ERR_COMM, "gradient exchange: the previous exchange was not ended (nb2_grad_exchange_end)");
     NB2_REQUIRE(!c->aborted, NB2_ERR_COMM, "gradient exchange: the communicator was aborted");
     NB2_REQUIRE(ncols <= c->max_cols, NB2_ERR_SHAPE, "gradient exchange: ncols=%lld exceeds the communicator's max_cols=%lld",
                 (long long)ncols, (long long)c->max_cols);
-    if (ncols == 0) return 0;
-    NB2_REQUIRE(grads != nullptr && (partials != nullptr || n_partials == 0), NB2_ERR_NULL, "gradient exchange: NULL pointer");
+    NB2_REQUIRE(ncols == 0 || (grads != nullptr && (partials != nullptr || n_partials == 0)), NB2_ERR_NULL, "gradient exchange: NULL pointer");
+    NB2_REQUIRE(!(c->outstanding && c->out_pending == grads && ncols > 0), NB2_ERR_COMM,
+                "gradient exchange: the previous exchange into this buffer is still outstanding (end it, or alternate two buffers)");
     cudaStream_t st = (cudaStream_t)stream;
     if (c->mode == NB2_EXCHANGE_NCCL) {
+        int rc = nb2_grad_exchange_end(c, stream);           // one allreduce in flight on the side stream
+        if (rc != 0 || ncols == 0) return rc;
         const NcclApi* api = nccl_api();
-        int rc = nb2_colreduce_partials(partials, n_partials, ncols, grads, stream);
+        rc = nb2_colreduce_partials(partials, n_partials, ncols, grads, stream);
         if (rc != 0) return rc;
         rc = cuda_status(cudaEventRecord(c->ready, st), "gradient exchange: fork");
         if (rc == 0) rc = cuda_status(cudaStreamWaitEvent(c->side, c->ready, 0), "gradient exchange: fork");
@@ -442,21 +451,14 @@ int nb2_grad_exchange_begin(nb2_comm* c, const float* partials, int64_t n_partia
         if (rc == 0) rc = cuda_status(cudaEventRecord(c->done, c->side), "gradient exchange: join");
         if (rc != 0) return rc;
     } else {
+        if (ncols == 0) return nb2_grad_exchange_end(c, stream);
+        // the outstanding exchange, if any, is collected by the same launch that posts this one
+        const uint32_t prev_step = c->step;
         c->step += 1;
         if (c->step == 0) c->step = 1;
-        PeerPtrs pp;
-        for (int r = 0; r < kMaxRanks; ++r) { pp.slots[r] = c->peer_slots[r]; pp.flags[r] = c->peer_flags[r]; }
-        const int grid = (int)((ncols + XC_COLS - 1) / XC_COLS);
-        const int parity = (int)(c->step & 1u);
-        const bool vec = ncols % 4 == 0 && aligned16(partials);
-        cudaError_t e;
-        if (vec)
-            e = launch_pdl(colreduce_post_kernel<true>, dim3(grid), dim3(XC_THREADS), 0, st, partials, (int)n_partials, ncols, pp,
-                           c->rank, c->world, c->max_cols, c->ctas_max, parity, c->step);
-        else
-            e = launch_pdl(colreduce_post_kernel<false>, dim3(grid), dim3(XC_THREADS), 0, st, partials, (int)n_partials, ncols, pp,
-                           c->rank, c->world, c->max_cols, c->ctas_max, parity, c->step);
-        if (e != cudaSuccess) return cuda_status(e, "colreduce_post_kernel launch");
+        const int rc = launch_exchange(c, partials, n_partials, ncols, c->step, c->outstanding ? c->out_pending : nullptr,
+                                       c->outstanding ? c->ncols_pending : 0, prev_step, st, (long long)kWaitCycleLimit);
+        if (rc != 0) return rc;
     }
     c->outstanding = true;
     c->out_pending = grads;
@@ -469,11 +471,8 @@ int nb2_grad_exchange_end(nb2_comm* c, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
     c->outstanding = false;
     if (c->mode == NB2_EXCHANGE_NCCL) return cuda_status(cudaStreamWaitEvent(st, c->done, 0), "gradient exchange: join");
-    const int grid = (int)((c->ncols_pending + XC_COLS - 1) / XC_COLS);
-    const cudaError_t e = launch_pdl(exchange_collect_kernel, dim3(grid), dim3(64), 0, st, (const float*)c->slots,
-                                     (const uint32_t*)c->flags, c->out_pending, c->ncols_pending, c->world, c->max_cols,
-                                     c->ctas_max, (int)(c->step & 1u), c->step, device_status_ptr(), (long long)kWaitCycleLimit);
-    if (e != cudaSuccess) return cuda_status(e, "exchange_collect_kernel launch");
+    const int rc = launch_exchange(c, nullptr, 0, 0, 0, c->out_pending, c->ncols_pending, c->step, st, (long long)kWaitCycleLimit);
+    if (rc != 0) return rc;
     return cuda_status(cudaEventRecord(c->done, st), "gradient exchange: completion event");
 }
 
@@ -495,10 +494,9 @@ int nb2_selftest_peer_wait(nb2_comm* c, int64_t cycle_limit, void* stream) {
     NB2_REQUIRE(c != nullptr && c->mode == NB2_EXCHANGE_PEER, NB2_ERR_NULL, "peer-wait self-test: needs a communicator in the peer form");
     NB2_REQUIRE(cycle_limit > 0 && cycle_limit <= 2000000000LL, NB2_ERR_SHAPE, "peer-wait self-test: cycle_limit=%lld must be in (0, 2e9]", (long long)cycle_limit);
     NB2_REQUIRE(!c->outstanding, NB2_ERR_COMM, "peer-wait self-test: an exchange is outstanding");
-    const cudaError_t e = launch_pdl(exchange_collect_kernel, dim3(1), dim3(64), 0, (cudaStream_t)stream, (const float*)c->slots,
-                                     (const uint32_t*)c->flags, (float*)nullptr, (int64_t)0, c->world, c->max_cols, c->ctas_max,
-                                     (int)((c->step + 1u) & 1u), c->step + 0x40000001u, device_status_ptr(), (long long)cycle_limit);
-    return cuda_status(e, "peer-wait self-test launch");
+    // collect 32 columns of an exchange number nobody has stored; the sums (never formed) would go to the slot buffer itself
+    return launch_exchange(c, nullptr, 0, 0, 0, reinterpret_cast<float*>(c->slots), XC_COLS, c->step + 0x40000001u,
+                           (cudaStream_t)stream, (long long)cycle_limit);
 }
 
 int nb2_comm_abort(nb2_comm* c) {
@@ -583,9 +581,12 @@ int nb2_step_run(nb2_step* s, const void* x, const void* dy, const void* gamma, 
     int rc = rms ? nb2_rmsnorm_fwd(x, gamma, y, s->rstd, s->rows, s->D, s->eps, s->dtype, s->act, stream)
                  : nb2_layernorm_fwd(x, gamma, beta, y, s->mean, s->rstd, s->rows, s->D, s->eps, s->dtype, s->act, stream);
     if (rc != 0) return rc;
-    // the previous step's exchange had this step's forward to finish in
-    rc = nb2_grad_exchange_end(s->comm, stream);
-    if (rc != 0) return rc;
+    // The previous step's exchange had this step's forward to finish in.  NCCL form: the stream joins the side
+    // stream here.  Peer form: nothing to do, the launch that posts this step's sums collects the previous ones.
+    if (s->comm != nullptr && s->comm->mode == NB2_EXCHANGE_NCCL) {
+        rc = nb2_grad_exchange_end(s->comm, stream);
+        if (rc != 0) return rc;
+    }
     int64_t parts = 0;
     rc = rms ? nb2_rmsnorm_bwd(x, dy, gamma, s->rstd, dx, s->partials, &parts, s->rows, s->D, s->dtype, s->act, stream)
              : nb2_layernorm_bwd(x, dy, gamma, beta, s->mean, s->rstd, dx, s->partials, &parts, s->rows, s->D, s->dtype, s->act, stream);
