@@ -575,8 +575,14 @@ class StepRunner:
                                         self._ct.byref(self.nparts), self.rows, self.D, self.code, w.act, st))
 
     def reduce(self, st):
+        """The partial reduce; with a communicator, the call that also starts (and, one call later, completes) the
+        sum over ranks, as the step driver issues it."""
         abi, P, L = self.abi, self._ptrs(), self.abi.lib()
-        abi.check(L.nb2_colreduce_partials(P(self.partials), self.nparts.value, self.ncols, P(self.grads[0]), st))
+        if self.comm is None:
+            abi.check(L.nb2_colreduce_partials(P(self.partials), self.nparts.value, self.ncols, P(self.grads[0]), st))
+        else:
+            self.k += 1
+            abi.check(L.nb2_grad_exchange_begin(self.comm.handle, P(self.partials), self.nparts.value, self.ncols, P(self.grads[self.k & 1]), st))
 
     def close(self):
         self.step.close()
@@ -641,12 +647,14 @@ def kernel_times(runner: StepRunner, n_prof: int):
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(n_prof)]
     for i in range(3):
         runner.fwd(st); runner.bwd(st); runner.reduce(st)
+    runner.finish()
     torch.cuda.synchronize()
     for i in range(n_prof):
         ev[i][0].record(stream); runner.fwd(st)
         ev[i][1].record(stream); runner.bwd(st)
         ev[i][2].record(stream); runner.reduce(st)
         ev[i][3].record(stream)
+    runner.finish()
     torch.cuda.synchronize()
     t_fwd = float(np.mean([ev[i][0].elapsed_time(ev[i][1]) for i in range(n_prof)])) / 1e3
     t_bwd = float(np.mean([ev[i][1].elapsed_time(ev[i][2]) for i in range(n_prof)])) / 1e3

@@ -70,7 +70,8 @@ enum {
     NB2_WS_NORM_BWD = 0,      /* per-CTA dgamma/dbeta (or dweight) partials */
     NB2_WS_EMBEDDING_BWD = 1, /* sort keys + radix-sort temporary           */
     NB2_WS_ROPE_TABLE = 2,    /* cos/sin table [S, hd/2, 2] fp32            */
-    NB2_WS_BERT_EMBEDDING_BWD = 3 /* norm partials + type-row sums + sort scratch */
+    NB2_WS_BERT_EMBEDDING_BWD = 3, /* norm partials + type-row sums + sort scratch */
+    NB2_WS_LINEAR = 4         /* tile-scheduler scratch of the tensor-core linear layer */
 };
 
 int nb2_abi_version(void);
@@ -113,6 +114,7 @@ int nb2_selftest_bounded_wait(int64_t cycle_limit, int64_t* waited_cycles, void*
  *   NB2_WS_EMBEDDING_BWD : a = tokens, b = vocab rows -> sort scratch
  *   NB2_WS_ROPE_TABLE    : a = seq_len, b = head_dim  -> cos/sin table
  *   NB2_WS_BERT_EMBEDDING_BWD : a = (B << 32) | S, b = (vocab << 32) | D
+ *   NB2_WS_LINEAR        : a, b unused                -> a fixed upper bound
  * Returns 0 for unknown `op`.
  */
 size_t nb2_workspace_bytes(int op, int64_t a, int64_t b, int dtype);
@@ -332,6 +334,28 @@ int nb2_bert_embedding_ln_bwd(const void* sum, const void* dy, const void* ids, 
                               int64_t B, int64_t S, int64_t vocab, int64_t D,
                               int dtype, int index_type,
                               void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------ *
+ * Fully connected layer with its bias and activation in the GEMM's epilogue:
+ *   y[M, N] = act( x[M, K] . weight[N, K]^T + bias[N] )
+ * Replaces Nott's FC layer -- torch::nn::Linear bound into a RegisteredLayer with
+ * the activation that follows it (src/layer/details/fc.hpp:31-49), run as
+ * `layer.forward` then `apply(layer.activation, .)` by the feed-forward loop of the
+ * transformer blocks (src/block/details/transformers/classic.hpp:446-452): a GEMM
+ * plus a bias pass plus an activation pass over [M, N] in libtorch.
+ * bf16 operands and output, fp32 accumulation on the tcgen05 tensor cores
+ * (accumulators in TMEM, operands staged by TMA from this GPU's memory only); the
+ * bias row and the activation are applied to the fp32 accumulator tile in registers
+ * before its single store.  weight is torch::nn::Linear's [out_features,
+ * in_features] tensor as it is; bias may be NULL.  z_out (may be NULL) receives the
+ * pre-activation x.W^T + bias rounded to bf16 -- what the backward of the
+ * activation needs (nb2_act_bwd).  N and K must be multiples of 8.  fp32 layers are
+ * not taken (NB2_ERR_DTYPE): TF32 tensor cores do not meet the fp32 tolerance.
+ * workspace: nb2_workspace_bytes(NB2_WS_LINEAR, 0, 0, dtype) bytes.
+ * ------------------------------------------------------------------ */
+int nb2_linear_bias_act_fwd(const void* x, const void* weight, const void* bias, void* z_out, void* y,
+                            int64_t M, int64_t N, int64_t K, int dtype, int act,
+                            void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------ *
  * Rotary embedding, rotate-half pairing (i, i + hd/2).  The reference has no

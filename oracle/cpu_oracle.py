@@ -63,6 +63,26 @@ def act(x, dy, act_code):
     return dict(y=y, dx=dx)
 
 
+def linear_act(x, weight, bias, act_code):
+    """The FC layer of the reference (torch::nn::Linear then apply(activation), src/layer/details/fc.hpp:31-49):
+    z = x @ weight.T + bias in fp64 on the given fp32 values, y = act(z) -> dict(z, y)."""
+    z = np.asarray(x, np.float64) @ np.asarray(weight, np.float64).T
+    if bias is not None:
+        z = z + np.asarray(bias, np.float64)
+    return dict(z=z, y=act64(z, act_code))
+
+
+def act64(z, act_code):
+    """GELU (exact erf) / SiLU / identity in fp64 on fp64 input (gelu.hpp:11-15, silu.hpp:12-16)."""
+    from math import erf, sqrt
+    z = np.asarray(z, np.float64)
+    if act_code == ACT_GELU:
+        return 0.5 * z * (1.0 + np.vectorize(erf)(z / sqrt(2.0)))
+    if act_code == ACT_SILU:
+        return z / (1.0 + np.exp(-z))
+    return z.copy()
+
+
 def silu_gate(a, b, dy):
     """a, b: 2-D fp32 arrays, possibly row-strided views with unit column stride."""
     assert a.dtype == np.float32 and b.dtype == np.float32

@@ -174,6 +174,25 @@ int ref_act(const float* x, const float* dy, int64_t n, int act, int compute, fl
     });
 }
 
+// The fully connected layer as the reference builds and runs it: torch::nn::Linear(in, out).bias(b)
+// (src/layer/details/fc.hpp:36-38), then Activation::Details::apply(layer.activation, .)
+// (src/block/details/transformers/classic.hpp:446-452).  weight is [N, K], bias [N] or NULL.
+int ref_fc_act(const float* x, const float* weight, const float* bias, int64_t M, int64_t N, int64_t K, int act, int compute,
+               float* z, float* y) {
+    return guarded([&] {
+        torch::nn::Linear fc(torch::nn::LinearOptions(K, N).bias(bias != nullptr));
+        fc->to(compute_type(compute));
+        {
+            torch::NoGradGuard ng;
+            fc->weight.copy_(wrap(weight, {N, K}, compute));
+            if (bias != nullptr) fc->bias.copy_(wrap(bias, {N}, compute));
+        }
+        auto pre = fc->forward(wrap(x, {M, K}, compute));
+        store(pre, z);
+        store(Nott::Activation::Details::apply(act_type(act), pre), y);
+    });
+}
+
 // apply(SwiGLU) on one [rows, 2H] tensor; dinput is [rows, 2H].
 int ref_swiglu(const float* input, const float* dy, int64_t rows, int64_t H, int compute,
                float* out, float* dinput) {

@@ -115,6 +115,16 @@ def bert_embedding(word, pos, type_table, gamma, beta, ids, dy=None, compute=0):
     return dict(y=y, dword=dword, dpos=dpos, dtype=dtype, dgamma=dg, dbeta=db)
 
 
+def fc_act(x, weight, bias, act_code, compute=0):
+    """torch::nn::Linear then apply(activation), the reference's FC layer (fc.hpp:31-49) -> dict(z, y)."""
+    x, weight, bias = _f32(x), _f32(weight), _f32(bias)
+    M, K = x.shape
+    N = weight.shape[0]
+    z = np.empty((M, N), np.float32); y = np.empty((M, N), np.float32)
+    _chk(lib().ref_fc_act(_p(x), _p(weight), _p(bias), c_int64(M), c_int64(N), c_int64(K), c_int(act_code), c_int(compute), _p(z), _p(y)))
+    return dict(z=z, y=y)
+
+
 def bert_embedding_from_embeddings(inp, pos, type_table, gamma, beta, dy=None, compute=0):
     """BertEmbedding fed ready-made [B, S, D] embeddings (bert.hpp:164-171) instead of token ids."""
     inp, pos, type_table, gamma, beta, dy = map(_f32, (inp, pos, type_table, gamma, beta, dy))

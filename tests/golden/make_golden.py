@@ -137,6 +137,19 @@ def main():
             rec[f"{k}_{tag}"] = v
     np.savez(OUT / "bert_embedding_float_input.npz", **rec)
 
+    # FC layer: torch::nn::Linear then apply(activation) (fc.hpp:31-49), bf16-representable operands
+    gen = torch.Generator().manual_seed(50)
+    M, N, K = 24, 40, 64
+    fx, fw, fb = randn(gen, M, K, bf16=True), randn(gen, N, K, scale=0.1, bf16=True), randn(gen, N, scale=0.1, bf16=True)
+    rec = dict(x=fx, weight=fw, bias=fb)
+    for act_name, code in (("none", 0), ("gelu", 1), ("silu", 2)):
+        for tag, compute in (("f32", 0), ("f64", 1)):
+            r = R.fc_act(fx, fw, fb, code, compute)
+            rec[f"{act_name}_y_{tag}"] = r["y"]
+            rec[f"z_{tag}"] = r["z"]
+    rec["nobias_gelu_y_f64"] = R.fc_act(fx, fw, None, 1, 1)["y"]
+    np.savez(OUT / "fc_act.npz", **rec)
+
     gen = torch.Generator().manual_seed(12)
     table = randn(gen, 64, 40, scale=0.02)
     ids = torch.randint(0, 64, (3, 9), generator=gen).numpy().astype(np.int64)

@@ -191,3 +191,14 @@ def test_attention_dropout_oracle_matches_reference_modules(golden_dir, name):
     # the module's noise has the moments it should: mean 1, std sqrt(p/(1-p))
     p = float(g["p"])
     assert abs(g["plain_noise_f32"].mean() - 1.0) < 0.05 and abs(g["plain_noise_f32"].std() - np.sqrt(p / (1 - p))) < 0.05
+
+
+def test_fc_layer_oracle_matches_reference(golden_dir):
+    """Golden = torch::nn::Linear followed by apply(activation), the reference's FC layer (fc.hpp:31-49)."""
+    g = load(golden_dir, "fc_act")
+    for name, code in (("none", O.ACT_NONE), ("gelu", O.ACT_GELU), ("silu", O.ACT_SILU)):
+        o = O.linear_act(g["x"], g["weight"], g["bias"], code)
+        np.testing.assert_allclose(o["y"], g[f"{name}_y_f64"], rtol=2e-7, atol=1e-7)      # fp64 module output stored as fp32
+        tol.fp32_close(o["y"], g[f"{name}_y_f32"], rtol=1e-5, atol=2e-6)
+        np.testing.assert_allclose(o["z"], g["z_f64"], rtol=2e-7, atol=1e-7)
+    np.testing.assert_allclose(O.linear_act(g["x"], g["weight"], None, O.ACT_GELU)["y"], g["nobias_gelu_y_f64"], rtol=2e-7, atol=1e-7)

@@ -46,6 +46,24 @@ def _nccl_include() -> list[str]:
     return []
 
 
+def _cutlass_include() -> list[str]:
+    """CUTLASS/CuTe headers (header-only) for the tensor-core linear layer; the tree vendored with flashinfer."""
+    cands = []
+    if os.environ.get("CUTLASS_PATH"):
+        cands.append(Path(os.environ["CUTLASS_PATH"]))
+    try:
+        import importlib.util
+        spec = importlib.util.find_spec("flashinfer")
+        if spec is not None and spec.submodule_search_locations:
+            cands.append(Path(list(spec.submodule_search_locations)[0]) / "data" / "cutlass")
+    except Exception:
+        pass
+    for root in cands:
+        if (root / "include" / "cutlass" / "cutlass.h").exists():
+            return ["-I", str(root / "include"), "-I", str(root / "tools" / "util" / "include")]
+    return []
+
+
 def _sources() -> list[Path]:
     return sorted(CSRC.glob("*.cu"))
 
@@ -72,6 +90,11 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     def compile_one(src: Path) -> Path:
         obj = OBJ_DIR / (src.stem + ".o")
         cmd = [nvcc, *NVCC_FLAGS, *_nccl_include(), "-c", str(src), "-o", str(obj)]
+        if src.name.startswith("linear_tc"):
+            inc = _cutlass_include()
+            if not inc:
+                raise RuntimeError("CUTLASS headers not found (set CUTLASS_PATH): the tensor-core linear layer cannot be built")
+            cmd[1:1] = [*inc, "-diag-suppress", "20012"]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         res = subprocess.run(cmd, capture_output=True, text=True)

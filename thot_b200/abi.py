@@ -16,7 +16,7 @@ import torch
 F32, BF16 = 0, 1
 ACT_NONE, ACT_GELU, ACT_SILU = 0, 1, 2
 I32, I64 = 0, 1
-WS_NORM_BWD, WS_EMBEDDING_BWD, WS_ROPE_TABLE, WS_BERT_EMBEDDING_BWD = 0, 1, 2, 3
+WS_NORM_BWD, WS_EMBEDDING_BWD, WS_ROPE_TABLE, WS_BERT_EMBEDDING_BWD, WS_LINEAR = 0, 1, 2, 3, 4
 EXCHANGE_NCCL, EXCHANGE_PEER = 0, 1
 NORM_LAYER, NORM_RMS = 0, 1
 COMM_ID_BYTES = 128
@@ -38,6 +38,7 @@ _SIGNATURES = {
     "nb2_attention_softmax_dropout_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
                                                   c_int64, c_int64, c_int64, c_int64, c_double, c_int, c_int, c_void_p]),
     "nb2_attention_softmax_dropout_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_double, c_int, c_void_p]),
+    "nb2_linear_bias_act_fwd": (c_int, [c_void_p] * 5 + [c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "nb2_selftest_bounded_wait": (c_int, [c_int64, c_void_p, c_void_p]),
     "nb2_workspace_bytes": (c_size_t, [c_int, c_int64, c_int64, c_int]),
     "nb2_layernorm_fwd": (c_int, [c_void_p] * 6 + [c_int64, c_int64, c_double, c_int, c_int, c_void_p]),
@@ -420,6 +421,27 @@ def attention_softmax_bwd(attn, dattn, scale: float, noise=None):
     check(lib().nb2_attention_softmax_bwd(_p(attn), _p(dattn), _p(out), attn.numel() // max(S, 1), S, scale,
                                           dtype_code(attn.dtype), _stream()))
     return out
+
+
+# ------------------------------------------------------------------- linear
+_linear_ws = {}
+
+
+def linear_bias_act_fwd(x, weight, bias=None, act: int = ACT_NONE, want_z: bool = False):
+    """y = act(x @ weight.T + bias) on the tensor cores (bf16).  x [M, K], weight [N, K] (torch.nn.Linear's layout),
+    bias [N] or None -> (y [M, N], z [M, N] or None)."""
+    _dev(x)
+    M, K = x.shape
+    N = weight.shape[0]
+    y = torch.empty(M, N, dtype=x.dtype, device=x.device)
+    z = torch.empty(M, N, dtype=x.dtype, device=x.device) if want_z else None
+    key = (x.device.index, )
+    ws = _linear_ws.get(key)
+    if ws is None:
+        ws = _linear_ws[key] = torch.empty(workspace_bytes(WS_LINEAR, 0, 0, BF16), dtype=torch.uint8, device=x.device)
+    check(lib().nb2_linear_bias_act_fwd(_p(x), _p(weight), _p(bias), _p(z), _p(y), M, N, K, dtype_code(x.dtype), act, _p(ws), ws.numel(),
+                                        _stream()))
+    return y, z
 
 
 # --------------------------------------------------------------------- rope

@@ -222,6 +222,7 @@ size_t nb2_workspace_bytes(int op, int64_t a, int64_t b, int dtype) {
             const size_t type_ws = ((size_t)(S + 1) * D * sizeof(float) + 255) & ~(size_t)255;
             return norm_ws + type_ws + embedding_bwd_workspace(tokens, vocab) + 512;
         }
+        case NB2_WS_LINEAR: return (size_t)1 << 20;
         case NB2_WS_ROPE_TABLE: return a > 0 && b > 1 ? (size_t)a * (size_t)(b / 2) * 2 * sizeof(float) : 0;
         default: return 0;
     }
@@ -516,6 +517,24 @@ int nb2_attention_softmax_dropout_bwd(const void* attn_pre, const void* noise, c
     int rc = require_device();
     if (rc != 0) return rc;
     return launch_attention_softmax_bwd(attn_pre, dout, dscores, rows, S, (float)scale, dtype, (cudaStream_t)stream, noise);
+}
+
+int nb2_linear_bias_act_fwd(const void* x, const void* weight, const void* bias, void* z_out, void* y, int64_t M, int64_t N,
+                            int64_t K, int dtype, int act, void* workspace, size_t workspace_bytes, void* stream) {
+    NB2_REQUIRE(dtype == NB2_BF16, NB2_ERR_DTYPE, "linear: dtype=%d (the tensor-core path takes bf16; fp32 layers stay with the host framework's GEMM)", dtype);
+    NB2_REQUIRE(act_ok(act), NB2_ERR_DTYPE, "linear: unknown activation %d", act);
+    NB2_REQUIRE(M >= 0 && N > 0 && K > 0 && M < ((int64_t)1 << 31) && N < ((int64_t)1 << 31) && K < ((int64_t)1 << 31), NB2_ERR_SHAPE,
+                "linear: M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
+    NB2_REQUIRE(N % 8 == 0 && K % 8 == 0, NB2_ERR_SHAPE, "linear: N=%lld and K=%lld must be multiples of 8 (16-byte rows for the bulk tensor copies)",
+                (long long)N, (long long)K);
+    if (M == 0) return 0;
+    NB2_REQUIRE(x && weight && y, NB2_ERR_NULL, "linear: x, weight and y must be non-NULL");
+    NB2_REQUIRE(aligned16(x) && aligned16(weight) && aligned16(y) && (bias == nullptr || aligned16(bias)) && (z_out == nullptr || aligned16(z_out)),
+                NB2_ERR_ALIGN, "linear: pointers must be 16-byte aligned");
+    int rc = require_device();
+    if (rc != 0) return rc;
+    if (z_out != nullptr) return launch_linear_aux(x, weight, bias, z_out, y, M, N, K, act, workspace, workspace_bytes, (cudaStream_t)stream);
+    return launch_linear_plain(x, weight, bias, y, M, N, K, act, workspace, workspace_bytes, (cudaStream_t)stream);
 }
 
 int nb2_rope_table(float* cos_sin, const int32_t* positions, int64_t S, int64_t hd, double theta, void* stream) {
