@@ -292,6 +292,8 @@ def run_suite(args):
         _suite_act(abi, timed, dev, g)
     if want("attention"):
         _suite_attention(abi, timed, dev, g)
+    if want("linear"):
+        _suite_linear(abi, results, dev, g)
     abi.device_status()
     _emit({"suite": results, "peak_gbs": peak, "unit": "GB/s", "data": "synthetic",
            "note": "timings include torch's output allocation from its caching allocator"})
@@ -406,6 +408,42 @@ def _suite_attention(abi, timed, dev, g):
         timed(f"attention_softmax+dropout_bwd {nm} [16,16,1024,1024] (3 reads, 1 write)",
               lambda: abi.attention_softmax_bwd(at, da_, 0.125, noise=nz), 4 * sc.numel() * e)
         del sc, da_, at, mk, nz
+
+
+def _suite_linear(abi, results, dev, g):
+    """The FC layer with bias + GELU in the GEMM's epilogue (tensor cores, bf16) at feed-forward sizes, against the
+    measured cuBLAS bf16 rate of this box and against libtorch's own linear -> gelu on the same tensors."""
+    import torch.nn.functional as F
+    peaks_file = ROOT / "MEASURED_PEAKS.json"
+    peak_tf = float(json.loads(peaks_file.read_text())["bf16_tflops"]) if peaks_file.exists() else 1590.0
+    bf = torch.bfloat16
+    for (M, N, K) in ((16384, 4096, 1024), (16384, 1024, 4096), (32768, 3072, 768), (8192, 8192, 8192)):
+        x = torch.randn(M, K, device=dev, generator=g).to(bf); w = (torch.randn(N, K, device=dev, generator=g) / K ** 0.5).to(bf)
+        b = (0.1 * torch.randn(N, device=dev, generator=g)).to(bf)
+
+        def timeit(fn, iters=20):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / iters / 1e3
+
+        ours = timeit(lambda: abi.linear_bias_act_fwd(x, w, b, abi.ACT_GELU))
+        ours_z = timeit(lambda: abi.linear_bias_act_fwd(x, w, b, abi.ACT_GELU, want_z=True))
+        lib_ = timeit(lambda: F.gelu(F.linear(x, w, b)))
+        flops = 2.0 * M * N * K
+        results.append({"op": f"linear+bias+gelu bf16 [{M},{K}]x[{N},{K}]^T (tcgen05, epilogue fused)", "us": ours * 1e6,
+                        "tflops": flops / ours / 1e12, "frac_of_measured_bf16_peak": flops / ours / 1e12 / peak_tf,
+                        "with_pre_activation_output_us": ours_z * 1e6,
+                        "libtorch_linear_then_gelu_us": lib_ * 1e6, "speedup_vs_libtorch": lib_ / ours,
+                        "algorithmic_bytes": 2 * (M * K + N * K + M * N), "achieved_gbs": 2 * (M * K + N * K + M * N) / ours / 1e9,
+                        "frac_of_measured_peak": None, "frac_of_nominal_8000": None})
+        del x, w, b
 
 
 # ------------------------------------------------------------ cfg5 sweep
@@ -781,7 +819,7 @@ def main():
     ap.add_argument("--sweep", action="store_true", help="whole-box sweep: 2^20 rows x D in {768..8192}, both norms, both dtypes")
     ap.add_argument("--suite", action="store_true", help="time the other kernels of the path (1 GPU) instead of the step")
     ap.add_argument("--only", default="", help="with --suite: run only the groups named here, comma separated "
-                    "(rmsnorm, addnorm, gate, embedding, bert, rope, act, attention); with --sweep: only these points "
+                    "(rmsnorm, addnorm, gate, embedding, bert, rope, act, attention, linear); with --sweep: only these points "
                     "(cfg5:ln:bf16:2048 or ln:bf16)")
     args = ap.parse_args()
     if args.warmup < 3:

@@ -15,6 +15,15 @@ from thot_b200 import abi
 pytestmark = pytest.mark.gpu
 
 
+def gemm_check(got, ref, x, w, b, what):
+    """bf16 outputs of a K-term fp32-accumulated dot product: within 2 bf16 ulp of the fp64 result, or -- where the
+    terms cancel -- inside the accumulation's own error bound 4 u sum_k |x_k w_k| (u = 2^-24), the GEMM counterpart
+    of the absolute floor the row kernels' checks use."""
+    bound = 2.0 ** -22 * (np.abs(x).astype(np.float64) @ np.abs(w).astype(np.float64).T + (0 if b is None else np.abs(b)))
+    ok = tol.bf16_ulp_mask(bits(got), ref) | (np.abs(got.float().cpu().numpy().astype(np.float64) - ref) <= bound)
+    assert ok.all(), f"{what}: {(~ok).sum()} of {ok.size} elements outside 2 bf16 ulp and the accumulation bound"
+
+
 def test_golden_reference_fc_layer(golden_dir):
     z = np.load(golden_dir / "fc_act.npz")
     x, w, b = (to_dev(z[k], torch.bfloat16) for k in ("x", "weight", "bias"))
@@ -36,8 +45,9 @@ def test_against_oracle(act, M, N, K):
     b = (0.1 * torch.randn(N, generator=gen)).bfloat16()
     ref = O.linear_act(x.float().numpy(), w.float().numpy(), b.float().numpy(), act)
     y, pre = abi.linear_bias_act_fwd(x.cuda(), w.cuda(), b.cuda(), act, want_z=True)
-    check(pre, ref["z"], "z")
-    check(y, ref["y"], "y")
+    xn, wn, bn = x.float().numpy(), w.float().numpy(), b.float().numpy()
+    gemm_check(pre, ref["z"], xn, wn, bn, "z")
+    gemm_check(y, ref["y"], xn, wn, bn, "y")             # |act'| <= 1.13, so the same bound carries over
     assert abi.device_status() == 0
 
 
@@ -52,7 +62,7 @@ def test_feed_forward_size_sampled_rows_and_bias_linearity():
     y, _ = abi.linear_bias_act_fwd(x, w, b, abi.ACT_GELU)
     idx = torch.linspace(0, M - 1, 40).long().cuda()
     ref = O.linear_act(x[idx].float().cpu().numpy(), w.float().cpu().numpy(), b.float().cpu().numpy(), O.ACT_GELU)
-    check(y[idx], ref["y"], "sampled rows")
+    gemm_check(y[idx], ref["y"], x[idx].float().cpu().numpy(), w.float().cpu().numpy(), b.float().cpu().numpy(), "sampled rows")
     assert torch.equal(y, abi.linear_bias_act_fwd(x, w, b, abi.ACT_GELU)[0])           # deterministic
     z0, _ = abi.linear_bias_act_fwd(x, w, None, abi.ACT_NONE)
     z1, _ = abi.linear_bias_act_fwd(x, w, torch.full((N,), 2.0, device="cuda").bfloat16(), abi.ACT_NONE)
@@ -65,3 +75,29 @@ def test_argument_checks():
     assert L.nb2_linear_bias_act_fwd(None, None, None, None, None, 4, 12, 8, abi.BF16, 0, None, 0, None) == -2    # N % 8
     assert L.nb2_linear_bias_act_fwd(None, None, None, None, None, 0, 8, 8, abi.BF16, 0, None, 0, None) == 0      # empty
     assert L.nb2_linear_bias_act_fwd(None, None, None, None, None, 4, 8, 8, abi.BF16, 0, None, 0, None) == -1     # NULL
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("act_type,act", [(7, "gelu"), (6, "silu"), (0, "none")])      # Nott::Activation::Type: GeLU = 7, SiLU = 6
+def test_linear_module_forward_and_backward_match_torch(dtype, act_type, act):
+    """The C++ drop-in for the FC layer (parameter names of torch::nn::Linear, activation fused) against
+    torch.nn.functional.linear + activation + autograd on the same GPU tensors."""
+    import torch.nn.functional as F
+    from thot_b200 import _nott_b200_host as host
+    B, S, K, N = 3, 50, 256, 512
+    gen = torch.Generator().manual_seed(2)
+    x = torch.randn(B, S, K, generator=gen).to(dtype).cuda(); w = (torch.randn(N, K, generator=gen) / 16).to(dtype).cuda()
+    b = (0.1 * torch.randn(N, generator=gen)).to(dtype).cuda(); dy = torch.randn(B, S, N, generator=gen).to(dtype).cuda()
+    names, out = host.linear_module_step(x, w, b, act_type, dy)
+    assert names == ["weight", "bias"]
+    xr, wr, br = (t.float().clone().requires_grad_(True) for t in (x, w, b))
+    z = F.linear(xr, wr, br)
+    yr = {"gelu": F.gelu, "silu": F.silu, "none": lambda t: t}[act](z)
+    yr.backward(dy.float())
+    rtol, atol = (2e-2, 2e-2) if dtype == torch.bfloat16 else (1e-4, 1e-4)
+    for got, want in zip(out, (yr, xr.grad, wr.grad, br.grad)):
+        torch.testing.assert_close(got.float(), want.detach(), rtol=rtol, atol=atol * max(1.0, float(want.abs().max())))
+    if dtype == torch.bfloat16:      # the forward is the fused tensor-core call: 2 bf16 ulp of the fp64 oracle
+        ref = O.linear_act(x.float().cpu().numpy().reshape(-1, K), w.float().cpu().numpy(), b.float().cpu().numpy(),
+                           {"gelu": O.ACT_GELU, "silu": O.ACT_SILU, "none": O.ACT_NONE}[act])
+        check(out[0].reshape(-1, N), ref["y"], "module y")

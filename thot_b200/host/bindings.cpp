@@ -43,6 +43,28 @@ PYBIND11_MODULE(_nott_b200_host, m) {
         if (noise.has_value()) return kernel->forward_with_noise(q, k, v, *noise);
         return kernel->forward(q, k, v);
     });
+    // FC layer: Linear + fused activation, forward and backward; returns y, dx, dweight, dbias
+    m.def("linear_module_step", [](torch::Tensor x, torch::Tensor weight, c10::optional<torch::Tensor> bias, int64_t act_type, torch::Tensor dy) {
+        pybind11::gil_scoped_release nogil;
+        nb::LinearOptions opt;
+        opt.in_features = weight.size(1); opt.out_features = weight.size(0); opt.bias = bias.has_value();
+        opt.activation = static_cast<nb::ActivationType>(act_type);
+        nb::Linear mod(opt);
+        mod->to(x.device(), x.scalar_type());
+        {
+            torch::NoGradGuard ng;
+            mod->weight.copy_(weight);
+            if (bias.has_value()) mod->bias.copy_(*bias);
+        }
+        auto xin = x.clone().requires_grad_(true);
+        auto y = mod->forward(xin);
+        y.backward(dy);
+        std::vector<std::string> names;
+        for (auto& kv : mod->named_parameters()) names.push_back(kv.key());
+        std::vector<torch::Tensor> out{y.detach(), xin.grad(), mod->weight.grad()};
+        if (bias.has_value()) out.push_back(mod->bias.grad());
+        return std::make_pair(names, out);
+    });
     m.def("rotary_table", [](int64_t S, int64_t hd, double theta, torch::Device device) {
         return nb::RotaryTable(S, hd, theta, device).table();
     });

@@ -458,6 +458,103 @@ inline torch::Tensor apply(ActivationType type, torch::Tensor input) {
     }
 }
 
+// ------------------------------------------------------------- fully connected (+act)
+// torch::nn::Linear followed by the layer's activation (src/layer/details/fc.hpp:31-49 and the feed-forward loop,
+// src/block/details/transformers/classic.hpp:446-452) as one autograd node.  bf16 CUDA tensors whose widths are
+// multiples of 8 run the tcgen05 GEMM with the bias and the activation in its epilogue; any other dtype or width
+// keeps libtorch's GEMM (as in the reference) and only the activation runs here.
+struct LinearActFunction : public torch::autograd::Function<LinearActFunction> {
+    static torch::Tensor forward(torch::autograd::AutogradContext* ctx, torch::Tensor input, torch::Tensor weight,
+                                 c10::optional<torch::Tensor> bias_opt, int64_t act) {
+        detail::require_cuda(input, "Linear");
+        const auto K = input.size(-1), N = weight.size(0);
+        if (weight.dim() != 2 || weight.size(1) != K) throw std::invalid_argument("Linear: weight must be [out_features, in_features].");
+        auto x = input.contiguous().view({-1, K});
+        auto w = detail::param_like(weight, x);
+        torch::Tensor b = bias_opt.has_value() ? detail::param_like(*bias_opt, x) : torch::Tensor();
+        const bool needs_grad = torch::GradMode::is_enabled() &&
+                                (input.requires_grad() || weight.requires_grad() || (b.defined() && bias_opt->requires_grad()));
+        const bool tensor_core = x.scalar_type() == torch::kBFloat16 && N % 8 == 0 && K % 8 == 0;
+        torch::Tensor y, z;
+        if (tensor_core) {
+            const auto M = x.size(0);
+            y = torch::empty({M, N}, x.options());
+            if (needs_grad && act != NB2_ACT_NONE) z = torch::empty({M, N}, x.options());
+            auto ws = torch::empty({(int64_t)nb2_workspace_bytes(NB2_WS_LINEAR, 0, 0, NB2_BF16)}, x.options().dtype(torch::kUInt8));
+            detail::check(nb2_linear_bias_act_fwd(x.data_ptr(), w.data_ptr(), detail::ptr_or_null(b), z.defined() ? z.data_ptr() : nullptr,
+                                                  y.data_ptr(), M, N, K, NB2_BF16, (int)act, ws.data_ptr(), (size_t)ws.numel(),
+                                                  detail::stream()),
+                          "nb2_linear_bias_act_fwd");
+        } else {
+            z = torch::linear(x, w, b.defined() ? c10::optional<torch::Tensor>(b) : c10::nullopt);
+            if (act == NB2_ACT_NONE) {
+                y = z;
+            } else {
+                y = torch::empty_like(z);
+                detail::check(nb2_act_fwd(z.data_ptr(), y.data_ptr(), z.numel(), detail::dtype_code(z, "Linear"), (int)act, detail::stream()),
+                              "nb2_act_fwd");
+            }
+        }
+        ctx->save_for_backward({x, w, z.defined() ? z : torch::Tensor()});
+        ctx->saved_data["act"] = act;
+        ctx->saved_data["has_bias"] = b.defined();
+        auto shape = input.sizes().vec();
+        shape.back() = N;
+        return y.view(shape);
+    }
+    static torch::autograd::tensor_list backward(torch::autograd::AutogradContext* ctx, torch::autograd::tensor_list grads) {
+        auto saved = ctx->get_saved_variables();
+        auto x = saved[0], w = saved[1], z = saved[2];
+        const auto act = ctx->saved_data["act"].toInt();
+        const auto N = w.size(0);
+        auto dy = grads[0].contiguous().view({-1, N}).to(x.scalar_type());
+        torch::Tensor dz = dy;
+        if (act != NB2_ACT_NONE) {
+            dz = torch::empty_like(dy);
+            detail::check(nb2_act_bwd(z.data_ptr(), dy.data_ptr(), dz.data_ptr(), dz.numel(), detail::dtype_code(dz, "Linear backward"),
+                                      (int)act, detail::stream()),
+                          "nb2_act_bwd");
+        }
+        auto dx = torch::matmul(dz, w);                         // the two backward GEMMs stay libtorch calls, as in the reference
+        auto dw = torch::matmul(dz.t(), x);
+        torch::Tensor db;
+        if (ctx->saved_data["has_bias"].toBool()) db = dz.sum(0);
+        auto shape = grads[0].sizes().vec();
+        shape.back() = x.size(1);
+        return {dx.view(shape), dw, db, torch::Tensor()};
+    }
+};
+
+struct LinearOptions {                 // FCOptions (fc.hpp:19-23) plus the activation the layer is registered with
+    std::int64_t in_features{};
+    std::int64_t out_features{};
+    bool bias{true};
+    ActivationType activation{ActivationType::Identity};
+};
+
+class LinearImpl : public torch::nn::Module {
+public:
+    explicit LinearImpl(LinearOptions options) : options_(options) {
+        if (options_.in_features <= 0 || options_.out_features <= 0)
+            throw std::invalid_argument("Fully connected layers require positive in/out features.");       // fc.hpp:33-35
+        if (detail::fused_act_code(options_.activation) < 0)
+            throw std::invalid_argument("Linear can fuse Identity, GeLU, SiLU or Swish only.");
+        // torch::nn::Linear's own parameters, names and initialisation
+        torch::nn::Linear init(torch::nn::LinearOptions(options_.in_features, options_.out_features).bias(options_.bias));
+        weight = register_parameter("weight", init->weight.detach().clone());
+        if (options_.bias) bias = register_parameter("bias", init->bias.detach().clone());
+    }
+    torch::Tensor forward(torch::Tensor input) {
+        if (!input.defined()) throw std::invalid_argument("Linear requires a defined input tensor.");
+        return LinearActFunction::apply(std::move(input), weight, detail::opt(bias), (int64_t)detail::fused_act_code(options_.activation));
+    }
+    torch::Tensor weight, bias;
+
+private:
+    LinearOptions options_{};
+};
+TORCH_MODULE(Linear);
+
 // -------------------------------------------------------------------------- embedding
 struct EmbeddingFunction : public torch::autograd::Function<EmbeddingFunction> {
     static torch::Tensor forward(torch::autograd::AutogradContext* ctx, torch::Tensor weight, torch::Tensor ids) {
