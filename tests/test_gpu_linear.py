@@ -51,9 +51,9 @@ def test_against_oracle(act, M, N, K):
     assert abi.device_status() == 0
 
 
-def test_feed_forward_size_sampled_rows_and_bias_linearity():
+def test_feed_forward_size_sampled_rows_and_bias_as_a_column():
     """[16384, 1024] x [4096, 1024]^T, the up-projection of a transformer block's feed forward: rows sampled against
-    the oracle; with the identity epilogue, adding a constant to the bias adds it to every output (before rounding)."""
+    the oracle; the bias epilogue agrees with the same bias folded into the product as one more column of K."""
     M, N, K = 16384, 4096, 1024
     gen = torch.Generator(device="cuda").manual_seed(1)
     x = torch.randn(M, K, device="cuda", generator=gen).bfloat16()
@@ -64,9 +64,13 @@ def test_feed_forward_size_sampled_rows_and_bias_linearity():
     ref = O.linear_act(x[idx].float().cpu().numpy(), w.float().cpu().numpy(), b.float().cpu().numpy(), O.ACT_GELU)
     gemm_check(y[idx], ref["y"], x[idx].float().cpu().numpy(), w.float().cpu().numpy(), b.float().cpu().numpy(), "sampled rows")
     assert torch.equal(y, abi.linear_bias_act_fwd(x, w, b, abi.ACT_GELU)[0])           # deterministic
-    z0, _ = abi.linear_bias_act_fwd(x, w, None, abi.ACT_NONE)
-    z1, _ = abi.linear_bias_act_fwd(x, w, torch.full((N,), 2.0, device="cuda").bfloat16(), abi.ACT_NONE)
-    tol.bf16_ulp_close(bits(z1[idx]), z0[idx].float().cpu().numpy().astype(np.float64) + 2.0, max_ulp=1)
+    # the bias as one more column of K (x' = [x | 1 0...], w' = [w | b 0...]) is the same sum: bias path == plain GEMM path
+    xp = torch.cat([x, torch.zeros(M, 8, device="cuda", dtype=torch.bfloat16)], 1); xp[:, K] = 1
+    wp = torch.cat([w, torch.zeros(N, 8, device="cuda", dtype=torch.bfloat16)], 1); wp[:, K] = b
+    z_bias, _ = abi.linear_bias_act_fwd(x, w, b, abi.ACT_NONE)
+    z_col, _ = abi.linear_bias_act_fwd(xp.contiguous(), wp.contiguous(), None, abi.ACT_NONE)
+    gemm_check(z_col[idx], z_bias[idx].float().cpu().numpy().astype(np.float64), x[idx].float().cpu().numpy(), w.float().cpu().numpy(),
+               b.float().cpu().numpy(), "bias as a column of K")
 
 
 def test_argument_checks():

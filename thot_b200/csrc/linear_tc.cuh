@@ -8,9 +8,9 @@
 // the accumulator tile leaves TMEM once, gets the bias row and the activation in registers and is stored.
 //
 // The mainloop and the epilogue pipeline are CUTLASS's sm_100 collectives (tcgen05.mma issued by one thread,
-// operands staged by TMA -- this CTA only, cluster 1x1x1, so no multicast load is generated -- accumulators in
-// TMEM, tcgen05.ld for the epilogue); the activation functors are this library's own (the same fitted erfc
-// GELU and SiLU as the row kernels), plugged into the epilogue visitor tree.
+// operands staged by TMA from this GPU's memory, every tile with a single consumer so that no multicast load is
+// generated, accumulators in TMEM, tcgen05.ld for the epilogue); the activation functors are this library's own
+// (the same fitted erfc GELU and SiLU as the row kernels), plugged into the epilogue visitor tree.
 #pragma once
 
 #include "cutlass/cutlass.h"
@@ -22,6 +22,9 @@
 #include "cutlass/epilogue/collective/collective_builder.hpp"
 #include "cutlass/epilogue/fusion/operations.hpp"
 #include "cutlass/util/packed_stride.hpp"
+
+#include <stdlib.h>
+#include <string.h>
 
 #include "nb2_common.cuh"
 
@@ -55,11 +58,23 @@ template <class T> using EpilogueGelu = EpilogueAct<NB2_ACT_GELU, T>;
 template <class T> using EpilogueSilu = EpilogueAct<NB2_ACT_SILU, T>;
 
 using LinElem = cutlass::bfloat16_t;
-using LinTile = cute::Shape<cute::_128, cute::_128, cute::_64>;
-using LinCluster = cute::Shape<cute::_1, cute::_1, cute::_1>;
+// Two tilings.  PAIR = false: one SM per 128 x 128 tile, cluster 1x1x1.  PAIR = true: two SMs of a 2x1 cluster
+// share one 256 x 128 tile (tcgen05.mma.cta_group::2, each CTA stages its own half of the operands; with a
+// cluster of 2 along M and 1 along N no operand tile has a second consumer, so the loads stay plain, non-multicast
+// TMA copies).  The pair form is the default for M >= 256.
+template <bool PAIR> struct LinShape {
+    using Tile = cute::Shape<cute::_128, cute::_128, cute::_64>;
+    using Cluster = cute::Shape<cute::_1, cute::_1, cute::_1>;
+};
+template <> struct LinShape<true> {
+    using Tile = cute::Shape<cute::_256, cute::_128, cute::_64>;
+    using Cluster = cute::Shape<cute::_2, cute::_1, cute::_1>;
+};
 
-template <class FusionOp>
+template <class FusionOp, bool PAIR>
 struct LinearGemm {
+    using LinTile = typename LinShape<PAIR>::Tile;
+    using LinCluster = typename LinShape<PAIR>::Cluster;
     using CollectiveEpilogue = typename cutlass::epilogue::collective::CollectiveBuilder<
         cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, LinTile, LinCluster,
         cutlass::epilogue::collective::EpilogueTileAuto, float, float,
@@ -80,13 +95,13 @@ struct LinearGemm {
 constexpr size_t kLinearWorkspaceBytes = 1 << 20;
 
 // One launch.  z_out == nullptr: D = act(acc + bias).  z_out given (AUX): also stores acc + bias, the backward's input.
-template <template <class> class Act, bool AUX>
+template <template <class> class Act, bool AUX, bool PAIR>
 int run_linear(const void* x, const void* w, const void* bias, void* z_out, void* y, int64_t M, int64_t N, int64_t K,
                void* workspace, size_t workspace_bytes, cudaStream_t st) {
     using FusionPlain = cutlass::epilogue::fusion::LinCombPerColBiasEltAct<Act, LinElem, float, LinElem>;
     using FusionAux = cutlass::epilogue::fusion::LinCombPerColBiasEltActAux<cutlass::layout::RowMajor, Act, LinElem, float, LinElem, LinElem>;
     using Fusion = std::conditional_t<AUX, FusionAux, FusionPlain>;
-    using G = LinearGemm<Fusion>;
+    using G = LinearGemm<Fusion, PAIR>;
     using Gemm = typename G::Gemm;
     using StrideA = typename Gemm::GemmKernel::StrideA;
     using StrideB = typename Gemm::GemmKernel::StrideB;
@@ -133,15 +148,34 @@ int run_linear(const void* x, const void* w, const void* bias, void* z_out, void
     return 0;
 }
 
+// NB2_LINEAR_TILE=single|pair overrides the choice of tiling, for measurements
+static inline int linear_tile_override() {
+    static int cached = -1;
+    if (cached < 0) {
+        const char* e = getenv("NB2_LINEAR_TILE");
+        cached = (e == nullptr) ? 0 : (strcmp(e, "single") == 0 ? 1 : (strcmp(e, "pair") == 0 ? 2 : 0));
+    }
+    return cached;
+}
+
+template <bool AUX, bool PAIR>
+int run_linear_tile(const void* x, const void* w, const void* bias, void* z_out, void* y, int64_t M, int64_t N, int64_t K, int act,
+                    void* workspace, size_t workspace_bytes, cudaStream_t st) {
+    switch (act) {
+        case NB2_ACT_NONE: return run_linear<EpilogueNone, AUX, PAIR>(x, w, bias, z_out, y, M, N, K, workspace, workspace_bytes, st);
+        case NB2_ACT_GELU: return run_linear<EpilogueGelu, AUX, PAIR>(x, w, bias, z_out, y, M, N, K, workspace, workspace_bytes, st);
+        case NB2_ACT_SILU: return run_linear<EpilogueSilu, AUX, PAIR>(x, w, bias, z_out, y, M, N, K, workspace, workspace_bytes, st);
+        default: set_error("linear: unknown activation %d", act); return NB2_ERR_DTYPE;
+    }
+}
+
 template <bool AUX>
 int run_linear_act(const void* x, const void* w, const void* bias, void* z_out, void* y, int64_t M, int64_t N, int64_t K, int act,
                    void* workspace, size_t workspace_bytes, cudaStream_t st) {
-    switch (act) {
-        case NB2_ACT_NONE: return run_linear<EpilogueNone, AUX>(x, w, bias, z_out, y, M, N, K, workspace, workspace_bytes, st);
-        case NB2_ACT_GELU: return run_linear<EpilogueGelu, AUX>(x, w, bias, z_out, y, M, N, K, workspace, workspace_bytes, st);
-        case NB2_ACT_SILU: return run_linear<EpilogueSilu, AUX>(x, w, bias, z_out, y, M, N, K, workspace, workspace_bytes, st);
-        default: set_error("linear: unknown activation %d", act); return NB2_ERR_DTYPE;
-    }
+    const int ov = linear_tile_override();
+    const bool pair = ov == 2 || (ov == 0 && M >= 256);
+    if (pair) return run_linear_tile<AUX, true>(x, w, bias, z_out, y, M, N, K, act, workspace, workspace_bytes, st);
+    return run_linear_tile<AUX, false>(x, w, bias, z_out, y, M, N, K, act, workspace, workspace_bytes, st);
 }
 
 }  // namespace nb2

@@ -21,7 +21,10 @@ PYBIND11_MODULE(_nott_b200_host, m) {
     });
     m.def("apply", [](int64_t type, torch::Tensor x) { return nb::apply(static_cast<nb::ActivationType>(type), std::move(x)); });
     m.def("silu_gate", [](torch::Tensor gate, torch::Tensor up) { return nb::silu_gate(gate, up); });
-    m.def("embedding", [](torch::Tensor weight, torch::Tensor ids) { return nb::EmbeddingFunction::apply(std::move(weight), std::move(ids)); });
+    m.def("embedding", [](torch::Tensor weight, torch::Tensor ids) {
+        const bool training = torch::GradMode::is_enabled() && weight.requires_grad();
+        return nb::EmbeddingFunction::apply(std::move(weight), std::move(ids), training);
+    });
     m.def("attention_softmax", [](torch::Tensor scores, c10::optional<torch::Tensor> mask, c10::optional<torch::Tensor> padding,
                                   double scale, bool causal) {
         pybind11::gil_scoped_release nogil;

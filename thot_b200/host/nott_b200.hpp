@@ -464,16 +464,17 @@ inline torch::Tensor apply(ActivationType type, torch::Tensor input) {
 // multiples of 8 run the tcgen05 GEMM with the bias and the activation in its epilogue; any other dtype or width
 // keeps libtorch's GEMM (as in the reference) and only the activation runs here.
 struct LinearActFunction : public torch::autograd::Function<LinearActFunction> {
+    // `training`: a backward will follow (decided by the caller: grad mode is always off inside a forward), so the
+    // pre-activation is kept.
     static torch::Tensor forward(torch::autograd::AutogradContext* ctx, torch::Tensor input, torch::Tensor weight,
-                                 c10::optional<torch::Tensor> bias_opt, int64_t act) {
+                                 c10::optional<torch::Tensor> bias_opt, int64_t act, bool training) {
         detail::require_cuda(input, "Linear");
         const auto K = input.size(-1), N = weight.size(0);
         if (weight.dim() != 2 || weight.size(1) != K) throw std::invalid_argument("Linear: weight must be [out_features, in_features].");
         auto x = input.contiguous().view({-1, K});
         auto w = detail::param_like(weight, x);
         torch::Tensor b = bias_opt.has_value() ? detail::param_like(*bias_opt, x) : torch::Tensor();
-        const bool needs_grad = torch::GradMode::is_enabled() &&
-                                (input.requires_grad() || weight.requires_grad() || (b.defined() && bias_opt->requires_grad()));
+        const bool needs_grad = training;
         const bool tensor_core = x.scalar_type() == torch::kBFloat16 && N % 8 == 0 && K % 8 == 0;
         torch::Tensor y, z;
         if (tensor_core) {
@@ -521,7 +522,7 @@ struct LinearActFunction : public torch::autograd::Function<LinearActFunction> {
         if (ctx->saved_data["has_bias"].toBool()) db = dz.sum(0);
         auto shape = grads[0].sizes().vec();
         shape.back() = x.size(1);
-        return {dx.view(shape), dw, db, torch::Tensor()};
+        return {dx.view(shape), dw, db, torch::Tensor(), torch::Tensor()};
     }
 };
 
@@ -546,7 +547,8 @@ public:
     }
     torch::Tensor forward(torch::Tensor input) {
         if (!input.defined()) throw std::invalid_argument("Linear requires a defined input tensor.");
-        return LinearActFunction::apply(std::move(input), weight, detail::opt(bias), (int64_t)detail::fused_act_code(options_.activation));
+        const bool training = torch::GradMode::is_enabled() && (input.requires_grad() || weight.requires_grad() || (bias.defined() && bias.requires_grad()));
+        return LinearActFunction::apply(std::move(input), weight, detail::opt(bias), (int64_t)detail::fused_act_code(options_.activation), training);
     }
     torch::Tensor weight, bias;
 
@@ -557,7 +559,8 @@ TORCH_MODULE(Linear);
 
 // -------------------------------------------------------------------------- embedding
 struct EmbeddingFunction : public torch::autograd::Function<EmbeddingFunction> {
-    static torch::Tensor forward(torch::autograd::AutogradContext* ctx, torch::Tensor weight, torch::Tensor ids) {
+    // `training`: a backward will follow (the caller decides: grad mode is always off inside a forward)
+    static torch::Tensor forward(torch::autograd::AutogradContext* ctx, torch::Tensor weight, torch::Tensor ids, bool training = false) {
         detail::require_cuda(weight, "Embedding");
         if (ids.scalar_type() != torch::kInt64 && ids.scalar_type() != torch::kInt32)
             throw std::invalid_argument("Embedding expects int32 or int64 token ids.");
@@ -570,7 +573,7 @@ struct EmbeddingFunction : public torch::autograd::Function<EmbeddingFunction> {
         // The backward's index (token runs per table row) depends on the ids alone: it is built here, on a
         // pool stream beside the gather, and joined before returning, so the backward is one kernel.
         torch::Tensor index;
-        if (weight.requires_grad() && torch::GradMode::is_enabled() && flat.size(0) > 0) {
+        if (training && flat.size(0) > 0) {
             const auto ws = nb2_workspace_bytes(NB2_WS_EMBEDDING_BWD, flat.size(0), vocab, code);
             index = torch::empty({(int64_t)ws}, w.options().dtype(torch::kUInt8));
             auto cur = at::cuda::getCurrentCUDAStream();
@@ -617,7 +620,7 @@ struct EmbeddingFunction : public torch::autograd::Function<EmbeddingFunction> {
                                             detail::stream()),
                           "nb2_embedding_bwd");
         }
-        return {dtable, torch::Tensor()};
+        return {dtable, torch::Tensor(), torch::Tensor()};
     }
 };
 
@@ -628,7 +631,9 @@ public:
             throw std::invalid_argument("Embedding requires positive vocabulary and embedding sizes.");
         weight = register_parameter("weight", torch::randn({num_embeddings, embedding_dim}));   // N(0,1), as torch::nn::Embedding
     }
-    torch::Tensor forward(const torch::Tensor& ids) { return EmbeddingFunction::apply(weight, ids); }
+    torch::Tensor forward(const torch::Tensor& ids) {
+        return EmbeddingFunction::apply(weight, ids, torch::GradMode::is_enabled() && weight.requires_grad());
+    }
     torch::Tensor weight;
 };
 TORCH_MODULE(Embedding);
