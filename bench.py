@@ -292,7 +292,7 @@ def run_suite(args):
         _suite_act(abi, timed, dev, g)
     if want("attention"):
         _suite_attention(abi, timed, dev, g)
-    if want("linear"):
+    if want("linear") and abi.linear_available():
         _suite_linear(abi, results, dev, g)
     abi.device_status()
     _emit({"suite": results, "peak_gbs": peak, "unit": "GB/s", "data": "synthetic",

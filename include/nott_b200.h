@@ -62,7 +62,8 @@ enum {
     NB2_ERR_WORKSPACE = -5,   /* workspace too small                      */
     NB2_ERR_DEVICE = -6,      /* device-side status word reported a fault */
     NB2_ERR_COMM = -7,        /* the gradient exchange failed or its communicator was aborted */
-    NB2_ERR_COMM_TIMEOUT = -8 /* the gradient exchange did not finish before the deadline */
+    NB2_ERR_COMM_TIMEOUT = -8, /* the gradient exchange did not finish before the deadline */
+    NB2_ERR_UNAVAILABLE = -9  /* an optional part of the library is not installed */
 };
 
 /* which operation a workspace query is for */
@@ -352,7 +353,12 @@ int nb2_bert_embedding_ln_bwd(const void* sum, const void* dy, const void* ids, 
  * activation needs (nb2_act_bwd).  N and K must be multiples of 8.  fp32 layers are
  * not taken (NB2_ERR_DTYPE): TF32 tensor cores do not meet the fp32 tolerance.
  * workspace: nb2_workspace_bytes(NB2_WS_LINEAR, 0, 0, dtype) bytes.
+ * The kernels live in a second library, libnott_b200_linear.so, that this one opens
+ * from its own folder on the first call; where it is not installed the call
+ * returns NB2_ERR_UNAVAILABLE (nb2_linear_available() tells beforehand) and every
+ * other entry point is unaffected.
  * ------------------------------------------------------------------ */
+int nb2_linear_available(void);
 int nb2_linear_bias_act_fwd(const void* x, const void* weight, const void* bias, void* z_out, void* y,
                             int64_t M, int64_t N, int64_t K, int dtype, int act,
                             void* workspace, size_t workspace_bytes, void* stream);

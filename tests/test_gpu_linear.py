@@ -12,7 +12,8 @@ from tests import tol
 from tests.gpu_util import bits, check, to_dev
 from thot_b200 import abi
 
-pytestmark = pytest.mark.gpu
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(not abi.linear_available(), reason="libnott_b200_linear.so is not installed next to the core library")]
 
 
 def gemm_check(got, ref, x, w, b, what):

@@ -39,6 +39,7 @@ _SIGNATURES = {
                                                   c_int64, c_int64, c_int64, c_int64, c_double, c_int, c_int, c_void_p]),
     "nb2_attention_softmax_dropout_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_double, c_int, c_void_p]),
     "nb2_linear_bias_act_fwd": (c_int, [c_void_p] * 5 + [c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "nb2_linear_available": (c_int, []),
     "nb2_selftest_bounded_wait": (c_int, [c_int64, c_void_p, c_void_p]),
     "nb2_workspace_bytes": (c_size_t, [c_int, c_int64, c_int64, c_int]),
     "nb2_layernorm_fwd": (c_int, [c_void_p] * 6 + [c_int64, c_int64, c_double, c_int, c_int, c_void_p]),
@@ -425,6 +426,11 @@ def attention_softmax_bwd(attn, dattn, scale: float, noise=None):
 
 # ------------------------------------------------------------------- linear
 _linear_ws = {}
+
+
+def linear_available() -> bool:
+    """Is libnott_b200_linear.so (the tensor-core linear kernels) installed next to the core library?"""
+    return bool(lib().nb2_linear_available())
 
 
 def linear_bias_act_fwd(x, weight, bias=None, act: int = ACT_NONE, want_z: bool = False):

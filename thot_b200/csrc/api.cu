@@ -533,9 +533,9 @@ int nb2_linear_bias_act_fwd(const void* x, const void* weight, const void* bias,
                 NB2_ERR_ALIGN, "linear: pointers must be 16-byte aligned");
     int rc = require_device();
     if (rc != 0) return rc;
-    if (z_out != nullptr) return launch_linear_aux(x, weight, bias, z_out, y, M, N, K, act, workspace, workspace_bytes, (cudaStream_t)stream);
-    return launch_linear_plain(x, weight, bias, y, M, N, K, act, workspace, workspace_bytes, (cudaStream_t)stream);
+    return launch_linear(x, weight, bias, z_out, y, M, N, K, act, workspace, workspace_bytes, (cudaStream_t)stream);
 }
+int nb2_linear_available(void) { return linear_library_present() ? 1 : 0; }
 
 int nb2_rope_table(float* cos_sin, const int32_t* positions, int64_t S, int64_t hd, double theta, void* stream) {
     NB2_REQUIRE(S >= 0 && hd >= 2 && hd % 2 == 0, NB2_ERR_SHAPE, "rope table: S=%lld head_dim=%lld (need an even head_dim >= 2)", (long long)S, (long long)hd);

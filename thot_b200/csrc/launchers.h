@@ -37,10 +37,9 @@ int launch_attention_softmax_fwd(const void* scores, const uint8_t* key_padding,
 int launch_attention_softmax_bwd(const void* attn, const void* dattn, void* dscores, int64_t rows, int64_t S, float scale,
                                  int dtype, cudaStream_t st, const void* noise = nullptr);
 
-// tensor-core linear layer (linear_tc_*.cu)
-int launch_linear_plain(const void* x, const void* w, const void* bias, void* y, int64_t M, int64_t N, int64_t K, int act,
-                        void* workspace, size_t workspace_bytes, cudaStream_t st);
-int launch_linear_aux(const void* x, const void* w, const void* bias, void* z_out, void* y, int64_t M, int64_t N, int64_t K, int act,
-                      void* workspace, size_t workspace_bytes, cudaStream_t st);
+// tensor-core linear layer: lives in libnott_b200_linear.so (thot_b200/csrc_linear), loaded on first use
+int launch_linear(const void* x, const void* w, const void* bias, void* z_out, void* y, int64_t M, int64_t N, int64_t K, int act,
+                  void* workspace, size_t workspace_bytes, cudaStream_t st);
+bool linear_library_present();
 
 }  // namespace nb2

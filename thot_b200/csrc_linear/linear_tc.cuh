@@ -23,12 +23,29 @@
 #include "cutlass/epilogue/fusion/operations.hpp"
 #include "cutlass/util/packed_stride.hpp"
 
+#include <stdarg.h>
+#include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
 
-#include "nb2_common.cuh"
+#include "../csrc/nb2_common.cuh"
 
+// This translation unit is built into a library of its own (libnott_b200_linear.so) that the core library loads on
+// first use: it is the only part of the tree that instantiates CUTLASS collectives.  It reports errors through a
+// caller-provided buffer and uses nothing of the core library but the inline device functions of nb2_common.cuh.
 namespace nb2 {
+
+struct LinErr {
+    char* buf;
+    size_t len;
+    void set(const char* fmt, ...) const {
+        if (buf == nullptr || len == 0) return;
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(buf, len, fmt, ap);
+        va_end(ap);
+    }
+};
 
 // activation functors for the epilogue visitor tree: scalar and fragment (Array) forms
 template <int ACT, class T>
@@ -97,7 +114,7 @@ constexpr size_t kLinearWorkspaceBytes = 1 << 20;
 // One launch.  z_out == nullptr: D = act(acc + bias).  z_out given (AUX): also stores acc + bias, the backward's input.
 template <template <class> class Act, bool AUX, bool PAIR>
 int run_linear(const void* x, const void* w, const void* bias, void* z_out, void* y, int64_t M, int64_t N, int64_t K,
-               void* workspace, size_t workspace_bytes, cudaStream_t st) {
+               void* workspace, size_t workspace_bytes, cudaStream_t st, const LinErr& err) {
     using FusionPlain = cutlass::epilogue::fusion::LinCombPerColBiasEltAct<Act, LinElem, float, LinElem>;
     using FusionAux = cutlass::epilogue::fusion::LinCombPerColBiasEltActAux<cutlass::layout::RowMajor, Act, LinElem, float, LinElem, LinElem>;
     using Fusion = std::conditional_t<AUX, FusionAux, FusionPlain>;
@@ -126,24 +143,29 @@ int run_linear(const void* x, const void* w, const void* bias, void* z_out, void
     }
     Gemm gemm;
     if (gemm.can_implement(args) != cutlass::Status::kSuccess) {
-        set_error("linear: shape M=%lld N=%lld K=%lld is not supported by the tensor-core kernel (N and K must be multiples of 8)",
-                  (long long)M, (long long)N, (long long)K);
+        err.set("linear: shape M=%lld N=%lld K=%lld is not supported by the tensor-core kernel (N and K must be multiples of 8)",
+                (long long)M, (long long)N, (long long)K);
         return NB2_ERR_SHAPE;
     }
     const size_t need = Gemm::get_workspace_size(args);
     if (need > workspace_bytes || (need > 0 && workspace == nullptr)) {
-        set_error("linear: workspace %zu < required %zu", workspace_bytes, need);
+        err.set("linear: workspace %zu < required %zu", workspace_bytes, need);
         return NB2_ERR_WORKSPACE;
     }
     cutlass::Status s = gemm.initialize(args, workspace, st);
     if (s != cutlass::Status::kSuccess) {
-        set_error("linear: kernel initialisation failed (%s)", cutlassGetStatusString(s));
+        err.set("linear: kernel initialisation failed (%s)", cutlassGetStatusString(s));
         return NB2_ERR_SHAPE;
     }
     s = gemm.run(st);
     if (s != cutlass::Status::kSuccess) {
         const cudaError_t e = cudaGetLastError();
-        return e != cudaSuccess ? cuda_status(e, "linear (tcgen05 GEMM) launch") : (set_error("linear: launch failed (%s)", cutlassGetStatusString(s)), NB2_ERR_SHAPE);
+        if (e != cudaSuccess) {
+            err.set("linear (tcgen05 GEMM) launch: %s (%s)", cudaGetErrorString(e), cudaGetErrorName(e));
+            return (int)e;
+        }
+        err.set("linear: launch failed (%s)", cutlassGetStatusString(s));
+        return NB2_ERR_SHAPE;
     }
     return 0;
 }
@@ -160,22 +182,22 @@ static inline int linear_tile_override() {
 
 template <bool AUX, bool PAIR>
 int run_linear_tile(const void* x, const void* w, const void* bias, void* z_out, void* y, int64_t M, int64_t N, int64_t K, int act,
-                    void* workspace, size_t workspace_bytes, cudaStream_t st) {
+                    void* workspace, size_t workspace_bytes, cudaStream_t st, const LinErr& err) {
     switch (act) {
-        case NB2_ACT_NONE: return run_linear<EpilogueNone, AUX, PAIR>(x, w, bias, z_out, y, M, N, K, workspace, workspace_bytes, st);
-        case NB2_ACT_GELU: return run_linear<EpilogueGelu, AUX, PAIR>(x, w, bias, z_out, y, M, N, K, workspace, workspace_bytes, st);
-        case NB2_ACT_SILU: return run_linear<EpilogueSilu, AUX, PAIR>(x, w, bias, z_out, y, M, N, K, workspace, workspace_bytes, st);
-        default: set_error("linear: unknown activation %d", act); return NB2_ERR_DTYPE;
+        case NB2_ACT_NONE: return run_linear<EpilogueNone, AUX, PAIR>(x, w, bias, z_out, y, M, N, K, workspace, workspace_bytes, st, err);
+        case NB2_ACT_GELU: return run_linear<EpilogueGelu, AUX, PAIR>(x, w, bias, z_out, y, M, N, K, workspace, workspace_bytes, st, err);
+        case NB2_ACT_SILU: return run_linear<EpilogueSilu, AUX, PAIR>(x, w, bias, z_out, y, M, N, K, workspace, workspace_bytes, st, err);
+        default: err.set("linear: unknown activation %d", act); return NB2_ERR_DTYPE;
     }
 }
 
 template <bool AUX>
 int run_linear_act(const void* x, const void* w, const void* bias, void* z_out, void* y, int64_t M, int64_t N, int64_t K, int act,
-                   void* workspace, size_t workspace_bytes, cudaStream_t st) {
+                   void* workspace, size_t workspace_bytes, cudaStream_t st, const LinErr& err) {
     const int ov = linear_tile_override();
     const bool pair = ov == 2 || (ov == 0 && M >= 256);
-    if (pair) return run_linear_tile<AUX, true>(x, w, bias, z_out, y, M, N, K, act, workspace, workspace_bytes, st);
-    return run_linear_tile<AUX, false>(x, w, bias, z_out, y, M, N, K, act, workspace, workspace_bytes, st);
+    if (pair) return run_linear_tile<AUX, true>(x, w, bias, z_out, y, M, N, K, act, workspace, workspace_bytes, st, err);
+    return run_linear_tile<AUX, false>(x, w, bias, z_out, y, M, N, K, act, workspace, workspace_bytes, st, err);
 }
 
 }  // namespace nb2
