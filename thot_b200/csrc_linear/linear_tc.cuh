@@ -109,8 +109,6 @@ struct LinearGemm {
     using Gemm = cutlass::gemm::device::GemmUniversalAdapter<Kernel>;
 };
 
-constexpr size_t kLinearWorkspaceBytes = 1 << 20;
-
 // One launch.  z_out == nullptr: D = act(acc + bias).  z_out given (AUX): also stores acc + bias, the backward's input.
 template <template <class> class Act, bool AUX, bool PAIR>
 int run_linear(const void* x, const void* w, const void* bias, void* z_out, void* y, int64_t M, int64_t N, int64_t K,
