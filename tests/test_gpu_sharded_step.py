@@ -194,3 +194,24 @@ def test_two_ranks_sum_to_the_unsharded_gradients(tmp_path, exchange):
         tol.long_sum_close(got[r][D:], ref["dbeta"], rows)
     dx = np.concatenate([np.load(tmp_path / f"dx{r}.npy") for r in range(world)])
     tol.fp32_close(dx, ref["dx"])
+
+
+@pytest.mark.parametrize("exchange", [abi.EXCHANGE_NCCL, abi.EXCHANGE_PEER])
+def test_cpp_step_driver_classes(exchange):
+    """Nott::B200::Communicator / ShardedNormStep (the C++ wrappers over nb2_comm / nb2_step) give the same bits as
+    the separate ABI calls."""
+    from thot_b200 import _nott_b200_host as host
+    rows, D = 2000, 1024
+    x, _ = make((rows, D), 1, torch.float32); dy, _ = make((rows, D), 2, torch.float32)
+    g, _ = make((D,), 3, torch.float32, 0.02, 1.0); b, _ = make((D,), 4, torch.float32, 0.02)
+    y, dx, g0, g1 = host.sharded_norm_steps(False, exchange, x, dy, g, b, 7, 1e-5, 3)       # 7 = Nott::Activation::Type::GeLU
+    y0, mean, rstd = abi.layernorm_fwd(x, g, b, 1e-5, abi.ACT_GELU)
+    dx0, gb0 = abi.layernorm_bwd(x, dy, g, b, mean, rstd, abi.ACT_GELU)
+    assert torch.equal(y, y0) and torch.equal(dx, dx0)
+    assert torch.equal(g0, gb0.reshape(-1)) and torch.equal(g1, gb0.reshape(-1))
+    w, _ = make((D,), 5, torch.bfloat16, 0.02, 1.0)
+    xb, dyb = x.bfloat16(), dy.bfloat16()
+    y, dx, g0, g1 = host.sharded_norm_steps(True, exchange, xb, dyb, w, None, 6, 1e-6, 2)   # 6 = SiLU
+    yr, rstd = abi.rmsnorm_fwd(xb, w, 1e-6, abi.ACT_SILU)
+    dxr, dw = abi.rmsnorm_bwd(xb, dyb, w, rstd, abi.ACT_SILU)
+    assert torch.equal(y, yr) and torch.equal(dx, dxr) and torch.equal(g1, dw) and torch.equal(g0, dw)

@@ -68,6 +68,20 @@ PYBIND11_MODULE(_nott_b200_host, m) {
         if (bias.has_value()) out.push_back(mod->bias.grad());
         return std::make_pair(names, out);
     });
+    // the C++ step driver on a one-rank communicator: three steps with alternating gradient buffers
+    m.def("sharded_norm_steps", [](bool rms, int64_t exchange, torch::Tensor x, torch::Tensor dy, torch::Tensor weight,
+                                   c10::optional<torch::Tensor> bias, int64_t act_type, double eps, int64_t steps) {
+        pybind11::gil_scoped_release nogil;
+        auto comm = std::make_shared<nb::Communicator>(std::vector<uint8_t>{}, 0, 1, (int)exchange, (rms ? 1 : 2) * x.size(1));
+        nb::ShardedNormStep step(comm, rms, x.size(0), x.size(1), x.scalar_type(), static_cast<nb::ActivationType>(act_type), eps);
+        auto y = torch::empty_like(x), dx = torch::empty_like(x);
+        std::vector<torch::Tensor> grads{torch::zeros({(rms ? 1 : 2) * x.size(1)}, x.options().dtype(torch::kFloat32)),
+                                         torch::zeros({(rms ? 1 : 2) * x.size(1)}, x.options().dtype(torch::kFloat32))};
+        for (int64_t k = 0; k < steps; ++k) step.run(x, dy, weight, bias.value_or(torch::Tensor()), y, dx, grads[k & 1]);
+        step.finish();
+        comm->wait(10.0);
+        return std::vector<torch::Tensor>{y, dx, grads[0], grads[1]};
+    });
     m.def("rotary_table", [](int64_t S, int64_t hd, double theta, torch::Device device) {
         return nb::RotaryTable(S, hd, theta, device).table();
     });

@@ -908,6 +908,78 @@ private:
 TORCH_MODULE(ScaledDotProductKernel);
 
 
+// ------------------------------------------------------------- row-sharded training step
+// One process per GPU, rows (batch x sequence) split over the ranks: the reference itself runs on one device
+// (src/core.hpp:1706-1708) and consumes parameter gradients only in the optimizer step (src/core.hpp:3811-3820).
+// Communicator wraps nb2_comm (the sum over ranks of the fp32 parameter gradients: NCCL allreduce on a side stream,
+// or peer stores over NVLink fused into the partial reduce); ShardedNormStep wraps nb2_step (forward, backward,
+// partial reduce and exchange of one norm layer in one call).  Status codes become exceptions as everywhere here;
+// a failed or timed-out exchange is a std::runtime_error.
+class Communicator {
+public:
+    static std::vector<uint8_t> make_id() {                 // rank 0; the other ranks receive it over any host channel
+        std::vector<uint8_t> id(NB2_COMM_ID_BYTES);
+        detail::check(nb2_comm_unique_id(id.data()), "nb2_comm_unique_id");
+        return id;
+    }
+    Communicator(const std::vector<uint8_t>& id, int rank, int world, int exchange = NB2_EXCHANGE_NCCL, int64_t max_cols = 2 * 8192) {
+        if (world > 1 && id.size() != NB2_COMM_ID_BYTES) throw std::invalid_argument("Communicator: the id must have NB2_COMM_ID_BYTES bytes.");
+        detail::check(nb2_comm_create(&comm_, world > 1 ? id.data() : nullptr, rank, world, exchange, max_cols), "nb2_comm_create");
+    }
+    Communicator(const Communicator&) = delete;
+    Communicator& operator=(const Communicator&) = delete;
+    ~Communicator() { nb2_comm_destroy(comm_); }
+    // blocks the host until the exchange started last has finished; throws (after aborting the communicator) on an
+    // asynchronous error or when `timeout_s` passes
+    void wait(double timeout_s) {
+        const int rc = nb2_comm_wait(comm_, timeout_s);
+        if (rc != 0) throw std::runtime_error(std::string("gradient exchange: ") + nb2_last_error_string());
+    }
+    nb2_comm* get() const { return comm_; }
+
+private:
+    nb2_comm* comm_{nullptr};
+};
+
+class ShardedNormStep {
+public:
+    // `comm` may be null (single GPU).  rms: RMSNorm (weight only), else LayerNorm (weight, bias).
+    ShardedNormStep(std::shared_ptr<Communicator> comm, bool rms, int64_t rows, int64_t D, torch::ScalarType dtype,
+                    ActivationType activation, double eps)
+        : comm_(std::move(comm)), rms_(rms), rows_(rows), D_(D) {
+        const int act = detail::fused_act_code(activation);
+        if (act < 0) throw std::invalid_argument("ShardedNormStep can fuse Identity, GeLU, SiLU or Swish only.");
+        if (dtype != torch::kFloat32 && dtype != torch::kBFloat16) throw std::invalid_argument("ShardedNormStep supports float32 and bfloat16.");
+        detail::check(nb2_step_create(&step_, comm_ ? comm_->get() : nullptr, rms ? NB2_NORM_RMS : NB2_NORM_LAYER, rows, D,
+                                      dtype == torch::kFloat32 ? NB2_F32 : NB2_BF16, act, eps),
+                      "nb2_step_create");
+    }
+    ShardedNormStep(const ShardedNormStep&) = delete;
+    ShardedNormStep& operator=(const ShardedNormStep&) = delete;
+    ~ShardedNormStep() { nb2_step_destroy(step_); }
+
+    // y, dx: this rank's [rows, D] outputs; grads: [2*D] (LayerNorm: dgamma | dbeta) or [D] fp32, complete after the
+    // next run() or finish() in stream order: pass two buffers alternately.
+    void run(const torch::Tensor& x, const torch::Tensor& dy, const torch::Tensor& weight, const torch::Tensor& bias,
+             torch::Tensor& y, torch::Tensor& dx, torch::Tensor& grads) {
+        detail::require_cuda(x, "ShardedNormStep");
+        if (x.dim() != 2 || x.size(0) != rows_ || x.size(1) != D_ || !x.is_contiguous() || !dy.is_contiguous() || dy.sizes() != x.sizes())
+            throw std::invalid_argument("ShardedNormStep expects contiguous [rows, D] activations of the size it was built for.");
+        if (grads.scalar_type() != torch::kFloat32 || grads.numel() != (rms_ ? 1 : 2) * D_ || !grads.is_contiguous())
+            throw std::invalid_argument("ShardedNormStep expects a contiguous fp32 gradient buffer of (rms ? 1 : 2) * D elements.");
+        detail::check(nb2_step_run(step_, x.data_ptr(), dy.data_ptr(), weight.data_ptr(), rms_ ? nullptr : detail::ptr_or_null(bias),
+                                   y.data_ptr(), dx.data_ptr(), grads.data_ptr<float>(), detail::stream()),
+                      "nb2_step_run");
+    }
+    void finish() { detail::check(nb2_step_finish(step_, detail::stream()), "nb2_step_finish"); }
+
+private:
+    std::shared_ptr<Communicator> comm_;
+    nb2_step* step_{nullptr};
+    bool rms_;
+    int64_t rows_, D_;
+};
+
 struct RotaryFunction : public torch::autograd::Function<RotaryFunction> {
     static torch::Tensor forward(torch::autograd::AutogradContext* ctx, torch::Tensor x, torch::Tensor table) {
         detail::require_cuda(x, "rotary");
