@@ -58,3 +58,22 @@ def test_abi_argument_checks_return_before_touching_a_device():
     assert L.nb2_embedding_index(None, 0, 10, 0, None, 0, None) == 0                                         # no tokens
     assert L.nb2_selftest_bounded_wait(0, None, None) == -2
     assert b"cycle_limit" in L.nb2_last_error_string()
+
+
+def test_reference_arm_prints_the_same_config_and_the_requested_steps(bench):
+    """`bench.py --impl reference` needs no GPU: one JSON line with the GPU arm's metric, unit and config object, the
+    requested steps and warm-up, an e2e object that repeats the value with zero copy bytes, and a cpu_baseline record."""
+    import json
+    import subprocess
+    from oracle import reference as R
+    if not R.available():
+        pytest.skip("oracle/_ref/libnott_ref.so not built (needs the reference checkout)")
+    out = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--steps", "2", "--warmup", "1",
+                          "--workload", "cfg5:ln:fp32:1024:4096"], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["metric"] == bench.METRIC and line["unit"] == bench.UNIT
+    assert (line["steps"], line["warmup"], line["n_gpus"], line["higher_is_better"]) == (2, 1, 1, True)
+    assert line["config"] == bench.config_of(bench.Workload("cfg5:ln:fp32:1024:4096", 1), 1)
+    assert line["e2e"] == {"value": line["value"], "unit": bench.UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert line["cpu_baseline"]["kind"] == "reference" and line["cpu_baseline"]["cores"] >= 1 and line["gpu_launches"] == 0
