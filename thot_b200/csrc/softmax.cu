@@ -102,8 +102,8 @@ struct RowPos {
 // instructions per score and was bound by issue (ncu: 71% issue slots busy, ALU pipe 60%).
 constexpr int kSmPad = 1, kSmMask = 2, kSmCausal = 4, kSmNoise = 8;
 
-template <typename T, int TPR, int VPT, int FLAGS, int MINB = 3>
-__global__ void __launch_bounds__((TPR > 256 ? TPR : 256), (TPR > 256 ? 1 : MINB))
+template <typename T, int TPR, int VPT, int FLAGS>
+__global__ void __launch_bounds__((TPR > 256 ? TPR : 256), (TPR > 256 ? 1 : 3))
 softmax_fwd_kernel(const T* __restrict__ scores, const SoftmaxMask m, T* __restrict__ out,
                    int64_t rows, int64_t H, int64_t Tq, int S, float scale) {
     constexpr int EPV = VecTraits<T>::EPV;
@@ -382,11 +382,11 @@ int pick_softmax_tpr(int64_t nvec, int vpt = 4) {
     return 0;
 }
 
-int64_t row_grid(int64_t rows, int tpr, int minb = 3) {
+int64_t row_grid(int64_t rows, int tpr) {
     const int threads = tpr > 256 ? tpr : 256;
     const int rpc = threads / tpr;
     const int64_t need = (rows + rpc - 1) / rpc;
-    const int64_t cap = (int64_t)sm_count() * (tpr > 256 ? 1 : minb) * 4;      // a few CTAs per slot: rows are short-lived
+    const int64_t cap = (int64_t)sm_count() * (tpr > 256 ? 1 : 3) * 4;      // a few CTAs per slot: rows are short-lived
     return need < cap ? (need < 1 ? 1 : need) : cap;
 }
 
@@ -394,14 +394,6 @@ template <typename T, int TPR, int FLAGS>
 int launch_fwd_flags(const void* scores, const SoftmaxMask& m, void* out, int64_t rows, int64_t H, int64_t Tq, int64_t S,
                      float scale, cudaStream_t st) {
     constexpr int THREADS = TPR > 256 ? TPR : 256;
-    // bf16 rows of up to 256 threads with an additive mask: 4 CTAs per SM (64 registers) when NB2_SOFTMAX_OCC=4 (measurement switch)
-    if constexpr (sizeof(T) == 2 && TPR <= 256 && (FLAGS & kSmMask) != 0 && (FLAGS & kSmNoise) == 0) {
-        static const bool occ4 = [] { const char* e = getenv("NB2_SOFTMAX_OCC"); return e != nullptr && e[0] == '4'; }();
-        if (occ4)
-            return cuda_status(launch_pdl(softmax_fwd_kernel<T, TPR, fwd_vpt<T>(), FLAGS, 4>, dim3((unsigned)row_grid(rows, TPR, 4)), dim3(THREADS), 0, st,
-                                          (const T*)scores, m, (T*)out, rows, H, Tq, (int)S, scale),
-                               "softmax_fwd_kernel launch");
-    }
     return cuda_status(launch_pdl(softmax_fwd_kernel<T, TPR, fwd_vpt<T>(), FLAGS>, dim3((unsigned)row_grid(rows, TPR)), dim3(THREADS), 0, st,
                                   (const T*)scores, m, (T*)out, rows, H, Tq, (int)S, scale),
                        "softmax_fwd_kernel launch");
