@@ -626,6 +626,50 @@ class StepRunner:
         self.step.close()
 
 
+def make_comm(abi, dist, rank, world, mode, dev):
+    """The library's communicator for this run.  Before any timing the exchange is checked once against
+    torch.distributed on a known vector; if the peer form cannot be set up or does not agree on this box (no peer
+    access between some pair of GPUs, say) every rank switches to the NCCL form together and the JSON line says so."""
+    def build(m):
+        box = [abi.comm_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        return abi.Comm(box[0], rank, world, m, max_cols=2 * 8192)
+
+    def agrees(c):
+        v = torch.arange(4096, device=dev, dtype=torch.float32) * (rank + 1) * 0.25
+        want = v.clone()
+        dist.all_reduce(want)
+        for _ in range(3):                                   # both slot parities
+            got = v.clone()
+            c.allreduce_(got)
+        torch.cuda.synchronize()
+        abi.device_status()
+        return bool(torch.equal(got, want))
+
+    note = None
+    ok, comm = 1, None
+    try:
+        comm = build(mode)
+        ok = 1 if agrees(comm) else 0
+    except Exception as exc:                                 # set-up or a bounded wait that ran out
+        ok, note = 0, str(exc)[:200]
+    flag = torch.tensor([ok], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if int(flag.item()) == 1:
+        return comm, mode, None
+    if mode == abi.EXCHANGE_NCCL:
+        raise SystemExit(f"bench: the gradient exchange does not work on this box ({note})")
+    try:
+        if comm is not None:
+            comm.close()
+    except Exception:
+        pass
+    comm = build(abi.EXCHANGE_NCCL)
+    if not agrees(comm):
+        raise SystemExit("bench: neither exchange form works on this box")
+    return comm, abi.EXCHANGE_NCCL, "peer form failed its self-check on this box (%s); NCCL form used" % (note or "result mismatch")
+
+
 def timed_steps(runner: StepRunner, steps: int, warmup: int, world: int, dev, clocks=None, trace=None):
     """W untimed steps, then exactly K steps between barrier + synchronize on both sides, CUDA events
     on the launching stream, max over ranks.  Returns seconds per step.  `trace` (a dict) receives this
@@ -805,9 +849,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
-    ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer"],
-                    help="how the parameter gradients are summed over ranks: NCCL allreduce on a side stream, "
-                         "or the library's own peer-store exchange fused into the partial reduce")
+    ap.add_argument("--exchange", default="peer", choices=["nccl", "peer"],
+                    help="how the parameter gradients are summed over ranks: the library's own peer-store exchange fused into "
+                         "the partial reduce (default: measured faster at 2 and 4 GPUs, no SM held by a collective), or an NCCL "
+                         "allreduce on a side stream")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-comparator", action="store_true")
@@ -851,12 +896,11 @@ def main():
     clocks = ClockSampler(local).start()          # before the warm-up; it samples only inside the timed region
     comm = None
     mode = abi.EXCHANGE_PEER if args.exchange == "peer" else abi.EXCHANGE_NCCL
+    exchange_note = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)     # plumbing: barrier, max over ranks, passing the id
-        box = [abi.comm_unique_id() if rank == 0 else None]
-        dist.broadcast_object_list(box, src=0)
-        comm = abi.Comm(box[0], rank, world, mode, max_cols=2 * 8192)
+        comm, mode, exchange_note = make_comm(abi, dist, rank, world, mode, dev)
     abi.lib().nb2_reserve_sms(max(args.reserve_sms, 0))
 
     runner = StepRunner(w, comm, dev, seed=1234 + rank)
@@ -948,7 +992,7 @@ def main():
             "scaling": w.scaling, "vs_baseline": None,
             "dtype": "f32" if w.dtype == torch.float32 else "bf16", "data": "synthetic",
             "config": config_of(w, world),
-            "exchange": exchange, "reserved_sms": max(args.reserve_sms, 0),
+            "exchange": exchange, "exchange_note": exchange_note, "reserved_sms": max(args.reserve_sms, 0),
             "rows_per_s": w.rows_per_rank * world / sec_per_step,
             "frac_of_measured_per_gpu": value / world / peak,
             "frac_of_nominal_8000_per_gpu": value / world / 8000.0,
