@@ -215,3 +215,21 @@ def test_cpp_step_driver_classes(exchange):
     yr, rstd = abi.rmsnorm_fwd(xb, w, 1e-6, abi.ACT_SILU)
     dxr, dw = abi.rmsnorm_bwd(xb, dyb, w, rstd, abi.ACT_SILU)
     assert torch.equal(y, yr) and torch.equal(dx, dxr) and torch.equal(g1, dw) and torch.equal(g0, dw)
+
+
+@pytest.mark.parametrize("exchange", [abi.EXCHANGE_NCCL, abi.EXCHANGE_PEER])
+def test_a_rank_without_rows_contributes_zeros(exchange):
+    """More ranks than rows: a rank whose shard is empty still takes part in the exchange, with zero sums."""
+    D = 256
+    comm = abi.Comm(None, 0, 1, exchange, max_cols=2 * D)
+    step = abi.NormStep(comm, "ln", 0, D, torch.float32, abi.ACT_GELU, 1e-5)
+    e = torch.empty(0, D, device="cuda")
+    g = torch.ones(D, device="cuda"); b = torch.zeros(D, device="cuda")
+    grads = [torch.full((2 * D,), float("nan"), device="cuda") for _ in range(2)]
+    for k in range(2):
+        step.run(e, e, g, b, e, e, grads[k])
+    step.finish()
+    torch.cuda.synchronize()
+    assert float(grads[0].abs().sum()) == 0.0 and float(grads[1].abs().sum()) == 0.0
+    step.close(); comm.close()
+    assert abi.device_status() == 0
