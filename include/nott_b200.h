@@ -532,6 +532,14 @@ int nb2_comm_abort(nb2_comm* comm);
 int nb2_selftest_comm_watchdog(int polls_until_done, int polls_until_error, int error_code, double timeout_s,
                                int* aborts_host);
 int nb2_selftest_peer_wait(nb2_comm* comm, int64_t cycle_limit, void* stream);
+/*
+ * `world` (<= 16) communicators of the PEER form in one process on the current device, linked to one another as the
+ * ranks of a box would be (every peer buffer is local memory), written to comms[0..world).  For tests of the
+ * exchange with more ranks than GPUs: issue every rank's nb2_grad_exchange_begin for a step before any rank's begin
+ * for the next step (then no launch waits for a later one), nb2_grad_exchange_end for every rank at the end, and
+ * destroy each with nb2_comm_destroy.  No counterpart in the reference.
+ */
+int nb2_selftest_comm_group(nb2_comm** comms, int world, int64_t max_cols);
 
 /*
  * One training step of the fused norm->activation path on this rank's row

@@ -233,3 +233,36 @@ def test_a_rank_without_rows_contributes_zeros(exchange):
     assert float(grads[0].abs().sum()) == 0.0 and float(grads[1].abs().sum()) == 0.0
     step.close(); comm.close()
     assert abi.device_status() == 0
+
+
+@pytest.mark.parametrize("world", [2, 5, 8, 16])
+def test_peer_exchange_with_many_ranks_on_one_gpu(world):
+    """The peer exchange with up to 16 ranks' worth of data on one GPU: `world` linked communicators whose "peer"
+    buffers are all local.  Every rank's begin of a step is issued before any rank's begin of the next, so each
+    launch's collect phase finds the previous step already stored by everyone.  Every rank must end up with the same
+    bits: the fp64 sum of the ranks' fp32 sums in rank order, rounded once."""
+    ncols, parts = 2 * 1024 + 8, 37                       # a column count that is not a multiple of the 32-column CTA tile
+    comms = abi.comm_group(world, ncols)
+    gen = torch.Generator(device="cuda").manual_seed(world)
+    steps = 3
+    grads = [[torch.full((ncols,), float("nan"), device="cuda") for _ in range(2)] for _ in range(world)]
+    want = []
+    for k in range(steps):
+        per_rank = []
+        for r, c in enumerate(comms):
+            p = torch.randn(parts, ncols, device="cuda", generator=gen)
+            per_rank.append(p.double().sum(0).float())    # what the partial reduce leaves on rank r (fp64 sum, rounded)
+            c.exchange_begin(p, parts, grads[r][k & 1])
+        total = torch.zeros(ncols, dtype=torch.float64, device="cuda")
+        for v in per_rank:                                # rank order
+            total += v.double()
+        want.append(total.float())
+    for c in comms:
+        c.exchange_end()
+    torch.cuda.synchronize()
+    assert abi.device_status() == 0
+    for r in range(world):
+        assert torch.equal(grads[r][(steps - 1) & 1], want[steps - 1]), f"rank {r}, last step"
+        assert torch.equal(grads[r][(steps - 2) & 1], want[steps - 2]), f"rank {r}, the step before"
+    for c in comms:
+        c.close()

@@ -79,6 +79,7 @@ _SIGNATURES = {
     "nb2_comm_abort": (c_int, [c_void_p]),
     "nb2_selftest_comm_watchdog": (c_int, [c_int, c_int, c_int, c_double, POINTER(c_int)]),
     "nb2_selftest_peer_wait": (c_int, [c_void_p, c_int64, c_void_p]),
+    "nb2_selftest_comm_group": (c_int, [POINTER(c_void_p), c_int, c_int64]),
     "nb2_step_create": (c_int, [POINTER(c_void_p), c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_double]),
     "nb2_step_destroy": (c_int, [c_void_p]),
     "nb2_step_run": (c_int, [c_void_p] * 8 + [c_void_p]),
@@ -553,6 +554,18 @@ class Comm:
             self.close()
         except Exception:
             pass
+
+
+def comm_group(world: int, max_cols: int):
+    """`world` linked peer-form communicators on the current device (see nb2_selftest_comm_group): a list of Comm."""
+    arr = (c_void_p * world)()
+    check(lib().nb2_selftest_comm_group(arr, world, max_cols))
+    out = []
+    for r in range(world):
+        c = Comm.__new__(Comm)
+        c._h, c.rank, c.world, c.exchange = c_void_p(arr[r]), r, world, EXCHANGE_PEER
+        out.append(c)
+    return out
 
 
 class NormStep:

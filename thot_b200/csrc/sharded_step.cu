@@ -499,6 +499,40 @@ int nb2_selftest_peer_wait(nb2_comm* c, int64_t cycle_limit, void* stream) {
                            (cudaStream_t)stream, (long long)cycle_limit);
 }
 
+// `world` communicators of the peer form in ONE process, all on the current device, linked to one another as if
+// they were the ranks of a box (every "peer" buffer is local memory).  It lets a single GPU run the peer exchange with
+// 2-16 ranks' worth of data: the caller issues every rank's begin for step k before any rank's begin for step k+1, so
+// the collect phase of each launch finds all it waits for already stored (no launch ever waits for a later one).
+int nb2_selftest_comm_group(nb2_comm** comms, int world, int64_t max_cols) {
+    NB2_REQUIRE(comms != nullptr, NB2_ERR_NULL, "comm group: NULL output");
+    NB2_REQUIRE(world >= 1 && world <= kMaxRanks && max_cols > 0 && max_cols <= ((int64_t)1 << 24), NB2_ERR_SHAPE,
+                "comm group: world=%d max_cols=%lld", world, (long long)max_cols);
+    for (int r = 0; r < world; ++r) comms[r] = nullptr;
+    int rc = 0;
+    for (int r = 0; r < world && rc == 0; ++r) rc = nb2_comm_create(&comms[r], nullptr, 0, 1, NB2_EXCHANGE_PEER, max_cols);
+    if (rc != 0) {
+        for (int r = 0; r < world; ++r) { nb2_comm_destroy(comms[r]); comms[r] = nullptr; }
+        return rc;
+    }
+    // each was made as a one-rank communicator with room for one slot; give every rank a buffer for `world` slots
+    for (int r = 0; r < world && rc == 0; ++r) {
+        nb2_comm* c = comms[r];
+        cudaFree(c->slots);
+        c->slots = nullptr;
+        const size_t bytes = (size_t)2 * world * c->max_cols * sizeof(uint2);
+        rc = cuda_status(cudaMalloc((void**)&c->slots, bytes), "comm group: receive buffer");
+        if (rc == 0) rc = cuda_status(cudaMemset(c->slots, 0, bytes), "comm group: clearing the receive buffer");
+        c->rank = r;
+        c->world = world;
+    }
+    for (int r = 0; r < world && rc == 0; ++r)
+        for (int q = 0; q < world; ++q) comms[r]->peer_slots[q] = comms[q]->slots;
+    if (rc != 0) {
+        for (int r = 0; r < world; ++r) { nb2_comm_destroy(comms[r]); comms[r] = nullptr; }
+    }
+    return rc;
+}
+
 int nb2_comm_abort(nb2_comm* c) {
     NB2_REQUIRE(c != nullptr, NB2_ERR_NULL, "comm abort: NULL communicator");
     nccl_abort(c);
