@@ -61,11 +61,8 @@ struct NcclApi {
     char why[256] = "";
 };
 
-static const NcclApi* nccl_api() {
-    static NcclApi api;
-    static bool tried = false;
-    if (tried) return api.handle != nullptr ? &api : nullptr;
-    tried = true;
+static NcclApi load_nccl() {
+    NcclApi api;
     const char* env = getenv("NB2_NCCL_LIB");
     void* h = nullptr;
     if (env != nullptr && *env) h = dlopen(env, RTLD_NOW | RTLD_LOCAL);
@@ -75,7 +72,7 @@ static const NcclApi* nccl_api() {
     if (h == nullptr) h = dlopen("libnccl.so", RTLD_NOW | RTLD_LOCAL);
     if (h == nullptr) {
         snprintf(api.why, sizeof(api.why), "libnccl.so.2 not found (%s); set NB2_NCCL_LIB to its path", dlerror());
-        return nullptr;
+        return api;
     }
     bool ok = true;
     auto sym = [&](const char* name) {
@@ -91,9 +88,18 @@ static const NcclApi* nccl_api() {
     api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(sym("ncclAllReduce"));
     api.AllGather = reinterpret_cast<decltype(api.AllGather)>(sym("ncclAllGather"));
     api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(sym("ncclGetErrorString"));
-    if (!ok) return nullptr;
-    api.handle = h;
-    return &api;
+    if (ok) api.handle = h;
+    return api;
+}
+
+// loaded once per process, by whichever thread asks first (a function-local static is initialised under a lock)
+static const NcclApi& nccl_state() {
+    static const NcclApi api = load_nccl();
+    return api;
+}
+static const NcclApi* nccl_api() {
+    const NcclApi& api = nccl_state();
+    return api.handle != nullptr ? &api : nullptr;
 }
 
 static int nccl_status(const NcclApi* api, ncclResult_t r, const char* what) {
@@ -316,7 +322,7 @@ extern "C" {
 int nb2_comm_unique_id(void* id_host) {
     NB2_REQUIRE(id_host != nullptr, NB2_ERR_NULL, "comm id: NULL output");
     const NcclApi* api = nccl_api();
-    NB2_REQUIRE(api != nullptr, NB2_ERR_COMM, "NCCL is not available (libnccl.so.2 could not be loaded; NB2_NCCL_LIB names another path)");
+    NB2_REQUIRE(api != nullptr, NB2_ERR_COMM, "NCCL is not available: %s", nccl_state().why);
     static_assert(NB2_COMM_ID_BYTES == NCCL_UNIQUE_ID_BYTES, "the id is NCCL's");
     ncclUniqueId id;
     int rc = nccl_status(api, api->GetUniqueId(&id), "ncclGetUniqueId");
@@ -344,7 +350,7 @@ int nb2_comm_create(nb2_comm** comm, const void* id_host, int rank, int world, i
     const NcclApi* api = nullptr;
     if (world > 1) {
         api = nccl_api();
-        if (api == nullptr) { comm_free(c); set_error("comm create: NCCL is not available (set NB2_NCCL_LIB)"); return NB2_ERR_COMM; }
+        if (api == nullptr) { comm_free(c); set_error("comm create: NCCL is not available: %s", nccl_state().why); return NB2_ERR_COMM; }
         ncclUniqueId id;
         memcpy(&id, id_host, sizeof(id));
         CM_NCCL(api->CommInitRank(&c->nccl, world, id, rank));
