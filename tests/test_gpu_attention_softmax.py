@@ -61,6 +61,41 @@ def test_against_oracle(dtype, B, H, T, S, mask_rank, use_padding, causal):
     check(ds.reshape(-1, S), (scale * an * (dn - dot)).reshape(-1, S), "dscores")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("B,H,T,S,mask_rank,use_padding,causal,with_noise", [
+    (2, 4, 33, 128, 3, False, False, False),      # one warp per row; 66 (batch, position) pairs do not fill the groups evenly
+    (1, 16, 40, 1024, 2, True, True, False),      # a [T, S] mask under padding and the causal cut
+    (3, 5, 7, 2048, 3, True, False, True),        # several warps per row, odd head count, dropout noise
+    (2, 8, 300, 256, 3, False, True, True),       # more pairs than one pass of the grid covers
+])
+def test_mask_shared_by_the_heads_kept_per_position(dtype, B, H, T, S, mask_rank, use_padding, causal, with_noise):
+    """With one mask row serving all heads of a (batch, position) pair the forward walks the heads innermost and keeps
+    the row in registers.  Checked against the oracle, and bit for bit against the same call with the mask expanded to
+    [B, H, T, S] (a head stride, so rows go in memory order and the mask is read per row)."""
+    scores, sn = make((B, H, T, S), 11, dtype, 2.0)
+    mask, mn = make((T, S) if mask_rank == 2 else (B, T, S), 12, dtype)
+    padding = None
+    if use_padding:
+        padding = torch.zeros(B, S, dtype=torch.bool)
+        padding[-1, S - S // 3:] = True
+    pad_dev = None if padding is None else padding.cuda()
+    noise = None
+    if with_noise:
+        noise = ((torch.rand(B, H, T, S, generator=torch.Generator().manual_seed(13)) >= 0.25).float() * 1.25).to(dtype).cuda()
+    scale = 1.0 / math.sqrt(64)
+    full = (mask if mask_rank == 3 else mask[None]).reshape(-1, 1, T, S).expand(B, H, T, S).contiguous()
+    got = abi.attention_softmax_fwd(scores, scale, pad_dev, mask, causal, noise=noise)
+    flat = abi.attention_softmax_fwd(scores, scale, pad_dev, full, causal, noise=noise)
+    if with_noise:
+        assert torch.equal(got[0], flat[0]) and torch.equal(got[1], flat[1])
+        attn = got[1]
+    else:
+        assert torch.equal(got, flat)
+        attn = got
+    ref = O.attention_softmax(sn, scale, None if padding is None else padding.numpy(), mn, causal, None)
+    check(attn.reshape(-1, S), ref["attn"].reshape(-1, S), "attn")
+
+
 def test_a_fully_masked_row_is_nan_like_the_reference():
     scores, _ = make((1, 1, 2, 64), 1, torch.float32)
     padding = torch.ones(1, 64, dtype=torch.bool, device="cuda")

@@ -12,6 +12,9 @@
 // thread), rows of a CTA independent of one another; persistent grid-stride over rows.  Rows whose
 // length or alignment does not fit 16-byte vectors take a three-sweep kernel, one CTA per row.
 #include <math.h>
+#include <string.h>
+
+#include <type_traits>
 
 #include "launchers.h"
 
@@ -97,13 +100,49 @@ struct RowPos {
     }
 };
 
+// Which row a group works on and which comes next.  RowOrderFlat: rows in memory order, a fixed stride apart.
+// RowOrderHeadsInner: a group takes one (batch, target position) pair and walks its H heads before the next pair, so
+// that an additive mask shared by the heads is fetched once per pair and kept in registers (read once per head it
+// comes from L2 sixteen times at 16 heads, and that traffic, not DRAM, bounded the masked forward).
+struct RowOrderFlat {
+    int64_t row, rows, stride;
+    RowPos pos;
+    __device__ __forceinline__ RowOrderFlat(int64_t first, int64_t stride_, int64_t rows_, int64_t H, int64_t Tq)
+        : row(first), rows(rows_), stride(stride_), pos(first, stride_, H, Tq) {}
+    __device__ __forceinline__ bool valid() const { return row < rows; }
+    __device__ __forceinline__ void advance() { row += stride; pos.advance(); }
+    __device__ __forceinline__ int64_t b() const { return pos.b; }
+    __device__ __forceinline__ int h() const { return pos.h; }
+    __device__ __forceinline__ int t() const { return pos.t; }
+    __device__ __forceinline__ bool new_mask_row() const { return true; }
+};
+struct RowOrderHeadsInner {
+    int64_t row, pair, pairs, stride, b_;
+    int h_, t_, H, Tq;
+    __device__ __forceinline__ RowOrderHeadsInner(int64_t first, int64_t stride_, int64_t rows_, int64_t H_, int64_t Tq_)
+        : pair(first), pairs(rows_ / H_), stride(stride_), h_(0), H((int)H_), Tq((int)Tq_) { place(); }
+    __device__ __forceinline__ void place() { b_ = pair / Tq; t_ = (int)(pair - b_ * Tq); row = b_ * H * (int64_t)Tq + t_; }
+    __device__ __forceinline__ bool valid() const { return pair < pairs; }
+    __device__ __forceinline__ void advance() {
+        if (++h_ == H) { h_ = 0; pair += stride; place(); }       // one 64-bit division per H rows
+        else row += Tq;
+    }
+    __device__ __forceinline__ int64_t b() const { return b_; }
+    __device__ __forceinline__ int h() const { return h_; }
+    __device__ __forceinline__ int t() const { return t_; }
+    __device__ __forceinline__ bool new_mask_row() const { return h_ == 0; }
+};
+
 // FLAGS: bit 0 key padding present, bit 1 additive mask present, bit 2 causal.  Compile-time, so
 // that a call without masks spends nothing on them: with run-time tests the kernel executed 33
 // instructions per score and was bound by issue (ncu: 71% issue slots busy, ALU pipe 60%).
 constexpr int kSmPad = 1, kSmMask = 2, kSmCausal = 4, kSmNoise = 8;
 
-template <typename T, int TPR, int VPT, int FLAGS>
-__global__ void __launch_bounds__((TPR > 256 ? TPR : 256), (TPR > 256 ? 1 : 3))
+// HIN: heads innermost (RowOrderHeadsInner); only with an additive mask whose head stride is 0.  The kept mask row
+// takes 16 more registers: with a bf16 row (32 fp32 values per thread) that no longer fits three CTAs per SM without
+// 90-140 spilled bytes, so those are built for two.
+template <typename T, int TPR, int VPT, int FLAGS, bool HIN>
+__global__ void __launch_bounds__((TPR > 256 ? TPR : 256), (TPR > 256 ? 1 : ((HIN && sizeof(T) == 2) ? 2 : 3)))
 softmax_fwd_kernel(const T* __restrict__ scores, const SoftmaxMask m, T* __restrict__ out,
                    int64_t rows, int64_t H, int64_t Tq, int S, float scale) {
     constexpr int EPV = VecTraits<T>::EPV;
@@ -131,16 +170,29 @@ softmax_fwd_kernel(const T* __restrict__ scores, const SoftmaxMask m, T* __restr
             if (c < nvec && !(CAUSAL && c * EPV > t)) raw[j] = ld_stream(src + (size_t)c * EPV);
         }
     };
-    int64_t row = (int64_t)blockIdx.x * RPC + grp;
-    RowPos ahead(row, stride, H, Tq);                    // position of the row whose loads are issued next
-    if (row < rows) load_row(row, ahead.t, cur);
-    for (; row < rows; row += stride) {
-        const int t = ahead.t, h = ahead.h;
-        const int64_t b = ahead.b;
+    using Order = typename std::conditional<HIN, RowOrderHeadsInner, RowOrderFlat>::type;
+    Order at((int64_t)blockIdx.x * RPC + grp, stride, rows, H, Tq);      // the row being worked on; `ahead` is the one requested
+    uint4 mkeep[(MASK && HIN) ? VPT : 1];                                  // the pair's mask row, kept across its heads
+    if (at.valid()) load_row(at.row, at.t(), cur);
+    while (at.valid()) {
+        const int64_t row = at.row;
+        const int t = at.t(), h = at.h();
+        const int64_t b = at.b();
+        const bool fetch_mask = at.new_mask_row();
+        Order ahead = at;
         ahead.advance();
-        if (row + stride < rows) load_row(row + stride, ahead.t, nxt);
-        const T* mrow = MASK ? reinterpret_cast<const T*>(m.add_mask) + b * m.mask_sb + h * m.mask_sh + t * (int64_t)S : nullptr;
+        if (ahead.valid()) load_row(ahead.row, ahead.t(), nxt);
+        const T* mrow = MASK ? reinterpret_cast<const T*>(m.add_mask) + b * m.mask_sb + (HIN ? 0 : h * m.mask_sh) + t * (int64_t)S : nullptr;
         const uint8_t* prow = PAD ? m.key_padding + b * (int64_t)S : nullptr;
+        if constexpr (MASK && HIN) {
+            if (fetch_mask) {
+#pragma unroll
+                for (int j = 0; j < VPT; ++j) {
+                    const int c = tr + j * TPR;
+                    if (c < nvec && !(CAUSAL && c * EPV > t)) mkeep[j] = ld_param(mrow + (size_t)c * EPV);
+                }
+            }
+        }
         float v[VPT][EPV];
         float mx = -INFINITY;
 #pragma unroll
@@ -150,7 +202,8 @@ softmax_fwd_kernel(const T* __restrict__ scores, const SoftmaxMask m, T* __restr
             if (c < nvec && !(CAUSAL && c * EPV > t)) {
                 unpack<T>(cur[j], v[j]);
                 float mk[EPV];
-                if constexpr (MASK) unpack<T>(ld_param(mrow + (size_t)c * EPV), mk);
+                if constexpr (MASK && HIN) unpack<T>(mkeep[j], mk);
+                else if constexpr (MASK) unpack<T>(ld_param(mrow + (size_t)c * EPV), mk);
                 uint8_t pad[EPV];
                 if constexpr (PAD) {
                     if constexpr (EPV == 4) *reinterpret_cast<uint32_t*>(pad) = __ldg(reinterpret_cast<const uint32_t*>(prow + (size_t)c * EPV));
@@ -226,6 +279,7 @@ softmax_fwd_kernel(const T* __restrict__ scores, const SoftmaxMask m, T* __restr
 #pragma unroll
         for (int j = 0; j < VPT; ++j) cur[j] = nxt[j];
         parity ^= 1;
+        at = ahead;
     }
 }
 
@@ -262,23 +316,26 @@ softmax_bwd_kernel(const T* __restrict__ attn, const T* __restrict__ dattn, cons
     if (row < rows) load_row(row, cy, cd, cn);
     for (; row < rows; row += stride, parity ^= 1) {
         if (row + stride < rows) load_row(row + stride, ny, nd, nn);
-        float y[VPT][EPV], d[VPT][EPV];
+        // The row stays in its packed form across the reduction and is unpacked again afterwards: for bf16 the
+        // fp32 copies of both tensors (64 registers) next to two rows of three packed streams spilled.
         float dot = 0.f;
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
             const int c = tr + j * TPR;
             if (c < nvec) {
-                unpack<T>(cy[j], y[j]);
-                unpack<T>(cd[j], d[j]);
+                float y[EPV], d[EPV];
+                unpack<T>(cy[j], y);
+                unpack<T>(cd[j], d);
                 if constexpr (NOISE) {
                     float nv[EPV];
                     unpack<T>(cn[j], nv);
 #pragma unroll
-                    for (int e = 0; e < EPV; ++e) d[j][e] = __fmul_rn(d[j][e], nv[e]);   // rounded as a product: never fused into the subtraction below
-                    unpack<T>(pack<T>(d[j]), d[j]);              // the gradient of attn as a tensor of type T
+                    for (int e = 0; e < EPV; ++e) d[e] = __fmul_rn(d[e], nv[e]);   // rounded as a product: never fused into the subtraction below
+                    cd[j] = pack<T>(d);                          // the gradient of attn as a tensor of type T
+                    unpack<T>(cd[j], d);
                 }
 #pragma unroll
-                for (int e = 0; e < EPV; ++e) dot = fmaf(y[j][e], d[j][e], dot);
+                for (int e = 0; e < EPV; ++e) dot = fmaf(y[e], d[e], dot);
             }
         }
         dot = group_reduce<TPR, false>(dot, red_a[parity][grp], grp + 1);
@@ -287,9 +344,11 @@ softmax_bwd_kernel(const T* __restrict__ attn, const T* __restrict__ dattn, cons
         for (int j = 0; j < VPT; ++j) {
             const int c = tr + j * TPR;
             if (c < nvec) {
-                float o[EPV];
+                float y[EPV], d[EPV], o[EPV];
+                unpack<T>(cy[j], y);
+                unpack<T>(cd[j], d);
 #pragma unroll
-                for (int e = 0; e < EPV; ++e) o[e] = scale * (y[j][e] * (d[j][e] - dot));
+                for (int e = 0; e < EPV; ++e) o[e] = scale * (y[e] * (d[e] - dot));
                 st_stream(dst + (size_t)c * EPV, pack<T>(o));
             }
         }
@@ -390,11 +449,26 @@ int64_t row_grid(int64_t rows, int tpr) {
     return need < cap ? (need < 1 ? 1 : need) : cap;
 }
 
+// Heads innermost pays when the same mask row serves several heads; NB2_SOFTMAX_ORDER=flat switches it off for measurements.
+bool heads_inner_wanted(const SoftmaxMask& m, int64_t H) {
+    static const bool off = [] { const char* e = getenv("NB2_SOFTMAX_ORDER"); return e != nullptr && strcmp(e, "flat") == 0; }();
+    return !off && m.add_mask != nullptr && m.mask_sh == 0 && H >= 4;
+}
+
 template <typename T, int TPR, int FLAGS>
 int launch_fwd_flags(const void* scores, const SoftmaxMask& m, void* out, int64_t rows, int64_t H, int64_t Tq, int64_t S,
                      float scale, cudaStream_t st) {
     constexpr int THREADS = TPR > 256 ? TPR : 256;
-    return cuda_status(launch_pdl(softmax_fwd_kernel<T, TPR, fwd_vpt<T>(), FLAGS>, dim3((unsigned)row_grid(rows, TPR)), dim3(THREADS), 0, st,
+    if constexpr ((FLAGS & kSmMask) != 0 && TPR <= 256) {
+        if (heads_inner_wanted(m, H)) {
+            constexpr int RPC = THREADS / TPR;
+            const int64_t pairs = rows / H, need = (pairs + RPC - 1) / RPC, cap = (int64_t)sm_count() * (sizeof(T) == 2 ? 2 : 3) * 4;
+            return cuda_status(launch_pdl(softmax_fwd_kernel<T, TPR, fwd_vpt<T>(), FLAGS, true>, dim3((unsigned)(need < cap ? need : cap)),
+                                          dim3(THREADS), 0, st, (const T*)scores, m, (T*)out, rows, H, Tq, (int)S, scale),
+                               "softmax_fwd_kernel launch");
+        }
+    }
+    return cuda_status(launch_pdl(softmax_fwd_kernel<T, TPR, fwd_vpt<T>(), FLAGS, false>, dim3((unsigned)row_grid(rows, TPR)), dim3(THREADS), 0, st,
                                   (const T*)scores, m, (T*)out, rows, H, Tq, (int)S, scale),
                        "softmax_fwd_kernel launch");
 }
