@@ -62,11 +62,22 @@ struct EpilogueAct {
 template <int ACT, class T, int N>
 struct EpilogueAct<ACT, cutlass::Array<T, N>> {
     static const bool kIsHeavy = ACT != NB2_ACT_NONE;
+    // Fragments are processed as pairs on the packed fp32 pipe (fma.rn.f32x2: one issue slot for two columns; each
+    // half rounds as the scalar instruction would, so the values are those of the scalar form).  The epilogue runs on
+    // four warps per CTA beside the MMA, and with K <= 1024 it, not the mainloop, sets the tile time.
     CUTLASS_HOST_DEVICE cutlass::Array<T, N> operator()(cutlass::Array<T, N> const& v) const {
         cutlass::Array<T, N> y;
-        EpilogueAct<ACT, T> op;
+#if defined(__CUDA_ARCH__)
         CUTLASS_PRAGMA_UNROLL
-        for (int i = 0; i < N; ++i) y[i] = op(v[i]);
+        for (int i = 0; i + 1 < N; i += 2) {
+            const float2 r = act_fwd2<ACT, true>(make_float2(float(v[i]), float(v[i + 1])));
+            y[i] = T(r.x);
+            y[i + 1] = T(r.y);
+        }
+        if constexpr (N % 2 != 0) y[N - 1] = EpilogueAct<ACT, T>()(v[N - 1]);
+#else
+        y = v;
+#endif
         return y;
     }
 };
