@@ -102,7 +102,7 @@ struct RowPos {
 
 // Which row a group works on and which comes next.  RowOrderFlat: rows in memory order, a fixed stride apart.
 // RowOrderHeadsInner: a group takes one (batch, target position) pair and walks its H heads before the next pair, so
-// that an additive mask shared by the heads is fetched once per pair and kept in registers (read once per head it
+// that an additive mask shared by the heads is fetched once per pair and kept on chip (read once per head it
 // comes from L2 sixteen times at 16 heads, and that traffic, not DRAM, bounded the masked forward).
 struct RowOrderFlat {
     int64_t row, rows, stride;
@@ -138,11 +138,9 @@ struct RowOrderHeadsInner {
 // instructions per score and was bound by issue (ncu: 71% issue slots busy, ALU pipe 60%).
 constexpr int kSmPad = 1, kSmMask = 2, kSmCausal = 4, kSmNoise = 8;
 
-// HIN: heads innermost (RowOrderHeadsInner); only with an additive mask whose head stride is 0.  The kept mask row
-// takes 16 more registers: with a bf16 row (32 fp32 values per thread) that no longer fits three CTAs per SM without
-// 90-140 spilled bytes, so those are built for two.
+// HIN: heads innermost (RowOrderHeadsInner); only with an additive mask whose head stride is 0.
 template <typename T, int TPR, int VPT, int FLAGS, bool HIN>
-__global__ void __launch_bounds__((TPR > 256 ? TPR : 256), (TPR > 256 ? 1 : ((HIN && sizeof(T) == 2) ? 2 : 3)))
+__global__ void __launch_bounds__((TPR > 256 ? TPR : 256), (TPR > 256 ? 1 : 3))
 softmax_fwd_kernel(const T* __restrict__ scores, const SoftmaxMask m, T* __restrict__ out,
                    int64_t rows, int64_t H, int64_t Tq, int S, float scale) {
     constexpr int EPV = VecTraits<T>::EPV;
@@ -172,7 +170,9 @@ softmax_fwd_kernel(const T* __restrict__ scores, const SoftmaxMask m, T* __restr
     };
     using Order = typename std::conditional<HIN, RowOrderHeadsInner, RowOrderFlat>::type;
     Order at((int64_t)blockIdx.x * RPC + grp, stride, rows, H, Tq);      // the row being worked on; `ahead` is the one requested
-    uint4 mkeep[(MASK && HIN) ? VPT : 1];                                  // the pair's mask row, kept across its heads
+    // the pair's mask row, kept across its heads: every thread parks the vectors it will itself read back (no barrier
+    // needed), in shared memory rather than registers so that the row costs no occupancy
+    __shared__ uint4 mkeep[(MASK && HIN) ? VPT * THREADS : 1];
     if (at.valid()) load_row(at.row, at.t(), cur);
     while (at.valid()) {
         const int64_t row = at.row;
@@ -189,7 +189,7 @@ softmax_fwd_kernel(const T* __restrict__ scores, const SoftmaxMask m, T* __restr
 #pragma unroll
                 for (int j = 0; j < VPT; ++j) {
                     const int c = tr + j * TPR;
-                    if (c < nvec && !(CAUSAL && c * EPV > t)) mkeep[j] = ld_param(mrow + (size_t)c * EPV);
+                    if (c < nvec && !(CAUSAL && c * EPV > t)) mkeep[j * THREADS + threadIdx.x] = ld_param(mrow + (size_t)c * EPV);
                 }
             }
         }
@@ -202,7 +202,7 @@ softmax_fwd_kernel(const T* __restrict__ scores, const SoftmaxMask m, T* __restr
             if (c < nvec && !(CAUSAL && c * EPV > t)) {
                 unpack<T>(cur[j], v[j]);
                 float mk[EPV];
-                if constexpr (MASK && HIN) unpack<T>(mkeep[j], mk);
+                if constexpr (MASK && HIN) unpack<T>(mkeep[j * THREADS + threadIdx.x], mk);
                 else if constexpr (MASK) unpack<T>(ld_param(mrow + (size_t)c * EPV), mk);
                 uint8_t pad[EPV];
                 if constexpr (PAD) {
@@ -462,7 +462,7 @@ int launch_fwd_flags(const void* scores, const SoftmaxMask& m, void* out, int64_
     if constexpr ((FLAGS & kSmMask) != 0 && TPR <= 256) {
         if (heads_inner_wanted(m, H)) {
             constexpr int RPC = THREADS / TPR;
-            const int64_t pairs = rows / H, need = (pairs + RPC - 1) / RPC, cap = (int64_t)sm_count() * (sizeof(T) == 2 ? 2 : 3) * 4;
+            const int64_t pairs = rows / H, need = (pairs + RPC - 1) / RPC, cap = (int64_t)sm_count() * 3 * 4;
             return cuda_status(launch_pdl(softmax_fwd_kernel<T, TPR, fwd_vpt<T>(), FLAGS, true>, dim3((unsigned)(need < cap ? need : cap)),
                                           dim3(THREADS), 0, st, (const T*)scores, m, (T*)out, rows, H, Tq, (int)S, scale),
                                "softmax_fwd_kernel launch");
