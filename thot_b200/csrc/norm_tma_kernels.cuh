@@ -267,24 +267,33 @@ norm_fwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ res, const T*
     const int64_t stride = (int64_t)gridDim.x * RPC;
     uint64_t policy = 0;
     // leader: which source rows a logical row maps to (identity unless a gather is configured)
-    auto request = [&](int s, int64_t row) {
+    // `id` is the looked-up row of x when a gather is configured (ignored otherwise)
+    auto request = [&](int s, int64_t row, int64_t id) {
         int64_t xr = row, rr = row;
         if constexpr (RES) {
             if (gather.ids != nullptr) {
-                xr = gather_id(gather, row);
+                xr = id;
                 if (xr < 0 || xr >= gather.vocab) xr = 0;           // the consumers zero this row's x part
             }
             if (gather.res_period > 0) rr = row % gather.res_period;
         }
         request_rows(&full[s], ring + (size_t)s * slot_bytes, src, xr, src_res, rr, nullptr, 0, row_bytes, policy);
     };
+    const bool looked_up = RES && gather.ids != nullptr;
+    // With a gather every request needs its row's id first.  Ids are fetched one step before they are used -- by the
+    // leader for the row it will request next, by every thread for the row it will check next -- so that no id load
+    // sits between a freed slot and its next request.
+    int64_t lead_id = 0, seen_id = 0;
     if (tr == 0) {
         policy = policy_evict_first();
         for (int s = 0; s < stages; ++s) {
             const int64_t row = first + s * stride;
-            if (row < rows) request(s, row);
+            if (row < rows) request(s, row, looked_up ? gather_id(gather, row) : 0);
         }
+        const int64_t next = first + (int64_t)stages * stride;
+        if (looked_up && next < rows) lead_id = gather_id(gather, next);
     }
+    if (looked_up && first < rows) seen_id = gather_id(gather, first);
     uint4 epk[RES ? VPT : 1];                                  // the constant extra row of a gather, if any
     bool has_extra = false;
     if constexpr (RES) {
@@ -321,8 +330,9 @@ norm_fwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ res, const T*
         float2 sum2 = make_float2(0.f, 0.f);
         bool x_ok = true;
         if constexpr (RES) {
-            if (gather.ids != nullptr) {
-                const int64_t id = gather_id(gather, row);
+            if (looked_up) {
+                const int64_t id = seen_id;
+                if (row + stride < rows) seen_id = gather_id(gather, row + stride);
                 x_ok = id >= 0 && id < gather.vocab;
                 if (!x_ok && tr == 0 && gather.status != nullptr) { gather.status[0] = 1; gather.status[1] = row; }
             }
@@ -360,7 +370,10 @@ norm_fwd_tma_kernel(const T* __restrict__ x, const T* __restrict__ res, const T*
         if (group_gave_up<TPR>(gave_up)) break;
         if (tr == 0) {
             const int64_t ahead = row + (int64_t)stages * stride;
-            if (ahead < rows) request(s, ahead);
+            if (ahead < rows) {
+                request(s, ahead, lead_id);
+                if (looked_up && ahead + stride < rows) lead_id = gather_id(gather, ahead + stride);
+            }
         }
         if (++s == stages) { s = 0; phase ^= 1u; }
         if constexpr (RMS) {
