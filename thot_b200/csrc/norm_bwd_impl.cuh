@@ -76,10 +76,14 @@ static int launch_bwd_tma_shape(const NormArgs& a, TmaShape s, int64_t* n_partia
         else return launch_bwd_tma<T, 32, 3, ACT, RMS>(a, n_partials);
     }
     // RMSNorm bf16 rows of 4 KiB and more: 32 columns per thread (measured on B200 against the 16-column
-    // form: +3% at D = 2048, +8% at 4096, +14% at 8192, -1% at 1024).  LayerNorm's second accumulator
-    // column set does not fit the registers beside it (160 bytes spilled, 25% slower), so it stays.
+    // form with SiLU fused: +3% at D = 2048, +8% at 4096, +14% at 8192, -1% at 1024; with GELU +1-5%).
+    // Without a fused activation the 16-column form is the faster one up to D = 4096 (246 us against 295
+    // at [131072, 2048], 261 against 280 at [65536, 4096]) and the wide one only at 8192 (258 against 283).
+    // LayerNorm's second accumulator column set does not fit the registers beside it (160 bytes spilled,
+    // 25% slower), so it stays.
     if constexpr (EPV == 8 && RMS) {
-        if (a.dres == nullptr && a.D >= 2048 && norm_path_override() == 0) {
+        const int64_t wide_from = ACT == NB2_ACT_NONE ? 8192 : 2048;
+        if (a.dres == nullptr && a.D >= wide_from && norm_path_override() == 0) {
             int rc = kNotFused;
             switch (s.tpr) {       // s.tpr threads x 16 columns == s.tpr / 2 threads x 32 columns
                 case 64:  rc = launch_bwd_wide_bf16<32, ACT, RMS>(a, n_partials); break;
