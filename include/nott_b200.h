@@ -110,6 +110,16 @@ int nb2_device_status(unsigned int* status_host, int clear);
 int nb2_selftest_bounded_wait(int64_t cycle_limit, int64_t* waited_cycles, void* stream);
 
 /*
+ * Row order of nb2_attention_softmax_fwd when one additive mask row serves all heads (head stride 0).  0 (default):
+ * chosen by size -- heads innermost, mask row kept on chip across a (batch, position) pair's heads, when there are enough
+ * pairs to fill the GPU, memory order otherwise; 1: always memory order; 2: heads innermost whenever the mask allows it.
+ * Results do not depend on it (same arithmetic per row); it exists for measurements and tests.  Process-wide; the
+ * environment variable NB2_SOFTMAX_ORDER=flat|inner sets the initial value.  Returns the previous setting, or
+ * NB2_ERR_SHAPE for a value outside 0..2.  No counterpart in the reference.
+ */
+int nb2_attention_softmax_order(int order);
+
+/*
  * Workspace sizes, in bytes, for the calls that need scratch memory.
  *   NB2_WS_NORM_BWD      : a = rows, b = D            -> partials buffer
  *   NB2_WS_EMBEDDING_BWD : a = tokens, b = vocab rows -> sort scratch

@@ -116,3 +116,16 @@ def test_reserve_sms_is_a_host_side_setting_that_returns_the_previous_value():
         assert L.nb2_reserve_sms(0) == 0
     finally:
         L.nb2_reserve_sms(before)
+
+
+def test_softmax_row_order_is_a_host_side_setting_that_returns_the_previous_value():
+    from thot_b200 import abi
+    L = abi.lib()
+    before = L.nb2_attention_softmax_order(1)
+    try:
+        assert L.nb2_attention_softmax_order(2) == 1
+        assert L.nb2_attention_softmax_order(0) == 2
+        assert L.nb2_attention_softmax_order(3) == -2 and L.nb2_attention_softmax_order(-1) == -2      # NB2_ERR_SHAPE
+        assert L.nb2_attention_softmax_order(0) == 0                                                    # unchanged by the refusals
+    finally:
+        L.nb2_attention_softmax_order(before)

@@ -84,7 +84,11 @@ def test_mask_shared_by_the_heads_kept_per_position(dtype, B, H, T, S, mask_rank
         noise = ((torch.rand(B, H, T, S, generator=torch.Generator().manual_seed(13)) >= 0.25).float() * 1.25).to(dtype).cuda()
     scale = 1.0 / math.sqrt(64)
     full = (mask if mask_rank == 3 else mask[None]).reshape(-1, 1, T, S).expand(B, H, T, S).contiguous()
-    got = abi.attention_softmax_fwd(scores, scale, pad_dev, mask, causal, noise=noise)
+    before = abi.attention_softmax_order(2)            # these shapes are too small for the size rule to pick it
+    try:
+        got = abi.attention_softmax_fwd(scores, scale, pad_dev, mask, causal, noise=noise)
+    finally:
+        abi.attention_softmax_order(before)
     flat = abi.attention_softmax_fwd(scores, scale, pad_dev, full, causal, noise=noise)
     if with_noise:
         assert torch.equal(got[0], flat[0]) and torch.equal(got[1], flat[1])
@@ -255,3 +259,23 @@ def test_dropout_module_matches_torch_ops_given_the_same_noise():
     dropped = (kept == 0).float().mean().item()
     assert abs(dropped - p) < 0.03
     assert torch.allclose(ratio[kept != 0], torch.full_like(ratio[kept != 0], 1 / (1 - p)), rtol=1e-4)
+
+
+def test_row_order_setting_round_trip_and_size_rule():
+    """The order knob returns the previous value and rejects anything but 0..2; with the default setting a large shared
+    mask case and a small one both match the memory-order result bit for bit (whichever order the size rule picks)."""
+    assert abi.attention_softmax_order(1) == 0
+    assert abi.attention_softmax_order(0) == 1
+    with pytest.raises(abi.Nb2Error):
+        abi.attention_softmax_order(3)
+    assert abi.attention_softmax_order(0) == 0
+    for (B, H, T, S) in ((16, 4, 512, 128), (1, 8, 4, 128)):          # 8192 pairs: heads innermost; 4 pairs: memory order
+        scores, _ = make((B, H, T, S), 21, torch.bfloat16, 2.0)
+        mask, _ = make((B, T, S), 22, torch.bfloat16)
+        auto = abi.attention_softmax_fwd(scores, 0.125, None, mask, False)
+        abi.attention_softmax_order(1)
+        try:
+            flat = abi.attention_softmax_fwd(scores, 0.125, None, mask, False)
+        finally:
+            abi.attention_softmax_order(0)
+        assert torch.equal(auto, flat)

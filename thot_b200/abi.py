@@ -41,6 +41,7 @@ _SIGNATURES = {
     "nb2_linear_bias_act_fwd": (c_int, [c_void_p] * 5 + [c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "nb2_linear_available": (c_int, []),
     "nb2_selftest_bounded_wait": (c_int, [c_int64, c_void_p, c_void_p]),
+    "nb2_attention_softmax_order": (c_int, [c_int]),
     "nb2_workspace_bytes": (c_size_t, [c_int, c_int64, c_int64, c_int]),
     "nb2_layernorm_fwd": (c_int, [c_void_p] * 6 + [c_int64, c_int64, c_double, c_int, c_int, c_void_p]),
     "nb2_layernorm_bwd": (c_int, [c_void_p] * 8 + [POINTER(c_int64), c_int64, c_int64, c_int, c_int, c_void_p]),
@@ -554,6 +555,14 @@ class Comm:
             self.close()
         except Exception:
             pass
+
+
+def attention_softmax_order(order: int) -> int:
+    """0 by size, 1 memory order, 2 heads innermost whenever the mask is shared by the heads -> the previous setting."""
+    before = lib().nb2_attention_softmax_order(order)
+    if before < 0:
+        check(before)
+    return before
 
 
 def comm_group(world: int, max_cols: int):

@@ -175,6 +175,11 @@ extern "C" {
 int nb2_abi_version(void) { return NB2_ABI_VERSION; }
 const char* nb2_last_error_string(void) { return g_err; }
 int nb2_reserve_sms(int n) { return exchange_reserved_sms(n); }
+int nb2_attention_softmax_order(int order) {
+    const int before = set_softmax_order(order);
+    NB2_REQUIRE(before >= 0, NB2_ERR_SHAPE, "attention softmax order: %d is not 0, 1 or 2", order);
+    return before;
+}
 int nb2_sm_count(void) { return sm_count(); }
 
 int nb2_device_status(unsigned int* status_host, int clear) {

@@ -37,6 +37,8 @@ int launch_attention_softmax_fwd(const void* scores, const uint8_t* key_padding,
 int launch_attention_softmax_bwd(const void* attn, const void* dattn, void* dscores, int64_t rows, int64_t S, float scale,
                                  int dtype, cudaStream_t st, const void* noise = nullptr);
 
+int set_softmax_order(int order);      // 0 by size, 1 memory order, 2 heads innermost whenever the mask is shared by the heads
+
 // tensor-core linear layer: lives in libnott_b200_linear.so (thot_b200/csrc_linear), loaded on first use
 int launch_linear(const void* x, const void* w, const void* bias, void* z_out, void* y, int64_t M, int64_t N, int64_t K, int act,
                   void* workspace, size_t workspace_bytes, cudaStream_t st);

@@ -14,6 +14,7 @@
 #include <math.h>
 #include <string.h>
 
+#include <atomic>
 #include <type_traits>
 
 #include "launchers.h"
@@ -450,9 +451,23 @@ int64_t row_grid(int64_t rows, int tpr) {
 }
 
 // Heads innermost pays when the same mask row serves several heads; NB2_SOFTMAX_ORDER=flat switches it off for measurements.
-bool heads_inner_wanted(const SoftmaxMask& m, int64_t H) {
-    static const bool off = [] { const char* e = getenv("NB2_SOFTMAX_ORDER"); return e != nullptr && strcmp(e, "flat") == 0; }();
-    return !off && m.add_mask != nullptr && m.mask_sh == 0 && H >= 4;
+// It needs enough (batch, position) pairs to give every row group of a full grid several of them: with few pairs the
+// heads of one pair would run one after the other in a single group while most of the GPU idles.
+// Order override: 0 = by size, 1 = always memory order, 2 = heads innermost whenever the mask allows it.
+std::atomic<int> g_softmax_order{-1};
+int softmax_order() {
+    int v = g_softmax_order.load(std::memory_order_relaxed);
+    if (v < 0) {
+        const char* e = getenv("NB2_SOFTMAX_ORDER");
+        v = (e != nullptr && strcmp(e, "flat") == 0) ? 1 : (e != nullptr && strcmp(e, "inner") == 0) ? 2 : 0;
+        g_softmax_order.store(v, std::memory_order_relaxed);
+    }
+    return v;
+}
+bool heads_inner_wanted(const SoftmaxMask& m, int64_t H, int64_t pairs, int groups_per_cta) {
+    const int order = softmax_order();
+    if (order == 1 || m.add_mask == nullptr || m.mask_sh != 0 || H < 2) return false;
+    return order == 2 || (H >= 4 && pairs >= (int64_t)sm_count() * 3 * groups_per_cta * 2);
 }
 
 template <typename T, int TPR, int FLAGS>
@@ -460,9 +475,10 @@ int launch_fwd_flags(const void* scores, const SoftmaxMask& m, void* out, int64_
                      float scale, cudaStream_t st) {
     constexpr int THREADS = TPR > 256 ? TPR : 256;
     if constexpr ((FLAGS & kSmMask) != 0 && TPR <= 256) {
-        if (heads_inner_wanted(m, H)) {
-            constexpr int RPC = THREADS / TPR;
-            const int64_t pairs = rows / H, need = (pairs + RPC - 1) / RPC, cap = (int64_t)sm_count() * 3 * 4;
+        constexpr int RPC = THREADS / TPR;
+        const int64_t pairs = rows / H;
+        if (heads_inner_wanted(m, H, pairs, RPC)) {
+            const int64_t need = (pairs + RPC - 1) / RPC, cap = (int64_t)sm_count() * 3 * 4;
             return cuda_status(launch_pdl(softmax_fwd_kernel<T, TPR, fwd_vpt<T>(), FLAGS, true>, dim3((unsigned)(need < cap ? need : cap)),
                                           dim3(THREADS), 0, st, (const T*)scores, m, (T*)out, rows, H, Tq, (int)S, scale),
                                "softmax_fwd_kernel launch");
@@ -550,6 +566,13 @@ int launch_bwd_t(const void* attn, const void* dattn, const void* noise, void* d
 }
 
 }  // namespace
+
+int set_softmax_order(int order) {
+    if (order < 0 || order > 2) return -1;
+    const int before = softmax_order();
+    g_softmax_order.store(order, std::memory_order_relaxed);
+    return before;
+}
 
 int launch_attention_softmax_fwd(const void* scores, const uint8_t* key_padding, const void* add_mask, int64_t mask_sb,
                                  int64_t mask_sh, void* out, int64_t B, int64_t H, int64_t Tq, int64_t S, float scale,
