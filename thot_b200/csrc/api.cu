@@ -70,7 +70,7 @@ unsigned int* device_status_ptr() {
 // caller's stream (forked and joined with events, which a stream capture follows as well).
 // Never created while the caller's stream is capturing: the caller then gets nullptr and runs
 // the work in line.
-struct SideStream { cudaStream_t stream; cudaEvent_t fork, join; };
+struct SideStream { cudaStream_t stream; cudaEvent_t fork, join, fork2, join2; };
 static SideStream* side_stream(cudaStream_t user) {
     static thread_local SideStream streams[kMaxDevices] = {};
     static thread_local bool ready[kMaxDevices] = {};
@@ -81,7 +81,9 @@ static SideStream* side_stream(cudaStream_t user) {
         SideStream s = {};
         if (cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
         if (cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) != cudaSuccess ||
-            cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) != cudaSuccess) {
+            cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&s.fork2, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&s.join2, cudaEventDisableTiming) != cudaSuccess) {
             (void)cudaGetLastError();
             return nullptr;
         }
@@ -456,6 +458,15 @@ int nb2_bert_embedding_ln_bwd(const void* sum, const void* dy, const void* ids, 
     int64_t n = 0;
     rc = nb2_layernorm_bwd(sum, dy, gamma, nullptr, mean, rstd, dsum, partials, &n, tokens, D, dtype, NB2_ACT_NONE, stream);
     if (rc != 0) return rc;
+    // The position and type gradients read dsum and nothing else this call produces: on the side stream (behind the
+    // sort, long finished) they run beside the partial reduce and the word-table sum instead of after them.
+    if (side != nullptr) {
+        rc = cuda_status(cudaEventRecord(side->fork2, st), "bert embedding bwd: second fork");
+        if (rc == 0) rc = cuda_status(cudaStreamWaitEvent(side->stream, side->fork2, 0), "bert embedding bwd: second fork");
+        if (rc == 0) rc = launch_bert_embed_table_grads(dsum, dpos, dtype0, type_scratch, B, S, D, dtype, side->stream);
+        if (rc == 0) rc = cuda_status(cudaEventRecord(side->join2, side->stream), "bert embedding bwd: second join");
+        if (rc != 0) return rc;
+    }
     rc = nb2_colreduce_partials(partials, n, 2 * D, dgamma_dbeta, stream);
     if (rc != 0) return rc;
     if (ids != nullptr) {
@@ -465,6 +476,7 @@ int nb2_bert_embedding_ln_bwd(const void* sum, const void* dy, const void* ids, 
         rc = launch_embedding_bwd_sum(dsum, dword, tokens, vocab, D, dtype, sort_ws, st);
         if (rc != 0) return rc;
     }
+    if (side != nullptr) return cuda_status(cudaStreamWaitEvent(st, side->join2, 0), "bert embedding bwd: second join");
     return launch_bert_embed_table_grads(dsum, dpos, dtype0, type_scratch, B, S, D, dtype, st);
 }
 
