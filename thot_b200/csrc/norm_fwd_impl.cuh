@@ -29,7 +29,7 @@ static int launch_fwd_tma_nt(const NormArgs& a) {
 template <typename T, int TPR, int VPT, int ACT, bool RMS, bool RES>
 static int launch_fwd_tma_res(const NormArgs& a) {
     if constexpr ((TPR == 128 || TPR == 256) && !RES) {
-        if (fwd_threads(TPR, a.D * (int64_t)sizeof(T)) == 768) return launch_fwd_tma_nt<T, TPR, VPT, ACT, RMS, RES, 768>(a);
+        if (fwd_threads(TPR, a.D * (int64_t)sizeof(T), (int)sizeof(T), RMS, ACT == NB2_ACT_GELU) == 768) return launch_fwd_tma_nt<T, TPR, VPT, ACT, RMS, RES, 768>(a);
     }
     return launch_fwd_tma_nt<T, TPR, VPT, ACT, RMS, RES, 512>(a);
 }
@@ -90,7 +90,7 @@ static int launch_fwd_act(const NormArgs& a) {
             if (s.tpr != 0 && affine && tma_fits(a.D, (int)sizeof(T), s.tpr, 2)) return launch_fwd_tma_shape<T, ACT, RMS>(a, s);
             return kNotFused;
         }
-        if (s.tpr != 0 && affine && tma_preferred(RMS, a.D, (int)sizeof(T), false, ACT == NB2_ACT_GELU) && tma_fits(a.D, (int)sizeof(T), s.tpr, 1, fwd_threads(s.tpr, a.D * (int64_t)sizeof(T))))
+        if (s.tpr != 0 && affine && tma_preferred(RMS, a.D, (int)sizeof(T), false, ACT == NB2_ACT_GELU) && tma_fits(a.D, (int)sizeof(T), s.tpr, 1, fwd_threads(s.tpr, a.D * (int64_t)sizeof(T), (int)sizeof(T), RMS, ACT == NB2_ACT_GELU)))
             return launch_fwd_tma_shape<T, ACT, RMS>(a, s);
         switch (pick_tpr(a.D / EPV, fwd_vpt<T>())) {
             case 32:  return launch_fwd_cfg<T, 32, ACT, RMS>(a);
