@@ -127,11 +127,12 @@ static inline bool tma_preferred(bool rms, int64_t D, int elt, bool bwd, bool fu
 // does the ring of this shape fit the SM's shared memory at all
 // Forward CTAs: 16 warps (parameters in registers for fp32), or 24 (parameters read from shared memory per row).
 // Measured on B200 with the activation of the sweep fused, same box, both forms on the same inputs:
-//   LayerNorm bf16, rows of 8 KiB and more : 24 warps (0.82 against 0.74 of the copy rate at D = 4096, 0.76 against 0.63 at 8192)
-//   LayerNorm fp32, rows of 16 KiB and more: 24 warps (1.00 against 0.91 at D = 4096)
-//   LayerNorm fp32, 8 KiB rows (D = 2048)  : 16 warps (0.95 / 0.93 / 0.90 against 0.87 / 0.88 / 0.88 at 2^17 / 2^19 / 2^20 rows)
-//   RMSNorm                                : 16 warps (0.98 against 0.90 at fp32 D = 4096; level at 8192)
-//   narrower rows                          : 16 warps (24 measured -10% at D = 1024)
+//   LayerNorm bf16 with GELU fused, every width: 24 warps (0.85-0.87 of the copy rate against 0.74-0.75 at D = 1024, 0.82
+//                                                against 0.73 at 2048, 0.82 against 0.74 at 4096, 0.76 against 0.63 at 8192)
+//   LayerNorm fp32 with GELU, rows >= 16 KiB   : 24 warps (1.00 against 0.91 at D = 4096)
+//   LayerNorm fp32 with GELU, 8 KiB rows       : 16 warps (0.95 / 0.93 / 0.90 against 0.87 / 0.88 / 0.88 at 2^17 / 2^19 / 2^20 rows)
+//   LayerNorm fp32 with GELU, narrower rows    : 16 warps (24 measured -10% at D = 1024)
+//   RMSNorm                                    : 16 warps (0.98 against 0.90 at fp32 D = 4096; level at 8192)
 // and with no activation fused 16 warps win at every width (LayerNorm fp32 D = 4096: 0.95 against 0.89; bf16 D = 4096: 0.93
 // against 0.83; bf16 D = 8192: 0.90 against 0.87): the extra warps only pay for GELU's arithmetic.
 static inline int fwd_warps_override() {        // NB2_FWD_WARPS=16|24 forces one form where both exist (measurements)
@@ -139,12 +140,14 @@ static inline int fwd_warps_override() {        // NB2_FWD_WARPS=16|24 forces on
     return v;
 }
 static inline int fwd_threads(int tpr, int64_t row_bytes, int elt, bool rms, bool fused_gelu) {
-    if (tpr != 128 && tpr != 256) return 512;
+    const bool narrow = tpr == 32 || tpr == 64;            // these have a 24-warp form for bf16 LayerNorm + GELU only
+    if (!narrow && tpr != 128 && tpr != 256) return 512;
+    if (narrow && !(elt == 2 && !rms && fused_gelu)) return 512;
     const int ov = fwd_warps_override();
     if (ov == 16) return 512;
     if (ov == 24) return 768;
     if (rms || !fused_gelu) return 512;
-    return row_bytes >= (elt == 2 ? 8192 : 16384) ? 768 : 512;
+    return (elt == 2 || row_bytes >= 16384) ? 768 : 512;
 }
 static inline bool tma_fits(int64_t D, int elt, int tpr, int nsrc, int threads = kTmaThreads) {
     return tma_tiling(D, elt, tpr, nsrc, threads).smem <= kTmaMaxSmem;

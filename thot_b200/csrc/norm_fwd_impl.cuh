@@ -28,7 +28,8 @@ static int launch_fwd_tma_nt(const NormArgs& a) {
 
 template <typename T, int TPR, int VPT, int ACT, bool RMS, bool RES>
 static int launch_fwd_tma_res(const NormArgs& a) {
-    if constexpr ((TPR == 128 || TPR == 256) && !RES) {
+    if constexpr (!RES && (TPR == 128 || TPR == 256 ||
+                           ((TPR == 32 || TPR == 64) && sizeof(T) == 2 && ACT == NB2_ACT_GELU && !RMS))) {
         if (fwd_threads(TPR, a.D * (int64_t)sizeof(T), (int)sizeof(T), RMS, ACT == NB2_ACT_GELU) == 768) return launch_fwd_tma_nt<T, TPR, VPT, ACT, RMS, RES, 768>(a);
     }
     return launch_fwd_tma_nt<T, TPR, VPT, ACT, RMS, RES, 512>(a);
