@@ -130,7 +130,7 @@ static int launch_bwd_act(const NormArgs& a, int64_t* n_partials) {
             if (s.tpr != 0 && affine && tma_fits(a.D, (int)sizeof(T), s.tpr, 3)) return launch_bwd_tma_shape<T, ACT, RMS>(a, s, n_partials);
             return kNotFused;
         }
-        if (s.tpr != 0 && affine && tma_preferred(RMS, a.D, (int)sizeof(T), true) && tma_fits(a.D, (int)sizeof(T), s.tpr, 2))
+        if (s.tpr != 0 && affine && tma_preferred(RMS, a.D, (int)sizeof(T), true, ACT) && tma_fits(a.D, (int)sizeof(T), s.tpr, 2))
             return launch_bwd_tma_shape<T, ACT, RMS>(a, s, n_partials);
         switch (pick_tpr(a.D / EPV, bwd_vpt<T>())) {
             case 32:  return launch_bwd_cfg<T, 32, ACT, RMS>(a, n_partials);

@@ -116,12 +116,17 @@ static inline int64_t tma_grid(int64_t rows, int tpr, int sms, int threads = kTm
 //   rate; the ring only wins for rows of 16 KiB and more, and for the bf16 backward.
 //   That last rule holds with GELU fused (0.86 against 0.84 at 32 KiB rows); without an activation, or
 //   with SiLU, the LayerNorm forward ring wins there too (0.99 against 0.89, 0.92 against 0.88).
-static inline bool tma_preferred(bool rms, int64_t D, int elt, bool bwd, bool fused_gelu = true) {
+//   D = 768 is the one width with a three-vector ring form (768 = 64 x 3 x 4 = 32 x 3 x 8), while the register-row
+//   kernels cover it with four vectors per thread and a quarter of the lanes idle: there the ring also takes the
+//   RMSNorm fp32 backward (0.94 against 0.87 with SiLU fused) and, with an activation fused, the bf16 forward (0.87
+//   against 0.82); the fp32 forward stays (0.87 against 0.86).
+static inline bool tma_preferred(bool rms, int64_t D, int elt, bool bwd, int act = NB2_ACT_GELU) {
     const int ov = norm_path_override();
     if (ov == 1) return false;
     if (ov == 2) return true;
     const int64_t row_bytes = D * elt;
-    if (!rms) return bwd ? true : (elt == 2 || row_bytes <= 16384 || !fused_gelu);
+    if (!rms) return bwd ? true : (elt == 2 || row_bytes <= 16384 || act != NB2_ACT_GELU);
+    if (D == 768) return bwd ? true : (elt == 2 && act != NB2_ACT_NONE);
     return bwd ? (elt == 2 || row_bytes >= 16384) : (elt == 4 && row_bytes >= 16384);
 }
 // does the ring of this shape fit the SM's shared memory at all

@@ -91,7 +91,7 @@ static int launch_fwd_act(const NormArgs& a) {
             if (s.tpr != 0 && affine && tma_fits(a.D, (int)sizeof(T), s.tpr, 2)) return launch_fwd_tma_shape<T, ACT, RMS>(a, s);
             return kNotFused;
         }
-        if (s.tpr != 0 && affine && tma_preferred(RMS, a.D, (int)sizeof(T), false, ACT == NB2_ACT_GELU) && tma_fits(a.D, (int)sizeof(T), s.tpr, 1, fwd_threads(s.tpr, a.D * (int64_t)sizeof(T), (int)sizeof(T), RMS, ACT == NB2_ACT_GELU)))
+        if (s.tpr != 0 && affine && tma_preferred(RMS, a.D, (int)sizeof(T), false, ACT) && tma_fits(a.D, (int)sizeof(T), s.tpr, 1, fwd_threads(s.tpr, a.D * (int64_t)sizeof(T), (int)sizeof(T), RMS, ACT == NB2_ACT_GELU)))
             return launch_fwd_tma_shape<T, ACT, RMS>(a, s);
         switch (pick_tpr(a.D / EPV, fwd_vpt<T>())) {
             case 32:  return launch_fwd_cfg<T, 32, ACT, RMS>(a);
