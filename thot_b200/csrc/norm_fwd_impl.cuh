@@ -51,8 +51,16 @@ template <typename T, int ACT, bool RMS>
 static int launch_fwd_tma_shape(const NormArgs& a, TmaShape s) {
     constexpr int EPV = VecTraits<T>::EPV;
     if (s.vpt == 3) {
-        if constexpr (EPV == 4) return launch_fwd_tma<T, 64, 3, ACT, RMS>(a);
-        else return launch_fwd_tma<T, 32, 3, ACT, RMS>(a);
+        switch (s.tpr) {
+            case 32:  return launch_fwd_tma<T, 32, 3, ACT, RMS>(a);
+            case 64:  return launch_fwd_tma<T, 64, 3, ACT, RMS>(a);
+            case 128: return launch_fwd_tma<T, 128, 3, ACT, RMS>(a);
+            case 256: return launch_fwd_tma<T, 256, 3, ACT, RMS>(a);
+            case 512: if constexpr (EPV == 4) return launch_fwd_tma<T, 512, 3, ACT, RMS>(a);
+            default: break;
+        }
+        set_error("norm fwd: no three-vector ring kernel for threads-per-row %d", s.tpr);
+        return NB2_ERR_SHAPE;
     }
     switch (s.tpr) {
         case 32:  return launch_fwd_tma<T, 32, 4, ACT, RMS>(a);
