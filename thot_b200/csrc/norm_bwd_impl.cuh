@@ -83,6 +83,19 @@ static int launch_bwd_tma_shape(const NormArgs& a, TmaShape s, int64_t* n_partia
         set_error("norm bwd: no three-vector ring kernel for threads-per-row %d", s.tpr);
         return NB2_ERR_SHAPE;
     }
+    if (s.vpt == 5) {
+        if constexpr (EPV == 4) {
+            switch (s.tpr) {
+                case 32:  return launch_bwd_tma<T, 32, 5, ACT, RMS>(a, n_partials);
+                case 64:  return launch_bwd_tma<T, 64, 5, ACT, RMS>(a, n_partials);
+                case 128: return launch_bwd_tma<T, 128, 5, ACT, RMS>(a, n_partials);
+                case 256: return launch_bwd_tma<T, 256, 5, ACT, RMS>(a, n_partials);
+                default: break;
+            }
+        }
+        set_error("norm bwd: no five-vector ring kernel for threads-per-row %d", s.tpr);
+        return NB2_ERR_SHAPE;
+    }
     // RMSNorm bf16 rows of 4 KiB and more: 32 columns per thread (measured on B200 against the 16-column
     // form with SiLU fused: +3% at D = 2048, +8% at 4096, +14% at 8192, -1% at 1024; with GELU +1-5%).
     // Without a fused activation the 16-column form is the faster one up to D = 4096 (246 us against 295

@@ -78,6 +78,7 @@ static inline TmaShape tma_fwd_shape(int64_t D, int epv) {
     for (int tpr = 32; tpr <= 512; tpr *= 2) {
         if (D == (int64_t)tpr * 4 * epv) return {tpr, 4};
         if (D == (int64_t)tpr * 3 * epv && (epv == 4 || tpr <= 256)) return {tpr, 3};
+        if (D == (int64_t)tpr * 5 * epv && tpr <= 256) return {tpr, 5};                  // 5 * 2^k: 1280, 2560, 5120 (and 10240 bf16)
     }
     return {0, 0};
 }
@@ -86,6 +87,7 @@ static inline TmaShape tma_bwd_shape(int64_t D, int epv) {
     for (int tpr = 32; tpr <= 512; tpr *= 2) {
         if (D == (int64_t)tpr * 16) return {tpr, 16 / epv};
         if (D == (int64_t)tpr * 3 * epv && (epv == 4 || tpr <= 256)) return {tpr, 3};     // 12 fp32 / 24 bf16 columns per thread
+        if (epv == 4 && D == (int64_t)tpr * 20 && tpr <= 256) return {tpr, 5};               // 5 * 2^k in fp32: 20 columns per thread
     }
     return {0, 0};
 }
@@ -128,11 +130,12 @@ static inline bool tma_preferred(bool rms, int64_t D, int elt, bool bwd, int act
     if (ov == 1) return false;
     if (ov == 2) return true;
     const int64_t row_bytes = D * elt;
-    if (!rms) return bwd ? true : (elt == 2 || row_bytes <= 16384 || act != NB2_ACT_GELU);
+    if (!rms) return bwd ? true : (elt == 2 || row_bytes <= 16384 || act != NB2_ACT_GELU || D % 3 == 0 || D % 5 == 0);
     if (D == 768) return bwd ? true : (elt == 2 && act != NB2_ACT_NONE);
     // the wider 3 * 2^k widths (1536, 3072, 6144): ring in both directions and types (fp32 backward 0.93-1.02 against 0.80-0.89,
     // bf16 forward 0.85-0.93 against 0.76-0.82, fp32 forward level to +5%)
     if (D % 3 == 0 && D > 768) return true;
+    if (D % 5 == 0) return true;          // 5 * 2^k: the register-row kernels would leave up to 37% of the lanes idle
     return bwd ? (elt == 2 || row_bytes >= 16384) : (elt == 4 && row_bytes >= 16384);
 }
 // does the ring of this shape fit the SM's shared memory at all

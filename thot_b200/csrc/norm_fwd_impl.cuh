@@ -62,6 +62,17 @@ static int launch_fwd_tma_shape(const NormArgs& a, TmaShape s) {
         set_error("norm fwd: no three-vector ring kernel for threads-per-row %d", s.tpr);
         return NB2_ERR_SHAPE;
     }
+    if (s.vpt == 5) {
+        switch (s.tpr) {
+            case 32:  return launch_fwd_tma<T, 32, 5, ACT, RMS>(a);
+            case 64:  return launch_fwd_tma<T, 64, 5, ACT, RMS>(a);
+            case 128: return launch_fwd_tma<T, 128, 5, ACT, RMS>(a);
+            case 256: return launch_fwd_tma<T, 256, 5, ACT, RMS>(a);
+            default: break;
+        }
+        set_error("norm fwd: no five-vector ring kernel for threads-per-row %d", s.tpr);
+        return NB2_ERR_SHAPE;
+    }
     switch (s.tpr) {
         case 32:  return launch_fwd_tma<T, 32, 4, ACT, RMS>(a);
         case 64:  return launch_fwd_tma<T, 64, 4, ACT, RMS>(a);
