@@ -44,7 +44,8 @@ def test_golden_reference_outputs(golden_dir, name):
 # ring-fused shapes, and shapes that compose add + norm inside the call (odd width, ring too large)
 @pytest.mark.parametrize("kind", ["ln", "rms"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("rows,D", [(1, 1024), (700, 768), (3000, 1024), (257, 4096), (33, 513), (64, 8192), (5, 16384)])
+@pytest.mark.parametrize("rows,D", [(1, 1024), (700, 768), (3000, 1024), (257, 4096), (33, 513), (64, 8192), (5, 16384),
+                                     (333, 1536), (90, 3072), (40, 6144), (210, 1280), (130, 2560), (45, 5120)])     # 3 * 2^k and 5 * 2^k
 def test_against_oracle(kind, dtype, rows, D):
     eps = 1e-5 if kind == "ln" else 1e-6
     a, an = make((rows, D), 1, dtype); b, bn = make((rows, D), 2, dtype)
@@ -63,11 +64,20 @@ def test_against_oracle(kind, dtype, rows, D):
     else:
         # Shapes without a fused kernel run norm backward, then an add, and round to bf16 after each,
         # exactly as the reference's autograd does with bf16 tensors; the fused kernel rounds once.
-        # Either is accepted: within 2 ulp of the once-rounded or of the twice-rounded result.
+        # Either is accepted: within 2 ulp of the once-rounded or of the twice-rounded result.  In the two-step form
+        # the norm's own gradient is a bf16 tensor that may itself be 2 ulp off, and where the add cancels that error
+        # is many ulp of the small sum: there the bound is 2 ulp of the norm gradient, the larger operand.
         once = tol.bf16_ulp_mask(bits(dx), ref["dx"])
-        norm_only = tol.bf16_bits_to_f32(tol.to_bf16_bits(ref["dx"] - dsn.astype(np.float64)))
+        norm_exact = ref["dx"] - dsn.astype(np.float64)
+        norm_only = tol.bf16_bits_to_f32(tol.to_bf16_bits(norm_exact))
         twice = tol.bf16_ulp_mask(bits(dx), norm_only.astype(np.float64) + dsn)
-        assert (once | twice).all(), f"{(~(once | twice)).sum()} of {once.size} dx elements outside 2 bf16 ulp"
+        got = tol.bf16_bits_to_f32(bits(dx)).astype(np.float64)
+        ulp_norm = np.abs(norm_only.astype(np.float64)) * 2.0 ** -7          # >= one bf16 ulp at that magnitude
+        ulp_got = np.abs(got) * 2.0 ** -7
+        composed = np.abs(got - ref["dx"]) <= 2 * ulp_norm + ulp_got
+        ok = once | twice | composed
+        assert ok.all(), f"{(~ok).sum()} of {once.size} dx elements outside 2 bf16 ulp"
+        assert (once | twice).mean() > 0.9999, "the operand-sized bound is for isolated cancellations only"
     if kind == "ln":
         tol.long_sum_close(grads[0].cpu().numpy(), ref["dgamma"], rows)
         tol.long_sum_close(grads[1].cpu().numpy(), ref["dbeta"], rows)
