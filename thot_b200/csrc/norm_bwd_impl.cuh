@@ -83,6 +83,11 @@ static int launch_bwd_tma_shape(const NormArgs& a, TmaShape s, int64_t* n_partia
         set_error("norm bwd: no three-vector ring kernel for threads-per-row %d", s.tpr);
         return NB2_ERR_SHAPE;
     }
+    if constexpr (EPV == 8) {
+        if (s.tpr == 160) return s.vpt == 2 ? launch_bwd_tma<T, 160, 2, ACT, RMS, 480>(a, n_partials)
+                                            : launch_bwd_tma<T, 160, 1, ACT, RMS, 480>(a, n_partials);
+        if (s.tpr == 320) return launch_bwd_tma<T, 320, 2, ACT, RMS, 320>(a, n_partials);
+    }
     if (s.vpt == 5) {
         if constexpr (EPV == 4) {
             switch (s.tpr) {

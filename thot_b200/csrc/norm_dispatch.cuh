@@ -89,6 +89,11 @@ static inline TmaShape tma_bwd_shape(int64_t D, int epv) {
         if (D == (int64_t)tpr * 3 * epv && (epv == 4 || tpr <= 256)) return {tpr, 3};     // 12 fp32 / 24 bf16 columns per thread
         if (epv == 4 && D == (int64_t)tpr * 20 && tpr <= 256) return {tpr, 5};               // 5 * 2^k in fp32: 20 columns per thread
     }
+    // 5 * 2^k in bf16: 40 columns per thread do not fit the registers, so the row group itself takes a 5 * 2^k size
+    // (five or ten warps; CTAs of 480 and 320 threads): 16 columns per thread at 2560 and 5120, 8 at 1280
+    if (epv == 8 && D == 2560) return {160, 2};
+    if (epv == 8 && D == 5120) return {320, 2};
+    if (epv == 8 && D == 1280) return {160, 1};
     return {0, 0};
 }
 // ring depth: every row group gets `stages` row slots; one "layer" (a slot of every
