@@ -45,7 +45,8 @@ def test_golden_reference_outputs(golden_dir, name):
 @pytest.mark.parametrize("kind", ["ln", "rms"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("rows,D", [(1, 1024), (700, 768), (3000, 1024), (257, 4096), (33, 513), (64, 8192), (5, 16384),
-                                     (333, 1536), (90, 3072), (40, 6144), (210, 1280), (130, 2560), (45, 5120)])     # 3 * 2^k and 5 * 2^k
+                                     (333, 1536), (90, 3072), (40, 6144), (210, 1280), (130, 2560), (45, 5120),
+                                     (190, 1792), (110, 3584), (35, 7168)])     # 3 * 2^k, 5 * 2^k and 7 * 2^k
 def test_against_oracle(kind, dtype, rows, D):
     eps = 1e-5 if kind == "ln" else 1e-6
     a, an = make((rows, D), 1, dtype); b, bn = make((rows, D), 2, dtype)

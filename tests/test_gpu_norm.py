@@ -55,7 +55,8 @@ def test_golden_reference_outputs(golden_dir, name):
 SHAPES = [(1, 1), (3, 7), (33, 512), (5, 513), (300, 768), (64, 1024), (37, 2048), (19, 4096),
           (3, 8191), (9, 8192), (2, 16384), (4, 20000),
           (41, 384), (310, 1536), (150, 3072), (70, 6144),       # 3 * 2^k: three vectors per thread in the ring kernels
-          (77, 640), (330, 1280), (160, 2560), (75, 5120), (40, 10240)]    # 5 * 2^k: five (fp32 both directions, bf16 forward)
+          (77, 640), (330, 1280), (160, 2560), (75, 5120), (40, 10240),    # 5 * 2^k: five vectors, or 160/320-thread row groups
+          (230, 1792), (120, 3584), (60, 7168), (11, 14336)]               # 7 * 2^k: 224/448-thread row groups
 
 
 @pytest.mark.parametrize("kind", ["ln", "rms"])

@@ -83,6 +83,13 @@ static int launch_bwd_tma_shape(const NormArgs& a, TmaShape s, int64_t* n_partia
         set_error("norm bwd: no three-vector ring kernel for threads-per-row %d", s.tpr);
         return NB2_ERR_SHAPE;
     }
+    if (s.tpr == 224 || s.tpr == 448) {
+        constexpr int V8 = 8 / EPV;
+        if (s.tpr == 224) return s.vpt == V16 ? launch_bwd_tma<T, 224, V16, ACT, RMS, 448>(a, n_partials)
+                                              : launch_bwd_tma<T, 224, V8, ACT, RMS, 448>(a, n_partials);
+        return s.vpt == V16 ? launch_bwd_tma<T, 448, V16, ACT, RMS, 448>(a, n_partials)
+                            : launch_bwd_tma<T, 448, V8, ACT, RMS, 448>(a, n_partials);
+    }
     if constexpr (EPV == 8) {
         if (s.tpr == 160) return s.vpt == 2 ? launch_bwd_tma<T, 160, 2, ACT, RMS, 480>(a, n_partials)
                                             : launch_bwd_tma<T, 160, 1, ACT, RMS, 480>(a, n_partials);

@@ -80,6 +80,10 @@ static inline TmaShape tma_fwd_shape(int64_t D, int epv) {
         if (D == (int64_t)tpr * 3 * epv && (epv == 4 || tpr <= 256)) return {tpr, 3};
         if (D == (int64_t)tpr * 5 * epv && tpr <= 256) return {tpr, 5};                  // 5 * 2^k: 1280, 2560, 5120 (and 10240 bf16)
     }
+    // 7 * 2^k (1792, 3584, 7168; 14336 in bf16): row groups of 7 or 14 warps in CTAs of 448 threads
+    for (int tpr = 224; tpr <= 448; tpr *= 2)
+        for (int vpt = 4; vpt >= 2; vpt -= 2)
+            if (D == (int64_t)tpr * vpt * epv) return {tpr, vpt};
     return {0, 0};
 }
 // Backward: 16 elements per thread (its dgamma/dbeta accumulators take the registers).
@@ -94,6 +98,11 @@ static inline TmaShape tma_bwd_shape(int64_t D, int epv) {
     if (epv == 8 && D == 2560) return {160, 2};
     if (epv == 8 && D == 5120) return {320, 2};
     if (epv == 8 && D == 1280) return {160, 1};
+    // 7 * 2^k: groups of 224 or 448 threads, 16 columns per thread (8 at D = 1792)
+    for (int tpr = 224; tpr <= 448; tpr *= 2) {
+        if (D == (int64_t)tpr * 16) return {tpr, 16 / epv};
+        if (D == (int64_t)tpr * 8) return {tpr, 8 / epv};
+    }
     return {0, 0};
 }
 // ring depth: every row group gets `stages` row slots; one "layer" (a slot of every
@@ -135,12 +144,12 @@ static inline bool tma_preferred(bool rms, int64_t D, int elt, bool bwd, int act
     if (ov == 1) return false;
     if (ov == 2) return true;
     const int64_t row_bytes = D * elt;
-    if (!rms) return bwd ? true : (elt == 2 || row_bytes <= 16384 || act != NB2_ACT_GELU || D % 3 == 0 || D % 5 == 0);
+    if (!rms) return bwd ? true : (elt == 2 || row_bytes <= 16384 || act != NB2_ACT_GELU || D % 3 == 0 || D % 5 == 0 || D % 7 == 0);
     if (D == 768) return bwd ? true : (elt == 2 && act != NB2_ACT_NONE);
     // the wider 3 * 2^k widths (1536, 3072, 6144): ring in both directions and types (fp32 backward 0.93-1.02 against 0.80-0.89,
     // bf16 forward 0.85-0.93 against 0.76-0.82, fp32 forward level to +5%)
     if (D % 3 == 0 && D > 768) return true;
-    if (D % 5 == 0) return true;          // 5 * 2^k: the register-row kernels would leave up to 37% of the lanes idle
+    if (D % 5 == 0 || D % 7 == 0) return true;          // 5 * 2^k, 7 * 2^k: the register-row kernels would leave up to 37% of the lanes idle
     return bwd ? (elt == 2 || row_bytes >= 16384) : (elt == 4 && row_bytes >= 16384);
 }
 // does the ring of this shape fit the SM's shared memory at all

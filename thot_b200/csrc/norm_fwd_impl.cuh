@@ -47,9 +47,22 @@ static int launch_fwd_tma(const NormArgs& a) {
     return launch_fwd_tma_res<T, TPR, VPT, ACT, RMS, false>(a);
 }
 
+// a ring kernel with a given CTA size (the 7 * 2^k shapes: 448 threads)
+template <typename T, int TPR, int VPT, int ACT, bool RMS, int NT>
+static int launch_fwd_tma_fixed(const NormArgs& a) {
+    if (a.res != nullptr) {
+        if constexpr (ACT == NB2_ACT_NONE) return launch_fwd_tma_nt<T, TPR, VPT, ACT, RMS, true, NT>(a);
+        set_error("residual + norm is not fused with an activation");
+        return NB2_ERR_DTYPE;
+    }
+    return launch_fwd_tma_nt<T, TPR, VPT, ACT, RMS, false, NT>(a);
+}
+
 template <typename T, int ACT, bool RMS>
 static int launch_fwd_tma_shape(const NormArgs& a, TmaShape s) {
     constexpr int EPV = VecTraits<T>::EPV;
+    if (s.tpr == 224) return s.vpt == 4 ? launch_fwd_tma_fixed<T, 224, 4, ACT, RMS, 448>(a) : launch_fwd_tma_fixed<T, 224, 2, ACT, RMS, 448>(a);
+    if (s.tpr == 448) return s.vpt == 4 ? launch_fwd_tma_fixed<T, 448, 4, ACT, RMS, 448>(a) : launch_fwd_tma_fixed<T, 448, 2, ACT, RMS, 448>(a);
     if (s.vpt == 3) {
         switch (s.tpr) {
             case 32:  return launch_fwd_tma<T, 32, 3, ACT, RMS>(a);
